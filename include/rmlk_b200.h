@@ -1,0 +1,231 @@
+/*
+ * rmlk_b200 — B200 (sm_100a) operator kernels behind a C ABI.
+ *
+ * This header is the drop-in boundary for the reference project's `cuda` crate: every entry point
+ * below replaces the body of one launch wrapper in the reference's cuda/src/kernels/<op>.rs (cited
+ * per function), or one of the host-side memcpy / library paths in
+ * runtime/src/providers/cuda/backend/<op>.rs for the ops that have no kernel there.
+ *
+ * Conventions
+ *  - All tensor pointers are DEVICE pointers to dense row-major buffers owned by the caller; the
+ *    library never allocates, frees or retains them.  Shapes, strides, axes, perms and scalar
+ *    parameters are HOST values passed by value or as small host arrays; nothing is read back
+ *    from the device, so no entry point synchronises the stream.
+ *  - Strides are in ELEMENTS; a stride of 0 broadcasts that dimension (the reference's
+ *    runtime/src/utils/mod.rs:56-111 convention).  Rank is at most RMLK_MAX_RANK.  A scalar is
+ *    passed the way the reference passes it to kernels: rank 1, shape {1}
+ *    (runtime/src/providers/cuda/utils.rs:5-18).
+ *  - `stream` is a cudaStream_t (NULL = legacy default stream).  Work is enqueued on it and the
+ *    call returns; entry points are re-entrant and keep no mutable global state.
+ *  - Return value: RMLK_OK, an RMLK_ERR_* code, or RMLK_ERR_CUDA_BASE + cudaError_t.  Nothing
+ *    aborts or traps.  Kernels that can meet bad data (Gather / ScatterND indices) report through
+ *    a caller-provided device status word, as the reference's ScatterND does
+ *    (cuda/src/ptx/headers/scatter_op_macros.cuh:56-63, :82-85).
+ *  - rmlk_b200_last_error() returns a thread-local, human-readable message for the last non-OK
+ *    return on the calling thread.
+ */
+#ifndef RMLK_B200_H
+#define RMLK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define RMLK_MAX_RANK 8
+
+#if defined(__GNUC__)
+#define RMLK_API __attribute__((visibility("default")))
+#else
+#define RMLK_API
+#endif
+
+typedef void* rmlk_stream_t;
+
+/* Discriminants follow rmlk_schema::DataType's declaration order (schema/src/tensor.rs:347-375). */
+typedef enum {
+    RMLK_F16 = 0,
+    RMLK_F32 = 1,
+    RMLK_F64 = 2,
+    RMLK_I32 = 3,
+    RMLK_I64 = 4,
+    RMLK_UNDEFINED = 5,
+    RMLK_U8 = 6,
+    RMLK_I8 = 7,
+    RMLK_U16 = 8,
+    RMLK_I16 = 9,
+    RMLK_U32 = 10,
+    RMLK_U64 = 11,
+    RMLK_STRING = 12,
+    RMLK_BOOL = 13
+} rmlk_dtype;
+
+/* Mirrors rmlk_cuda::Error (cuda/src/error.rs:6-14). */
+typedef enum {
+    RMLK_OK = 0,
+    RMLK_ERR_INVALID_ARG = 1,       /* Error::InvalidArguments     */
+    RMLK_ERR_UNSUPPORTED_DTYPE = 2, /* UnsupportedDataType (runtime/src/core/error.rs:4-10) */
+    RMLK_ERR_NOT_CONTIGUOUS = 3,    /* Error::NonContiguousMemory  */
+    RMLK_ERR_INTERNAL = 4,          /* Error::Internal             */
+    RMLK_ERR_TIMEOUT = 5,
+    RMLK_ERR_KERNEL_STATUS = 6,     /* a device status word was non-zero (ScatterNdError::KernelFailed) */
+    RMLK_ERR_CUDA_BASE = 1000       /* + cudaError_t: Error::Cuda(code) */
+} rmlk_status;
+
+typedef enum {
+    RMLK_BIN_ADD = 0,
+    RMLK_BIN_SUB = 1,
+    RMLK_BIN_MUL = 2,
+    RMLK_BIN_DIV = 3,
+    RMLK_BIN_EQUAL = 4,  /* output dtype bool */
+    RMLK_BIN_GREATER = 5 /* output dtype bool */
+} rmlk_binary_op;
+
+typedef enum {
+    RMLK_UN_SQRT = 0,
+    RMLK_UN_NEG = 1,
+    RMLK_UN_SIN = 2,
+    RMLK_UN_COS = 3,
+    RMLK_UN_SIGMOID = 4,
+    RMLK_UN_RELU = 5
+} rmlk_unary_op;
+
+typedef enum {
+    RMLK_SCATTER_NONE = 0,
+    RMLK_SCATTER_ADD = 1,
+    RMLK_SCATTER_MUL = 2,
+    RMLK_SCATTER_MAX = 3,
+    RMLK_SCATTER_MIN = 4
+} rmlk_scatter_reduction;
+
+RMLK_API const char* rmlk_b200_last_error(void);
+RMLK_API const char* rmlk_b200_version(void);
+RMLK_API size_t rmlk_b200_dtype_size(int dtype);
+
+/* Add / Sub / Mul / Div / Equal / Greater with two-way broadcasting.
+ * Replaces rmlk_cuda::kernels::binary::compute_with_types (cuda/src/kernels/binary.rs:58-100) and
+ * the kernels {add,sub,mul,div,equal,greater}_fwd_* (cuda/src/ptx/headers/binary_op_macros.cuh:14-42).
+ * `shape` is the output shape; dtype in {f16,f32,f64,i32,i64}; Equal/Greater write 1-byte bools. */
+RMLK_API int rmlk_b200_binary(rmlk_stream_t stream, int op, int dtype, int rank, const int64_t* shape,
+                     const int64_t* a_strides, const int64_t* b_strides, const void* a, const void* b, void* out);
+
+/* Pow with independent base / exponent dtypes, output dtype = base dtype.
+ * Replaces rmlk_cuda::kernels::pow::compute (cuda/src/kernels/pow.rs:140-184), kernels
+ * pow_fwd_<base>_<exp> (cuda/src/ptx/pow.cu:6-65): base in {f16,f32,f64,i32,i64}, exponent in
+ * {u8,u16,u32,u64,i8,i16,i32,i64,f16,f32,f64}. */
+RMLK_API int rmlk_b200_pow(rmlk_stream_t stream, int base_dtype, int exp_dtype, int rank, const int64_t* shape,
+                  const int64_t* a_strides, const int64_t* b_strides, const void* base, const void* exponent,
+                  void* out);
+
+/* Sqrt / Neg / Sin / Cos over a contiguous buffer: replaces rmlk_cuda::kernels::unary::compute
+ * (cuda/src/kernels/unary.rs:10-42; kernels sqrt.cu, neg.cu, sin.cu, cos.cu).  Sigmoid / Relu replace
+ * rmlk_cuda::kernels::sigmoid::compute / relu::compute (cuda/src/kernels/activation.rs:6-39), which
+ * call cudnnActivationForward.  Float ops take {f16,f32,f64}; Neg and Relu also {i32,i64}. */
+RMLK_API int rmlk_b200_unary(rmlk_stream_t stream, int op, int dtype, size_t n, const void* in, void* out);
+
+/* Cast over a contiguous buffer: replaces rmlk_cuda::kernels::unary::explicit_io_types_compute
+ * (cuda/src/kernels/unary.rs:47-80; kernels cast_fwd_<src>_to_<dst>, cuda/src/ptx/cast.cu:6-124).
+ * Every pair over {f16,f32,f64,i8,u8,i16,u16,i32,u32,i64,u64,bool} is accepted. */
+RMLK_API int rmlk_b200_cast(rmlk_stream_t stream, int src_dtype, int dst_dtype, size_t n, const void* in, void* out);
+
+/* Where with three-way broadcasting: replaces rmlk_cuda::kernels::whereop::compute
+ * (cuda/src/kernels/whereop.rs:57-101; kernels where_fwd_*, cuda/src/ptx/headers/ternary_op_macro.cuh:1-34).
+ * `cond` is a 1-byte bool tensor; dtype (of x, y, out) in {f16,f32,f64,i32,i64}. */
+RMLK_API int rmlk_b200_where(rmlk_stream_t stream, int dtype, int rank, const int64_t* shape, const int64_t* x_strides,
+                    const int64_t* y_strides, const int64_t* cond_strides, const void* x, const void* y,
+                    const void* cond, void* out);
+
+/* ReduceMean over `axes` of a dense row-major input: replaces rmlk_cuda::kernels::reduce_mean::compute
+ * (cuda/src/kernels/reduce_mean.rs:40-93; kernels reduce_mean_fwd_*,
+ * cuda/src/ptx/headers/aggregation_op_macros.cuh:1-49).  Axes are normalised (0 <= axis < rank),
+ * unique, in any order.  The output is dense with the reduced dims removed or kept as 1 (same
+ * buffer either way).  dtype in {f16,f32,f64,i32,i64}; integers use the reference's unsigned
+ * accumulate (cuda/src/ptx/reduce_mean.cu:8-9). */
+RMLK_API int rmlk_b200_reduce_mean(rmlk_stream_t stream, int dtype, int rank, const int64_t* shape, int num_axes,
+                          const int64_t* axes, const void* in, void* out);
+
+/* Softmax over the last dimension of a [rows, cols] view: replaces rmlk_cuda::kernels::softmax::compute
+ * (cuda/src/kernels/softmax.rs:5-37, cudnnSoftmaxForward MODE_CHANNEL on [N,C,1,1]).  dtype f32 (the
+ * only one the reference dispatches, backend/softmax.rs:114-117), plus f16/f64. */
+RMLK_API int rmlk_b200_softmax(rmlk_stream_t stream, int dtype, int64_t rows, int64_t cols, const void* in, void* out);
+
+/* Gather along one axis of data viewed as [outer, axis_dim, inner]; out is [outer, n_idx, inner].
+ * Replaces the host loop of cuMemcpyDtoD calls in runtime/src/providers/cuda/backend/gather.rs:199-258
+ * (indices stay on the device; no D2H copy).  idx_dtype in {i32,i64}; negative indices wrap once.
+ * An index outside [-axis_dim, axis_dim) writes 1 to *status (if non-NULL) and the row is skipped. */
+RMLK_API int rmlk_b200_gather(rmlk_stream_t stream, int elem_size, int idx_dtype, int64_t outer, int64_t axis_dim,
+                     int64_t inner, int64_t n_idx, const void* data, const void* indices, void* out, int* status);
+
+/* ScatterND: out = data, then out[indices[t]] (op)= updates[t] for each index tuple t.
+ * Replaces rmlk_cuda::kernels::scatter_nd::compute (cuda/src/kernels/scatter_nd.rs:91-174; kernels
+ * scatter_nd{,_add,_mul,_max,_min}_fwd_*, cuda/src/ptx/headers/scatter_op_macros.cuh:19-93) and the
+ * data -> output copy of backend/scatter_nd.rs:128-129 (skipped when data == out).
+ * data is [data_shape...]; indices is [n_tuples, k] int64; updates is [n_tuples, slice_len] where
+ * slice_len = prod(data_shape[k:]).  *status (device int, zeroed by the caller) receives 1 for an
+ * index outside [-dim, dim), as the reference's `error` word does. */
+RMLK_API int rmlk_b200_scatter_nd(rmlk_stream_t stream, int reduction, int dtype, int data_rank, const int64_t* data_shape,
+                         int64_t n_tuples, int k, const void* data, const void* indices, const void* updates,
+                         void* out, int* status);
+
+/* Host helper: ONNX Slice normalisation.  Fills, per input axis, the clamped start, the step and the
+ * output extent.  Same arithmetic as runtime/src/providers/cuda/backend/slice.rs:358-464
+ * (compute_output_shape_helper) and the in-kernel copy of it,
+ * cuda/src/ptx/headers/slice_op_macros.cuh:24-75.  axes / steps may be NULL. */
+RMLK_API int rmlk_b200_slice_params(int rank, const int64_t* in_shape, int n, const int64_t* starts, const int64_t* ends,
+                           const int64_t* axes, const int64_t* steps, int64_t* out_starts, int64_t* out_steps,
+                           int64_t* out_shape);
+
+/* Slice with per-axis normalised start / step (from rmlk_b200_slice_params):
+ * out[i0,..] = in[start0 + step0*i0, ..].  Replaces rmlk_cuda::kernels::slice::compute
+ * (cuda/src/kernels/slice.rs:61-122; kernels slice_fwd_*_with_index_*). */
+RMLK_API int rmlk_b200_slice(rmlk_stream_t stream, int elem_size, int rank, const int64_t* in_shape,
+                    const int64_t* out_shape, const int64_t* starts, const int64_t* steps, const void* in,
+                    void* out);
+
+/* Transpose: out.shape[d] = in.shape[perm[d]].  Replaces rmlk_cuda::kernels::transpose::compute
+ * (cuda/src/kernels/transpose.rs:38-80; kernels transpose_fwd_*). */
+RMLK_API int rmlk_b200_transpose(rmlk_stream_t stream, int elem_size, int rank, const int64_t* in_shape,
+                        const int64_t* perm, const void* in, void* out);
+
+/* Concat of n_inputs tensors along an axis; every input is viewed as [outer, axis_dims[i] * inner].
+ * Replaces the nested cuMemcpyDtoD loops of runtime/src/providers/cuda/backend/concat.rs:28-76.
+ * Zero-length inputs are allowed. */
+RMLK_API int rmlk_b200_concat(rmlk_stream_t stream, int elem_size, int n_inputs, int64_t outer, int64_t inner,
+                     const int64_t* axis_dims, const void* const* inputs, void* out);
+
+/* Expand (right-aligned broadcast copy): replaces rmlk_cuda::kernels::expand::compute
+ * (cuda/src/kernels/expand.rs:35-76; kernels expand_fwd_*). */
+RMLK_API int rmlk_b200_expand(rmlk_stream_t stream, int elem_size, int in_rank, const int64_t* in_shape, int out_rank,
+                     const int64_t* out_shape, const void* in, void* out);
+
+/* Trilu on a [batch, rows, cols] view: replaces rmlk_cuda::kernels::trilu::compute
+ * (cuda/src/kernels/trilu.rs:36-78; kernels trilu_fwd_*).  Masked elements are written as zero. */
+RMLK_API int rmlk_b200_trilu(rmlk_stream_t stream, int elem_size, int64_t batch, int64_t rows, int64_t cols, int upper,
+                    int64_t k, const void* in, void* out);
+
+/* Range: out[i] = start + (T)i * delta for i < n, evaluated in T with two roundings, as the host loop
+ * of runtime/src/providers/cuda/backend/range.rs:195-205 does.  `start` / `delta` point to HOST scalars
+ * of `dtype` in {f16,f32,f64,i32,i64}. */
+RMLK_API int rmlk_b200_range(rmlk_stream_t stream, int dtype, int64_t n, const void* start, const void* delta, void* out);
+
+/* Fill a contiguous buffer with one value (`value` points to a HOST scalar of elem_size bytes).
+ * Replaces the host fill + H2D copy of runtime/src/providers/cuda/backend/constant_of_shape.rs:59-62. */
+RMLK_API int rmlk_b200_fill(rmlk_stream_t stream, int elem_size, int64_t n, const void* value, void* out);
+
+/* Batched row-major MatMul, C[b] = A[b] x B[b], fp32 accumulate:
+ * replaces rmlk_cuda::kernels::gemm::compute (cuda/src/kernels/gemm.rs:112-232,
+ * cublasGemmStridedBatchedEx).  A is [m,k], B is [k,n], C is [m,n], each dense; batch strides are in
+ * elements and may be 0 to broadcast an operand over the batch (the reference materialises copies,
+ * backend/matmul.rs:48-86).  dtype f32.  `workspace` is optional caller-owned device scratch of
+ * `workspace_bytes` (see rmlk_b200_matmul_workspace_bytes); NULL selects kernels that need none. */
+RMLK_API int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                     const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
+                     int64_t c_batch_stride, void* workspace, size_t workspace_bytes);
+RMLK_API size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RMLK_B200_H */

@@ -1,0 +1,127 @@
+// Shared device/host utilities for the rmlk_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <type_traits>
+
+#include "../../include/rmlk_b200.h"
+
+namespace rmlk {
+
+// ---------------------------------------------------------------------------------------------
+// error reporting
+// ---------------------------------------------------------------------------------------------
+void set_last_error(const std::string& msg);
+int fail(int code, const std::string& msg);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define RMLK_CHECK_LAUNCH(what)                                  \
+    do {                                                         \
+        cudaError_t _e = cudaGetLastError();                     \
+        if (_e != cudaSuccess) return ::rmlk::cuda_fail(_e, what); \
+    } while (0)
+
+#define RMLK_CUDA(call)                                           \
+    do {                                                          \
+        cudaError_t _e = (call);                                  \
+        if (_e != cudaSuccess) return ::rmlk::cuda_fail(_e, #call); \
+    } while (0)
+
+// Number of SMs of the current device (cached per device; an immutable capability table).
+int sm_count();
+
+inline size_t dtype_size(int dt) {
+    switch (dt) {
+        case RMLK_F16: case RMLK_U16: case RMLK_I16: return 2;
+        case RMLK_F32: case RMLK_I32: case RMLK_U32: return 4;
+        case RMLK_F64: case RMLK_I64: case RMLK_U64: return 8;
+        case RMLK_U8: case RMLK_I8: case RMLK_BOOL: return 1;
+        default: return 0;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// 32-bit fast division (valid for dividends < 2^31), in the style of the well-known
+// multiply-high + shift scheme: q = umulhi(n, mul) >> shr for d != 1.
+// ---------------------------------------------------------------------------------------------
+struct FastDiv {
+    uint32_t d, mul, shr;
+    FastDiv() : d(1), mul(0), shr(0) {}
+    explicit FastDiv(uint32_t div) : d(div), mul(0), shr(0) {
+        if (div > 1) {
+            uint32_t lg = 0;
+            while ((1ull << lg) < div) lg++;
+            const uint32_t p = 31 + lg;
+            mul = static_cast<uint32_t>(((1ull << p) + div - 1) / div);
+            shr = p - 32;
+        }
+    }
+    __host__ __device__ __forceinline__ uint32_t div(uint32_t n) const {
+#ifdef __CUDA_ARCH__
+        return d == 1 ? n : (__umulhi(n, mul) >> shr);
+#else
+        return d == 1 ? n : static_cast<uint32_t>((static_cast<uint64_t>(n) * mul) >> 32) >> shr;
+#endif
+    }
+    __host__ __device__ __forceinline__ void divmod(uint32_t n, uint32_t& q, uint32_t& r) const {
+        q = div(n);
+        r = n - q * d;
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+// aligned element packs: the compiler emits one 128-bit access per 16 bytes
+// ---------------------------------------------------------------------------------------------
+template <typename T, int N>
+struct alignas((sizeof(T) * N) >= 16 ? 16 : (sizeof(T) * N)) Pack {
+    T v[N];
+};
+
+template <typename T, int N>
+__device__ __forceinline__ Pack<T, N> load_pack(const T* p) {
+    return *reinterpret_cast<const Pack<T, N>*>(p);
+}
+template <typename T, int N>
+__device__ __forceinline__ void store_pack(T* p, const Pack<T, N>& v) {
+    *reinterpret_cast<Pack<T, N>*>(p) = v;
+}
+
+// Streaming (read-once) 128-bit load that does not allocate in L1.
+__device__ __forceinline__ uint4 ld_stream_u4(const void* p) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                 : "l"(p));
+    return r;
+}
+
+template <int BYTES>
+struct BytesT;
+template <> struct BytesT<1> { using type = uint8_t; };
+template <> struct BytesT<2> { using type = uint16_t; };
+template <> struct BytesT<4> { using type = uint32_t; };
+template <> struct BytesT<8> { using type = uint64_t; };
+template <> struct BytesT<16> { using type = uint4; };
+
+inline bool aligned_to(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
+
+inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+// Grid size for a flat kernel: enough blocks to cover `items`, capped so the grid stays a modest
+// multiple of the SM count (the kernels are grid-stride).
+inline unsigned flat_grid(int64_t items, int block, int per_sm_blocks) {
+    int64_t need = ceil_div64(items, block);
+    int64_t cap = static_cast<int64_t>(sm_count()) * per_sm_blocks;
+    if (need < 1) need = 1;
+    return static_cast<unsigned>(need < cap ? need : cap);
+}
+
+inline cudaStream_t as_stream(rmlk_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+
+}  // namespace rmlk

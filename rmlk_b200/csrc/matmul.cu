@@ -1,0 +1,400 @@
+// fp32 MatMul: C[b] = A[b] x B[b], row-major, fp32 accumulate.
+//
+// Two kernels, chosen by shape in rmlk_b200_matmul:
+//
+//  skinny_kernel   M <= 16 (decode GEMV / small-batch decode).  Memory-bound: every element of B is
+//                  read exactly once with 128-bit loads along N; a CTA owns a 32-column strip and its
+//                  256 threads are 8 column-quads x 32 k-lanes, 8 independent 128-bit loads in flight
+//                  per thread.  The A rows of the current k-chunk are staged in shared memory as
+//                  [k][m] so one LDS.128 feeds four FMAs rows.  When the strip count cannot fill the
+//                  GPU, K is also split across CTAs into a caller-provided scratch buffer that a
+//                  second kernel sums in a fixed order (deterministic, no atomics).
+//
+//  gemm_kernel     everything else.  Shared-memory tiled SIMT GEMM (BM x BN x 16, 256 threads,
+//                  register micro-tiles, double-buffered) with guarded edges, any M/N/K.
+//
+// The reference calls cublasGemmStridedBatchedEx with CUBLAS_COMPUTE_32F
+// (cuda/src/kernels/gemm.rs:206-231); both kernels accumulate in fp32 with FMA.
+#include "common.cuh"
+
+namespace rmlk {
+
+// ---------------------------------------------------------------------------------------------
+// skinny
+// ---------------------------------------------------------------------------------------------
+constexpr int SK_COLS = 32;    // columns per CTA
+constexpr int SK_KC = 256;     // k-chunk staged in shared memory
+constexpr int SK_THREADS = 256;
+
+struct SkinnyParams {
+    const float* a;
+    const float* b;
+    float* c;          // final output, or the split-K scratch when ksplit > 1
+    int64_t M, N, K;
+    int64_t sa, sb, sc;  // batch strides (elements)
+    int64_t k_per_split;
+    int ksplit;
+    int vec_b;           // B rows are 16-byte aligned (N % 4 == 0 and base aligned)
+};
+
+template <int MB>
+__global__ void __launch_bounds__(SK_THREADS) skinny_kernel(SkinnyParams p) {
+    constexpr int SA = MB >= 8 ? MB + 4 : MB;  // padded row stride: fewer bank conflicts while staging
+    __shared__ __align__(16) float sA[SK_KC * SA];
+    __shared__ __align__(16) float sRed[8 * MB * SK_COLS];
+    const int tx = threadIdx.x & 7;   // column quad
+    const int ty = threadIdx.x >> 3;  // k lane 0..31
+    const int64_t batch = blockIdx.z;
+    const int split = blockIdx.y;
+    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * SK_COLS + tx * 4;
+    const float* __restrict__ A = p.a + batch * p.sa;
+    const float* __restrict__ B = p.b + batch * p.sb;
+    const int64_t kbeg = static_cast<int64_t>(split) * p.k_per_split;
+    const int64_t kend = kbeg + p.k_per_split < p.K ? kbeg + p.k_per_split : p.K;
+
+    float acc[MB][4];
+#pragma unroll
+    for (int m = 0; m < MB; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[m][j] = 0.f;
+
+    const bool full_cols = p.vec_b && (n0 + 3 < p.N);
+    for (int64_t kc = kbeg; kc < kend; kc += SK_KC) {
+        const int kn = static_cast<int>(kend - kc < SK_KC ? kend - kc : SK_KC);
+        __syncthreads();
+        // stage A[:, kc:kc+kn] as sA[k][m]
+        for (int i = threadIdx.x; i < SK_KC * MB; i += SK_THREADS) {
+            const int m = i / SK_KC, k = i - m * SK_KC;  // consecutive threads -> consecutive k (coalesced)
+            float v = 0.f;
+            if (m < p.M && k < kn) v = A[static_cast<int64_t>(m) * p.K + kc + k];
+            sA[k * SA + m] = v;
+        }
+        __syncthreads();
+        float4 bv[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int k = ty + u * 32;
+            bv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k < kn) {
+                const float* src = B + (kc + k) * p.N + n0;
+                if (full_cols) {
+                    const uint4 raw = ld_stream_u4(src);
+                    bv[u] = make_float4(__uint_as_float(raw.x), __uint_as_float(raw.y), __uint_as_float(raw.z), __uint_as_float(raw.w));
+                } else {
+                    if (n0 + 0 < p.N) bv[u].x = src[0];
+                    if (n0 + 1 < p.N) bv[u].y = src[1];
+                    if (n0 + 2 < p.N) bv[u].z = src[2];
+                    if (n0 + 3 < p.N) bv[u].w = src[3];
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int k = ty + u * 32;
+            const float* arow = sA + k * SA;
+            float av[MB];
+            if constexpr (MB % 4 == 0) {
+#pragma unroll
+                for (int m = 0; m < MB; m += 4) {
+                    const float4 t = *reinterpret_cast<const float4*>(arow + m);
+                    av[m] = t.x; av[m + 1] = t.y; av[m + 2] = t.z; av[m + 3] = t.w;
+                }
+            } else {
+#pragma unroll
+                for (int m = 0; m < MB; m++) av[m] = arow[m];
+            }
+#pragma unroll
+            for (int m = 0; m < MB; m++) {
+                acc[m][0] = fmaf(av[m], bv[u].x, acc[m][0]);
+                acc[m][1] = fmaf(av[m], bv[u].y, acc[m][1]);
+                acc[m][2] = fmaf(av[m], bv[u].z, acc[m][2]);
+                acc[m][3] = fmaf(av[m], bv[u].w, acc[m][3]);
+            }
+        }
+    }
+    // reduce the 32 k-lanes: 4 inside each warp by shuffle, 8 warps through shared memory
+#pragma unroll
+    for (int m = 0; m < MB; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float v = acc[m][j];
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            acc[m][j] = v;
+        }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane < 8) {
+#pragma unroll
+        for (int m = 0; m < MB; m++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) sRed[(warp * MB + m) * SK_COLS + lane * 4 + j] = acc[m][j];
+    }
+    __syncthreads();
+    float* __restrict__ C = p.c + (p.ksplit > 1 ? (static_cast<int64_t>(split) * gridDim.z + batch) * p.M * p.N : batch * p.sc);
+    for (int i = threadIdx.x; i < MB * SK_COLS; i += SK_THREADS) {
+        const int m = i / SK_COLS, c = i - m * SK_COLS;
+        const int64_t n = static_cast<int64_t>(blockIdx.x) * SK_COLS + c;
+        if (m < p.M && n < p.N) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) s += sRed[(w * MB + m) * SK_COLS + c];
+            C[static_cast<int64_t>(m) * p.N + n] = s;
+        }
+    }
+}
+
+// Sum the split-K partials [ksplit][batch][M*N] in split order.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, float* __restrict__ c, int ksplit,
+                                                            int64_t batch, int64_t mn, int64_t sc) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= batch * mn) return;
+    const int64_t b = i / mn, e = i - b * mn;
+    float s = 0.f;
+    for (int k = 0; k < ksplit; k++) s += part[(static_cast<int64_t>(k) * batch + b) * mn + e];
+    c[b * sc + e] = s;
+}
+
+// ---------------------------------------------------------------------------------------------
+// tiled SIMT GEMM
+// ---------------------------------------------------------------------------------------------
+constexpr int GM_BK = 16;
+
+struct GemmParams {
+    const float* a;
+    const float* b;
+    float* c;
+    int64_t M, N, K;
+    int64_t sa, sb, sc;
+    int vec_a, vec_b;  // rows of A / B are 16-byte aligned
+};
+
+template <int BM, int BN>
+__global__ void __launch_bounds__(256) gemm_kernel(GemmParams p) {
+    constexpr int TM = BM / 16, TN = BN / 16;
+    __shared__ __align__(16) float As[2][GM_BK][BM + 4];
+    __shared__ __align__(16) float Bs[2][GM_BK][BN + 4];
+    const int tid = threadIdx.x;
+    const int tx = tid & 15, ty = tid >> 4;
+    const int64_t batch = blockIdx.z;
+    const int64_t m0 = static_cast<int64_t>(blockIdx.y) * BM, n0 = static_cast<int64_t>(blockIdx.x) * BN;
+    const float* __restrict__ A = p.a + batch * p.sa;
+    const float* __restrict__ B = p.b + batch * p.sb;
+    float* __restrict__ C = p.c + batch * p.sc;
+
+    // loader mapping: A tile is BM x 16 (k contiguous): quads along k -> BM*4 quads; B tile is 16 x BN: BN/4 quads per row
+    constexpr int A_QUADS = BM * GM_BK / 4, B_QUADS = BN * GM_BK / 4;
+    constexpr int A_PER = (A_QUADS + 255) / 256, B_PER = (B_QUADS + 255) / 256;
+    float4 ra[A_PER], rb[B_PER];
+
+    auto load_tiles = [&](int64_t k0) {
+#pragma unroll
+        for (int i = 0; i < A_PER; i++) {
+            const int q = tid + i * 256;
+            ra[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (q < A_QUADS) {
+                const int row = q >> 2, kq = (q & 3) * 4;
+                const int64_t gm = m0 + row, gk = k0 + kq;
+                if (gm < p.M) {
+                    const float* src = A + gm * p.K + gk;
+                    if (p.vec_a && gk + 3 < p.K) {
+                        ra[i] = *reinterpret_cast<const float4*>(src);
+                    } else {
+                        if (gk + 0 < p.K) ra[i].x = src[0];
+                        if (gk + 1 < p.K) ra[i].y = src[1];
+                        if (gk + 2 < p.K) ra[i].z = src[2];
+                        if (gk + 3 < p.K) ra[i].w = src[3];
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < B_PER; i++) {
+            const int q = tid + i * 256;
+            rb[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (q < B_QUADS) {
+                const int row = q / (BN / 4), cq = (q - row * (BN / 4)) * 4;
+                const int64_t gk = k0 + row, gn = n0 + cq;
+                if (gk < p.K) {
+                    const float* src = B + gk * p.N + gn;
+                    if (p.vec_b && gn + 3 < p.N) {
+                        rb[i] = *reinterpret_cast<const float4*>(src);
+                    } else {
+                        if (gn + 0 < p.N) rb[i].x = src[0];
+                        if (gn + 1 < p.N) rb[i].y = src[1];
+                        if (gn + 2 < p.N) rb[i].z = src[2];
+                        if (gn + 3 < p.N) rb[i].w = src[3];
+                    }
+                }
+            }
+        }
+    };
+    auto store_tiles = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < A_PER; i++) {
+            const int q = tid + i * 256;
+            if (q < A_QUADS) {
+                const int row = q >> 2, kq = (q & 3) * 4;
+                As[buf][kq + 0][row] = ra[i].x;
+                As[buf][kq + 1][row] = ra[i].y;
+                As[buf][kq + 2][row] = ra[i].z;
+                As[buf][kq + 3][row] = ra[i].w;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < B_PER; i++) {
+            const int q = tid + i * 256;
+            if (q < B_QUADS) {
+                const int row = q / (BN / 4), cq = (q - row * (BN / 4)) * 4;
+                *reinterpret_cast<float4*>(&Bs[buf][row][cq]) = rb[i];
+            }
+        }
+    };
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++) acc[i][j] = 0.f;
+
+    const int64_t nk = (p.K + GM_BK - 1) / GM_BK;
+    load_tiles(0);
+    store_tiles(0);
+    __syncthreads();
+    for (int64_t kt = 0; kt < nk; kt++) {
+        const int buf = static_cast<int>(kt & 1);
+        if (kt + 1 < nk) load_tiles((kt + 1) * GM_BK);
+#pragma unroll
+        for (int k = 0; k < GM_BK; k++) {
+            float a[TM], b[TN];
+            // thread (ty, tx) owns rows ty*4 + {0..3} (+64 for the second half when TM == 8) and the
+            // matching column pattern: 4-wide pieces keep the shared-memory reads 128-bit and conflict-free
+#pragma unroll
+            for (int i = 0; i < TM; i += 4) {
+                const float4 v = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4 + i * 16]);
+                a[i] = v.x; a[i + 1] = v.y; a[i + 2] = v.z; a[i + 3] = v.w;
+            }
+#pragma unroll
+            for (int j = 0; j < TN; j += 4) {
+                const float4 v = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4 + j * 16]);
+                b[j] = v.x; b[j + 1] = v.y; b[j + 2] = v.z; b[j + 3] = v.w;
+            }
+#pragma unroll
+            for (int i = 0; i < TM; i++)
+#pragma unroll
+                for (int j = 0; j < TN; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (kt + 1 < nk) {
+            store_tiles(buf ^ 1);
+            __syncthreads();
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < TM; i++) {
+        const int64_t gm = m0 + ty * 4 + (i / 4) * 64 + (i % 4);
+        if (gm >= p.M) continue;
+#pragma unroll
+        for (int j = 0; j < TN; j += 4) {
+            const int64_t gn = n0 + tx * 4 + (j / 4) * 64;
+            float* dst = C + gm * p.N + gn;
+            if (p.vec_b && gn + 3 < p.N) {
+                *reinterpret_cast<float4*>(dst) = make_float4(acc[i][j], acc[i][j + 1], acc[i][j + 2], acc[i][j + 3]);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; e++)
+                    if (gn + e < p.N) dst[e] = acc[i][j + e];
+            }
+        }
+    }
+}
+
+template <int MB>
+static void skinny_launch(cudaStream_t st, const SkinnyParams& p, dim3 grid) {
+    skinny_kernel<MB><<<grid, SK_THREADS, 0, st>>>(p);
+}
+
+static int skinny_plan(int64_t batch, int64_t n, int64_t k) {
+    // number of K splits that brings the grid to about two CTAs per SM
+    const int64_t strips = ceil_div64(n, SK_COLS) * batch;
+    const int64_t target = 2ll * sm_count();
+    if (strips >= target) return 1;
+    int64_t s = ceil_div64(target, strips);
+    const int64_t max_s = ceil_div64(k, 2 * SK_KC);  // keep at least two chunks per split
+    if (s > max_s) s = max_s;
+    if (s < 1) s = 1;
+    return static_cast<int>(s > 64 ? 64 : s);
+}
+
+}  // namespace rmlk
+
+using namespace rmlk;
+
+extern "C" size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k) {
+    if (dtype != RMLK_F32 || batch <= 0 || m <= 0 || n <= 0 || k <= 0 || m > 16) return 0;
+    const int s = skinny_plan(batch, n, k);
+    return s > 1 ? static_cast<size_t>(s) * batch * m * n * sizeof(float) : 0;
+}
+
+extern "C" int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                                const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
+                                int64_t c_batch_stride, void* workspace, size_t workspace_bytes) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for matmul (f32 only)");
+    if (batch < 0 || m < 0 || n < 0 || k < 0) return fail(RMLK_ERR_INVALID_ARG, "matmul: negative extent");
+    if (batch == 0 || m == 0 || n == 0) return RMLK_OK;
+    if (!c) return fail(RMLK_ERR_INVALID_ARG, "matmul: NULL output");
+    cudaStream_t st = as_stream(stream);
+    if (k == 0) {  // empty sum: C = 0
+        for (int64_t bi = 0; bi < batch; bi++)
+            RMLK_CUDA(cudaMemsetAsync(static_cast<float*>(c) + bi * c_batch_stride, 0, static_cast<size_t>(m) * n * sizeof(float), st));
+        return RMLK_OK;
+    }
+    if (!a || !b) return fail(RMLK_ERR_INVALID_ARG, "matmul: NULL operand");
+    if (batch > 65535) return fail(RMLK_ERR_INVALID_ARG, "matmul: batch exceeds 65535");
+    const bool b_rows_aligned = (n % 4 == 0) && aligned_to(b, 16) && (b_batch_stride % 4 == 0);
+    if (m <= 16) {
+        SkinnyParams p;
+        p.a = static_cast<const float*>(a);
+        p.b = static_cast<const float*>(b);
+        p.M = m; p.N = n; p.K = k;
+        p.sa = a_batch_stride; p.sb = b_batch_stride; p.sc = c_batch_stride;
+        p.vec_b = b_rows_aligned ? 1 : 0;
+        int ksplit = skinny_plan(batch, n, k);
+        const size_t need = static_cast<size_t>(ksplit) * batch * m * n * sizeof(float);
+        if (ksplit > 1 && (!workspace || workspace_bytes < need)) ksplit = 1;
+        p.ksplit = ksplit;
+        p.k_per_split = ksplit > 1 ? ceil_div64(ceil_div64(k, ksplit), SK_KC) * SK_KC : k;
+        if (ksplit > 1) p.ksplit = ksplit = static_cast<int>(ceil_div64(k, p.k_per_split));
+        p.c = ksplit > 1 ? static_cast<float*>(workspace) : static_cast<float*>(c);
+        dim3 grid(static_cast<unsigned>(ceil_div64(n, SK_COLS)), ksplit, static_cast<unsigned>(batch));
+        if (m == 1) skinny_launch<1>(st, p, grid);
+        else if (m == 2) skinny_launch<2>(st, p, grid);
+        else if (m <= 4) skinny_launch<4>(st, p, grid);
+        else if (m <= 8) skinny_launch<8>(st, p, grid);
+        else skinny_launch<16>(st, p, grid);
+        RMLK_CHECK_LAUNCH("skinny_kernel");
+        if (ksplit > 1) {
+            const int64_t total = batch * m * n;
+            splitk_reduce_kernel<<<static_cast<unsigned>(ceil_div64(total, 256)), 256, 0, st>>>(
+                static_cast<const float*>(workspace), static_cast<float*>(c), ksplit, batch, m * n, c_batch_stride);
+            RMLK_CHECK_LAUNCH("splitk_reduce_kernel");
+        }
+        return RMLK_OK;
+    }
+    GemmParams g;
+    g.a = static_cast<const float*>(a);
+    g.b = static_cast<const float*>(b);
+    g.c = static_cast<float*>(c);
+    g.M = m; g.N = n; g.K = k;
+    g.sa = a_batch_stride; g.sb = b_batch_stride; g.sc = c_batch_stride;
+    g.vec_a = ((k % 4 == 0) && aligned_to(a, 16) && (a_batch_stride % 4 == 0)) ? 1 : 0;
+    g.vec_b = (b_rows_aligned && aligned_to(c, 16) && (c_batch_stride % 4 == 0)) ? 1 : 0;
+    const int64_t tiles128 = ceil_div64(m, 128) * ceil_div64(n, 128) * batch;
+    if (m > 64 && tiles128 >= sm_count()) {
+        dim3 grid(static_cast<unsigned>(ceil_div64(n, 128)), static_cast<unsigned>(ceil_div64(m, 128)), static_cast<unsigned>(batch));
+        gemm_kernel<128, 128><<<grid, 256, 0, st>>>(g);
+    } else {
+        dim3 grid(static_cast<unsigned>(ceil_div64(n, 64)), static_cast<unsigned>(ceil_div64(m, 64)), static_cast<unsigned>(batch));
+        gemm_kernel<64, 64><<<grid, 256, 0, st>>>(g);
+    }
+    RMLK_CHECK_LAUNCH("gemm_kernel");
+    return RMLK_OK;
+}

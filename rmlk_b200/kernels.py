@@ -1,0 +1,285 @@
+"""Python bindings of the kernel launchers declared in include/rmlk_b200.h.
+
+Thin mirror of the reference's launch wrappers (cuda/src/kernels/*.rs): arguments are device buffers
+(torch CUDA tensors are used purely as memory handles) plus host-side shapes / strides, and every
+call lands in librmlk_b200.so.  Outputs are allocated by the caller or, for convenience in tests, by
+these helpers with `torch.empty` — the library itself never allocates.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Sequence
+
+import torch
+
+from . import dtypes as dt
+from ._lib import last_error, lib
+
+BIN = {"add": 0, "sub": 1, "mul": 2, "div": 3, "equal": 4, "greater": 5}
+UN = {"sqrt": 0, "neg": 1, "sin": 2, "cos": 3, "sigmoid": 4, "relu": 5}
+SCATTER = {"none": 0, "add": 1, "mul": 2, "max": 3, "min": 4}
+
+
+class RmlkError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"rmlk_b200 error {code}: {msg}")
+        self.code = code
+        self.msg = msg
+
+
+def _check(rc: int):
+    if rc != 0:
+        raise RmlkError(rc, last_error())
+
+
+def _i64(vals: Sequence[int]):
+    return (ctypes.c_int64 * max(len(vals), 1))(*[int(v) for v in vals])
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if t is not None and (not t.is_cuda or not t.is_contiguous()):
+            raise ValueError("rmlk_b200 kernels take contiguous CUDA tensors")
+
+
+def dense_strides(shape):
+    s = [1] * len(shape)
+    for i in range(len(shape) - 2, -1, -1):
+        s[i] = s[i + 1] * shape[i + 1]
+    return s
+
+
+def broadcast_strides(shape, out_shape):
+    """Element strides of a dense tensor of `shape` viewed as `out_shape` (0 on broadcast dims),
+    right-aligned — reference runtime/src/utils/mod.rs:93-111."""
+    st = dense_strides(shape)
+    n = len(out_shape)
+    r = [0] * n
+    for i in range(n):
+        j = i - (n - len(shape))
+        if j >= 0 and shape[j] == out_shape[i] and shape[j] != 1:
+            r[i] = st[j]
+    return r
+
+
+def _kshape(t):
+    return [1] if t.dim() == 0 else list(t.shape)
+
+
+def binary(op: str, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(a, b, out)
+    osh = list(torch.broadcast_shapes(tuple(_kshape(a)), tuple(_kshape(b))))
+    odt = torch.bool if op in ("equal", "greater") else a.dtype
+    if out is None:
+        out = torch.empty(osh if (a.dim() or b.dim()) else [], dtype=odt, device=a.device)
+    _check(lib().rmlk_b200_binary(_stream(), BIN[op], dt.from_torch(a.dtype), len(osh), _i64(osh),
+                                  _i64(broadcast_strides(_kshape(a), osh)), _i64(broadcast_strides(_kshape(b), osh)),
+                                  _ptr(a), _ptr(b), _ptr(out)))
+    return out
+
+
+def pow_(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(a, b, out)
+    osh = list(torch.broadcast_shapes(tuple(_kshape(a)), tuple(_kshape(b))))
+    if out is None:
+        out = torch.empty(osh if (a.dim() or b.dim()) else [], dtype=a.dtype, device=a.device)
+    _check(lib().rmlk_b200_pow(_stream(), dt.from_torch(a.dtype), dt.from_torch(b.dtype), len(osh), _i64(osh),
+                               _i64(broadcast_strides(_kshape(a), osh)), _i64(broadcast_strides(_kshape(b), osh)),
+                               _ptr(a), _ptr(b), _ptr(out)))
+    return out
+
+
+def unary(op: str, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(x, out)
+    if out is None:
+        out = torch.empty_like(x)
+    _check(lib().rmlk_b200_unary(_stream(), UN[op], dt.from_torch(x.dtype), ctypes.c_size_t(x.numel()), _ptr(x), _ptr(out)))
+    return out
+
+
+def cast(x: torch.Tensor, to: torch.dtype, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(x, out)
+    if out is None:
+        out = torch.empty(x.shape, dtype=to, device=x.device)
+    _check(lib().rmlk_b200_cast(_stream(), dt.from_torch(x.dtype), dt.from_torch(to), ctypes.c_size_t(x.numel()), _ptr(x), _ptr(out)))
+    return out
+
+
+def where(cond: torch.Tensor, x: torch.Tensor, y: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(cond, x, y, out)
+    osh = list(torch.broadcast_shapes(tuple(_kshape(x)), tuple(_kshape(y)), tuple(_kshape(cond))))
+    if out is None:
+        out = torch.empty(osh if (x.dim() or y.dim() or cond.dim()) else [], dtype=x.dtype, device=x.device)
+    _check(lib().rmlk_b200_where(_stream(), dt.from_torch(x.dtype), len(osh), _i64(osh),
+                                 _i64(broadcast_strides(_kshape(x), osh)), _i64(broadcast_strides(_kshape(y), osh)),
+                                 _i64(broadcast_strides(_kshape(cond), osh)), _ptr(x), _ptr(y), _ptr(cond), _ptr(out)))
+    return out
+
+
+def reduce_mean(x: torch.Tensor, axes: Sequence[int], keepdims: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(x, out)
+    sh = _kshape(x)
+    rank = len(sh)
+    ax = sorted(a + rank if a < 0 else a for a in axes)
+    osh = [1 if d in ax else sh[d] for d in range(rank)] if keepdims else [sh[d] for d in range(rank) if d not in ax]
+    if out is None:
+        out = torch.empty(osh, dtype=x.dtype, device=x.device)
+    _check(lib().rmlk_b200_reduce_mean(_stream(), dt.from_torch(x.dtype), rank, _i64(sh), len(ax), _i64(ax), _ptr(x), _ptr(out)))
+    return out
+
+
+def softmax(x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(x, out)
+    if out is None:
+        out = torch.empty_like(x)
+    cols = x.shape[-1]
+    rows = x.numel() // cols if cols else 0
+    _check(lib().rmlk_b200_softmax(_stream(), dt.from_torch(x.dtype), ctypes.c_int64(rows), ctypes.c_int64(cols), _ptr(x), _ptr(out)))
+    return out
+
+
+def gather(data: torch.Tensor, indices: torch.Tensor, axis: int = 0, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(data, indices, status)
+    axis = axis + data.dim() if axis < 0 else axis
+    sh = list(data.shape)
+    outer = 1
+    for d in sh[:axis]:
+        outer *= d
+    inner = 1
+    for d in sh[axis + 1:]:
+        inner *= d
+    osh = sh[:axis] + list(indices.shape) + sh[axis + 1:]
+    out = torch.empty(osh, dtype=data.dtype, device=data.device)
+    _check(lib().rmlk_b200_gather(_stream(), data.element_size(), dt.from_torch(indices.dtype), ctypes.c_int64(outer),
+                                  ctypes.c_int64(sh[axis]), ctypes.c_int64(inner), ctypes.c_int64(indices.numel()),
+                                  _ptr(data), _ptr(indices), _ptr(out), _ptr(status)))
+    return out
+
+
+def scatter_nd(data: torch.Tensor, indices: torch.Tensor, updates: torch.Tensor, reduction: str = "none",
+               status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _require_cuda(data, indices, updates, status)
+    k = indices.shape[-1] if indices.dim() > 1 else 1
+    n_tuples = indices.numel() // k if k else 0
+    out = torch.empty_like(data)
+    _check(lib().rmlk_b200_scatter_nd(_stream(), SCATTER[reduction], dt.from_torch(data.dtype), data.dim(), _i64(list(data.shape)),
+                                      ctypes.c_int64(n_tuples), k, _ptr(data), _ptr(indices), _ptr(updates), _ptr(out), _ptr(status)))
+    return out
+
+
+def slice_params(in_shape, starts, ends, axes=None, steps=None):
+    rank = len(in_shape)
+    os_, ost, osh = _i64([0] * rank), _i64([0] * rank), _i64([0] * rank)
+    _check(lib().rmlk_b200_slice_params(rank, _i64(in_shape), len(starts), _i64(starts), _i64(ends),
+                                        None if axes is None else _i64(axes), None if steps is None else _i64(steps), os_, ost, osh))
+    return list(os_)[:rank], list(ost)[:rank], list(osh)[:rank]
+
+
+def slice_(x: torch.Tensor, starts, ends, axes=None, steps=None) -> torch.Tensor:
+    _require_cuda(x)
+    st, sp, osh = slice_params(list(x.shape), starts, ends, axes, steps)
+    out = torch.empty(osh, dtype=x.dtype, device=x.device)
+    _check(lib().rmlk_b200_slice(_stream(), x.element_size(), x.dim(), _i64(list(x.shape)), _i64(osh), _i64(st), _i64(sp), _ptr(x), _ptr(out)))
+    return out
+
+
+def transpose(x: torch.Tensor, perm=None) -> torch.Tensor:
+    _require_cuda(x)
+    if perm is None:
+        perm = list(range(x.dim()))[::-1]
+    out = torch.empty([x.shape[p] for p in perm], dtype=x.dtype, device=x.device)
+    _check(lib().rmlk_b200_transpose(_stream(), x.element_size(), x.dim(), _i64(list(x.shape)), _i64(perm), _ptr(x), _ptr(out)))
+    return out
+
+
+def concat(inputs: Sequence[torch.Tensor], axis: int) -> torch.Tensor:
+    _require_cuda(*inputs)
+    rank = inputs[0].dim()
+    axis = axis + rank if axis < 0 else axis
+    sh = list(inputs[0].shape)
+    outer = 1
+    for d in sh[:axis]:
+        outer *= d
+    inner = 1
+    for d in sh[axis + 1:]:
+        inner *= d
+    dims = [t.shape[axis] for t in inputs]
+    osh = sh[:axis] + [sum(dims)] + sh[axis + 1:]
+    out = torch.empty(osh, dtype=inputs[0].dtype, device=inputs[0].device)
+    ptrs = (ctypes.c_void_p * len(inputs))(*[t.data_ptr() for t in inputs])
+    _check(lib().rmlk_b200_concat(_stream(), inputs[0].element_size(), len(inputs), ctypes.c_int64(outer), ctypes.c_int64(inner),
+                                  _i64(dims), ptrs, _ptr(out)))
+    return out
+
+
+def expand(x: torch.Tensor, shape) -> torch.Tensor:
+    _require_cuda(x)
+    osh = list(torch.broadcast_shapes(tuple(x.shape), tuple(int(v) for v in shape)))
+    out = torch.empty(osh, dtype=x.dtype, device=x.device)
+    ish = _kshape(x)
+    _check(lib().rmlk_b200_expand(_stream(), x.element_size(), len(ish), _i64(ish), len(osh), _i64(osh), _ptr(x), _ptr(out)))
+    return out
+
+
+def trilu(x: torch.Tensor, k: int = 0, upper: bool = True) -> torch.Tensor:
+    _require_cuda(x)
+    if x.dim() == 0:
+        b, r, c = 1, 1, 1
+    elif x.dim() == 1:
+        b, r, c = 1, 1, x.shape[0]
+    else:
+        r, c = x.shape[-2], x.shape[-1]
+        b = x.numel() // (r * c) if r * c else 0
+    out = torch.empty_like(x)
+    _check(lib().rmlk_b200_trilu(_stream(), x.element_size(), ctypes.c_int64(b), ctypes.c_int64(r), ctypes.c_int64(c), int(bool(upper)),
+                                 ctypes.c_int64(int(k)), _ptr(x), _ptr(out)))
+    return out
+
+
+def range_(start, delta, n: int, dtype: torch.dtype, device="cuda") -> torch.Tensor:
+    import numpy as np
+    npdt = dt.to_numpy(dt.from_torch(dtype))
+    s = np.array([start], dtype=npdt)
+    d = np.array([delta], dtype=npdt)
+    out = torch.empty([n], dtype=dtype, device=device)
+    _check(lib().rmlk_b200_range(_stream(), dt.from_torch(dtype), ctypes.c_int64(n), ctypes.c_void_p(s.ctypes.data),
+                                 ctypes.c_void_p(d.ctypes.data), _ptr(out)))
+    return out
+
+
+def fill(value, n: int, dtype: torch.dtype, device="cuda") -> torch.Tensor:
+    import numpy as np
+    v = np.array([value], dtype=dt.to_numpy(dt.from_torch(dtype)))
+    out = torch.empty([n], dtype=dtype, device=device)
+    _check(lib().rmlk_b200_fill(_stream(), out.element_size(), ctypes.c_int64(n), ctypes.c_void_p(v.ctypes.data), _ptr(out)))
+    return out
+
+
+def matmul_workspace_bytes(batch: int, m: int, n: int, k: int) -> int:
+    return int(lib().rmlk_b200_matmul_workspace_bytes(dt.F32, ctypes.c_int64(batch), ctypes.c_int64(m), ctypes.c_int64(n), ctypes.c_int64(k)))
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a: [..., m, k], b: [..., k, n] with equal batch products or one of them unbatched (rank 2)."""
+    _require_cuda(a, b, out, workspace)
+    m, k = a.shape[-2], a.shape[-1]
+    n = b.shape[-1]
+    ba = a.numel() // (m * k) if m * k else 1
+    bb = b.numel() // (k * n) if k * n else 1
+    batch = max(ba, bb)
+    lead = list(a.shape[:-2]) if ba >= bb else list(b.shape[:-2])
+    if out is None:
+        out = torch.empty(lead + [m, n], dtype=a.dtype, device=a.device)
+    _check(lib().rmlk_b200_matmul(_stream(), dt.from_torch(a.dtype), ctypes.c_int64(batch), ctypes.c_int64(m), ctypes.c_int64(n),
+                                  ctypes.c_int64(k), _ptr(a), ctypes.c_int64(m * k if ba > 1 else 0), _ptr(b),
+                                  ctypes.c_int64(k * n if bb > 1 else 0), _ptr(out), ctypes.c_int64(m * n), _ptr(workspace),
+                                  ctypes.c_size_t(0 if workspace is None else workspace.numel() * workspace.element_size())))
+    return out
