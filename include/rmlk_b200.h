@@ -151,6 +151,11 @@ RMLK_API int rmlk_b200_reduce_mean(rmlk_stream_t stream, int dtype, int rank, co
  * only one the reference dispatches, backend/softmax.rs:114-117), plus f16/f64. */
 RMLK_API int rmlk_b200_softmax(rmlk_stream_t stream, int dtype, int64_t rows, int64_t cols, const void* in, void* out);
 
+/* Softmax over the middle dimension of an [outer, channels, inner] view — the reference's second
+ * accepted form, axis 1 of a rank-4 tensor in cuDNN's MODE_CHANNEL (backend/softmax.rs:45-50). f32. */
+RMLK_API int rmlk_b200_softmax_strided(rmlk_stream_t stream, int dtype, int64_t outer, int64_t channels, int64_t inner,
+                                       const void* in, void* out);
+
 /* Gather along one axis of data viewed as [outer, axis_dim, inner]; out is [outer, n_idx, inner].
  * Replaces the host loop of cuMemcpyDtoD calls in runtime/src/providers/cuda/backend/gather.rs:199-258
  * (indices stay on the device; no D2H copy).  idx_dtype in {i32,i64}; negative indices wrap once.
@@ -213,6 +218,11 @@ RMLK_API int rmlk_b200_range(rmlk_stream_t stream, int dtype, int64_t n, const v
 /* Fill a contiguous buffer with one value (`value` points to a HOST scalar of elem_size bytes).
  * Replaces the host fill + H2D copy of runtime/src/providers/cuda/backend/constant_of_shape.rs:59-62. */
 RMLK_API int rmlk_b200_fill(rmlk_stream_t stream, int elem_size, int64_t n, const void* value, void* out);
+
+/* Writes up to 32 eight-byte words, passed by value from HOST memory, to device memory with a
+ * one-block kernel (no copy-engine round trip).  Used for Shape outputs and other tiny host-computed
+ * tensors that the reference uploads with a synchronous memcpy_htod (backend/shape.rs:67-72). */
+RMLK_API int rmlk_b200_store_small(rmlk_stream_t stream, int n_words, const uint64_t* words, void* out);
 
 /* Batched row-major MatMul, C[b] = A[b] x B[b], fp32 accumulate:
  * replaces rmlk_cuda::kernels::gemm::compute (cuda/src/kernels/gemm.rs:112-232,

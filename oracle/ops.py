@@ -288,7 +288,7 @@ def transpose(x: np.ndarray, perm=None) -> np.ndarray:
         raise ValueError("InvalidPermLength")
     if any(p < 0 or p >= x.ndim for p in perm):
         raise ValueError("PermIndexOutOfBounds")
-    return np.ascontiguousarray(np.transpose(x, perm))
+    return np.transpose(x, perm).copy(order="C")
 
 
 def slice_params(in_shape, starts, ends, axes=None, steps=None):

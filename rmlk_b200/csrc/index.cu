@@ -241,6 +241,11 @@ __global__ void __launch_bounds__(256) fill_kernel(uint64_t n, U value, U* __res
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < n; i += static_cast<uint64_t>(gridDim.x) * 256) out[i] = value;
 }
 
+struct SmallWords { uint64_t w[32]; };
+__global__ void store_small_kernel(SmallWords v, int n, uint64_t* __restrict__ out) {
+    if (threadIdx.x < n) out[threadIdx.x] = v.w[threadIdx.x];
+}
+
 // ---------------------------------------------------------------------------------------------
 // ScatterND
 // ---------------------------------------------------------------------------------------------
@@ -437,6 +442,8 @@ extern "C" int rmlk_b200_slice(rmlk_stream_t stream, int elem_size, int rank, co
                                const int64_t* starts, const int64_t* steps, const void* in, void* out) {
     if (rank < 1 || rank > RMLK_MAX_RANK || !in_shape || !out_shape || !starts || !steps)
         return fail(RMLK_ERR_INVALID_ARG, "slice: rank must be in [1, 8]");
+    for (int d = 0; d < rank; d++)
+        if (out_shape[d] == 0) return RMLK_OK;  // empty result: nothing to write
     if (!in || !out) return fail(RMLK_ERR_INVALID_ARG, "slice: NULL tensor pointer");
     int64_t in_stride[RMLK_MAX_RANK], eff[RMLK_MAX_RANK];
     int64_t run = 1, base = 0, n_out = 1;
@@ -632,4 +639,15 @@ extern "C" int rmlk_b200_scatter_nd(rmlk_stream_t stream, int reduction, int dty
         case RMLK_I32: return scatter_typed<int32_t>(st, reduction, p, indices, updates, out, status);
         default: return scatter_typed<int64_t>(st, reduction, p, indices, updates, out, status);
     }
+}
+
+extern "C" int rmlk_b200_store_small(rmlk_stream_t stream, int n_words, const uint64_t* words, void* out) {
+    if (n_words < 0 || n_words > 32) return fail(RMLK_ERR_INVALID_ARG, "store_small: at most 32 words");
+    if (n_words == 0) return RMLK_OK;
+    if (!words || !out || !aligned_to(out, 8)) return fail(RMLK_ERR_INVALID_ARG, "store_small: bad pointer");
+    SmallWords v;
+    for (int i = 0; i < 32; i++) v.w[i] = i < n_words ? words[i] : 0;
+    store_small_kernel<<<1, 32, 0, as_stream(stream)>>>(v, n_words, static_cast<uint64_t*>(out));
+    RMLK_CHECK_LAUNCH("store_small_kernel");
+    return RMLK_OK;
 }

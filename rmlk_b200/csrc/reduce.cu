@@ -334,6 +334,22 @@ __global__ void __launch_bounds__(BLOCK) softmax_generic_kernel(uint64_t rows, u
         for (uint64_t c = t; c < cols; c += G) dst[c] = static_cast<T>(sm_exp(static_cast<C>(src[c]) - mx) / sum);
 }
 
+// Softmax over the middle dim of [outer, C, inner]: one thread per (outer, inner) position, coalesced
+// along `inner`, three passes over C (the column stays in L1/L2).
+__global__ void __launch_bounds__(256) softmax_strided_kernel(uint64_t outer, uint64_t C, uint64_t inner, const float* __restrict__ in,
+                                                              float* __restrict__ out) {
+    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= outer * inner) return;
+    const uint64_t o = i / inner, r = i - o * inner;
+    const float* src = in + o * C * inner + r;
+    float* dst = out + o * C * inner + r;
+    float mx = -INFINITY;
+    for (uint64_t c = 0; c < C; c++) mx = fmaxf(mx, src[c * inner]);
+    float sum = 0.f;
+    for (uint64_t c = 0; c < C; c++) sum += expf(src[c * inner] - mx);
+    for (uint64_t c = 0; c < C; c++) dst[c * inner] = expf(src[c * inner] - mx) / sum;
+}
+
 template <int G, int NP>
 static void softmax_regs_launch(cudaStream_t st, uint64_t rows, uint32_t cols, const float* in, float* out) {
     constexpr int ROWS = 256 / G;
@@ -408,4 +424,19 @@ extern "C" int rmlk_b200_softmax(rmlk_stream_t stream, int dtype, int64_t rows, 
         return RMLK_OK;
     }
     return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for softmax");
+}
+
+extern "C" int rmlk_b200_softmax_strided(rmlk_stream_t stream, int dtype, int64_t outer, int64_t channels, int64_t inner,
+                                         const void* in, void* out) {
+    if (outer < 0 || channels < 0 || inner < 0) return fail(RMLK_ERR_INVALID_ARG, "softmax: negative extent");
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for softmax");
+    if (outer == 0 || channels == 0 || inner == 0) return RMLK_OK;
+    if (!in || !out) return fail(RMLK_ERR_INVALID_ARG, "softmax: NULL tensor pointer");
+    if (inner == 1) return rmlk_b200_softmax(stream, dtype, outer, channels, in, out);
+    const uint64_t n = static_cast<uint64_t>(outer) * inner;
+    softmax_strided_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+        static_cast<uint64_t>(outer), static_cast<uint64_t>(channels), static_cast<uint64_t>(inner), static_cast<const float*>(in),
+        static_cast<float*>(out));
+    RMLK_CHECK_LAUNCH("softmax_strided_kernel");
+    return RMLK_OK;
 }

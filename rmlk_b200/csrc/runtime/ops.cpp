@@ -1,0 +1,978 @@
+// Per-op backends: dtype dispatch, ONNX shape inference, output allocation and the kernel call.
+// One function per reference backend file (runtime/src/providers/cuda/backend/<op>.rs, cited at each).
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <limits>
+
+#include "runtime.h"
+
+namespace rmlk {
+namespace rt {
+
+namespace {
+
+using Shape = std::vector<int64_t>;
+
+bool is_int_dtype(int dt) {
+    switch (dt) {
+        case RMLK_I8: case RMLK_U8: case RMLK_I16: case RMLK_U16: case RMLK_I32: case RMLK_U32: case RMLK_I64: case RMLK_U64: case RMLK_BOOL:
+            return true;
+        default:
+            return false;
+    }
+}
+bool is_float_dtype(int dt) { return dt == RMLK_F16 || dt == RMLK_F32 || dt == RMLK_F64; }
+
+bool in_set(int dt, std::initializer_list<int> s) { return std::find(s.begin(), s.end(), dt) != s.end(); }
+
+int64_t prod(const Shape& s, size_t b = 0, size_t e = static_cast<size_t>(-1)) {
+    if (e > s.size()) e = s.size();
+    int64_t n = 1;
+    for (size_t i = b; i < e; i++) n *= s[i];
+    return n;
+}
+
+// Scalars are presented to kernels as shape [1] (reference runtime/src/providers/cuda/utils.rs:5-18).
+Shape kshape(const Tensor& t) { return t.is_scalar() ? Shape{1} : t.shape; }
+
+Shape dense_strides(const Shape& s) {
+    Shape st(s.size(), 1);
+    for (int i = static_cast<int>(s.size()) - 2; i >= 0; i--) st[i] = st[i + 1] * s[i + 1];
+    return st;
+}
+
+// runtime/src/utils/mod.rs:114-143
+bool broadcast_shape(const Shape& a, const Shape& b, Shape& out) {
+    const size_t n = std::max(a.size(), b.size());
+    out.assign(n, 1);
+    for (size_t i = 0; i < n; i++) {
+        const int64_t ad = i >= n - a.size() ? a[i - (n - a.size())] : 1;
+        const int64_t bd = i >= n - b.size() ? b[i - (n - b.size())] : 1;
+        if (ad != bd && ad != 1 && bd != 1) return false;
+        out[i] = std::max(ad, bd);
+        if (ad == 0 || bd == 0) out[i] = 0;
+    }
+    return true;
+}
+
+// runtime/src/utils/mod.rs:93-111: stride 0 wherever the operand is broadcast
+Shape broadcast_strides(const Shape& shape, const Shape& out) {
+    const Shape st = dense_strides(shape);
+    Shape r(out.size(), 0);
+    for (size_t i = 0; i < out.size(); i++) {
+        if (i + shape.size() < out.size()) continue;
+        const size_t j = i - (out.size() - shape.size());
+        if (shape[j] == out[i] && shape[j] != 1) r[i] = st[j];
+    }
+    return r;
+}
+
+std::string shape_str(const Shape& s) {
+    std::string r = "[";
+    for (size_t i = 0; i < s.size(); i++) r += (i ? ", " : "") + std::to_string(s[i]);
+    return r + "]";
+}
+
+// runtime/src/utils/mod.rs:159-182
+int64_t normalize_index(int64_t index, int64_t size) {
+    const int64_t n = index < 0 ? size + index : index;
+    if (n < 0 || n > size) raise(RMLK_ERR_INVALID_ARG, "axis out of bound " + std::to_string(index));
+    return n;
+}
+
+struct Ctx {
+    Instance& I;
+    const NodeDef& n;
+    Tensor* in(size_t i) const {
+        if (i >= n.inputs.size() || n.inputs[i] < 0) return nullptr;
+        Tensor& t = I.values[n.inputs[i]];
+        if (!t.present) raise(RMLK_ERR_INVALID_ARG, "input value `" + I.g.values[n.inputs[i]].name + "` has no data");
+        return &t;
+    }
+    Tensor& req(size_t i) const {
+        Tensor* t = in(i);
+        if (!t) raise(RMLK_ERR_INVALID_ARG, "missing input " + std::to_string(i));
+        return *t;
+    }
+    Tensor& out(size_t i) const {
+        if (i >= n.outputs.size()) raise(RMLK_ERR_INVALID_ARG, "missing output " + std::to_string(i));
+        return I.values[n.outputs[i]];
+    }
+    const Attr* attr(const char* name) const {
+        auto it = n.attrs.find(name);
+        return it == n.attrs.end() ? nullptr : &it->second;
+    }
+    int64_t attr_int(const char* name, int64_t dflt) const {
+        const Attr* a = attr(name);
+        return (a && a->kind == Attr::INT) ? a->i : dflt;
+    }
+    // Allocate output i with the given dtype/shape (init_payload in the reference).
+    Tensor& make(size_t i, int dtype, const Shape& shape) const {
+        Tensor& o = out(i);
+        o.dtype = dtype;
+        o.shape = shape;
+        o.mirror_valid = false;
+        o.mi.clear();
+        o.mf.clear();
+        I.alloc_output(n.outputs[i], o);
+        o.present = true;
+        return o;
+    }
+    // Zero-copy view of `src` with a new shape (Reshape / Unsqueeze / Flatten).
+    Tensor& view(size_t i, const Tensor& src, const Shape& shape) const {
+        Tensor& o = out(i);
+        const int vid = n.outputs[i];
+        const bool bound = I.binding_of_out[vid] >= 0;
+        o.dtype = src.dtype;
+        o.shape = shape;
+        o.mirror_valid = src.mirror_valid;
+        o.mi = src.mi;
+        o.mf = src.mf;
+        if (bound) {  // a carried output must own its storage
+            I.alloc_output(vid, o);
+            if (o.nbytes()) check_cuda(cudaMemcpyAsync(o.data, src.data, o.nbytes(), cudaMemcpyDeviceToDevice, I.stream), "view copy");
+            I.launches++;
+        } else {
+            o.data = src.data;
+            o.storage = src.storage;
+            if (o.storage) o.storage->refs++;
+        }
+        o.present = true;
+        return o;
+    }
+    rmlk_stream_t stream() const { return reinterpret_cast<rmlk_stream_t>(I.stream); }
+    void launched(int k = 1) const { I.launches += k; }
+};
+
+// ---- host mirrors ---------------------------------------------------------------------------
+void set_mirror_i(Tensor& t, const std::vector<int64_t>& v) {
+    t.mi = v;
+    t.mf.clear();
+    t.mirror_valid = true;
+}
+void set_mirror_f(Tensor& t, const std::vector<double>& v) {
+    t.mf = v;
+    t.mi.clear();
+    t.mirror_valid = true;
+}
+bool small_mirrored(const Tensor& t) { return t.mirror_valid && t.numel() <= HOST_MIRROR_MAX; }
+
+double round_to(int dt, double v) {
+    if (dt == RMLK_F32) return static_cast<double>(static_cast<float>(v));
+    return v;  // f64 (f16 mirrors are not kept)
+}
+
+// Broadcasted element index helper for mirror arithmetic (all tensors are tiny).
+int64_t bindex(const Shape& shape, const Shape& out, int64_t lin) {
+    const Shape ost = dense_strides(out);
+    const Shape st = broadcast_strides(shape, out);
+    int64_t off = 0;
+    for (size_t d = 0; d < out.size(); d++) {
+        const int64_t c = (lin / ost[d]) % out[d];
+        off += c * st[d];
+    }
+    return off;
+}
+
+// ---------------------------------------------------------------------------------------------
+// broadcast elementwise family
+// ---------------------------------------------------------------------------------------------
+// backend/binary.rs:18-162 with backend/{add,sub,mul,div,equal,greater}.rs
+void op_binary(const Ctx& c, int bop) {
+    Tensor& a = c.req(0);
+    Tensor& b = c.req(1);
+    if (!in_set(a.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_I64})) unsupported_dtype(a.dtype, "binary op");
+    if (a.dtype != b.dtype) raise(RMLK_ERR_INVALID_ARG, "binary op: operand data types differ (" + dtype_name(a.dtype) + " vs " + dtype_name(b.dtype) + ")");
+    Shape oshape;
+    if (!broadcast_shape(a.shape, b.shape, oshape))
+        raise(RMLK_ERR_INVALID_ARG, "incompatible tensor shapes: " + shape_str(a.shape) + " " + shape_str(b.shape));
+    const bool cmp = bop == RMLK_BIN_EQUAL || bop == RMLK_BIN_GREATER;
+    Tensor& o = c.make(0, cmp ? RMLK_BOOL : a.dtype, oshape);
+    const Shape ks = (a.is_scalar() && b.is_scalar()) ? Shape{1} : oshape;
+    const Shape as = broadcast_strides(kshape(a), ks), bs = broadcast_strides(kshape(b), ks);
+    check_rc(rmlk_b200_binary(c.stream(), bop, a.dtype, static_cast<int>(ks.size()), ks.data(), as.data(), bs.data(), a.data, b.data, o.data));
+    c.launched();
+    if (small_mirrored(a) && small_mirrored(b) && o.numel() <= HOST_MIRROR_MAX && a.dtype != RMLK_F16) {
+        const int64_t n = o.numel();
+        const bool isf = is_float_dtype(a.dtype);
+        std::vector<int64_t> ri(isf && !cmp ? 0 : n);
+        std::vector<double> rf(isf && !cmp ? n : 0);
+        for (int64_t i = 0; i < n; i++) {
+            const int64_t ia = bindex(a.shape, oshape, i), ib = bindex(b.shape, oshape, i);
+            if (isf) {
+                const double x = a.mf[ia], y = b.mf[ib];
+                switch (bop) {
+                    case RMLK_BIN_ADD: rf[i] = round_to(a.dtype, x + y); break;
+                    case RMLK_BIN_SUB: rf[i] = round_to(a.dtype, x - y); break;
+                    case RMLK_BIN_MUL: rf[i] = round_to(a.dtype, x * y); break;
+                    case RMLK_BIN_DIV: rf[i] = round_to(a.dtype, x / y); break;
+                    case RMLK_BIN_EQUAL: ri[i] = x == y; break;
+                    default: ri[i] = x > y; break;
+                }
+            } else {
+                const int64_t x = a.mi[ia], y = b.mi[ib];
+                auto wrap = [&](int64_t v) { return a.dtype == RMLK_I32 ? static_cast<int64_t>(static_cast<int32_t>(v)) : v; };
+                switch (bop) {
+                    case RMLK_BIN_ADD: ri[i] = wrap(static_cast<int64_t>(static_cast<uint64_t>(x) + static_cast<uint64_t>(y))); break;
+                    case RMLK_BIN_SUB: ri[i] = wrap(static_cast<int64_t>(static_cast<uint64_t>(x) - static_cast<uint64_t>(y))); break;
+                    case RMLK_BIN_MUL: ri[i] = wrap(static_cast<int64_t>(static_cast<uint64_t>(x) * static_cast<uint64_t>(y))); break;
+                    case RMLK_BIN_DIV: ri[i] = (y == 0 || (x == std::numeric_limits<int64_t>::min() && y == -1)) ? 0 : wrap(x / y); break;
+                    case RMLK_BIN_EQUAL: ri[i] = x == y; break;
+                    default: ri[i] = x > y; break;
+                }
+            }
+        }
+        if (isf && !cmp) set_mirror_f(o, rf); else set_mirror_i(o, ri);
+    }
+}
+
+// backend/pow.rs:95-132
+void op_pow(const Ctx& c) {
+    Tensor& a = c.req(0);
+    Tensor& b = c.req(1);
+    if (!in_set(a.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_I64})) unsupported_dtype(a.dtype, "pow base");
+    if (!in_set(b.dtype, {RMLK_U8, RMLK_U16, RMLK_U32, RMLK_U64, RMLK_I8, RMLK_I16, RMLK_I32, RMLK_I64, RMLK_F16, RMLK_F32, RMLK_F64}))
+        unsupported_dtype(b.dtype, "pow exponent");
+    Shape oshape;
+    if (!broadcast_shape(a.shape, b.shape, oshape))
+        raise(RMLK_ERR_INVALID_ARG, "incompatible tensor shapes: " + shape_str(a.shape) + " " + shape_str(b.shape));
+    Tensor& o = c.make(0, a.dtype, oshape);
+    const Shape ks = (a.is_scalar() && b.is_scalar()) ? Shape{1} : oshape;
+    const Shape as = broadcast_strides(kshape(a), ks), bs = broadcast_strides(kshape(b), ks);
+    check_rc(rmlk_b200_pow(c.stream(), a.dtype, b.dtype, static_cast<int>(ks.size()), ks.data(), as.data(), bs.data(), a.data, b.data, o.data));
+    c.launched();
+}
+
+// backend/unary.rs:12-50 (+ sqrt/neg/sin/cos.rs); backend/activation.rs:30-155 (sigmoid.rs, relu.rs)
+void op_unary(const Ctx& c, int uop) {
+    Tensor& x = c.req(0);
+    const bool ints_ok = uop == RMLK_UN_NEG || uop == RMLK_UN_RELU;
+    if (!(is_float_dtype(x.dtype) || (ints_ok && in_set(x.dtype, {RMLK_I32, RMLK_I64})))) unsupported_dtype(x.dtype, "unary op");
+    Tensor& o = c.make(0, x.dtype, x.shape);
+    check_rc(rmlk_b200_unary(c.stream(), uop, x.dtype, static_cast<size_t>(x.numel()), x.data, o.data));
+    c.launched();
+    if (uop == RMLK_UN_NEG && small_mirrored(x) && x.dtype != RMLK_F16) {
+        if (is_float_dtype(x.dtype)) {
+            std::vector<double> r(x.mf);
+            for (double& v : r) v = -v;
+            set_mirror_f(o, r);
+        } else {
+            std::vector<int64_t> r(x.mi);
+            for (int64_t& v : r) v = -v;
+            set_mirror_i(o, r);
+        }
+    }
+}
+
+int onnx_to_dtype(int64_t code) {
+    switch (code) {
+        case 1: return RMLK_F32; case 2: return RMLK_U8; case 3: return RMLK_I8; case 4: return RMLK_U16; case 5: return RMLK_I16;
+        case 6: return RMLK_I32; case 7: return RMLK_I64; case 8: return RMLK_STRING; case 9: return RMLK_BOOL; case 10: return RMLK_F16;
+        case 11: return RMLK_F64; case 12: return RMLK_U32; case 13: return RMLK_U64;
+        default: raise(RMLK_ERR_INVALID_ARG, "cast: unknown data type code " + std::to_string(code));
+    }
+}
+
+int64_t wrap_int(int dt, int64_t v) {
+    switch (dt) {
+        case RMLK_I8: return static_cast<int8_t>(v); case RMLK_U8: return static_cast<uint8_t>(v);
+        case RMLK_I16: return static_cast<int16_t>(v); case RMLK_U16: return static_cast<uint16_t>(v);
+        case RMLK_I32: return static_cast<int32_t>(v); case RMLK_U32: return static_cast<uint32_t>(v);
+        case RMLK_BOOL: return v != 0;
+        default: return v;
+    }
+}
+
+// backend/cast.rs:29-179
+void op_cast(const Ctx& c) {
+    Tensor& x = c.req(0);
+    const Attr* to = c.attr("to");
+    if (!to || to->kind != Attr::INT) raise(RMLK_ERR_INVALID_ARG, "missing `to` cast attribute");
+    const int dst = onnx_to_dtype(to->i);
+    // The op accepts the pairs the reference's backend dispatches (backend/cast.rs:30-67) and rejects the
+    // rest with the same "unsupported" error, although the kernel launcher takes every pair.
+    {
+        const int s = x.dtype;
+        const bool sf = is_float_dtype(s), df = is_float_dtype(dst);
+        const bool s4 = in_set(s, {RMLK_I32, RMLK_U32, RMLK_I64, RMLK_U64}), d4 = in_set(dst, {RMLK_I32, RMLK_U32, RMLK_I64, RMLK_U64});
+        bool ok = (sf && (df || d4) && s != dst) || (s4 && df);
+        ok = ok || (s == RMLK_I32 && dst == RMLK_I64) || (s == RMLK_I64 && dst == RMLK_I32) || (s == RMLK_U32 && dst == RMLK_U64) ||
+             (s == RMLK_U64 && dst == RMLK_U32) || (s == RMLK_BOOL && dst == RMLK_F32);
+        if (!ok) raise(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported cast: " + dtype_name(s) + " -> " + dtype_name(dst));
+    }
+    Tensor& o = c.make(0, dst, x.shape);
+    check_rc(rmlk_b200_cast(c.stream(), x.dtype, dst, static_cast<size_t>(x.numel()), x.data, o.data));
+    c.launched();
+    if (small_mirrored(x) && x.dtype != RMLK_F16 && dst != RMLK_F16) {
+        const int64_t n = x.numel();
+        if (is_float_dtype(dst)) {
+            std::vector<double> r(n);
+            for (int64_t i = 0; i < n; i++) r[i] = round_to(dst, is_float_dtype(x.dtype) ? x.mf[i] : static_cast<double>(x.mi[i]));
+            set_mirror_f(o, r);
+        } else {
+            std::vector<int64_t> r(n);
+            bool ok = true;
+            for (int64_t i = 0; i < n; i++) {
+                if (is_float_dtype(x.dtype)) {
+                    const double v = x.mf[i];
+                    if (!(std::fabs(v) < 9.0e18)) { ok = false; break; }  // saturating / NaN cases: leave to the device
+                    r[i] = dst == RMLK_BOOL ? (v != 0.0) : wrap_int(dst, static_cast<int64_t>(v));
+                } else {
+                    r[i] = wrap_int(dst, x.mi[i]);
+                }
+            }
+            if (ok) set_mirror_i(o, r);
+        }
+    }
+}
+
+// backend/whereop.rs:43-264
+void op_where(const Ctx& c) {
+    Tensor& cond = c.req(0);
+    Tensor& x = c.req(1);
+    Tensor& y = c.req(2);
+    if (!in_set(x.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_I64})) unsupported_dtype(x.dtype, "where");
+    if (cond.dtype != RMLK_BOOL) raise(RMLK_ERR_INVALID_ARG, "where: condition must be a bool tensor");
+    if (x.dtype != y.dtype) raise(RMLK_ERR_INVALID_ARG, "where: x and y data types differ");
+    Shape inter, oshape;
+    if (!broadcast_shape(x.shape, y.shape, inter) || !broadcast_shape(inter, cond.shape, oshape))
+        raise(RMLK_ERR_INVALID_ARG, "incompatible shapes for broadcast: " + shape_str(x.shape) + " " + shape_str(y.shape) + " " + shape_str(cond.shape));
+    Tensor& o = c.make(0, x.dtype, oshape);
+    const Shape ks = oshape.empty() ? Shape{1} : oshape;
+    const Shape xs = broadcast_strides(kshape(x), ks), ys = broadcast_strides(kshape(y), ks), cs = broadcast_strides(kshape(cond), ks);
+    check_rc(rmlk_b200_where(c.stream(), x.dtype, static_cast<int>(ks.size()), ks.data(), xs.data(), ys.data(), cs.data(), x.data, y.data, cond.data, o.data));
+    c.launched();
+    if (small_mirrored(x) && small_mirrored(y) && small_mirrored(cond) && o.numel() <= HOST_MIRROR_MAX && x.dtype != RMLK_F16) {
+        const int64_t n = o.numel();
+        const bool isf = is_float_dtype(x.dtype);
+        std::vector<int64_t> ri(isf ? 0 : n);
+        std::vector<double> rf(isf ? n : 0);
+        for (int64_t i = 0; i < n; i++) {
+            const bool z = cond.mi[bindex(cond.shape, oshape, i)] != 0;
+            const int64_t ix = bindex(x.shape, oshape, i), iy = bindex(y.shape, oshape, i);
+            if (isf) rf[i] = z ? x.mf[ix] : y.mf[iy]; else ri[i] = z ? x.mi[ix] : y.mi[iy];
+        }
+        if (isf) set_mirror_f(o, rf); else set_mirror_i(o, ri);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// reductions
+// ---------------------------------------------------------------------------------------------
+// backend/reduce_mean.rs:47-310
+void op_reduce_mean(const Ctx& c) {
+    Tensor& x = c.req(0);
+    if (!in_set(x.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_I64})) unsupported_dtype(x.dtype, "reduce_mean");
+    const int64_t rank = x.is_scalar() ? 1 : static_cast<int64_t>(x.shape.size());
+    const bool noop = c.attr_int("noop_with_empty_axes", 0) > 0;
+    const bool keepdims = c.attr_int("keepdims", 1) > 0;
+    bool have_axes = false;
+    std::vector<int64_t> axes;
+    if (Tensor* at = c.in(1)) {
+        if (at->numel() > 0) {
+            for (int64_t v : c.I.host_i64(*at)) axes.push_back(normalize_index(v, rank));
+            have_axes = true;
+        } else if (at->is_scalar()) {
+            raise(RMLK_ERR_INVALID_ARG, "ScalarAxisNotAllowed");
+        }
+    } else if (const Attr* a = c.attr("axes")) {
+        if (a->kind == Attr::INTS && !a->ints.empty()) {
+            for (int64_t v : a->ints) axes.push_back(normalize_index(v, rank));
+            have_axes = true;
+        }
+    } else {
+        for (int64_t i = 0; i < rank; i++) axes.push_back(i);
+        have_axes = true;
+    }
+    if (!have_axes && noop) {  // copy the input (copy_input_to_output, reduce_mean.rs:229-244)
+        Tensor& o = c.make(0, x.dtype, x.shape);
+        if (o.nbytes()) check_cuda(cudaMemcpyAsync(o.data, x.data, o.nbytes(), cudaMemcpyDeviceToDevice, c.I.stream), "reduce_mean copy");
+        c.launched();
+        return;
+    }
+    if (!have_axes) for (int64_t i = 0; i < rank; i++) axes.push_back(i);
+    std::vector<bool> reduced(rank, false);
+    for (int64_t a : axes) {
+        if (a >= rank) raise(RMLK_ERR_INVALID_ARG, "AxisOutOfBounds");
+        if (reduced[a]) raise(RMLK_ERR_INVALID_ARG, "DuplicateAxis");
+        reduced[a] = true;
+    }
+    Shape oshape;
+    if (!x.is_scalar()) {
+        if (!keepdims && static_cast<int64_t>(axes.size()) > rank) raise(RMLK_ERR_INVALID_ARG, "AxesLargerThanRank");
+        for (int64_t d = 0; d < rank; d++) {
+            if (reduced[d]) { if (keepdims) oshape.push_back(1); }
+            else oshape.push_back(x.shape[d]);
+        }
+    }
+    Tensor& o = c.make(0, x.dtype, oshape);
+    const Shape ks = kshape(x);
+    if (x.numel() == 0) return;
+    check_rc(rmlk_b200_reduce_mean(c.stream(), x.dtype, static_cast<int>(ks.size()), ks.data(), static_cast<int>(axes.size()), axes.data(), x.data, o.data));
+    c.launched();
+}
+
+// backend/softmax.rs:31-158
+void op_softmax(const Ctx& c) {
+    Tensor& x = c.req(0);
+    if (x.dtype != RMLK_F32) unsupported_dtype(x.dtype, "softmax");
+    const int64_t axis = c.attr_int("axis", -1);
+    const int64_t rank = static_cast<int64_t>(x.shape.size());
+    if (!(axis == -1 || (axis == 1 && rank == 4)))
+        raise(RMLK_ERR_INVALID_ARG, "unsupported input values: unsupported inputs axis `" + std::to_string(axis) + "` and rank `" + std::to_string(rank) + "`");
+    if (rank == 0) raise(RMLK_ERR_INVALID_ARG, "softmax: scalar input");
+    Tensor& o = c.make(0, x.dtype, x.shape);
+    if (axis == -1) {
+        const int64_t cols = x.shape[rank - 1];
+        check_rc(rmlk_b200_softmax(c.stream(), x.dtype, cols ? x.numel() / cols : 0, cols, x.data, o.data));
+    } else {
+        check_rc(rmlk_b200_softmax_strided(c.stream(), x.dtype, x.shape[0], x.shape[1], x.shape[2] * x.shape[3], x.data, o.data));
+    }
+    c.launched();
+}
+
+// ---------------------------------------------------------------------------------------------
+// MatMul — backend/matmul.rs:223-356
+// ---------------------------------------------------------------------------------------------
+void op_matmul(const Ctx& c) {
+    Tensor& a = c.req(0);
+    Tensor& b = c.req(1);
+    if (!in_set(a.dtype, {RMLK_F32})) unsupported_dtype(a.dtype, "matmul");
+    if (b.dtype != a.dtype) raise(RMLK_ERR_INVALID_ARG, "matmul: operand data types differ");
+    const size_t ar = a.shape.size(), br = b.shape.size();
+    if (ar == 0 || br == 0) raise(RMLK_ERR_INVALID_ARG, "ZeroRank");
+    const int64_t m = ar == 1 ? 1 : a.shape[ar - 2], ka = a.shape[ar - 1];
+    const int64_t kb = br == 1 ? b.shape[0] : b.shape[br - 2], n = br == 1 ? 1 : b.shape[br - 1];
+    const int64_t ba = ar > 2 ? prod(a.shape, 0, ar - 2) : 1, bb = br > 2 ? prod(b.shape, 0, br - 2) : 1;
+    if (ka != kb) raise(RMLK_ERR_INVALID_ARG, "IncompatibleDimForMul");
+    if (ba != bb && ba != 1 && bb != 1) raise(RMLK_ERR_INVALID_ARG, "IncompatibleDimForBroadcast");
+    const int64_t batch = std::max(ba, bb);
+    // Output shape: NumPy matmul.  (The reference collapses the leading batch dims of rank >= 3 results
+    // into one, matmul.rs:321-333; the buffer contents are identical.)
+    Shape lead;
+    if (ar > 2 && (ba >= bb || br <= 2)) lead.assign(a.shape.begin(), a.shape.end() - 2);
+    else if (br > 2) lead.assign(b.shape.begin(), b.shape.end() - 2);
+    Shape oshape = lead;
+    if (ar > 1) oshape.push_back(m);
+    if (br > 1) oshape.push_back(n);
+    Tensor& o = c.make(0, a.dtype, oshape);
+    if (o.numel() == 0) return;
+    // A weight shared by every batch entry (rank <= 2 right operand) folds the batch into M: one
+    // pass over B instead of the reference's per-batch copies (matmul.rs:48-86).
+    int64_t eb = batch, em = m, sa = ba > 1 ? m * ka : 0, sb = bb > 1 ? kb * n : 0, sc = m * n;
+    if (bb == 1 && ba > 1) {
+        em = ba * m;
+        eb = 1;
+        sa = sb = 0;
+        sc = em * n;
+    }
+    const size_t need = rmlk_b200_matmul_workspace_bytes(a.dtype, eb, em, n, ka);
+    void* ws = need ? c.I.matmul_ws.ensure(need) : nullptr;
+    check_rc(rmlk_b200_matmul(c.stream(), a.dtype, eb, em, n, ka, a.data, sa, b.data, sb, o.data, sc, ws, need));
+    c.launched(need ? 2 : 1);
+}
+
+// ---------------------------------------------------------------------------------------------
+// indexing / layout
+// ---------------------------------------------------------------------------------------------
+// backend/gather.rs:28-258
+void op_gather(const Ctx& c) {
+    Tensor& data = c.req(0);
+    Tensor& idx = c.req(1);
+    if (!in_set(data.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_U32, RMLK_I64, RMLK_U64})) unsupported_dtype(data.dtype, "gather");
+    if (!in_set(idx.dtype, {RMLK_I32, RMLK_I64})) unsupported_dtype(idx.dtype, "gather indices");
+    if (data.is_scalar()) raise(RMLK_ERR_INVALID_ARG, "scalar input data not allowed");
+    const int64_t rank = static_cast<int64_t>(data.shape.size());
+    const int64_t axis = normalize_index(c.attr_int("axis", 0), rank);
+    if (axis >= rank) raise(RMLK_ERR_INVALID_ARG, "rank axis mismatch");
+    Shape oshape(data.shape.begin(), data.shape.begin() + axis);
+    oshape.insert(oshape.end(), idx.shape.begin(), idx.shape.end());
+    oshape.insert(oshape.end(), data.shape.begin() + axis + 1, data.shape.end());
+    const int64_t axis_dim = data.shape[axis];
+    if (small_mirrored(idx)) {  // host-visible indices are validated up front, as the reference does for all of them
+        for (int64_t v : idx.mi)
+            if (v < -axis_dim || v >= axis_dim) raise(RMLK_ERR_INVALID_ARG, "axis out of bound " + std::to_string(v));
+    }
+    Tensor& o = c.make(0, data.dtype, oshape);
+    const int64_t outer = prod(data.shape, 0, axis), inner = prod(data.shape, axis + 1);
+    check_rc(rmlk_b200_gather(c.stream(), static_cast<int>(dtype_size_of(data.dtype)), idx.dtype, outer, axis_dim, inner, idx.numel(), data.data,
+                              idx.data, o.data, static_cast<int*>(c.I.status_word.ptr)));
+    c.launched();
+    if (small_mirrored(data) && small_mirrored(idx) && o.numel() <= HOST_MIRROR_MAX && data.dtype != RMLK_F16) {
+        const int64_t n_idx = idx.numel();
+        const bool isf = is_float_dtype(data.dtype);
+        std::vector<int64_t> ri;
+        std::vector<double> rf;
+        for (int64_t ou = 0; ou < outer; ou++)
+            for (int64_t j = 0; j < n_idx; j++) {
+                int64_t ix = idx.mi[j];
+                if (ix < 0) ix += axis_dim;
+                for (int64_t e = 0; e < inner; e++) {
+                    const int64_t src = (ou * axis_dim + ix) * inner + e;
+                    if (isf) rf.push_back(data.mf[src]); else ri.push_back(data.mi[src]);
+                }
+            }
+        if (isf) set_mirror_f(o, rf); else set_mirror_i(o, ri);
+    }
+}
+
+// backend/scatter_nd.rs:30-210
+void op_scatter_nd(const Ctx& c) {
+    Tensor& data = c.req(0);
+    Tensor& idx = c.req(1);
+    Tensor& upd = c.req(2);
+    if (!in_set(data.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_I64})) unsupported_dtype(data.dtype, "scatter_nd");
+    if (data.is_scalar() || idx.is_scalar() || upd.is_scalar()) raise(RMLK_ERR_INVALID_ARG, "scalar inputs are not allowed");
+    if (idx.dtype != RMLK_I64) unsupported_dtype(idx.dtype, "scatter_nd indices");
+    if (upd.dtype != data.dtype) raise(RMLK_ERR_INVALID_ARG, "scatter_nd: updates data type differs from data");
+    int red = RMLK_SCATTER_NONE;
+    if (const Attr* a = c.attr("reduction")) {
+        if (a->kind != Attr::STRING) raise(RMLK_ERR_INVALID_ARG, "scatter_nd: `reduction` must be a string");
+        const std::string& s = a->s;
+        if (s == "none" || s == "None") red = RMLK_SCATTER_NONE;
+        else if (s == "add" || s == "Add") red = RMLK_SCATTER_ADD;
+        else if (s == "mul" || s == "Mul") red = RMLK_SCATTER_MUL;
+        else if (s == "max" || s == "Max") red = RMLK_SCATTER_MAX;
+        else if (s == "min" || s == "Min") red = RMLK_SCATTER_MIN;
+        else raise(RMLK_ERR_INVALID_ARG, "unknown value `" + s + "` for `reduction`");
+    }
+    const size_t ir = idx.shape.size();
+    const int64_t k = ir > 1 ? idx.shape[ir - 1] : 1;
+    const int64_t n_tuples = ir > 1 ? prod(idx.shape, 0, ir - 1) : prod(idx.shape);
+    if (k < 1 || k > static_cast<int64_t>(data.shape.size())) raise(RMLK_ERR_INVALID_ARG, "scatter_nd: index tuple longer than the data rank");
+    const int64_t slice_len = prod(data.shape, static_cast<size_t>(k));
+    if (upd.numel() != n_tuples * slice_len) raise(RMLK_ERR_INVALID_ARG, "scatter_nd: updates shape does not match indices and data");
+    Tensor& o = c.make(0, data.dtype, data.shape);
+    check_rc(rmlk_b200_scatter_nd(c.stream(), red, data.dtype, static_cast<int>(data.shape.size()), data.shape.data(), n_tuples, static_cast<int>(k),
+                                  data.data, idx.data, upd.data, o.data, static_cast<int*>(c.I.status_word.ptr)));
+    c.launched(2);
+}
+
+// backend/slice.rs:49-464
+void op_slice(const Ctx& c) {
+    Tensor& x = c.req(0);
+    Tensor& starts = c.req(1);
+    Tensor& ends = c.req(2);
+    Tensor* axes = c.in(3);
+    Tensor* steps = c.in(4);
+    if (starts.dtype != ends.dtype) raise(RMLK_ERR_INVALID_ARG, "StartAndEndDataTypeMismatch");
+    if (!in_set(x.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_I64}) || !in_set(starts.dtype, {RMLK_I32, RMLK_I64}))
+        unsupported_dtype(x.dtype, "slice");
+    const int rank = static_cast<int>(x.shape.size());
+    if (rank < 1 || rank > RMLK_MAX_RANK) raise(RMLK_ERR_INVALID_ARG, "slice: rank must be in [1, 8]");
+    const std::vector<int64_t> sv = c.I.host_i64(starts), ev = c.I.host_i64(ends);
+    std::vector<int64_t> av, pv;
+    if (axes) av = c.I.host_i64(*axes);
+    if (steps) pv = c.I.host_i64(*steps);
+    if (sv.size() != ev.size()) raise(RMLK_ERR_INVALID_ARG, "slice: starts and ends differ in length");
+    if (axes && av.size() != sv.size()) raise(RMLK_ERR_INVALID_ARG, "slice: axes and starts differ in length");
+    if (steps && pv.size() != (axes ? av.size() : sv.size())) raise(RMLK_ERR_INVALID_ARG, "StepsAndAxesLengthMismatch");
+    // i32 index tensors: the reference clamps in i32; sentinels INT_MIN / INT_MAX behave the same in i64.
+    int64_t ost[RMLK_MAX_RANK], osp[RMLK_MAX_RANK], osh[RMLK_MAX_RANK];
+    check_rc(rmlk_b200_slice_params(rank, x.shape.data(), static_cast<int>(sv.size()), sv.data(), ev.data(), axes ? av.data() : nullptr,
+                                    steps ? pv.data() : nullptr, ost, osp, osh));
+    Shape oshape(osh, osh + rank);
+    Tensor& o = c.make(0, x.dtype, oshape);
+    if (o.numel() == 0) return;
+    check_rc(rmlk_b200_slice(c.stream(), static_cast<int>(dtype_size_of(x.dtype)), rank, x.shape.data(), osh, ost, osp, x.data, o.data));
+    c.launched();
+    if (small_mirrored(x) && rank == 1 && x.dtype != RMLK_F16) {
+        const bool isf = is_float_dtype(x.dtype);
+        std::vector<int64_t> ri;
+        std::vector<double> rf;
+        for (int64_t i = 0; i < osh[0]; i++) {
+            const int64_t s = ost[0] + osp[0] * i;
+            if (isf) rf.push_back(x.mf[s]); else ri.push_back(x.mi[s]);
+        }
+        if (isf) set_mirror_f(o, rf); else set_mirror_i(o, ri);
+    }
+}
+
+// backend/transpose.rs:44-178
+void op_transpose(const Ctx& c) {
+    Tensor& x = c.req(0);
+    if (!in_set(x.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_I64})) unsupported_dtype(x.dtype, "transpose");
+    const int rank = static_cast<int>(x.shape.size());
+    std::vector<int64_t> perm;
+    if (const Attr* a = c.attr("perm")) {
+        if (a->kind != Attr::INTS) raise(RMLK_ERR_INVALID_ARG, "transpose: `perm` must be a list of ints");
+        perm = a->ints;
+        if (static_cast<int>(perm.size()) != rank) raise(RMLK_ERR_INVALID_ARG, "InvalidPermLength");
+        for (int64_t p : perm)
+            if (p < 0 || p >= rank) raise(RMLK_ERR_INVALID_ARG, "PermIndexOutOfBounds { index: " + std::to_string(p) + " }");
+    } else {
+        for (int i = rank - 1; i >= 0; i--) perm.push_back(i);
+    }
+    Shape oshape(rank);
+    for (int d = 0; d < rank; d++) oshape[d] = x.shape[perm[d]];
+    Tensor& o = c.make(0, x.dtype, oshape);
+    if (rank == 0) {
+        check_cuda(cudaMemcpyAsync(o.data, x.data, o.nbytes(), cudaMemcpyDeviceToDevice, c.I.stream), "transpose scalar copy");
+        c.launched();
+        return;
+    }
+    if (rank > RMLK_MAX_RANK) raise(RMLK_ERR_INVALID_ARG, "transpose: rank must be at most 8");
+    if (o.numel() == 0) return;
+    check_rc(rmlk_b200_transpose(c.stream(), static_cast<int>(dtype_size_of(x.dtype)), rank, x.shape.data(), perm.data(), x.data, o.data));
+    c.launched();
+}
+
+// backend/concat.rs:28-198
+void op_concat(const Ctx& c) {
+    Tensor& first = c.req(0);
+    if (!in_set(first.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_U32, RMLK_I64, RMLK_U64})) unsupported_dtype(first.dtype, "concat");
+    if (first.is_scalar()) raise(RMLK_ERR_INVALID_ARG, "scalars are not allowed");
+    const Attr* ax = c.attr("axis");
+    if (!ax || ax->kind != Attr::INT) raise(RMLK_ERR_INVALID_ARG, "`axis` is missing");
+    const int64_t rank = static_cast<int64_t>(first.shape.size());
+    const int64_t axis = normalize_index(ax->i, rank);
+    if (axis >= rank) raise(RMLK_ERR_INVALID_ARG, "axis out of bound " + std::to_string(ax->i));
+    std::vector<const void*> ptrs;
+    std::vector<int64_t> dims;
+    std::vector<Tensor*> ins;
+    Shape oshape = first.shape;
+    int64_t total = 0;
+    for (size_t i = 0; i < c.n.inputs.size(); i++) {
+        Tensor* t = c.in(i);
+        if (!t) break;
+        if (static_cast<int64_t>(t->shape.size()) != rank)
+            raise(RMLK_ERR_INVALID_ARG, "ShapeMismatch { index: " + std::to_string(i) + ", base_rank: " + std::to_string(rank) + ", found_rank: " + std::to_string(t->shape.size()) + " }");
+        if (t->dtype != first.dtype) raise(RMLK_ERR_INVALID_ARG, "concat: input data types differ");
+        for (int64_t d = 0; d < rank; d++)
+            if (d != axis && t->shape[d] != first.shape[d])
+                raise(RMLK_ERR_INVALID_ARG, "DimensionMismatch { axis: " + std::to_string(d) + ", dim: " + std::to_string(t->shape[d]) + ", expected_dim: " + std::to_string(first.shape[d]) + " }");
+        total += t->shape[axis];
+        ptrs.push_back(t->data);
+        dims.push_back(t->shape[axis]);
+        ins.push_back(t);
+    }
+    oshape[axis] = total;
+    Tensor& o = c.make(0, first.dtype, oshape);
+    if (o.numel() == 0) return;
+    check_rc(rmlk_b200_concat(c.stream(), static_cast<int>(dtype_size_of(first.dtype)), static_cast<int>(ptrs.size()), prod(first.shape, 0, axis),
+                              prod(first.shape, axis + 1), dims.data(), ptrs.data(), o.data));
+    c.launched();
+    bool all = rank == 1 && first.dtype != RMLK_F16 && o.numel() <= HOST_MIRROR_MAX;
+    for (Tensor* t : ins) all = all && small_mirrored(*t);
+    if (all) {
+        if (is_float_dtype(first.dtype)) {
+            std::vector<double> r;
+            for (Tensor* t : ins) r.insert(r.end(), t->mf.begin(), t->mf.end());
+            set_mirror_f(o, r);
+        } else {
+            std::vector<int64_t> r;
+            for (Tensor* t : ins) r.insert(r.end(), t->mi.begin(), t->mi.end());
+            set_mirror_i(o, r);
+        }
+    }
+}
+
+// backend/expand.rs:49-216
+void op_expand(const Ctx& c) {
+    Tensor& x = c.req(0);
+    Tensor& sh = c.req(1);
+    if (!in_set(x.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_U32, RMLK_I64, RMLK_U64})) unsupported_dtype(x.dtype, "expand");
+    if (sh.dtype != RMLK_I64) unsupported_dtype(sh.dtype, "expand shape");
+    const std::vector<int64_t> target = c.I.host_i64(sh);
+    for (int64_t v : target)
+        if (v < 0) raise(RMLK_ERR_INVALID_ARG, "expand: negative dimension in shape");
+    Shape oshape;
+    if (!broadcast_shape(x.shape, target, oshape))
+        raise(RMLK_ERR_INVALID_ARG, "incompatible shapes for broadcast: " + shape_str(x.shape) + " " + shape_str(target));
+    if (oshape.size() > RMLK_MAX_RANK) raise(RMLK_ERR_INVALID_ARG, "expand: rank must be at most 8");
+    Tensor& o = c.make(0, x.dtype, oshape);
+    if (o.numel() == 0) return;
+    const Shape ish = kshape(x);
+    const Shape ks = oshape.empty() ? Shape{1} : oshape;
+    check_rc(rmlk_b200_expand(c.stream(), static_cast<int>(dtype_size_of(x.dtype)), static_cast<int>(ish.size()), ish.data(), static_cast<int>(ks.size()),
+                              ks.data(), x.data, o.data));
+    c.launched();
+    if (small_mirrored(x) && o.numel() <= HOST_MIRROR_MAX && x.dtype != RMLK_F16) {
+        const int64_t n = o.numel();
+        if (is_float_dtype(x.dtype)) {
+            std::vector<double> r(n);
+            for (int64_t i = 0; i < n; i++) r[i] = x.mf[bindex(x.shape, oshape, i)];
+            set_mirror_f(o, r);
+        } else {
+            std::vector<int64_t> r(n);
+            for (int64_t i = 0; i < n; i++) r[i] = x.mi[bindex(x.shape, oshape, i)];
+            set_mirror_i(o, r);
+        }
+    }
+}
+
+// backend/trilu.rs:48-146
+void op_trilu(const Ctx& c) {
+    Tensor& x = c.req(0);
+    if (!in_set(x.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_U32, RMLK_I64, RMLK_U64})) unsupported_dtype(x.dtype, "trilu");
+    const bool upper = c.attr_int("upper", 1) != 0;
+    int64_t k = 0;
+    if (Tensor* kt = c.in(1)) {
+        if (!kt->is_scalar()) raise(RMLK_ERR_INVALID_ARG, "InvalidKTensor");
+        if (kt->dtype != RMLK_I64) unsupported_dtype(kt->dtype, "trilu k");
+        k = c.I.host_i64(*kt)[0];
+    }
+    Tensor& o = c.make(0, x.dtype, x.shape);
+    if (o.numel() == 0) return;
+    // [batch, R, C] view: runtime/src/utils/mod.rs:226-239
+    int64_t b = 1, r = 1, cc = 1;
+    const size_t rank = x.shape.size();
+    if (rank == 1) cc = x.shape[0];
+    else if (rank >= 2) { r = x.shape[rank - 2]; cc = x.shape[rank - 1]; b = prod(x.shape, 0, rank - 2); }
+    check_rc(rmlk_b200_trilu(c.stream(), static_cast<int>(dtype_size_of(x.dtype)), b, r, cc, upper ? 1 : 0, k, x.data, o.data));
+    c.launched();
+}
+
+// backend/range.rs:28-205
+void op_range(const Ctx& c) {
+    Tensor& s = c.req(0);
+    Tensor& l = c.req(1);
+    Tensor& d = c.req(2);
+    if (!in_set(s.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_I64})) unsupported_dtype(s.dtype, "range");
+    if (l.dtype != s.dtype || d.dtype != s.dtype) raise(RMLK_ERR_INVALID_ARG, "range: start, limit and delta must share a data type");
+    if (s.numel() != 1 || l.numel() != 1 || d.numel() != 1) raise(RMLK_ERR_INVALID_ARG, "range: inputs must be scalars");
+    int64_t count = 0;
+    union { int32_t i32; int64_t i64; float f32; double f64; uint16_t f16; } sv{}, dv{};
+    if (is_int_dtype(s.dtype)) {
+        const int64_t start = c.I.host_i64(s)[0], limit = c.I.host_i64(l)[0], delta = c.I.host_i64(d)[0];
+        if (delta == 0) raise(RMLK_ERR_INVALID_ARG, "range: delta must not be zero");
+        count = std::max<int64_t>((limit - start) / delta, 0);  // truncating division (range.rs:140-152)
+        if (s.dtype == RMLK_I32) { sv.i32 = static_cast<int32_t>(start); dv.i32 = static_cast<int32_t>(delta); }
+        else { sv.i64 = start; dv.i64 = delta; }
+    } else {
+        if (s.dtype == RMLK_F16) unsupported_dtype(s.dtype, "range (f16 scalars are not mirrored on the host)");
+        const double start = c.I.host_f64(s)[0], limit = c.I.host_f64(l)[0], delta = c.I.host_f64(d)[0];
+        double cnt;
+        if (s.dtype == RMLK_F32) {
+            cnt = std::ceil((static_cast<float>(limit) - static_cast<float>(start)) / static_cast<float>(delta));
+            sv.f32 = static_cast<float>(start);
+            dv.f32 = static_cast<float>(delta);
+        } else {
+            cnt = std::ceil((limit - start) / delta);
+            sv.f64 = start;
+            dv.f64 = delta;
+        }
+        if (!(cnt >= 0.0) || cnt > 9.0e15) raise(RMLK_ERR_INVALID_ARG, "ConversionError");
+        count = static_cast<int64_t>(cnt);
+    }
+    Tensor& o = c.make(0, s.dtype, Shape{count});
+    if (count == 0) return;
+    check_rc(rmlk_b200_range(c.stream(), s.dtype, count, &sv, &dv, o.data));
+    c.launched();
+    if (count <= HOST_MIRROR_MAX) {
+        if (is_int_dtype(s.dtype)) {
+            std::vector<int64_t> r(count);
+            const int64_t st = s.dtype == RMLK_I32 ? sv.i32 : sv.i64, de = s.dtype == RMLK_I32 ? dv.i32 : dv.i64;
+            for (int64_t i = 0; i < count; i++) r[i] = wrap_int(s.dtype, st + i * de);
+            set_mirror_i(o, r);
+        } else {
+            std::vector<double> r(count);
+            for (int64_t i = 0; i < count; i++) {
+                if (s.dtype == RMLK_F32) {
+                    const float pr = static_cast<float>(i) * dv.f32;
+                    r[i] = static_cast<double>(sv.f32 + pr);
+                } else {
+                    r[i] = sv.f64 + static_cast<double>(i) * dv.f64;
+                }
+            }
+            set_mirror_f(o, r);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// shape-only ops: metadata changes, no payload copies
+// ---------------------------------------------------------------------------------------------
+// backend/reshape.rs:60-160
+void op_reshape(const Ctx& c) {
+    Tensor& x = c.req(0);
+    Tensor& sh = c.req(1);
+    if (sh.dtype != RMLK_I64) unsupported_dtype(sh.dtype, "reshape shape");
+    const bool allow_zero = c.attr_int("allowzero", 0) != 0;
+    std::vector<int64_t> dims = sh.shape.empty() ? std::vector<int64_t>{} : c.I.host_i64(sh);
+    Shape target(dims.size(), 0);
+    int neg = -1;
+    bool has_zero = false;
+    for (size_t i = 0; i < dims.size(); i++) {
+        if (dims[i] == -1) {
+            if (neg >= 0 || (allow_zero && has_zero)) raise(RMLK_ERR_INVALID_ARG, "ZeroDim and negative dimensions are not allowed");
+            neg = static_cast<int>(i);
+            target[i] = 1;
+        } else if (dims[i] == 0) {
+            if (allow_zero && neg >= 0) raise(RMLK_ERR_INVALID_ARG, "ZeroDim and negative dimensions are not allowed");
+            has_zero = true;
+            if (!allow_zero) {
+                if (i >= x.shape.size()) raise(RMLK_ERR_INVALID_ARG, "index out of range");
+                target[i] = x.shape[i];
+            }
+        } else if (dims[i] < 0) {
+            raise(RMLK_ERR_INVALID_ARG, "invalid index");
+        } else {
+            target[i] = dims[i];
+        }
+    }
+    const int64_t total = x.numel();
+    if (neg >= 0) {
+        const int64_t cur = prod(target);
+        if (cur == 0) {
+            if (total != 0) raise(RMLK_ERR_INVALID_ARG, "unable to hold the same number of elements");
+        } else {
+            if (total % cur != 0) raise(RMLK_ERR_INVALID_ARG, "unable to hold the same number of elements");
+            target[neg] = total / cur;
+        }
+    }
+    if (prod(target) != total) raise(RMLK_ERR_INVALID_ARG, "unable to hold the same number of elements");
+    c.view(0, x, target);
+}
+
+// backend/unsqueeze.rs:60-130
+void op_unsqueeze(const Ctx& c) {
+    Tensor& x = c.req(0);
+    std::vector<int64_t> axes;
+    if (Tensor* at = c.in(1)) {
+        if (at->shape.size() != 1) raise(RMLK_ERR_INVALID_ARG, "InvalidAxesRank");
+        axes = c.I.host_i64(*at);
+    } else if (const Attr* a = c.attr("axes")) {
+        axes = a->ints;
+    } else {
+        raise(RMLK_ERR_INVALID_ARG, "unsqueeze: missing axes");
+    }
+    for (size_t i = 0; i < axes.size(); i++)
+        for (size_t j = i + 1; j < axes.size(); j++)
+            if (axes[i] == axes[j]) raise(RMLK_ERR_INVALID_ARG, "DuplicateAxes");
+    const int64_t erank = static_cast<int64_t>(axes.size() + x.shape.size());
+    Shape oshape(erank, 0);
+    for (int64_t a : axes) {
+        const int64_t n = normalize_index(a, erank);
+        if (n >= erank) raise(RMLK_ERR_INVALID_ARG, "axis out of bound " + std::to_string(a));
+        oshape[n] = -1;
+    }
+    size_t src = 0;
+    for (int64_t i = 0; i < erank; i++) {
+        if (oshape[i] == -1) oshape[i] = 1;
+        else oshape[i] = x.shape[src++];
+    }
+    c.view(0, x, oshape);
+}
+
+// runtime/src/providers/cpu/flatten.rs
+void op_flatten(const Ctx& c) {
+    Tensor& x = c.req(0);
+    const int64_t rank = static_cast<int64_t>(x.shape.size());
+    int64_t axis = c.attr_int("axis", 1);
+    if (axis < 0) axis += rank;
+    if (axis < 0 || axis > rank) raise(RMLK_ERR_INVALID_ARG, "flatten: axis out of range");
+    c.view(0, x, Shape{prod(x.shape, 0, axis), prod(x.shape, axis)});
+}
+
+void store_small_i64(const Ctx& c, Tensor& o, const std::vector<int64_t>& vals) {
+    // values travel as kernel parameters; larger tensors go through an async copy from the mirror
+    const int64_t n = static_cast<int64_t>(vals.size());
+    for (int64_t b = 0; b < n; b += 32) {
+        const int cnt = static_cast<int>(std::min<int64_t>(32, n - b));
+        check_rc(rmlk_b200_store_small(c.stream(), cnt, reinterpret_cast<const uint64_t*>(vals.data() + b), static_cast<int64_t*>(o.data) + b));
+        c.launched();
+    }
+}
+
+// backend/shape.rs:30-80
+void op_shape(const Ctx& c) {
+    Tensor& x = c.req(0);
+    const int64_t rank = static_cast<int64_t>(x.shape.size());
+    int64_t start = c.attr_int("start", 0), end = c.attr_int("end", rank);
+    if (start < 0) start += rank;
+    if (end < 0) end += rank;
+    start = std::min(std::max<int64_t>(start, 0), rank);
+    end = std::min(std::max<int64_t>(end, 0), rank);
+    std::vector<int64_t> vals;
+    for (int64_t i = start; i < end; i++) vals.push_back(x.shape[i]);
+    Tensor& o = c.make(0, RMLK_I64, Shape{static_cast<int64_t>(vals.size())});
+    store_small_i64(c, o, vals);
+    set_mirror_i(o, vals);
+}
+
+// backend/constant_of_shape.rs:30-70
+void op_constant_of_shape(const Ctx& c) {
+    Tensor& sh = c.req(0);
+    if (sh.dtype != RMLK_I64) unsupported_dtype(sh.dtype, "constant_of_shape shape");
+    const std::vector<int64_t> dims = c.I.host_i64(sh);
+    for (int64_t v : dims)
+        if (v < 0) raise(RMLK_ERR_INVALID_ARG, "constant_of_shape: negative dimension");
+    int dtype = RMLK_F32;
+    uint8_t value[8] = {0};
+    if (const Attr* a = c.attr("value")) {
+        if (a->kind != Attr::TENSOR || a->t_data.size() < dtype_size_of(a->t_dtype) || dtype_size_of(a->t_dtype) == 0)
+            raise(RMLK_ERR_INVALID_ARG, "constant_of_shape: `value` must be a one-element tensor");
+        dtype = a->t_dtype;
+        std::memcpy(value, a->t_data.data(), dtype_size_of(dtype));
+    }
+    Tensor& o = c.make(0, dtype, dims);
+    if (o.numel() == 0) return;
+    check_rc(rmlk_b200_fill(c.stream(), static_cast<int>(dtype_size_of(dtype)), o.numel(), value, o.data));
+    c.launched();
+    if (o.numel() <= HOST_MIRROR_MAX && dtype != RMLK_F16) {
+        if (is_float_dtype(dtype)) {
+            double v = 0;
+            if (dtype == RMLK_F32) { float f; std::memcpy(&f, value, 4); v = f; } else std::memcpy(&v, value, 8);
+            set_mirror_f(o, std::vector<double>(o.numel(), v));
+        } else {
+            int64_t v = 0;
+            switch (dtype_size_of(dtype)) {
+                case 1: v = dtype == RMLK_I8 ? static_cast<int8_t>(value[0]) : value[0]; break;
+                case 2: { int16_t t; std::memcpy(&t, value, 2); v = dtype == RMLK_I16 ? t : static_cast<uint16_t>(t); break; }
+                case 4: { int32_t t; std::memcpy(&t, value, 4); v = dtype == RMLK_I32 ? t : static_cast<uint32_t>(t); break; }
+                default: std::memcpy(&v, value, 8); break;
+            }
+            set_mirror_i(o, std::vector<int64_t>(o.numel(), v));
+        }
+    }
+}
+
+}  // namespace
+
+size_t dtype_size_of(int dt) { return rmlk_b200_dtype_size(dt); }
+
+void Instance::run_node(const NodeDef& n) {
+    Ctx c{*this, n};
+    switch (n.op) {
+        case RMLK_OP_NOOP: case RMLK_OP_CONST: return;
+        case RMLK_OP_ADD: return op_binary(c, RMLK_BIN_ADD);
+        case RMLK_OP_SUB: return op_binary(c, RMLK_BIN_SUB);
+        case RMLK_OP_MUL: return op_binary(c, RMLK_BIN_MUL);
+        case RMLK_OP_DIV: return op_binary(c, RMLK_BIN_DIV);
+        case RMLK_OP_EQUAL: return op_binary(c, RMLK_BIN_EQUAL);
+        case RMLK_OP_GREATER: return op_binary(c, RMLK_BIN_GREATER);
+        case RMLK_OP_POW: return op_pow(c);
+        case RMLK_OP_SQRT: return op_unary(c, RMLK_UN_SQRT);
+        case RMLK_OP_NEG: return op_unary(c, RMLK_UN_NEG);
+        case RMLK_OP_SIN: return op_unary(c, RMLK_UN_SIN);
+        case RMLK_OP_COS: return op_unary(c, RMLK_UN_COS);
+        case RMLK_OP_SIGMOID: return op_unary(c, RMLK_UN_SIGMOID);
+        case RMLK_OP_RELU: return op_unary(c, RMLK_UN_RELU);
+        case RMLK_OP_CAST: return op_cast(c);
+        case RMLK_OP_WHERE: return op_where(c);
+        case RMLK_OP_REDUCE_MEAN: return op_reduce_mean(c);
+        case RMLK_OP_SOFTMAX: return op_softmax(c);
+        case RMLK_OP_MATMUL: return op_matmul(c);
+        case RMLK_OP_GATHER: return op_gather(c);
+        case RMLK_OP_SCATTER_ND: return op_scatter_nd(c);
+        case RMLK_OP_SLICE: return op_slice(c);
+        case RMLK_OP_TRANSPOSE: return op_transpose(c);
+        case RMLK_OP_CONCAT: return op_concat(c);
+        case RMLK_OP_EXPAND: return op_expand(c);
+        case RMLK_OP_TRILU: return op_trilu(c);
+        case RMLK_OP_RANGE: return op_range(c);
+        case RMLK_OP_RESHAPE: return op_reshape(c);
+        case RMLK_OP_UNSQUEEZE: return op_unsqueeze(c);
+        case RMLK_OP_FLATTEN: return op_flatten(c);
+        case RMLK_OP_SHAPE: return op_shape(c);
+        case RMLK_OP_CONSTANT_OF_SHAPE: return op_constant_of_shape(c);
+        case RMLK_OP_CONSTANT: return;  // materialised at instance creation
+        default:
+            raise(RMLK_ERR_INVALID_ARG, "op " + std::to_string(n.op) + " is outside the operator path this library implements");
+    }
+}
+
+}  // namespace rt
+}  // namespace rmlk

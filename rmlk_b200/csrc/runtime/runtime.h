@@ -1,0 +1,175 @@
+// Host runtime types: graph description, tensors, device arena, instance.
+// Host side of the operator path; the reference counterparts are cited in include/rmlk_b200_runtime.h.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <map>
+#include <memory>
+#include <stdexcept>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../../include/rmlk_b200_runtime.h"
+
+namespace rmlk {
+namespace rt {
+
+// Error carrying an rmlk_status; thrown inside the runtime, converted at the C ABI.
+struct Error : std::runtime_error {
+    int code;
+    Error(int c, const std::string& m) : std::runtime_error(m), code(c) {}
+};
+[[noreturn]] inline void raise(int code, const std::string& msg) { throw Error(code, msg); }
+std::string dtype_name(int dt);
+[[noreturn]] void unsupported_dtype(int dt, const char* what);
+
+struct Attr {
+    enum Kind { INT, INTS, FLOAT, STRING, TENSOR } kind = INT;
+    int64_t i = 0;
+    std::vector<int64_t> ints;
+    float f = 0.f;
+    std::string s;
+    int t_dtype = RMLK_UNDEFINED;
+    std::vector<int64_t> t_dims;
+    std::vector<uint8_t> t_data;
+};
+
+struct ValueDef {
+    std::string name;
+    int dtype = RMLK_UNDEFINED;
+    std::vector<int64_t> dims;  // 0 = dynamic
+    bool is_input = false, is_output = false, is_const = false;
+    std::shared_ptr<std::vector<uint8_t>> data;  // initializer payload (host), shared between graph copies
+    const void* device_data = nullptr;           // or: initializer already resident on the device
+};
+
+struct NodeDef {
+    int op = RMLK_OP_NOOP;
+    std::vector<int> inputs;   // value ids, -1 = omitted optional input
+    std::vector<int> outputs;  // value ids
+    std::map<std::string, Attr> attrs;
+};
+
+struct Graph {
+    std::vector<ValueDef> values;
+    std::unordered_map<std::string, int> by_name;
+    std::vector<NodeDef> nodes;
+    int add_value(const std::string& name, int dtype, int rank, const int64_t* dims);
+    int find(const std::string& name) const;
+};
+
+// Small integer / float tensors (shapes, axes, slice bounds, Range scalars) carry a host mirror so
+// that shape inference never waits on the GPU.  The reference reads these back with a synchronous
+// D2H copy in every op that needs them (e.g. backend/expand.rs:152-153, backend/slice.rs:276-334).
+constexpr int64_t HOST_MIRROR_MAX = 64;
+
+struct Storage;
+
+struct Tensor {
+    int dtype = RMLK_UNDEFINED;
+    std::vector<int64_t> shape;  // empty = scalar
+    void* data = nullptr;        // device
+    Storage* storage = nullptr;  // arena ownership (null: weights, inputs, carried buffers)
+    bool present = false;
+    bool mirror_valid = false;
+    std::vector<int64_t> mi;  // integer / bool mirror
+    std::vector<double> mf;   // float mirror
+    int64_t numel() const {
+        int64_t n = 1;
+        for (int64_t d : shape) n *= d;
+        return n;
+    }
+    bool is_scalar() const { return shape.empty(); }
+    size_t nbytes() const;
+};
+
+// Device memory for intermediates: bump allocation over large blocks plus a size-keyed free list, so
+// that a buffer released after its last consumer was enqueued (single stream: stream order makes
+// the reuse safe) serves a later op of the same run.  Everything is handed back at the start of the
+// next run.  Replaces the reference's 4 KiB CudaBump with per-tensor cuMemAlloc fallback
+// (runtime/src/providers/cuda/allocator.rs:96-139).
+struct Storage {
+    void* ptr = nullptr;
+    size_t size = 0;
+    int refs = 0;
+};
+
+class Arena {
+  public:
+    explicit Arena(size_t block_bytes) : block_bytes_(block_bytes) {}
+    ~Arena();
+    Storage* alloc(size_t bytes);
+    void release(Storage* s);  // drop one reference; at zero the buffer returns to the free list
+    void reset();
+    size_t peak() const { return peak_; }
+
+  private:
+    struct Block {
+        char* base;
+        size_t size, used;
+    };
+    void* bump(size_t bytes);
+    std::vector<Block> blocks_;
+    std::multimap<size_t, void*> free_;
+    std::vector<std::unique_ptr<Storage>> live_;
+    size_t block_bytes_, bumped_ = 0, peak_ = 0;
+};
+
+// A persistent device buffer that grows geometrically.
+struct DeviceBuffer {
+    void* ptr = nullptr;
+    size_t cap = 0;
+    void* ensure(size_t bytes);
+    void release();
+};
+
+struct Binding {  // output value -> input value, double-buffered
+    int out_id, in_id;
+    DeviceBuffer buf[2];
+    int cur = 0;  // buffer the NEXT run writes
+    Tensor carried;  // what the next run reads as the input
+    bool have = false;
+};
+
+struct Instance {
+    Graph g;
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    std::vector<Tensor> values;
+    std::vector<DeviceBuffer> input_bufs;  // per value id (only inputs use theirs)
+    DeviceBuffer weights;
+    std::unique_ptr<Arena> arena;
+    DeviceBuffer status_word;   // device int for gather / scatter_nd diagnostics
+    DeviceBuffer matmul_ws;     // split-K scratch
+    std::vector<Binding> bindings;
+    std::vector<Tensor> const_nodes;       // per node: the materialised `value` of a Constant op
+    std::vector<int> last_use;             // per value id: index of the last node reading it (-1: never)
+    std::vector<uint8_t> input_fed;        // per value id: fed for the coming run
+    std::vector<uint8_t> persistent;       // per value id: initializer / Constant output / input (kept across runs)
+    std::vector<int> binding_of_out;       // per value id: index into `bindings` if it is a carried output, else -1
+    int64_t launches = 0, syncs = 0;
+    bool status_dirty = false;
+
+    ~Instance();
+    // gives `t` (the tensor of value `value_id`, dtype/shape already set) device memory
+    void alloc_output(int value_id, Tensor& t);
+    void run();
+    // host view of a small tensor: mirror if valid, else a synchronous D2H copy
+    std::vector<int64_t> host_i64(const Tensor& t);
+    std::vector<double> host_f64(const Tensor& t);
+    void run_node(const NodeDef& n);
+    void release_value(int value_id);
+    void check_status();
+};
+
+size_t dtype_size_of(int dt);
+
+void check_cuda(cudaError_t e, const char* what);
+void check_rc(int rc);
+
+}  // namespace rt
+}  // namespace rmlk

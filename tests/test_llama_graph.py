@@ -1,0 +1,191 @@
+"""The Llama-shaped op graph: construction checked on the CPU, execution checked on the GPU.
+
+CPU: the op list of rmlk_b200.llama.build_graph, walked by the numpy interpreter (oracle/graph_cpu.py), must
+equal an independently written dense numpy decoder (float64) for prefill and for incremental decode with a
+KV cache.  GPU: the same graphs through librmlk_b200.so must match the interpreter — end-to-end logits at
+rel 1e-4 (the path's stated bar), including BASELINE config 2 (one Llama-3.2-1B-shaped layer, 128-token prefill
+then 32 decode steps).
+"""
+import numpy as np
+import pytest
+
+from oracle import graph_cpu
+from rmlk_b200 import llama
+
+TINY = llama.LlamaConfig(hidden=64, n_heads=4, n_kv_heads=2, head_dim=16, ffn=128, vocab=97, n_layers=2)
+
+
+def dense_reference(cfg, w, ids):
+    """Plain float64 decoder over the whole sequence ids [B,T] -> logits [B,T,V] (no cache, no op graph)."""
+    w = {k: v.astype(np.float64) for k, v in w.items()}
+    B, T = ids.shape
+    x = w["embed"][ids]
+    half = cfg.head_dim // 2
+    inv = 1.0 / (cfg.rope_theta ** (np.arange(0, cfg.head_dim, 2) / cfg.head_dim))
+    ang = np.arange(T)[:, None] * inv[None, :]
+    cos = np.cos(np.concatenate([ang, ang], -1))[None, None]
+    sin = np.sin(np.concatenate([ang, ang], -1))[None, None]
+
+    def norm(v, g):
+        return v / np.sqrt((v * v).mean(-1, keepdims=True) + cfg.rms_eps) * g
+
+    def rope(v):
+        rot = np.concatenate([-v[..., half:], v[..., :half]], -1)
+        return v * cos + rot * sin
+
+    mask = np.where(np.arange(T)[None, :] > np.arange(T)[:, None], -np.inf, 0.0)
+    for l in range(cfg.n_layers):
+        h = norm(x, w[f"l{l}.ln1"])
+        q = (h @ w[f"l{l}.wq"]).reshape(B, T, cfg.n_heads, cfg.head_dim).transpose(0, 2, 1, 3)
+        k = (h @ w[f"l{l}.wk"]).reshape(B, T, cfg.n_kv_heads, cfg.head_dim).transpose(0, 2, 1, 3)
+        v = (h @ w[f"l{l}.wv"]).reshape(B, T, cfg.n_kv_heads, cfg.head_dim).transpose(0, 2, 1, 3)
+        q, k = rope(q), rope(k)
+        k = np.repeat(k, cfg.n_heads // cfg.n_kv_heads, axis=1)
+        v = np.repeat(v, cfg.n_heads // cfg.n_kv_heads, axis=1)
+        s = q @ k.transpose(0, 1, 3, 2) / np.sqrt(cfg.head_dim) + mask
+        p = np.exp(s - s.max(-1, keepdims=True))
+        p /= p.sum(-1, keepdims=True)
+        o = (p @ v).transpose(0, 2, 1, 3).reshape(B, T, cfg.hidden)
+        x = x + o @ w[f"l{l}.wo"]
+        h2 = norm(x, w[f"l{l}.ln2"])
+        g = h2 @ w[f"l{l}.wgate"]
+        x = x + ((g / (1.0 + np.exp(-g))) * (h2 @ w[f"l{l}.wup"])) @ w[f"l{l}.wdown"]
+    return norm(x, w["ln_f"]) @ w["lm_head"]
+
+
+def feeds_for(cfg, ids, past, context):
+    b, s = ids.shape
+    t = context + s
+    f = {"input_ids": ids, "attention_mask": np.ones((b, t), np.int64),
+         "position_ids": np.broadcast_to(np.arange(context, t, dtype=np.int64), (b, s)).copy()}
+    for l in range(cfg.n_layers):
+        f[f"past_key_values.{l}.key"], f[f"past_key_values.{l}.value"] = past[l]
+    return f
+
+
+def cpu_decode(cfg, spec, ids, prefill):
+    """Prefill `prefill` tokens, then one token per step, through the CPU interpreter.  Returns the
+    logits of every position [B,T,V]."""
+    B, T = ids.shape
+    past = [(np.zeros((B, cfg.n_kv_heads, 0, cfg.head_dim), np.float32),) * 2 for _ in range(cfg.n_layers)]
+    outs = []
+    ctx = 0
+    for s0, s1 in [(0, prefill)] + [(t, t + 1) for t in range(prefill, T)]:
+        out = graph_cpu.run_graph(spec, feeds_for(cfg, ids[:, s0:s1], past, ctx))
+        past = [(out[f"present.{l}.key"], out[f"present.{l}.value"]) for l in range(cfg.n_layers)]
+        ctx = s1
+        outs.append(out["logits"])
+    return np.concatenate(outs, axis=1)
+
+
+def test_graph_matches_dense_decoder_on_cpu():
+    w = llama.make_weights_host(TINY, seed=1)
+    for k in w:  # larger weights so that attention is far from uniform
+        if k.startswith("l") and not k.endswith(("ln1", "ln2")) and k != "lm_head":
+            w[k] = (w[k] * 6).astype(np.float32)
+    spec = llama.build_graph(TINY, w)
+    ids = np.random.default_rng(0).integers(0, TINY.vocab, size=(3, 9))
+    want = dense_reference(TINY, w, ids)
+    got = cpu_decode(TINY, spec, ids, prefill=5)
+    assert got.shape == want.shape
+    assert np.max(np.abs(got - want)) / np.max(np.abs(want)) < 2e-5
+    # padding mask: a padded key position must not influence the other positions
+    f = feeds_for(TINY, ids[:, :6], [(np.zeros((3, TINY.n_kv_heads, 0, TINY.head_dim), np.float32),) * 2] * TINY.n_layers, 0)
+    f["attention_mask"] = f["attention_mask"].copy()
+    f["attention_mask"][:, 0] = 0
+    out_pad = graph_cpu.run_graph(spec, f)["logits"]
+    ids2 = ids[:, :6].copy()
+    ids2[:, 0] = (ids2[:, 0] + 1) % TINY.vocab
+    f2 = dict(f, input_ids=ids2)
+    out_pad2 = graph_cpu.run_graph(spec, f2)["logits"]
+    assert np.allclose(out_pad[:, 1:], out_pad2[:, 1:], atol=1e-6)
+
+
+def test_graph_is_unfused_reference_vocabulary():
+    from rmlk_b200.runtime import Op
+    spec = llama.build_graph(TINY, llama.make_weights_host(TINY))
+    names = {n.op for n in spec.nodes}
+    assert names <= {o.name for o in Op}
+    for must in ["Gather", "Pow", "ReduceMean", "Sqrt", "Div", "Range", "Sin", "Cos", "Trilu", "Where", "Equal", "Expand", "Slice", "Neg",
+                 "Concat", "Transpose", "MatMul", "Softmax", "Sigmoid", "Cast", "Reshape", "Unsqueeze", "Shape", "ConstantOfShape"]:
+        assert must in names, must
+    per_layer = sum(1 for n in spec.nodes if n.outputs[0].startswith("l0.") or n.outputs[0].startswith("present.0."))
+    assert per_layer >= 55
+
+
+# ------------------------------------------------------------------------------------------------
+# GPU
+# ------------------------------------------------------------------------------------------------
+def gpu_decode(cfg, spec, ids, prefill):
+    dec = llama.Decoder(cfg, spec)
+    dec.reset(ids.shape[0])
+    outs = [dec.step(ids[:, :prefill])]
+    launches = [dec.inst.last_launches]
+    for t in range(prefill, ids.shape[1]):
+        outs.append(dec.step(ids[:, t:t + 1]))
+        launches.append(dec.inst.last_launches)
+        assert dec.inst.last_syncs == 0
+    return np.concatenate(outs, axis=1), launches, dec
+
+
+@pytest.mark.gpu
+def test_tiny_decoder_gpu_vs_oracle(cuda):
+    w = llama.make_weights_host(TINY, seed=1)
+    for k in w:
+        if k.startswith("l") and not k.endswith(("ln1", "ln2")) and k != "lm_head":
+            w[k] = (w[k] * 6).astype(np.float32)
+    spec = llama.build_graph(TINY, w)
+    ids = np.random.default_rng(0).integers(0, TINY.vocab, size=(3, 12))
+    want = cpu_decode(TINY, spec, ids, prefill=5)
+    got, launches, dec = gpu_decode(TINY, spec, ids, prefill=5)
+    assert np.max(np.abs(got - want)) / np.max(np.abs(want)) <= 1e-4
+    assert np.array_equal(got.argmax(-1), want.argmax(-1))
+    assert launches[1] == launches[-1], "a decode step enqueues the same number of kernels at every context length"
+    # the carried KV cache equals the oracle's
+    d, shape, _ = dec.inst.value_info("present.1.key")
+    assert shape == [3, TINY.n_kv_heads, 12, TINY.head_dim]
+
+
+@pytest.mark.gpu
+def test_one_1b_shaped_layer_prefill_128_decode_32(cuda):
+    """BASELINE config 2: hidden 2048, 32 q heads, 8 kv heads, head_dim 64, FFN 8192, fp32, N(0, 0.02) init;
+    batch 1, 128-token prefill then 32 decode steps; every step's output against the CPU interpreter."""
+    cfg = llama.LLAMA_1B_ONE_LAYER
+    w = llama.make_weights_host(cfg, seed=0, with_embedding=False)
+    spec = llama.build_graph(cfg, w, with_embedding=False)
+    rng = np.random.default_rng(0)
+    T = 128 + 32
+    embeds = rng.standard_normal((1, T, cfg.hidden), dtype=np.float32)
+
+    def feeds(s0, s1, past):
+        f = {"inputs_embeds": embeds[:, s0:s1], "attention_mask": np.ones((1, s1), np.int64),
+             "position_ids": np.arange(s0, s1, dtype=np.int64)[None]}
+        f["past_key_values.0.key"], f["past_key_values.0.value"] = past
+        return f
+
+    from rmlk_b200.runtime import ModelInstance
+    inst = ModelInstance(spec.to_runtime())
+    inst.bind("present.0.key", "past_key_values.0.key")
+    inst.bind("present.0.value", "past_key_values.0.value")
+    empty = np.zeros((1, cfg.n_kv_heads, 0, cfg.head_dim), np.float32)
+    past = (empty, empty)
+    worst = 0.0
+    for step, (s0, s1) in enumerate([(0, 128)] + [(t, t + 1) for t in range(128, T)]):
+        f = feeds(s0, s1, past)
+        cpu = graph_cpu.run_graph(spec, f)
+        past = (cpu["present.0.key"], cpu["present.0.value"])
+        gf = dict(f)
+        if step > 0:  # the GPU side carries its own KV cache on the device
+            gf.pop("past_key_values.0.key")
+            gf.pop("past_key_values.0.value")
+        for k, v in gf.items():
+            inst.set_input(k, v)
+        inst.launch()
+        got = inst.read("hidden_out")
+        err = np.max(np.abs(got - cpu["hidden_out"])) / np.max(np.abs(cpu["hidden_out"]))
+        worst = max(worst, float(err))
+        assert inst.last_syncs == 0
+        if step in (0, 1, 32):
+            gk = inst.read("present.0.key")
+            assert np.max(np.abs(gk - cpu["present.0.key"])) <= 1e-4 * np.max(np.abs(cpu["present.0.key"]))
+    assert worst <= 1e-4, worst

@@ -7,8 +7,8 @@ import numpy as np
 def ulp_diff(a: np.ndarray, b: np.ndarray) -> int:
     """Largest distance in units in the last place between two float arrays of the same dtype
     (NaNs must coincide)."""
-    a = np.asarray(a)
-    b = np.asarray(b)
+    a = np.atleast_1d(np.asarray(a))
+    b = np.atleast_1d(np.asarray(b))
     assert a.shape == b.shape and a.dtype == b.dtype, (a.shape, b.shape, a.dtype, b.dtype)
     if a.size == 0:
         return 0
