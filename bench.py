@@ -1,0 +1,398 @@
+"""Headline benchmark: decode tok/s of a Llama-3.2-1B-shaped fp32 model run as un-fused ONNX-style ops.
+
+Workload (BASELINE config 3): 16 layers, hidden 2048, 32 q / 8 kv heads, head_dim 64, FFN 8192, vocab 128256,
+random-init weights; 64 independent requests per GPU decoded as one batch, 512-token uniform-random prompts,
+then greedy-style decode steps of one token per request (context 512 + step).  A "step" is one decode
+step over the 64 requests = one pass of the op graph through the host runtime and kernels of
+librmlk_b200.so.  Requests are sharded across GPUs with no collective (one process per GPU, weights
+replicated), so per-GPU work is fixed and scaling is "weak".
+
+    python bench.py --gpus 1 --steps 32 --warmup 3
+    python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...      # the CPU path (numpy oracle interpreter) on the host cores
+
+Prints ONE JSON line (rank 0).  `value` is device-resident (inputs already in HBM); `e2e` feeds host
+buffers and reads the logits back every step.  `roofline` is measured live for the dominant kernel
+(the weight-streaming MatMul); `cpu_baseline` times the CPU oracle on a bounded sample of the same step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+REQUESTS_PER_GPU = 64
+PROMPT = 512
+METRIC = "decode_tokens_per_s"
+UNIT = "tok/s"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def workload_config(cfg, batch, prompt):
+    return {
+        "workload": f"llama-3.2-1b-shaped fp32 decode as un-fused ONNX ops; {batch} requests per GPU decoded as one batch, "
+                    f"{prompt}-token uniform-random prompts, one token per request per step",
+        "layers": cfg.n_layers, "hidden": cfg.hidden, "heads": cfg.n_heads, "kv_heads": cfg.n_kv_heads, "head_dim": cfg.head_dim,
+        "ffn": cfg.ffn, "vocab": cfg.vocab, "requests_per_gpu": batch, "prompt_tokens": prompt,
+        "l2": "weights (4.9 GB) and KV cache exceed L2 (126 MB): every step streams them from HBM, no flush needed",
+        "sharding": "independent requests per GPU, weights replicated, no collective",
+    }
+
+
+# ---------------------------------------------------------------------------------------------------
+# clocks
+# ---------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = os.path.join("/tmp", f"rmlk_clocks_{os.getpid()}.csv")
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if not self.proc:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        try:
+            for line in open(self.path):
+                f = [x.strip() for x in line.split(",")]
+                if len(f) < 9:
+                    continue
+                try:
+                    sm.append(float(f[1]))
+                    mx.append(float(f[2]))
+                except ValueError:
+                    continue
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+            os.remove(self.path)
+        except Exception:
+            pass
+        if sm:
+            out["sm_mhz"] = statistics.median(sm)
+            out["sm_max_mhz"] = max(mx)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# CPU path (oracle): bounded sample of the same decode step
+# ---------------------------------------------------------------------------------------------------
+def cpu_decode_sample(cfg, batch, context, steps, seed=0):
+    """Times `steps` decode steps of `batch` requests at context `context` through the numpy oracle
+    interpreter with a synthetic KV cache.  Returns (tok/s, threads, description)."""
+    import torch
+    from oracle import graph_cpu
+    from rmlk_b200 import llama
+    threads = os.cpu_count() or 1
+    torch.manual_seed(seed)
+    w = {}
+    for name, shape in llama.weight_shapes(cfg).items():
+        if name == "lm_head":
+            continue
+        w[name] = (torch.ones(shape) if name.endswith(("ln1", "ln2", "ln_f")) else torch.randn(shape) * 0.02).numpy()
+    w["lm_head"] = np.ascontiguousarray(w["embed"].T)
+    spec = llama.build_graph(cfg, w)
+    rng = np.random.default_rng(seed)
+    past = [(rng.standard_normal((batch, cfg.n_kv_heads, context, cfg.head_dim), dtype=np.float32),
+             rng.standard_normal((batch, cfg.n_kv_heads, context, cfg.head_dim), dtype=np.float32)) for _ in range(cfg.n_layers)]
+    times = []
+    ctx = context
+    for s in range(steps + 1):  # first step is a warm-up (BLAS thread pool, page faults)
+        feeds = {"input_ids": rng.integers(0, cfg.vocab, size=(batch, 1)), "attention_mask": np.ones((batch, ctx + 1), np.int64),
+                 "position_ids": np.full((batch, 1), ctx, np.int64)}
+        for l in range(cfg.n_layers):
+            feeds[f"past_key_values.{l}.key"], feeds[f"past_key_values.{l}.value"] = past[l]
+        t0 = time.perf_counter()
+        out = graph_cpu.run_graph(spec, feeds, fast=True)
+        dt = time.perf_counter() - t0
+        if s > 0:
+            times.append(dt)
+        past = [(out[f"present.{l}.key"], out[f"present.{l}.value"]) for l in range(cfg.n_layers)]
+        ctx += 1
+    total = sum(times)
+    return batch * len(times) / total, threads, f"{batch} requests x {len(times)} decode steps at context {context}, synthetic KV cache, numpy oracle interpreter"
+
+
+def run_reference(args):
+    """--impl reference: the reference has no CPU build of its own for this path (Rust + CUDA only), so
+    the CPU arm is the numpy restatement of its op semantics (oracle/), on all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from rmlk_b200 import llama
+    cfg = llama.LLAMA_1B
+    batch = 8
+    steps = max(1, min(args.steps, 4))
+    v, threads, sample = cpu_decode_sample(cfg, batch, PROMPT, steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": 1,
+        "ms_per_step": 1000.0 * batch / v, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(cfg, REQUESTS_PER_GPU, PROMPT),
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------------------------------
+# GPU path
+# ---------------------------------------------------------------------------------------------------
+def time_kernel(fn, iters=20, warm=3):
+    import torch
+    for _ in range(warm):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def roofline_for_matmul(batch, peak_gbs, peak_kind):
+    """Live timing of the dominant kernel: the weight-streaming MatMul of the decode step at the FFN
+    gate/up shape [batch, 2048] x [2048, 8192].  A ring of weight matrices larger than L2 keeps every launch
+    reading its weights from HBM."""
+    import torch
+    from rmlk_b200 import kernels as K
+    m, k, n = batch, 2048, 8192
+    ring = [torch.randn(k, n, device="cuda") * 0.02 for _ in range(4)]   # 4 x 67 MB > 126 MB L2
+    x = torch.randn(m, k, device="cuda")
+    out = torch.empty(m, n, device="cuda")
+    ws_bytes = K.matmul_workspace_bytes(1, m, n, k)
+    ws = torch.empty(max(ws_bytes // 4, 1), device="cuda") if ws_bytes else None
+    state = {"i": 0}
+
+    def fn():
+        K.matmul(x, ring[state["i"] % len(ring)], out=out, workspace=ws)
+        state["i"] += 1
+
+    ms = time_kernel(fn, iters=40, warm=8)
+    algo_bytes = 4 * (m * k + k * n + m * n)
+    achieved = algo_bytes / (ms * 1e-3) / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs, "traffic": None,
+            "kernel": "matmul (weight streaming)", "shape": [m, k, n], "algorithmic_bytes_per_launch": algo_bytes,
+            "ms_per_launch": ms, "tflops": 2.0 * m * k * n / (ms * 1e-3) / 1e12, "peak_kind": f"of {peak_kind} copy bandwidth"}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from rmlk_b200 import dtypes as dt
+    from rmlk_b200 import llama
+
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+
+    cfg = llama.LLAMA_1B
+    B, P = args.requests, args.prompt
+    K_, W = args.steps, args.warmup
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        weights = llama.make_weights_device(cfg, seed=0)
+    stream.synchronize()
+    spec = llama.build_graph(cfg, weights, device_weights=True)
+    dec = llama.Decoder(cfg, spec, device=local, stream=stream.cuda_stream, arena_bytes=(2 << 30))
+    inst = dec.inst
+    rng = np.random.default_rng(1234 + rank)
+
+    # ---- prefill (untimed set-up): all requests, full prompts -------------------------------------
+    dec.reset(B)
+    prompt_ids = rng.integers(0, cfg.vocab, size=(B, P))
+    dec.feed(prompt_ids)
+    inst.launch()
+    inst.synchronize()
+    prefill_launches = inst.last_launches
+
+    total_steps = 2 * (W + K_)
+    ids_all = torch.from_numpy(rng.integers(0, cfg.vocab, size=(total_steps, B, 1))).pin_memory()
+    ids_dev = ids_all.to("cuda", non_blocking=True)
+    torch.cuda.synchronize()
+    mask_dev = torch.ones(B, P + total_steps + 1, dtype=torch.int64, device="cuda")
+    mask_host = torch.ones(B, P + total_steps + 1, dtype=torch.int64).pin_memory()
+    pos_host = torch.empty(B, 1, dtype=torch.int64).pin_memory()
+    logits_host = torch.empty(B, 1, cfg.vocab, dtype=torch.float32).pin_memory()
+
+    step_no = {"n": 0}
+
+    # inputs of the device-resident phase are built in HBM before the clock starts
+    dev_masks = [torch.ones(B, P + s + 1, dtype=torch.int64, device="cuda") for s in range(W + K_)]
+    dev_pos = [torch.full((B, 1), P + s, dtype=torch.int64, device="cuda") for s in range(W + K_)]
+    del mask_dev
+    torch.cuda.synchronize()
+
+    def device_step():
+        s = step_no["n"]
+        t = dec.context + 1
+        ids, mask, pos = ids_dev[s], dev_masks[s], dev_pos[s]
+        assert mask.shape[1] == t
+        inst.set_input_ptr("input_ids", dt.I64, [B, 1], ids.data_ptr(), True)
+        inst.set_input_ptr("attention_mask", dt.I64, [B, t], mask.data_ptr(), True)
+        inst.set_input_ptr("position_ids", dt.I64, [B, 1], pos.data_ptr(), True)
+        inst.launch()
+        dec.context = t
+        step_no["n"] += 1
+        return (ids, mask, pos)
+
+    def host_step():
+        s = step_no["n"]
+        t = dec.context + 1
+        pos_host.fill_(dec.context)
+        mask_view = mask_host.view(-1)[: B * t].view(B, t)   # contiguous [B, t] of ones in pinned memory
+        inst.set_input_ptr("input_ids", dt.I64, [B, 1], ids_all[s].data_ptr(), False)
+        inst.set_input_ptr("attention_mask", dt.I64, [B, t], mask_view.data_ptr(), False)
+        inst.set_input_ptr("position_ids", dt.I64, [B, 1], pos_host.data_ptr(), False)
+        inst.launch()
+        inst.read_into("logits", logits_host.data_ptr(), logits_host.numel() * 4)   # D2H + wait, like get_outputs
+        dec.context = t
+        step_no["n"] += 1
+        return B * 8 + B * t * 8 + B * 8
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    # ---- device-resident timing -----------------------------------------------------------------
+    with torch.cuda.stream(stream):
+        keep = []
+        for _ in range(W):
+            keep.append(device_step())
+        barrier()
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches = 0
+        e0.record(stream)
+        for _ in range(K_):
+            keep.append(device_step())
+            launches += inst.last_launches
+        e1.record(stream)
+        barrier()
+        clocks = sampler.stop() if rank == 0 else {}
+        dev_ms = max_over_ranks(e0.elapsed_time(e1))
+        decode_launches = inst.last_launches
+        inst.synchronize()
+        keep.clear()
+
+        # ---- end to end: host buffers in, logits out, every step --------------------------------
+        for _ in range(W):
+            host_step()
+        barrier()
+        h2d = 0
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record(stream)
+        wall0 = time.perf_counter()
+        for _ in range(K_):
+            h2d = host_step()
+        t1.record(stream)
+        barrier()
+        wall_ms = (time.perf_counter() - wall0) * 1000.0
+        e2e_ms = max_over_ranks(max(t0.elapsed_time(t1), wall_ms))
+
+    value = world * B * K_ / (dev_ms * 1e-3)
+    e2e_value = world * B * K_ / (e2e_ms * 1e-3)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peaks()
+    with torch.cuda.stream(stream):
+        roof = roofline_for_matmul(B, peak, peak_kind)
+    roof["peak_source"] = peak_kind
+    # whole-step view: algorithmic bytes of one decode step (weights once + KV cache read and rewritten) / step time
+    ctx_mid = P + W + K_ // 2
+    step_bytes = cfg.params * 4 + 2 * B * cfg.kv_bytes_per_token() * ctx_mid
+    roof["step_algorithmic_bytes"] = step_bytes
+    roof["step_achieved_gbs"] = step_bytes / (dev_ms / K_ * 1e-3) / 1e9
+    roof["step_frac"] = roof["step_achieved_gbs"] / peak
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        v, threads, sample = cpu_decode_sample(cfg, 8, P, 2)
+        cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K_, "warmup": W, "ms_per_step": dev_ms / K_,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, B, P),
+        "roofline": roof, "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * cfg.vocab * 4,
+                "ms_per_step": e2e_ms / K_},
+        "gpu_launches": launches, "launches_per_decode_step": decode_launches, "prefill_launches": prefill_launches,
+        "clocks": clocks, "context_range": [P + W, P + W + K_], "arena_peak_bytes": inst.arena_peak,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--requests", type=int, default=REQUESTS_PER_GPU)
+    ap.add_argument("--prompt", type=int, default=PROMPT)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
