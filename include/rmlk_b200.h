@@ -233,6 +233,11 @@ RMLK_API int rmlk_b200_store_small(rmlk_stream_t stream, int n_words, const uint
 RMLK_API int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                      const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
                      int64_t c_batch_stride, void* workspace, size_t workspace_bytes);
+/* Same, with a device status word: the tensor-core kernel's waits are bounded and write
+ * RMLK_ERR_TIMEOUT there (instead of hanging) if a copy or MMA never completes.  NULL = not reported. */
+RMLK_API int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                        const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
+                        int64_t c_batch_stride, void* workspace, size_t workspace_bytes, int* status);
 RMLK_API size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k);
 
 #ifdef __cplusplus

@@ -328,8 +328,19 @@ static int skinny_plan(int64_t batch, int64_t n, int64_t k) {
 
 using namespace rmlk;
 
+namespace rmlk {
+// tensor-core path (matmul_tc.cu)
+bool tc_matmul_eligible(int64_t m, int64_t n, int64_t k, const void* a, const void* w, const void* c);
+size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k);
+int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, const float* w, float* c, void* workspace,
+              size_t workspace_bytes, int* status, int* ksplit_out);
+bool tc_enabled();
+}  // namespace rmlk
+
 extern "C" size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k) {
-    if (dtype != RMLK_F32 || batch <= 0 || m <= 0 || n <= 0 || k <= 0 || m > 16) return 0;
+    if (dtype != RMLK_F32 || batch <= 0 || m <= 0 || n <= 0 || k <= 0) return 0;
+    if (batch == 1 && m > 16 && tc_enabled() && n % 128 == 0 && k % 32 == 0) return tc_matmul_workspace_bytes(m, n, k);
+    if (m > 16) return 0;
     const int s = skinny_plan(batch, n, k);
     return s > 1 ? static_cast<size_t>(s) * batch * m * n * sizeof(float) : 0;
 }
@@ -337,6 +348,13 @@ extern "C" size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int
 extern "C" int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                                 const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
                                 int64_t c_batch_stride, void* workspace, size_t workspace_bytes) {
+    return rmlk_b200_matmul_ex(stream, dtype, batch, m, n, k, a, a_batch_stride, b, b_batch_stride, c, c_batch_stride, workspace,
+                               workspace_bytes, nullptr);
+}
+
+extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                                   const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
+                                   int64_t c_batch_stride, void* workspace, size_t workspace_bytes, int* status) {
     if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for matmul (f32 only)");
     if (batch < 0 || m < 0 || n < 0 || k < 0) return fail(RMLK_ERR_INVALID_ARG, "matmul: negative extent");
     if (batch == 0 || m == 0 || n == 0) return RMLK_OK;
@@ -350,6 +368,19 @@ extern "C" int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, 
     if (!a || !b) return fail(RMLK_ERR_INVALID_ARG, "matmul: NULL operand");
     if (batch > 65535) return fail(RMLK_ERR_INVALID_ARG, "matmul: batch exceeds 65535");
     const bool b_rows_aligned = (n % 4 == 0) && aligned_to(b, 16) && (b_batch_stride % 4 == 0);
+    if (batch == 1 && tc_matmul_eligible(m, n, k, a, b, c)) {
+        int ksplit = 1;
+        if (int rc = tc_matmul(st, m, n, k, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c), workspace,
+                               workspace_bytes, status, &ksplit))
+            return rc;
+        if (ksplit > 1) {
+            const int64_t total = m * n;
+            splitk_reduce_kernel<<<static_cast<unsigned>(ceil_div64(total, 256)), 256, 0, st>>>(static_cast<const float*>(workspace),
+                                                                                                  static_cast<float*>(c), ksplit, 1, total, total);
+            RMLK_CHECK_LAUNCH("splitk_reduce_kernel");
+        }
+        return RMLK_OK;
+    }
     if (m <= 16) {
         SkinnyParams p;
         p.a = static_cast<const float*>(a);

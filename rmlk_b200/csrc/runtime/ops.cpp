@@ -469,7 +469,9 @@ void op_matmul(const Ctx& c) {
     }
     const size_t need = rmlk_b200_matmul_workspace_bytes(a.dtype, eb, em, n, ka);
     void* ws = need ? c.I.matmul_ws.ensure(need) : nullptr;
-    check_rc(rmlk_b200_matmul(c.stream(), a.dtype, eb, em, n, ka, a.data, sa, b.data, sb, o.data, sc, ws, need));
+    check_rc(rmlk_b200_matmul_ex(c.stream(), a.dtype, eb, em, n, ka, a.data, sa, b.data, sb, o.data, sc, ws, need,
+                                 static_cast<int*>(c.I.status_word.ptr)));
+    c.I.status_dirty = true;
     c.launched(need ? 2 : 1);
 }
 

@@ -503,3 +503,52 @@ def test_large_elementwise_and_copy_roundtrip():
     t = K.transpose(x, [0, 1, 3, 2])
     assert torch.equal(K.transpose(t, [0, 1, 3, 2]), x)
     assert torch.equal(t, x.permute(0, 1, 3, 2).contiguous())
+
+
+TC_CASES = [(64, 8192, 2048), (64, 2048, 2048), (64, 512, 2048), (64, 2048, 8192), (17, 128, 32), (33, 256, 64), (100, 384, 96), (128, 1024, 256),
+            (200, 256, 512), (300, 128, 2048), (64, 128256, 2048), (4096, 8192, 2048), (65, 128, 4096)]
+
+
+@pytest.mark.parametrize("case", TC_CASES)
+def test_matmul_tensor_core_3xtf32(case):
+    """Shapes that take the tcgen05 path (M > 16, N % 128 == 0, K % 32 == 0): fp32-level accuracy from the
+    3xTF32 split (far inside the rel 1e-4 bar), with and without the split-K scratch, deterministic, and
+    the bounded-wait status word stays clear."""
+    m, n, k = case
+    a = torch.randn(m, k, device="cuda") * 0.5
+    w = torch.randn(k, n, device="cuda") * 0.02
+    # reference in double on the GPU for the large cases (torch used as a checker only), numpy for small ones
+    want = (a.double() @ w.double())
+    scale = float(want.abs().max())
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    import ctypes
+    from rmlk_b200 import dtypes as dt
+    from rmlk_b200._lib import lib
+
+    def run(ws):
+        out = torch.empty(m, n, device="cuda")
+        rc = lib().rmlk_b200_matmul_ex(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), dt.F32, ctypes.c_int64(1), ctypes.c_int64(m),
+                                       ctypes.c_int64(n), ctypes.c_int64(k), ctypes.c_void_p(a.data_ptr()), ctypes.c_int64(0),
+                                       ctypes.c_void_p(w.data_ptr()), ctypes.c_int64(0), ctypes.c_void_p(out.data_ptr()), ctypes.c_int64(m * n),
+                                       ctypes.c_void_p(ws.data_ptr() if ws is not None else 0),
+                                       ctypes.c_size_t(ws.numel() * 4 if ws is not None else 0), ctypes.c_void_p(status.data_ptr()))
+        assert rc == 0
+        return out
+
+    got = run(None)
+    assert int(status.item()) == 0, "a bounded wait expired"
+    err = float((got.double() - want).abs().max()) / scale
+    assert err <= 2e-6, (case, err)
+    wsb = K.matmul_workspace_bytes(1, m, n, k)
+    if wsb:
+        ws = torch.empty(wsb // 4, device="cuda")
+        g2 = run(ws)
+        g3 = run(ws)
+        assert int(status.item()) == 0
+        assert float((g2.double() - want).abs().max()) / scale <= 2e-6
+        assert torch.equal(g2, g3)
+    # exact on small integers: hi/lo split must not lose anything when the products are exactly representable
+    ai = torch.randint(-8, 9, (m, k), device="cuda").float()
+    wi = torch.randint(-8, 9, (k, n), device="cuda").float()
+    a, w = ai, wi
+    assert torch.equal(run(None), (ai.double() @ wi.double()).float())
