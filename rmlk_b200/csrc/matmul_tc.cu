@@ -93,13 +93,15 @@ __device__ __forceinline__ void tc_mma_tf32(uint32_t d_tmem, uint64_t a_desc, ui
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, descriptor version 1 (Blackwell).
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// layout: 2 = 128-byte swizzle in 16-byte units (K-major operands), 1 = 128-byte swizzle in 32-byte units, the
+// form 32-bit MN-major operands need (TMA: CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint64_t layout = 2) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((addr >> 4) & 0x3fff);
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3fff) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3fff) << 32;
     d |= 1ull << 46;   // version
-    d |= 2ull << 61;   // SWIZZLE_128B
+    d |= layout << 61;
     return d;
 }
 
@@ -123,6 +125,7 @@ struct TcParams {
     int k_iters_total;
     int ksplit;
     int* status;
+    int debug;
 };
 
 template <int MT, int STAGES>
@@ -207,12 +210,19 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
                 const uint32_t w_hi = st, w_lo = st + L::W_BYTES, a_hi = st + 2 * L::W_BYTES, a_lo = a_hi + L::A_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < BK / 8; kk++) {
-                    // weights: slabs 4096 B apart along n (LBO), 8 k-rows = 1024 B per k-step (SBO)
-                    const uint64_t dw_hi = smem_desc(w_hi + kk * 1024, 4096, 1024);
-                    const uint64_t dw_lo = smem_desc(w_lo + kk * 1024, 4096, 1024);
+                    // weights (MN-major, 32-byte swizzle atoms): slabs of 32 columns 4096 B apart (LBO), groups of
+                    // 4 k-rows 512 B apart (SBO); a k-step of 8 rows advances the start by 1024 B
+                    const uint64_t dw_hi = smem_desc(w_hi + kk * 1024, 4096, 512, 1);
+                    const uint64_t dw_lo = smem_desc(w_lo + kk * 1024, 4096, 512, 1);
                     // activations: 8-row groups 1024 B apart (SBO), a k-step is 32 B inside the swizzled row
                     const uint64_t da_hi = smem_desc(a_hi + kk * 32, 16, 1024);
                     const uint64_t da_lo = smem_desc(a_lo + kk * 32, 16, 1024);
+                    if (p.debug == 6) {
+                        constexpr uint32_t idk = (1u << 4) | (2u << 7) | (2u << 10) | ((MT >> 3) << 17) | ((BN >> 4) << 24);
+                        tc_mma_tf32(tmem_base, da_hi, da_hi, idk, (it > 0 || kk > 0) ? 1u : 0u);
+                        continue;
+                    }
+                    if (p.debug == 7) continue;
                     tc_mma_tf32(tmem_base, dw_lo, da_hi, idesc, (it > 0 || kk > 0) ? 1u : 0u);
                     tc_mma_tf32(tmem_base, dw_hi, da_lo, idesc, 1u);
                     tc_mma_tf32(tmem_base, dw_hi, da_hi, idesc, 1u);
@@ -259,12 +269,22 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
 #pragma unroll
             for (int c0 = 0; c0 < MT; c0 += 32) {
                 uint32_t r[32];
+                if (p.debug == 5) {
+                    const uint32_t val = __float_as_uint(1000.0f * sub + lane + 0.01f * c0);
+                    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + c0 + 3), "r"(val) : "memory");
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                }
                 tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(sub * 32) << 16) + c0, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     const int64_t m = m0 + c0 + j;
-                    if (m < p.M) out[m * p.N + n] = __uint_as_float(r[j]);
+                    float v = __uint_as_float(r[j]);
+                    if (p.debug == 1) v = 7.0f;
+                    if (p.debug == 2) v = static_cast<float>(tmem_base);
+                    if (p.debug == 3) v = reinterpret_cast<float*>(base_ptr)[((c0 + j) * 128 + sub * 32 + lane) % 4096];
+                    if (p.debug == 4) v = reinterpret_cast<float*>(base_ptr + 2 * L::W_BYTES)[((c0 + j) * 32 + lane) % (MT * 32)];
+                    if (m < p.M) out[m * p.N + n] = v;
                 }
             }
         }
@@ -295,7 +315,8 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-static bool make_map_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer) {
+static bool make_map_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
+                        CUtensorMapSwizzle swizzle) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[2] = {inner, outer};
@@ -303,7 +324,7 @@ static bool make_map_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint6
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+              swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 template <int MT, int STAGES>
@@ -365,8 +386,8 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
     const int per = static_cast<int>(ceil_div64(k_iters, ksplit));
     ksplit = static_cast<int>(ceil_div64(k_iters, per));
     CUtensorMap tmW, tmA;
-    if (!tc::make_map_2d(&tmW, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 32, 32) ||
-        !tc::make_map_2d(&tmA, a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), 32, static_cast<uint32_t>(mt)))
+    if (!tc::make_map_2d(&tmW, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 32, 32, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B) ||
+        !tc::make_map_2d(&tmA, a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), 32, static_cast<uint32_t>(mt), CU_TENSOR_MAP_SWIZZLE_128B))
         return fail(RMLK_ERR_INTERNAL, "matmul: cuTensorMapEncodeTiled failed");
     tc::TcParams p;
     p.out = ksplit > 1 ? static_cast<float*>(workspace) : c;
@@ -375,6 +396,7 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
     p.k_iters_total = k_iters;
     p.ksplit = ksplit;
     p.status = status;
+    { const char* e = getenv("RMLK_B200_TC_DEBUG"); p.debug = e ? atoi(e) : 0; }
     dim3 grid(static_cast<unsigned>(n / tc::BN), static_cast<unsigned>(ksplit), static_cast<unsigned>(ceil_div64(m, mt)));
     *ksplit_out = ksplit;
     if (mt == 64) return tc::launch<64, 4>(st, tmW, tmA, p, grid);
