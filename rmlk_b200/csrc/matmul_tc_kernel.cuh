@@ -1,0 +1,170 @@
+// tc_gemm_kernel: one CTA computes a [MT x 128] tile of C (optionally one K-split of it).
+#pragma once
+
+#include "matmul_tc.cuh"
+
+namespace rmlk {
+namespace tc {
+
+template <int MT, int STAGES>
+__global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                              const __grid_constant__ CUtensorMap tmA, TcParams p) {
+    using L = SmemLayout<MT, STAGES>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + L::BAR_OFFSET;
+    // 8-byte slots: full[s], conv[s], empty[s], accum; then the TMEM base slot and the abort flag
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto conv_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+    auto empty_bar = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+    const uint32_t accum_bar = bars + 8u * (3 * STAGES);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base_ptr + L::BAR_OFFSET + 8 * (3 * STAGES + 1));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFFSET + 8 * (3 * STAGES + 1) + 8);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * BN;
+    const int split = blockIdx.y;
+    const int m0 = blockIdx.z * MT;
+    const int it_begin = split * p.k_iters_per_split;
+    int n_iters = p.k_iters_total - it_begin;
+    if (n_iters > p.k_iters_per_split) n_iters = p.k_iters_per_split;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(conv_bar(s), 128);
+            mbar_init(empty_bar(s), 1);
+        }
+        mbar_init(accum_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(L::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    // TMEM columns: [0, 2 MT) accumulators (hi*hi + lo*hi | hi*lo); stage s: weights hi at 2 MT + 64 s, lo 32 further
+    auto whi_col = [&](int s) { return static_cast<uint32_t>(2 * MT + 64 * s); };
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            for (int it = 0; it < n_iters; it++) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(empty_bar(s), ((it / STAGES) - 1) & 1, abort_flag, p.status)) break;
+                const uint32_t st = base + s * L::STAGE_BYTES;
+                const int k0 = (it_begin + it) * BK;
+                mbar_expect_tx(full_bar(s), L::W_BYTES + L::A_BYTES);
+#pragma unroll
+                for (int j = 0; j < 4; j++) tma_load_2d(st + j * 4096, &tmW, n0 + 32 * j, k0, full_bar(s));
+                tma_load_2d(st + L::W_BYTES, &tmA, k0, m0, full_bar(s));
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            // D fp32; A (weights, from TMEM) and B (activations, smem) tf32, both K-major; M = 128, N = MT
+            constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((MT >> 3) << 17) | ((BN >> 4) << 24);
+            constexpr uint32_t idesc_wide = (1u << 4) | (2u << 7) | (2u << 10) | (((2 * MT) >> 3) << 17) | ((BN >> 4) << 24);
+            for (int it = 0; it < n_iters; it++) {
+                const int s = it % STAGES;
+                if (!mbar_wait(conv_bar(s), (it / STAGES) & 1, abort_flag, p.status)) break;
+                tc_fence_after();
+                const uint32_t a_hi = base + s * L::STAGE_BYTES + L::W_BYTES;
+                const uint32_t w_hi = tmem_base + whi_col(s), w_lo = w_hi + 32;
+#pragma unroll
+                for (int kk = 0; kk < BK / 8; kk++) {
+                    // a k-step of 8 is 8 TMEM columns of the weights and 32 bytes inside the swizzled activation rows
+                    const uint64_t da_hi = smem_desc_k128(a_hi + kk * 32);
+                    // hi x [hi; lo]: the lo tile follows the hi tile in shared memory, so one descriptor with N = 2 MT
+                    // covers both and fills accumulator columns [0, MT) and [MT, 2 MT); then lo x hi into [0, MT)
+                    tc_mma_tf32_ts(tmem_base, w_hi + kk * 8, da_hi, idesc_wide, (it > 0 || kk > 0) ? 1u : 0u);
+                    tc_mma_tf32_ts(tmem_base, w_lo + kk * 8, da_hi, idesc, 1u);
+                }
+                tc_commit(empty_bar(s));
+            }
+            tc_commit(accum_bar);
+        }
+    } else {
+        // ---------------- converters, then epilogue ----------------
+        // two converter groups of four warps take alternate k-blocks, so that the latency of one block's
+        // shared-memory reads, TMEM stores and their completion wait overlaps the other group's work
+        const int cg = (warp - 2) >> 2;            // converter group 0 / 1
+        const int t = threadIdx.x - 64 - 128 * cg; // 0..127 inside the group
+        const int sub = warp & 3;                  // TMEM sub-partition (32 lanes) this warp owns
+        const uint32_t lane_field = static_cast<uint32_t>(sub * 32) << 16;
+        bool ok = true;
+        for (int it = cg; it < n_iters && ok; it += 2) {
+            const int s = it % STAGES;
+            ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag, p.status);
+            if (!ok) break;
+            uint8_t* st = base_ptr + s * L::STAGE_BYTES;
+            // weights: this thread owns column n0 + sub*32 + lane = TMEM lane sub*32 + lane; slab `sub` holds it.
+            // 32 k values go to TMEM as tf32 hi and lo (16 columns per store)
+            const float* wcol = reinterpret_cast<const float*>(st + sub * 4096) + lane;
+#pragma unroll
+            for (int half = 0; half < 2; half++) {
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const float x = wcol[(half * 16 + j) * 32];
+                    hi[j] = to_tf32(x);
+                    lo[j] = to_tf32(x - __uint_as_float(hi[j]));
+                }
+                tmem_st_x16(tmem_base + lane_field + whi_col(s) + half * 16, hi);
+                tmem_st_x16(tmem_base + lane_field + whi_col(s) + 32 + half * 16, lo);
+            }
+            // activations: split in shared memory, hi in place, lo into the twin tile at the same swizzled offsets
+            uint8_t* ahi = st + L::W_BYTES;
+            uint8_t* alo = ahi + L::A_BYTES;
+#pragma unroll 2
+            for (int c = t; c < static_cast<int>(L::A_BYTES / 16); c += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(ahi + 16 * c);
+                uint4 h, l;
+                h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
+                l.x = to_tf32(v.x - __uint_as_float(h.x));
+                l.y = to_tf32(v.y - __uint_as_float(h.y));
+                l.z = to_tf32(v.z - __uint_as_float(h.z));
+                l.w = to_tf32(v.w - __uint_as_float(h.w));
+                *reinterpret_cast<uint4*>(ahi + 16 * c) = h;
+                *reinterpret_cast<uint4*>(alo + 16 * c) = l;
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            fence_proxy_async();
+            tc_fence_before();
+            mbar_arrive(conv_bar(s));
+        }
+        if (ok) ok = mbar_wait(accum_bar, 0, abort_flag, p.status);
+        if (ok) {
+            tc_fence_after();
+            const int64_t n = n0 + sub * 32 + lane;
+            float* out = p.out + (p.ksplit > 1 ? static_cast<int64_t>(split) * p.M * p.N : 0);
+#pragma unroll
+            for (int c0 = 32 * cg; c0 < MT; c0 += 64) {
+                uint32_t r[32], q[32];
+                tmem_ld_x32(tmem_base + lane_field + c0, r);
+                tmem_ld_x32(tmem_base + lane_field + MT + c0, q);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const int64_t m = m0 + c0 + j;
+                    if (m < p.M) out[m * p.N + n] = __uint_as_float(r[j]) + __uint_as_float(q[j]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(L::TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace tc
+}  // namespace rmlk
