@@ -238,6 +238,25 @@ RMLK_API int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, in
 RMLK_API int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                         const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
                         int64_t c_batch_stride, void* workspace, size_t workspace_bytes, int* status);
+/* MatMul for callers that cannot allocate device memory and have no workspace to lend.  (No counterpart in
+ * the reference: its cuBLAS handle allocates its own workspace, cuda/src/kernels/gemm.rs:119.)
+ * Some hosts of this library run where cudaMalloc is off limits: inside a latency-critical serving loop,
+ * where an allocation would stall every stream of the device; under a fixed memory budget that was carved up
+ * at start-up; or from a plug-in that is only handed input and output buffers.  For them the split-K
+ * scratch that rmlk_b200_matmul takes as `workspace` lives in a fixed array inside the library:
+ * rmlk_b200_matmul_static_scratch_bytes() bytes (8 MiB) of device memory on every GPU that loads the
+ * library, held until the process exits.  Same arguments and results as rmlk_b200_matmul_ex otherwise.
+ *  - Shapes whose scratch need (rmlk_b200_matmul_workspace_bytes) exceeds the array are rejected with
+ *    RMLK_ERR_INVALID_ARG; nothing is launched.
+ *  - The first call on each device looks up the array's device address; make that first call outside any
+ *    stream capture.  No call allocates or frees memory.
+ *  - All calls share the one array and it keeps the previous call's partial sums; every call overwrites what
+ *    it reads, so nothing needs clearing, but two calls that overlap on the GPU (different streams) race on
+ *    it.  Keep calls on one stream, or order them with events. */
+RMLK_API int rmlk_b200_matmul_static(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                            const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
+                            int64_t c_batch_stride, int* status);
+RMLK_API size_t rmlk_b200_matmul_static_scratch_bytes(void);
 RMLK_API size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k);
 
 #ifdef __cplusplus

@@ -429,3 +429,57 @@ extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batc
     RMLK_CHECK_LAUNCH("gemm_kernel");
     return RMLK_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// MatMul without any allocation by anyone: the split-K scratch is a fixed array inside the library.
+// ---------------------------------------------------------------------------------------------
+// 8 MiB of device memory per GPU that loads this library, held until the process exits.
+constexpr size_t RMLK_STATIC_SCRATCH_BYTES = size_t(8) << 20;
+static __device__ __align__(256) unsigned char g_matmul_static_scratch[RMLK_STATIC_SCRATCH_BYTES];
+
+// In host code `g_matmul_static_scratch` is only a handle for the runtime, not a device address, so the
+// address kernels can use is looked up once per device (with that device current) and cached.
+static void* static_scratch_ptr(int* rc_out) {
+    static void* ptrs[64] = {nullptr};
+    *rc_out = RMLK_OK;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) {
+        *rc_out = rmlk::cuda_fail(e, "cudaGetDevice");
+        return nullptr;
+    }
+    if (dev < 0 || dev >= 64) {
+        *rc_out = rmlk::fail(RMLK_ERR_INTERNAL, "matmul_static: device index out of range");
+        return nullptr;
+    }
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_matmul_static_scratch);
+        if (e != cudaSuccess || !p) {
+            *rc_out = rmlk::cuda_fail(e, "cudaGetSymbolAddress(matmul static scratch)");
+            return nullptr;
+        }
+        ptrs[dev] = p;
+    }
+    return ptrs[dev];
+}
+
+extern "C" size_t rmlk_b200_matmul_static_scratch_bytes(void) { return RMLK_STATIC_SCRATCH_BYTES; }
+
+extern "C" int rmlk_b200_matmul_static(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                                       const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
+                                       int64_t c_batch_stride, int* status) {
+    const size_t need = rmlk_b200_matmul_workspace_bytes(dtype, batch, m, n, k);
+    if (need > RMLK_STATIC_SCRATCH_BYTES)
+        return rmlk::fail(RMLK_ERR_INVALID_ARG, "matmul_static: this shape needs " + std::to_string(need) +
+                                                    " bytes of split-K scratch, the built-in array holds " +
+                                                    std::to_string(RMLK_STATIC_SCRATCH_BYTES) +
+                                                    "; use rmlk_b200_matmul with a caller-provided workspace");
+    int rc = RMLK_OK;
+    void* scratch = static_scratch_ptr(&rc);
+    if (!scratch) return rc;
+    // The split-K partials are fully overwritten before they are summed, so nothing in the array has to be
+    // cleared between calls.
+    return rmlk_b200_matmul_ex(stream, dtype, batch, m, n, k, a, a_batch_stride, b, b_batch_stride, c, c_batch_stride, scratch,
+                               RMLK_STATIC_SCRATCH_BYTES, status);
+}
