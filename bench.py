@@ -172,44 +172,100 @@ def run_reference(args):
 # ---------------------------------------------------------------------------------------------------
 # GPU path
 # ---------------------------------------------------------------------------------------------------
-def time_kernel(fn, iters=20, warm=3):
+def time_graph(fn_of_i, n=16, replays=4):
+    """Device time per launch: n launches captured into a CUDA graph on a side stream, the graph replayed
+    between two events on that stream (no host launch overhead inside the timed region)."""
     import torch
-    for _ in range(warm):
-        fn()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for i in range(3):
+        fn_of_i(i)
     torch.cuda.synchronize()
-    e0.record()
-    for _ in range(iters):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / iters
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            for i in range(n):
+                fn_of_i(i)
+        g.replay()
+        s.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(s)
+        for _ in range(replays):
+            g.replay()
+        e1.record(s)
+        s.synchronize()
+    return e0.elapsed_time(e1) / (n * replays)
 
 
-def roofline_for_matmul(batch, peak_gbs, peak_kind):
-    """Live timing of the dominant kernel: the weight-streaming MatMul of the decode step at the FFN
-    gate/up shape [batch, 2048] x [2048, 8192].  A ring of weight matrices larger than L2 keeps every launch
-    reading its weights from HBM."""
+# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernel named by DOMINANT, from the
+# capture summarised under profiles/ (None until a capture of that kernel exists).
+DOMINANT = "expand_gqa"
+NCU_TRAFFIC_BYTES = {}
+
+
+def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):
+    """Live device timing of the decode step's heaviest kernels on the step's own shapes.  Every case rotates
+    over a ring of operands larger than L2 (126 MB), so reads come from HBM.  Returns {name: entry}."""
     import torch
     from rmlk_b200 import kernels as K
-    m, k, n = batch, 2048, 8192
-    ring = [torch.randn(k, n, device="cuda") * 0.02 for _ in range(4)]   # 4 x 67 MB > 126 MB L2
-    x = torch.randn(m, k, device="cuda")
-    out = torch.empty(m, n, device="cuda")
-    ws_bytes = K.matmul_workspace_bytes(1, m, n, k)
-    ws = torch.empty(max(ws_bytes // 4, 1), device="cuda") if ws_bytes else None
-    state = {"i": 0}
+    dev = "cuda"
+    B, T = batch, ctx
+    out = {}
 
-    def fn():
-        K.matmul(x, ring[state["i"] % len(ring)], out=out, workspace=ws)
-        state["i"] += 1
+    def ring(make, nbytes_each):
+        return [make() for _ in range(max(2, min(6, (252 << 20) // max(nbytes_each, 1) + 1)))]
 
-    ms = time_kernel(fn, iters=40, warm=8)
-    algo_bytes = 4 * (m * k + k * n + m * n)
-    achieved = algo_bytes / (ms * 1e-3) / 1e9
-    return {"bound": "hbm", "achieved": achieved, "peak": peak_gbs, "unit": "GB/s", "frac": achieved / peak_gbs, "traffic": None,
-            "kernel": "matmul (weight streaming)", "shape": [m, k, n], "algorithmic_bytes_per_launch": algo_bytes,
-            "ms_per_launch": ms, "tflops": 2.0 * m * k * n / (ms * 1e-3) / 1e12, "peak_kind": f"of {peak_kind} copy bandwidth"}
+    def add(name, kernel, fn, algo_bytes, shape, flops=0):
+        ms = time_graph(fn)
+        ach = algo_bytes / (ms * 1e-3) / 1e9
+        e = {"bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs,
+             "traffic": NCU_TRAFFIC_BYTES.get(name), "kernel": kernel, "shape": shape,
+             "algorithmic_bytes_per_launch": algo_bytes, "us_per_launch": ms * 1e3, "peak_kind": f"of {peak_kind} copy bandwidth"}
+        if flops:
+            e["tflops"] = flops / (ms * 1e-3) / 1e12
+        out[name] = e
+
+    # GQA Expand of the K / V cache: [B, 8, 1, T, 64] -> [B, 8, 4, T, 64]
+    src = ring(lambda: torch.randn(B, 8, 1, T, 64, device=dev), 4 * B * 8 * T * 64)
+    dst = torch.empty(B, 8, 4, T, 64, device=dev)
+    add("expand_gqa", "ew_vec_kernel1 (Expand)", lambda i: K.expand(src[i % len(src)], [1, 1, 4, 1, 1], out=dst),
+        4 * B * 8 * T * 64 * 5, [B, 8, 4, T, 64])
+    del src, dst
+    # K^T Transpose: [B, 32, T, 64] -> [B, 32, 64, T]
+    src = ring(lambda: torch.randn(B, 32, T, 64, device=dev), 4 * B * 32 * T * 64)
+    dst = torch.empty(B, 32, 64, T, device=dev)
+    add("transpose_kt", "transpose_tile64_kernel", lambda i: K.transpose(src[i % len(src)], [0, 1, 3, 2], out=dst),
+        8 * B * 32 * T * 64, [B, 32, T, 64])
+    # decode scores: B*32 problems [1, 64] x [64, T]
+    q = torch.randn(B * 32, 1, 64, device=dev)
+    kt = [t.view(B * 32, 64, T) for t in src]
+    sc = torch.empty(B * 32, 1, T, device=dev)
+    add("scores", "smallk_kernel<1>", lambda i: K.matmul(q, kt[i % len(kt)], out=sc), 4 * B * 32 * (64 + 64 * T + T),
+        [B * 32, 1, 64, T], flops=2 * B * 32 * 64 * T)
+    # decode context: B*32 problems [1, T] x [T, 64]
+    v = [t.view(B * 32, T, 64) for t in src]
+    p = torch.randn(B * 32, 1, T, device=dev)
+    cx = torch.empty(B * 32, 1, 64, device=dev)
+    add("context", "skinny_kernel<1>", lambda i: K.matmul(p, v[i % len(v)], out=cx), 4 * B * 32 * (T + 64 * T + 64),
+        [B * 32, 1, T, 64], flops=2 * B * 32 * 64 * T)
+    del src, dst, kt, v
+    # KV append Concat: [B, 8, T-1, 64] + [B, 8, 1, 64] along axis 2
+    past = ring(lambda: torch.randn(B, 8, T - 1, 64, device=dev), 4 * B * 8 * T * 64)
+    new = torch.randn(B, 8, 1, 64, device=dev)
+    dst = torch.empty(B, 8, T, 64, device=dev)
+    add("concat_kv", "concat_kernel", lambda i: K.concat([past[i % len(past)], new], 2, out=dst), 8 * B * 8 * T * 64, [B, 8, T, 64])
+    del past, dst
+    # weight-streaming MatMul at the FFN gate/up shape and at the lm_head
+    for name, (m, k, n) in (("matmul_ffn", (B, 2048, 8192)), ("matmul_lm_head", (B, 2048, 128256))):
+        w = ring(lambda: torch.randn(k, n, device=dev) * 0.02, 4 * k * n)
+        x = torch.randn(m, k, device=dev)
+        y = torch.empty(m, n, device=dev)
+        wsb = K.matmul_workspace_bytes(1, m, n, k)
+        ws = torch.empty(max(wsb // 4, 1), device=dev) if wsb else None
+        add(name, "tc_gemm_kernel (tcgen05 3xTF32)" if m > 16 else "skinny_kernel",
+            lambda i: K.matmul(x, w[i % len(w)], out=y, workspace=ws), 4 * (m * k + k * n + m * n), [m, k, n], flops=2 * m * k * n)
+        del w, x, y, ws
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_ours(args):
@@ -348,8 +404,13 @@ def run_ours(args):
         return
 
     peak, peak_kind = measured_peaks()
-    with torch.cuda.stream(stream):
-        roof = roofline_for_matmul(B, peak, peak_kind)
+    roof = {}
+    if not args.skip_kernel_roofline:
+        with torch.cuda.stream(stream):
+            per_kernel = kernel_rooflines(B, P + W + K_ // 2, peak, peak_kind)
+        roof = dict(per_kernel[DOMINANT])
+        roof["other_kernels"] = {k: {"kernel": v["kernel"], "achieved": v["achieved"], "frac": v["frac"], "us_per_launch": v["us_per_launch"]}
+                                 for k, v in per_kernel.items() if k != DOMINANT}
     roof["peak_source"] = peak_kind
     # whole-step view: algorithmic bytes of one decode step (weights once + KV cache read and rewritten) / step time
     ctx_mid = P + W + K_ // 2
@@ -387,6 +448,7 @@ def main():
     ap.add_argument("--requests", type=int, default=REQUESTS_PER_GPU)
     ap.add_argument("--prompt", type=int, default=PROMPT)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--skip-kernel-roofline", action="store_true", help="leave out the per-kernel timing (launch-list profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

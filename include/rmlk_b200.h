@@ -194,6 +194,13 @@ RMLK_API int rmlk_b200_slice(rmlk_stream_t stream, int elem_size, int rank, cons
 RMLK_API int rmlk_b200_transpose(rmlk_stream_t stream, int elem_size, int rank, const int64_t* in_shape,
                         const int64_t* perm, const void* in, void* out);
 
+/* Dense row-major copy of a strided view: out[i0,..] = in[sum_d i_d * strides[d]] (strides in elements; 0
+ * broadcasts a dim).  One launch replaces a chain of the reference's copying layout ops - Expand
+ * (cuda/src/kernels/expand.rs:35-76) followed by Reshape (a copy there, backend/reshape.rs) and Transpose
+ * (cuda/src/kernels/transpose.rs:38-80) - when the host runtime has kept the chain as a view. */
+RMLK_API int rmlk_b200_strided_copy(rmlk_stream_t stream, int elem_size, int rank, const int64_t* shape,
+                           const int64_t* strides, const void* in, void* out);
+
 /* Concat of n_inputs tensors along an axis; every input is viewed as [outer, axis_dims[i] * inner].
  * Replaces the nested cuMemcpyDtoD loops of runtime/src/providers/cuda/backend/concat.rs:28-76.
  * Zero-length inputs are allowed. */
@@ -238,6 +245,13 @@ RMLK_API int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, in
 RMLK_API int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                         const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
                         int64_t c_batch_stride, void* workspace, size_t workspace_bytes, int* status);
+/* C[b] = A[b] x B[b]^T with B stored [n,k] row-major: what MatMul(A, Transpose(B, swap of the last two dims))
+ * computes in the reference through a Transpose copy (cuda/src/kernels/transpose.rs:38-80) followed by
+ * cublasGemmStridedBatchedEx (cuda/src/kernels/gemm.rs:206-231), without the copy.  A is [m,k], C is [m,n],
+ * dense; batch strides in elements.  dtype f32. */
+RMLK_API int rmlk_b200_matmul_nt(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                        const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
+                        int64_t c_batch_stride);
 /* MatMul for callers that cannot allocate device memory and have no workspace to lend.  (No counterpart in
  * the reference: its cuBLAS handle allocates its own workspace, cuda/src/kernels/gemm.rs:119.)
  * Some hosts of this library run where cudaMalloc is off limits: inside a latency-critical serving loop,

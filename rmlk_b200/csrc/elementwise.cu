@@ -174,6 +174,29 @@ extern "C" int rmlk_b200_where(rmlk_stream_t stream, int dtype, int rank, const 
 #undef RMLK_CASE
 }
 
+// Expand whose broadcast dims form one block between a dense outer and a dense inner part
+// (out[o][r][i] = in[o][i], e.g. grouped-query attention repeating each KV head R times): every 16-byte
+// pack of the input is loaded once and stored R times, so the index arithmetic and the load are paid once
+// per R stores.
+__global__ void __launch_bounds__(256) expand_repeat_kernel(uint64_t in_packs, uint32_t inner_packs, FastDiv inner_div, uint32_t repeat,
+                                                            const uint4* __restrict__ in, uint4* __restrict__ out) {
+    const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (idx >= in_packs) return;
+    uint64_t o;
+    uint32_t i;
+    if (in_packs <= 0x7fffffffull) {
+        const uint32_t q = inner_div.div(static_cast<uint32_t>(idx));
+        o = q;
+        i = static_cast<uint32_t>(idx) - q * inner_packs;
+    } else {
+        o = idx / inner_packs;
+        i = static_cast<uint32_t>(idx - o * inner_packs);
+    }
+    const uint4 v = ld_stream_u4(in + idx);
+    uint4* dst = out + o * repeat * inner_packs + i;
+    for (uint32_t r = 0; r < repeat; r++) dst[static_cast<uint64_t>(r) * inner_packs] = v;
+}
+
 extern "C" int rmlk_b200_expand(rmlk_stream_t stream, int elem_size, int in_rank, const int64_t* in_shape,
                                 int out_rank, const int64_t* out_shape, const void* in, void* out) {
     if (int rc = ew_validate(out_rank, out_shape)) return rc;
@@ -195,6 +218,37 @@ extern "C" int rmlk_b200_expand(rmlk_stream_t stream, int elem_size, int in_rank
         }
     }
     cudaStream_t st = as_stream(stream);
+    {
+        // [dense outer] [broadcast block] [dense inner]?
+        int64_t outer = 1, repeat = 1, inner = 1;
+        int phase = 0;  // 0 outer, 1 broadcast, 2 inner
+        bool one_block = true;
+        for (int d = 0; d < out_rank && one_block; d++) {
+            if (out_shape[d] == 1) continue;
+            const bool bc = strides[d] == 0;
+            if (phase == 0) {
+                if (bc) { phase = 1; repeat *= out_shape[d]; } else outer *= out_shape[d];
+            } else if (phase == 1) {
+                if (bc) repeat *= out_shape[d]; else { phase = 2; inner *= out_shape[d]; }
+            } else {
+                if (bc) one_block = false; else inner *= out_shape[d];
+            }
+        }
+        const int64_t inner_bytes = inner * elem_size;
+        if (one_block && phase == 2 && repeat > 1 && repeat <= 64 && inner_bytes % 16 == 0 && inner_bytes / 16 <= 0x7fffffffll &&
+            aligned_to(in, 16) && aligned_to(out, 16) && (elem_size == 1 || elem_size == 2 || elem_size == 4 || elem_size == 8)) {
+            const uint64_t inner_packs = static_cast<uint64_t>(inner_bytes / 16);
+            const uint64_t in_packs = static_cast<uint64_t>(outer) * inner_packs;
+            if (in_packs == 0) return RMLK_OK;
+            if (in_packs / 256 < 0x7fffffffull) {
+                expand_repeat_kernel<<<static_cast<unsigned>((in_packs + 255) / 256), 256, 0, st>>>(
+                    in_packs, static_cast<uint32_t>(inner_packs), FastDiv(static_cast<uint32_t>(inner_packs)), static_cast<uint32_t>(repeat),
+                    static_cast<const uint4*>(in), static_cast<uint4*>(out));
+                RMLK_CHECK_LAUNCH("expand_repeat_kernel");
+                return RMLK_OK;
+            }
+        }
+    }
     switch (elem_size) {
         case 1: return ew_launch1<CopyF, uint8_t, uint8_t>(st, out_rank, out_shape, strides, static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out));
         case 2: return ew_launch1<CopyF, uint16_t, uint16_t>(st, out_rank, out_shape, strides, static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out));

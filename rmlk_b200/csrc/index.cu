@@ -158,6 +158,108 @@ __global__ void __launch_bounds__(256) transpose_tile_kernel(TileParams p, const
     }
 }
 
+// 4-byte elements through a 64 x 64 tile held as T[x][y] (pitch 64 words).  Word (x, y) lives at column
+//   4 * ((y >> 2) ^ ((x >> 2) & 7)) + ((y ^ x) & 3)
+// of row x: the 16-byte y-quads are XOR-swizzled with the x-quad index and the words inside a quad with the
+// low bits of x.  With that placement all four access patterns are free of bank conflicts: 16-byte global
+// loads scattered as scalar stores (8 x-quads x 4 rows per warp), scalar global loads (one row of 32 x per
+// warp), 16-byte shared loads feeding 16-byte global stores (16 y-quads x 2 x per warp) and scalar loads
+// (one x, 32 y per warp).  VIN / VOUT select 16-byte accesses on the input / output side; each needs that
+// side's extent, stride and batch strides to be multiples of 4 and its base pointer 16-byte aligned (the
+// host checks).  A side that fails the test, e.g. rows of odd length, uses coalesced 4-byte accesses.
+__device__ __forceinline__ uint32_t tile64_col(uint32_t x, uint32_t y) { return 4 * ((y >> 2) ^ ((x >> 2) & 7)) + ((y ^ x) & 3); }
+
+template <bool VIN, bool VOUT>
+__global__ void __launch_bounds__(256) transpose_tile64_kernel(TileParams p, const uint32_t* __restrict__ in, uint32_t* __restrict__ out) {
+    __shared__ __align__(16) uint32_t tile[64 * 64];
+    const uint32_t tiles_x = (p.nx + 63) / 64;
+    const uint32_t tiles_y = (p.ny + 63) / 64;
+    const uint64_t tiles_per_batch = static_cast<uint64_t>(tiles_x) * tiles_y;
+    const uint64_t total = tiles_per_batch * p.n_batches;
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (uint64_t tIdx = blockIdx.x; tIdx < total; tIdx += gridDim.x) {
+        uint64_t b = tIdx / tiles_per_batch;
+        const uint64_t r = tIdx - b * tiles_per_batch;
+        const uint32_t by = static_cast<uint32_t>(r / tiles_x), bx = static_cast<uint32_t>(r - static_cast<uint64_t>(by) * tiles_x);
+        int64_t in_b = 0, out_b = 0;
+        for (int j = 0; j < p.n_batch; j++) {
+            const uint64_t q = b / p.batch_dim[j];
+            const uint64_t c = b - q * p.batch_dim[j];
+            in_b += static_cast<int64_t>(c) * p.batch_in[j];
+            out_b += static_cast<int64_t>(c) * p.batch_out[j];
+            b = q;
+        }
+        const uint32_t x0 = bx * 64, y0 = by * 64;
+        if constexpr (VIN) {
+            uint4 v[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t u = warp + 8 * i;
+                const uint32_t xl = 4 * (8 * (u & 1) + (lane & 7)), yl = 4 * (u >> 1) + (lane >> 3);
+                v[i] = make_uint4(0, 0, 0, 0);
+                if (x0 + xl < p.nx && y0 + yl < p.ny)
+                    v[i] = ld_stream_u4(reinterpret_cast<const uint4*>(in + in_b + static_cast<int64_t>(y0 + yl) * p.in_stride_y + x0 + xl));
+            }
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t u = warp + 8 * i;
+                const uint32_t xl = 4 * (8 * (u & 1) + (lane & 7)), yl = 4 * (u >> 1) + (lane >> 3);
+                tile[(xl + 0) * 64 + tile64_col(xl + 0, yl)] = v[i].x;
+                tile[(xl + 1) * 64 + tile64_col(xl + 1, yl)] = v[i].y;
+                tile[(xl + 2) * 64 + tile64_col(xl + 2, yl)] = v[i].z;
+                tile[(xl + 3) * 64 + tile64_col(xl + 3, yl)] = v[i].w;
+            }
+        } else {
+            uint32_t v[16];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t yl = warp + 8 * i;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t xl = lane + 32 * h;
+                    v[2 * i + h] = 0;
+                    if (x0 + xl < p.nx && y0 + yl < p.ny) v[2 * i + h] = __ldg(in + in_b + static_cast<int64_t>(y0 + yl) * p.in_stride_y + x0 + xl);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t yl = warp + 8 * i;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t xl = lane + 32 * h;
+                    tile[xl * 64 + tile64_col(xl, yl)] = v[2 * i + h];
+                }
+            }
+        }
+        __syncthreads();
+        if constexpr (VOUT) {
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t xl = 2 * (warp + 8 * i) + (lane >> 4), yq = lane & 15;
+                if (x0 + xl < p.nx && y0 + 4 * yq < p.ny) {
+                    uint4 w = *reinterpret_cast<const uint4*>(&tile[xl * 64 + 4 * (yq ^ ((xl >> 2) & 7))]);
+                    // undo the in-quad permutation: slot e holds y = 4 * yq + (e ^ (x & 3))
+                    if (xl & 1) { uint32_t t = w.x; w.x = w.y; w.y = t; t = w.z; w.z = w.w; w.w = t; }
+                    if (xl & 2) { uint32_t t = w.x; w.x = w.z; w.z = t; t = w.y; w.y = w.w; w.w = t; }
+                    *reinterpret_cast<uint4*>(out + out_b + static_cast<int64_t>(x0 + xl) * p.out_stride_x + y0 + 4 * yq) = w;
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const uint32_t xl = warp + 8 * i;
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const uint32_t yl = lane + 32 * h;
+                    if (x0 + xl < p.nx && y0 + yl < p.ny)
+                        out[out_b + static_cast<int64_t>(x0 + xl) * p.out_stride_x + y0 + yl] = tile[xl * 64 + tile64_col(xl, yl)];
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Trilu
 // ---------------------------------------------------------------------------------------------
@@ -467,6 +569,36 @@ extern "C" int rmlk_b200_slice(rmlk_stream_t stream, int elem_size, int rank, co
     return strided_copy(as_stream(stream), elem_size, rank, out_shape, eff, src, out);
 }
 
+static int view_copy(cudaStream_t st, int elem_size, int n, int64_t* oshape, int64_t* ostr_in, const void* in, void* out);
+
+// Dense copy of an arbitrary strided view: strides in elements, 0 = broadcast, negative allowed as long as
+// every addressed element lies inside the caller's buffer.  Used by the host runtime to materialise a chain
+// of Expand / Reshape / Transpose that was kept as a view (one copy instead of one per op).  The reference has
+// no views: each of those ops copies (backend/expand.rs:49-216, backend/transpose.rs:44-178).
+extern "C" int rmlk_b200_strided_copy(rmlk_stream_t stream, int elem_size, int rank, const int64_t* shape, const int64_t* strides,
+                                      const void* in, void* out) {
+    if (rank < 0 || rank > RMLK_MAX_RANK || (rank > 0 && (!shape || !strides))) return fail(RMLK_ERR_INVALID_ARG, "strided_copy: rank must be in [0, 8]");
+    if (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "strided_copy: element size must be 1, 2, 4 or 8");
+    int64_t oshape[RMLK_MAX_RANK], ostr_in[RMLK_MAX_RANK];
+    int n = 0;
+    for (int d = 0; d < rank; d++) {
+        if (shape[d] < 0) return fail(RMLK_ERR_INVALID_ARG, "strided_copy: negative extent");
+        if (shape[d] == 0) return RMLK_OK;
+    }
+    if (!in || !out) return fail(RMLK_ERR_INVALID_ARG, "strided_copy: NULL tensor pointer");
+    for (int d = 0; d < rank; d++) {
+        if (shape[d] == 1) continue;
+        if (n > 0 && ostr_in[n - 1] == strides[d] * shape[d]) {
+            oshape[n - 1] *= shape[d];
+            ostr_in[n - 1] = strides[d];
+        } else {
+            oshape[n] = shape[d];
+            ostr_in[n++] = strides[d];
+        }
+    }
+    return view_copy(as_stream(stream), elem_size, n, oshape, ostr_in, in, out);
+}
+
 extern "C" int rmlk_b200_transpose(rmlk_stream_t stream, int elem_size, int rank, const int64_t* in_shape, const int64_t* perm,
                                    const void* in, void* out) {
     if (rank < 1 || rank > RMLK_MAX_RANK || !in_shape || !perm) return fail(RMLK_ERR_INVALID_ARG, "transpose: rank must be in [1, 8]");
@@ -498,12 +630,19 @@ extern "C" int rmlk_b200_transpose(rmlk_stream_t stream, int elem_size, int rank
             ostr_in[n++] = s;
         }
     }
-    cudaStream_t st = as_stream(stream);
+    return view_copy(as_stream(stream), elem_size, n, oshape, ostr_in, in, out);
+}
+
+// out (dense, row-major over oshape[0..n)) = the view of `in` whose dim d walks ostr_in[d] elements (0 for a
+// broadcast dim).  A view whose innermost stride is 1 goes to the strided-copy engine; one whose unit-stride
+// dim sits elsewhere goes through a shared-memory tile so that both sides stay coalesced.
+static int view_copy(cudaStream_t st, int elem_size, int n, int64_t* oshape, int64_t* ostr_in, const void* in, void* out) {
     if (n == 0) {
         oshape[0] = 1;
         ostr_in[0] = 1;
         n = 1;
     }
+    int64_t run = 1;
     if (ostr_in[n - 1] == 1 || n == 1) return strided_copy(st, elem_size, n, oshape, ostr_in, in, out);
     // innermost dimension moves: find the output position whose input stride is 1
     int px = -1;
@@ -531,6 +670,24 @@ extern "C" int rmlk_b200_transpose(rmlk_stream_t stream, int elem_size, int rank
         p.batch_out[p.n_batch] = out_stride[d];
         p.n_batches *= static_cast<uint64_t>(oshape[d]);
         p.n_batch++;
+    }
+    if (elem_size == 4) {
+        bool vin = p.nx % 4 == 0 && p.in_stride_y % 4 == 0 && reinterpret_cast<uintptr_t>(in) % 16 == 0;
+        bool vout = p.ny % 4 == 0 && p.out_stride_x % 4 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+        for (int j = 0; j < p.n_batch; j++) {
+            vin = vin && p.batch_in[j] % 4 == 0;
+            vout = vout && p.batch_out[j] % 4 == 0;
+        }
+        const uint64_t tiles64 = static_cast<uint64_t>((p.nx + 63) / 64) * ((p.ny + 63) / 64) * p.n_batches;
+        const unsigned grid64 = static_cast<unsigned>(tiles64 < (1u << 30) ? tiles64 : (1u << 30));
+        const uint32_t* src = static_cast<const uint32_t*>(in);
+        uint32_t* dst = static_cast<uint32_t*>(out);
+        if (vin && vout) transpose_tile64_kernel<true, true><<<grid64, 256, 0, st>>>(p, src, dst);
+        else if (vin) transpose_tile64_kernel<true, false><<<grid64, 256, 0, st>>>(p, src, dst);
+        else if (vout) transpose_tile64_kernel<false, true><<<grid64, 256, 0, st>>>(p, src, dst);
+        else transpose_tile64_kernel<false, false><<<grid64, 256, 0, st>>>(p, src, dst);
+        RMLK_CHECK_LAUNCH("transpose_tile64_kernel");
+        return RMLK_OK;
     }
     const uint64_t tiles = static_cast<uint64_t>((p.nx + 31) / 32) * ((p.ny + 31) / 32) * p.n_batches;
     const unsigned grid = static_cast<unsigned>(tiles < (1u << 30) ? tiles : (1u << 30));

@@ -143,6 +143,179 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_kernel(SkinnyParams p) {
     }
 }
 
+// Many small problems with a short K (decode attention scores: batch x heads problems of [1, 64] x [64, T]).
+// One thread owns four adjacent columns of one problem and walks all of K itself: no shared memory, no
+// reduction, B read once with 128-bit loads (a warp reads 512 contiguous bytes of a B row per k), A read with
+// 128-bit loads that are the same address across the lanes of a problem.  Needs N % 4 == 0, K % 4 == 0 and
+// 16-byte aligned operands and batch strides.
+template <int MB>
+__global__ void __launch_bounds__(256) smallk_kernel(SkinnyParams p, int64_t total_quads, uint32_t nq) {
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (idx >= total_quads) return;
+    const int64_t batch = idx / nq;
+    const int64_t n0 = (idx - batch * nq) * 4;
+    const float* __restrict__ A = p.a + batch * p.sa;
+    const float* __restrict__ B = p.b + batch * p.sb + n0;
+    float acc[MB][4];
+#pragma unroll
+    for (int m = 0; m < MB; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[m][j] = 0.f;
+    const int K = static_cast<int>(p.K);
+#pragma unroll 4
+    for (int k = 0; k < K; k += 4) {
+        uint4 bv[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) bv[u] = ld_stream_u4(B + static_cast<int64_t>(k + u) * p.N);
+#pragma unroll
+        for (int m = 0; m < MB; m++) {
+            if (m < p.M) {
+                const float4 av = __ldg(reinterpret_cast<const float4*>(A + static_cast<int64_t>(m) * p.K + k));
+                const float a4[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    acc[m][0] = fmaf(a4[u], __uint_as_float(bv[u].x), acc[m][0]);
+                    acc[m][1] = fmaf(a4[u], __uint_as_float(bv[u].y), acc[m][1]);
+                    acc[m][2] = fmaf(a4[u], __uint_as_float(bv[u].z), acc[m][2]);
+                    acc[m][3] = fmaf(a4[u], __uint_as_float(bv[u].w), acc[m][3]);
+                }
+            }
+        }
+    }
+    float* __restrict__ C = p.c + batch * p.sc + n0;
+#pragma unroll
+    for (int m = 0; m < MB; m++)
+        if (m < p.M) *reinterpret_cast<float4*>(C + static_cast<int64_t>(m) * p.N) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+}
+
+// The same walk for rows of B that are not 16-byte aligned (N % 4 != 0, e.g. a context length of 517): one
+// thread per column, 4-byte loads of B that a warp coalesces into 128 contiguous bytes per k, sixteen k in
+// flight per thread.  A still needs K % 4 == 0 and 16-byte alignment.
+template <int MB>
+__global__ void __launch_bounds__(256) smallk1_kernel(SkinnyParams p, int64_t total_cols, uint32_t n32) {
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (idx >= total_cols) return;
+    const int64_t batch = idx / n32;
+    const int64_t n0 = idx - batch * n32;
+    const float* __restrict__ A = p.a + batch * p.sa;
+    const float* __restrict__ B = p.b + batch * p.sb + n0;
+    float acc[MB];
+#pragma unroll
+    for (int m = 0; m < MB; m++) acc[m] = 0.f;
+    const int K = static_cast<int>(p.K);
+    int k = 0;
+    for (; k + 16 <= K; k += 16) {
+        float bv[16];
+#pragma unroll
+        for (int u = 0; u < 16; u++) bv[u] = __ldg(B + static_cast<int64_t>(k + u) * p.N);
+#pragma unroll
+        for (int m = 0; m < MB; m++) {
+            if (m < p.M) {
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float4 av = __ldg(reinterpret_cast<const float4*>(A + static_cast<int64_t>(m) * p.K + k + 4 * q));
+                    acc[m] = fmaf(av.x, bv[4 * q + 0], acc[m]);
+                    acc[m] = fmaf(av.y, bv[4 * q + 1], acc[m]);
+                    acc[m] = fmaf(av.z, bv[4 * q + 2], acc[m]);
+                    acc[m] = fmaf(av.w, bv[4 * q + 3], acc[m]);
+                }
+            }
+        }
+    }
+    for (; k < K; k++) {
+        const float b = __ldg(B + static_cast<int64_t>(k) * p.N);
+#pragma unroll
+        for (int m = 0; m < MB; m++)
+            if (m < p.M) acc[m] = fmaf(__ldg(A + static_cast<int64_t>(m) * p.K + k), b, acc[m]);
+    }
+    float* __restrict__ C = p.c + batch * p.sc + n0;
+#pragma unroll
+    for (int m = 0; m < MB; m++)
+        if (m < p.M) C[static_cast<int64_t>(m) * p.N] = acc[m];
+}
+
+// ---------------------------------------------------------------------------------------------
+// C = A x B^T with B stored [N][K] row-major (what MatMul(A, Transpose(B)) computes, without the copy)
+// ---------------------------------------------------------------------------------------------
+// Few rows of A and a short K (decode attention scores against a [T, head_dim] key cache): a warp owns 32
+// consecutive rows of B; LPR lanes share one row (each lane one 16-byte k-quad, so a warp-wide load reads
+// 32 / LPR whole rows = 512 contiguous bytes), the k-quads of A live in registers, and the partial dot
+// products are summed across the LPR lanes by shuffles.  For four rows of A the first two shuffle steps
+// exchange halves of the four partial sums instead of all of them (5 shuffles per row instead of 16).
+template <int MB, int LPR>
+__global__ void __launch_bounds__(256) nt_rows_kernel(SkinnyParams p, uint32_t chunks_per_batch, int64_t total_chunks) {
+    const int64_t wid = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 5;
+    if (wid >= total_chunks) return;
+    const int lane = threadIdx.x & 31;
+    const int64_t batch = wid / chunks_per_batch;
+    const int64_t n0 = (wid - batch * chunks_per_batch) * 32;
+    constexpr int RPI = 32 / LPR;  // rows per warp-wide load
+    const int sub = lane % LPR, rsel = lane / LPR;
+    const bool kin = 4 * sub < p.K;
+    float4 a[MB];
+#pragma unroll
+    for (int m = 0; m < MB; m++) {
+        a[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (kin && m < p.M) a[m] = __ldg(reinterpret_cast<const float4*>(p.a + batch * p.sa + static_cast<int64_t>(m) * p.K + 4 * sub));
+    }
+    const float* __restrict__ B = p.b + batch * p.sb + 4 * sub;
+    float* __restrict__ C = p.c + batch * p.sc;
+    constexpr int UN = LPR < 8 ? LPR : 8;
+    for (int it0 = 0; it0 < LPR; it0 += UN) {
+        uint4 bv[UN];
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int64_t n = n0 + (it0 + u) * RPI + rsel;
+            bv[u] = make_uint4(0, 0, 0, 0);
+            if (kin && n < p.N) bv[u] = ld_stream_u4(B + n * p.K);
+        }
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int64_t n = n0 + (it0 + u) * RPI + rsel;
+            const float bx = __uint_as_float(bv[u].x), by = __uint_as_float(bv[u].y), bz = __uint_as_float(bv[u].z), bw = __uint_as_float(bv[u].w);
+            float part[MB];
+#pragma unroll
+            for (int m = 0; m < MB; m++) part[m] = fmaf(a[m].w, bw, fmaf(a[m].z, bz, fmaf(a[m].y, by, a[m].x * bx)));
+            if constexpr (MB == 4 && LPR >= 4) {
+                const bool up1 = (sub & (LPR / 2)) != 0;
+                const float r0 = __shfl_xor_sync(0xffffffffu, up1 ? part[0] : part[2], LPR / 2);
+                const float r1 = __shfl_xor_sync(0xffffffffu, up1 ? part[1] : part[3], LPR / 2);
+                const float q0 = (up1 ? part[2] : part[0]) + r0;
+                const float q1 = (up1 ? part[3] : part[1]) + r1;
+                const bool up2 = (sub & (LPR / 4)) != 0;
+                const float r2 = __shfl_xor_sync(0xffffffffu, up2 ? q0 : q1, LPR / 4);
+                float v = (up2 ? q1 : q0) + r2;
+#pragma unroll
+                for (int off = LPR / 8; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                const int m = 2 * (up1 ? 1 : 0) + (up2 ? 1 : 0);
+                if ((sub & (LPR / 4 - 1)) == 0 && n < p.N && m < p.M) C[static_cast<int64_t>(m) * p.N + n] = v;
+            } else {
+#pragma unroll
+                for (int m = 0; m < MB; m++) {
+                    float v = part[m];
+#pragma unroll
+                    for (int off = LPR / 2; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                    if (sub == 0 && n < p.N && m < p.M) C[static_cast<int64_t>(m) * p.N + n] = v;
+                }
+            }
+        }
+    }
+}
+
+// Any other shape: one thread per output element, sequential fp32 dot product.
+__global__ void __launch_bounds__(256) nt_generic_kernel(SkinnyParams p, int64_t total) {
+    const int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (idx >= total) return;
+    const int64_t mn = p.M * p.N;
+    const int64_t batch = idx / mn, r = idx - batch * mn;
+    const int64_t m = r / p.N, n = r - m * p.N;
+    const float* __restrict__ A = p.a + batch * p.sa + m * p.K;
+    const float* __restrict__ B = p.b + batch * p.sb + n * p.K;
+    float s = 0.f;
+    for (int64_t k = 0; k < p.K; k++) s = fmaf(A[k], B[k], s);
+    p.c[batch * p.sc + r] = s;
+}
+
 // Sum the split-K partials [ksplit][batch][M*N] in split order.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, float* __restrict__ c, int ksplit,
                                                             int64_t batch, int64_t mn, int64_t sc) {
@@ -388,6 +561,28 @@ extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batc
         p.M = m; p.N = n; p.K = k;
         p.sa = a_batch_stride; p.sb = b_batch_stride; p.sc = c_batch_stride;
         p.vec_b = b_rows_aligned ? 1 : 0;
+        // many problems with a short K: one thread per column quad (or per column), no reduction
+        if (m <= 4 && k <= 256 && k % 4 == 0 && aligned_to(a, 16) && a_batch_stride % 4 == 0 && n <= 0x7fffffffll &&
+            batch * n >= 2048ll * sm_count() && batch * n < (1ll << 38)) {
+            p.ksplit = 1;
+            p.k_per_split = k;
+            p.c = static_cast<float*>(c);
+            if (b_rows_aligned && aligned_to(c, 16) && c_batch_stride % 4 == 0) {
+                const int64_t total_quads = batch * (n / 4);
+                const unsigned grid = static_cast<unsigned>(ceil_div64(total_quads, 256));
+                if (m == 1) smallk_kernel<1><<<grid, 256, 0, st>>>(p, total_quads, static_cast<uint32_t>(n / 4));
+                else if (m == 2) smallk_kernel<2><<<grid, 256, 0, st>>>(p, total_quads, static_cast<uint32_t>(n / 4));
+                else smallk_kernel<4><<<grid, 256, 0, st>>>(p, total_quads, static_cast<uint32_t>(n / 4));
+            } else {
+                const int64_t total_cols = batch * n;
+                const unsigned grid = static_cast<unsigned>(ceil_div64(total_cols, 256));
+                if (m == 1) smallk1_kernel<1><<<grid, 256, 0, st>>>(p, total_cols, static_cast<uint32_t>(n));
+                else if (m == 2) smallk1_kernel<2><<<grid, 256, 0, st>>>(p, total_cols, static_cast<uint32_t>(n));
+                else smallk1_kernel<4><<<grid, 256, 0, st>>>(p, total_cols, static_cast<uint32_t>(n));
+            }
+            RMLK_CHECK_LAUNCH("smallk_kernel");
+            return RMLK_OK;
+        }
         int ksplit = skinny_plan(batch, n, k);
         const size_t need = static_cast<size_t>(ksplit) * batch * m * n * sizeof(float);
         if (ksplit > 1 && (!workspace || workspace_bytes < need)) ksplit = 1;
@@ -427,6 +622,57 @@ extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batc
         gemm_kernel<64, 64><<<grid, 256, 0, st>>>(g);
     }
     RMLK_CHECK_LAUNCH("gemm_kernel");
+    return RMLK_OK;
+}
+
+template <int MB>
+static void nt_rows_launch(cudaStream_t st, const SkinnyParams& p, int64_t batch) {
+    const int64_t chunks = ceil_div64(p.N, 32);
+    const int64_t total = chunks * batch;
+    const unsigned grid = static_cast<unsigned>(ceil_div64(total, 8));
+    if (p.K <= 16) nt_rows_kernel<MB, 4><<<grid, 256, 0, st>>>(p, static_cast<uint32_t>(chunks), total);
+    else if (p.K <= 32) nt_rows_kernel<MB, 8><<<grid, 256, 0, st>>>(p, static_cast<uint32_t>(chunks), total);
+    else if (p.K <= 64) nt_rows_kernel<MB, 16><<<grid, 256, 0, st>>>(p, static_cast<uint32_t>(chunks), total);
+    else nt_rows_kernel<MB, 32><<<grid, 256, 0, st>>>(p, static_cast<uint32_t>(chunks), total);
+}
+
+extern "C" int rmlk_b200_matmul_nt(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k, const void* a,
+                                   int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c, int64_t c_batch_stride) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for matmul (f32 only)");
+    if (batch < 0 || m < 0 || n < 0 || k < 0) return fail(RMLK_ERR_INVALID_ARG, "matmul_nt: negative extent");
+    if (batch == 0 || m == 0 || n == 0) return RMLK_OK;
+    if (!c) return fail(RMLK_ERR_INVALID_ARG, "matmul_nt: NULL output");
+    cudaStream_t st = as_stream(stream);
+    if (k == 0) {
+        for (int64_t bi = 0; bi < batch; bi++)
+            RMLK_CUDA(cudaMemsetAsync(static_cast<float*>(c) + bi * c_batch_stride, 0, static_cast<size_t>(m) * n * sizeof(float), st));
+        return RMLK_OK;
+    }
+    if (!a || !b) return fail(RMLK_ERR_INVALID_ARG, "matmul_nt: NULL operand");
+    SkinnyParams p;
+    p.a = static_cast<const float*>(a);
+    p.b = static_cast<const float*>(b);
+    p.c = static_cast<float*>(c);
+    p.M = m; p.N = n; p.K = k;
+    p.sa = a_batch_stride; p.sb = b_batch_stride; p.sc = c_batch_stride;
+    p.k_per_split = k;
+    p.vec_b = 1;
+    const int64_t chunks = ceil_div64(n, 32) * batch;
+    if (m <= 8 && k <= 128 && k % 4 == 0 && aligned_to(a, 16) && aligned_to(b, 16) && a_batch_stride % 4 == 0 && b_batch_stride % 4 == 0 &&
+        batch <= 0x7fffffffll && chunks / 8 < 0x7fffffffll) {
+        p.ksplit = 1;
+        if (m == 1) nt_rows_launch<1>(st, p, batch);
+        else if (m == 2) nt_rows_launch<2>(st, p, batch);
+        else if (m <= 4) nt_rows_launch<4>(st, p, batch);
+        else nt_rows_launch<8>(st, p, batch);
+        RMLK_CHECK_LAUNCH("nt_rows_kernel");
+        return RMLK_OK;
+    }
+    const int64_t total = batch * m * n;
+    if (total / 256 >= 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "matmul_nt: output too large");
+    p.ksplit = 1;
+    nt_generic_kernel<<<static_cast<unsigned>(ceil_div64(total, 256)), 256, 0, st>>>(p, total);
+    RMLK_CHECK_LAUNCH("nt_generic_kernel");
     return RMLK_OK;
 }
 

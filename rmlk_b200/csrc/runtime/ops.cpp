@@ -84,11 +84,23 @@ int64_t normalize_index(int64_t index, int64_t size) {
 struct Ctx {
     Instance& I;
     const NodeDef& n;
-    Tensor* in(size_t i) const {
+    // Input i as it is: possibly a deferred view (Tensor::lazy).
+    Tensor* raw(size_t i) const {
         if (i >= n.inputs.size() || n.inputs[i] < 0) return nullptr;
         Tensor& t = I.values[n.inputs[i]];
         if (!t.present) raise(RMLK_ERR_INVALID_ARG, "input value `" + I.g.values[n.inputs[i]].name + "` has no data");
         return &t;
+    }
+    // Input i as a dense tensor; a deferred view is copied out first.
+    Tensor* in(size_t i) const {
+        Tensor* t = raw(i);
+        if (t && t->lazy) I.materialize(*t);
+        return t;
+    }
+    // May output i stay a view of another buffer?  Not if it leaves the graph or is carried to the next run.
+    bool may_defer(size_t i) const {
+        const int vid = n.outputs[i];
+        return !I.g.values[vid].is_output && I.binding_of_out[vid] < 0;
     }
     Tensor& req(size_t i) const {
         Tensor* t = in(i);
@@ -115,6 +127,7 @@ struct Ctx {
         o.mirror_valid = false;
         o.mi.clear();
         o.mf.clear();
+        o.lazy = false;
         I.alloc_output(n.outputs[i], o);
         o.present = true;
         return o;
@@ -137,7 +150,28 @@ struct Ctx {
             o.data = src.data;
             o.storage = src.storage;
             if (o.storage) o.storage->refs++;
+            // regrouping the dims of a deferred view leaves its element order, hence pshape / pstride, alone
+            o.lazy = src.lazy;
+            o.pshape = src.pshape;
+            o.pstride = src.pstride;
         }
+        o.present = true;
+        return o;
+    }
+    // Output i becomes a deferred view of base's buffer: logical `shape`, elements enumerated by pshape / pstride.
+    Tensor& defer(size_t i, const Tensor& base, const Shape& shape, const Shape& pshape, const Shape& pstride) const {
+        Tensor& o = out(i);
+        o.dtype = base.dtype;
+        o.shape = shape;
+        o.mirror_valid = false;
+        o.mi.clear();
+        o.mf.clear();
+        o.data = base.data;
+        o.storage = base.storage;
+        if (o.storage) o.storage->refs++;
+        o.lazy = true;
+        o.pshape = pshape;
+        o.pstride = pstride;
         o.present = true;
         return o;
     }
@@ -173,6 +207,96 @@ int64_t bindex(const Shape& shape, const Shape& out, int64_t lin) {
         off += c * st[d];
     }
     return off;
+}
+
+// ---- deferred views -------------------------------------------------------------------------
+// Physical dims of a tensor: pshape / pstride of a deferred view, else its shape with dense strides.
+void phys_of(const Tensor& t, Shape& ps, Shape& pst) {
+    if (t.lazy) {
+        ps = t.pshape;
+        pst = t.pstride;
+    } else {
+        ps = t.shape;
+        pst = dense_strides(t.shape);
+    }
+}
+
+// One run [begin, end) of consecutive physical dims per logical dim, products equal.  False when the edge
+// of a logical dim falls inside a physical dim (the view was regrouped in a way the caller cannot follow).
+bool group_dims(const Shape& logical, const Shape& ps, std::vector<std::pair<int, int>>& groups) {
+    groups.clear();
+    int p = 0;
+    const int np = static_cast<int>(ps.size());
+    for (size_t d = 0; d < logical.size(); d++) {
+        const int begin = p;
+        int64_t run = 1;
+        if (logical[d] <= 0) return false;
+        while (run < logical[d]) {
+            if (p >= np) return false;
+            run *= ps[p++];
+        }
+        if (run != logical[d]) return false;
+        groups.push_back({begin, p});
+    }
+    for (; p < np; p++)
+        if (ps[p] != 1) return false;
+    return true;
+}
+
+void push_dim(Shape& ps, Shape& pst, int64_t size, int64_t stride) {
+    if (size == 1) return;
+    ps.push_back(size);
+    pst.push_back(stride);
+}
+
+// A deferred right operand of MatMul that is a dense [k, n] (or, transposed, a dense [n, k]) matrix per
+// batch entry, whose batch dims are `outer` entries `sb` elements apart followed by `fold` entries that
+// all read the same matrix (stride 0: a broadcast such as grouped-query attention's repeated KV heads).
+struct LazyB {
+    bool transposed = false;
+    int64_t outer = 1, fold = 1, sb = 0;
+};
+bool analyze_lazy_b(const Tensor& b, int64_t k, int64_t n, LazyB& r) {
+    const size_t br = b.shape.size();
+    if (br < 2) return false;
+    std::vector<std::pair<int, int>> groups;
+    if (!group_dims(b.shape, b.pshape, groups)) return false;
+    auto single = [&](const std::pair<int, int>& g, int64_t& stride) {
+        int cnt = 0;
+        stride = 0;
+        for (int p = g.first; p < g.second; p++)
+            if (b.pshape[p] != 1) {
+                cnt++;
+                stride = b.pstride[p];
+            }
+        return cnt <= 1;
+    };
+    int64_t sk = 0, sn = 0;
+    if (!single(groups[br - 2], sk) || !single(groups[br - 1], sn)) return false;
+    const bool nn = (n == 1 || sn == 1) && (k == 1 || sk == n);
+    const bool nt = (k == 1 || sk == 1) && (n == 1 || sn == k);
+    if (!nn && !nt) return false;
+    r.transposed = !nn;
+    Shape bd, bs;
+    for (size_t d = 0; d + 2 < br; d++)
+        for (int p = groups[d].first; p < groups[d].second; p++) push_dim(bd, bs, b.pshape[p], b.pstride[p]);
+    r.fold = 1;
+    while (!bd.empty() && bs.back() == 0) {
+        r.fold *= bd.back();
+        bd.pop_back();
+        bs.pop_back();
+    }
+    r.outer = 1;
+    r.sb = 0;
+    if (!bd.empty()) {
+        r.sb = bs.back();
+        for (size_t i = bd.size(); i-- > 0;) {
+            if (i + 1 < bd.size() && bs[i] != bs[i + 1] * bd[i + 1]) return false;
+            r.outer *= bd[i];
+        }
+        if (r.sb <= 0) return false;
+    }
+    return true;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -437,7 +561,9 @@ void op_softmax(const Ctx& c) {
 // ---------------------------------------------------------------------------------------------
 void op_matmul(const Ctx& c) {
     Tensor& a = c.req(0);
-    Tensor& b = c.req(1);
+    Tensor* braw = c.raw(1);
+    if (!braw) raise(RMLK_ERR_INVALID_ARG, "missing input 1");
+    Tensor& b = *braw;  // may be a deferred view; made dense below unless the kernels can read it as it is
     if (!in_set(a.dtype, {RMLK_F32})) unsupported_dtype(a.dtype, "matmul");
     if (b.dtype != a.dtype) raise(RMLK_ERR_INVALID_ARG, "matmul: operand data types differ");
     const size_t ar = a.shape.size(), br = b.shape.size();
@@ -458,6 +584,31 @@ void op_matmul(const Ctx& c) {
     if (br > 1) oshape.push_back(n);
     Tensor& o = c.make(0, a.dtype, oshape);
     if (o.numel() == 0) return;
+    if (b.lazy) {
+        // Right operand still a view (Expand / Reshape / Transpose chain).  If it is a dense matrix per batch
+        // entry, possibly transposed, possibly repeated over trailing batch dims, the kernels read the
+        // base buffer directly: the repeats become extra rows of A (they share one B), the transposition
+        // selects the A x B^T kernel.  Otherwise it is copied out once and the dense path below runs.
+        LazyB lb;
+        bool usable = ar >= 2 && br >= 2 && (ba == bb || bb == 1) && ka > 0 && analyze_lazy_b(b, kb, n, lb) && lb.outer * lb.fold == bb;
+        const int64_t em = usable ? (bb == 1 ? ba : lb.fold) * m : 0;  // one shared B: every batch entry of A is extra rows
+        usable = usable && (!lb.transposed || (em <= 8 && ka <= 128 && ka % 4 == 0));
+        if (usable) {
+            if (lb.transposed) {
+                check_rc(rmlk_b200_matmul_nt(c.stream(), a.dtype, lb.outer, em, n, ka, a.data, em * ka, b.data, lb.sb, o.data, em * n));
+                c.launched();
+            } else {
+                const size_t need = rmlk_b200_matmul_workspace_bytes(a.dtype, lb.outer, em, n, ka);
+                void* ws = need ? c.I.matmul_ws.ensure(need) : nullptr;
+                check_rc(rmlk_b200_matmul_ex(c.stream(), a.dtype, lb.outer, em, n, ka, a.data, em * ka, b.data, lb.sb, o.data, em * n, ws, need,
+                                             static_cast<int*>(c.I.status_word.ptr)));
+                c.I.status_dirty = true;
+                c.launched(need ? 2 : 1);
+            }
+            return;
+        }
+        c.I.materialize(b);
+    }
     // A weight shared by every batch entry (rank <= 2 right operand) folds the batch into M: one
     // pass over B instead of the reference's per-batch copies (matmul.rs:48-86).
     int64_t eb = batch, em = m, sa = ba > 1 ? m * ka : 0, sb = bb > 1 ? kb * n : 0, sc = m * n;
@@ -593,8 +744,43 @@ void op_slice(const Ctx& c) {
 
 // backend/transpose.rs:44-178
 void op_transpose(const Ctx& c) {
+    Tensor* xr = c.raw(0);
+    if (!xr) raise(RMLK_ERR_INVALID_ARG, "missing input 0");
+    if (!in_set(xr->dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_I64})) unsupported_dtype(xr->dtype, "transpose");
+    // Large tensors that stay inside the graph are permuted as a view; the copy happens when (and if) a
+    // consumer needs dense data, together with any Expand / Transpose deferred before it.
+    if (c.may_defer(0) && xr->numel() > HOST_MIRROR_MAX && xr->shape.size() <= RMLK_MAX_RANK) {
+        const int rank = static_cast<int>(xr->shape.size());
+        std::vector<int64_t> perm;
+        const Attr* a = c.attr("perm");
+        bool ok = true;
+        if (a) {
+            ok = a->kind == Attr::INTS && static_cast<int>(a->ints.size()) == rank;
+            if (ok) perm = a->ints;
+            std::vector<char> seen(rank, 0);
+            for (size_t i = 0; ok && i < perm.size(); i++) {
+                ok = perm[i] >= 0 && perm[i] < rank && !seen[perm[i]];
+                if (ok) seen[perm[i]] = 1;
+            }
+        } else {
+            for (int i = rank - 1; i >= 0; i--) perm.push_back(i);
+        }
+        Shape ps, pst;
+        std::vector<std::pair<int, int>> groups;
+        phys_of(*xr, ps, pst);
+        if (ok && group_dims(xr->shape, ps, groups)) {
+            Shape oshape(rank), nps, npst;
+            for (int d = 0; d < rank; d++) {
+                oshape[d] = xr->shape[perm[d]];
+                for (int p = groups[perm[d]].first; p < groups[perm[d]].second; p++) push_dim(nps, npst, ps[p], pst[p]);
+            }
+            if (nps.size() <= RMLK_MAX_RANK) {
+                c.defer(0, *xr, oshape, nps, npst);
+                return;
+            }
+        }
+    }
     Tensor& x = c.req(0);
-    if (!in_set(x.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_I64})) unsupported_dtype(x.dtype, "transpose");
     const int rank = static_cast<int>(x.shape.size());
     std::vector<int64_t> perm;
     if (const Attr* a = c.attr("perm")) {
@@ -672,17 +858,44 @@ void op_concat(const Ctx& c) {
 
 // backend/expand.rs:49-216
 void op_expand(const Ctx& c) {
-    Tensor& x = c.req(0);
+    Tensor* xr = c.raw(0);
+    if (!xr) raise(RMLK_ERR_INVALID_ARG, "missing input 0");
     Tensor& sh = c.req(1);
-    if (!in_set(x.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_U32, RMLK_I64, RMLK_U64})) unsupported_dtype(x.dtype, "expand");
+    if (!in_set(xr->dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_U32, RMLK_I64, RMLK_U64})) unsupported_dtype(xr->dtype, "expand");
     if (sh.dtype != RMLK_I64) unsupported_dtype(sh.dtype, "expand shape");
     const std::vector<int64_t> target = c.I.host_i64(sh);
     for (int64_t v : target)
         if (v < 0) raise(RMLK_ERR_INVALID_ARG, "expand: negative dimension in shape");
     Shape oshape;
-    if (!broadcast_shape(x.shape, target, oshape))
-        raise(RMLK_ERR_INVALID_ARG, "incompatible shapes for broadcast: " + shape_str(x.shape) + " " + shape_str(target));
+    if (!broadcast_shape(xr->shape, target, oshape))
+        raise(RMLK_ERR_INVALID_ARG, "incompatible shapes for broadcast: " + shape_str(xr->shape) + " " + shape_str(target));
     if (oshape.size() > RMLK_MAX_RANK) raise(RMLK_ERR_INVALID_ARG, "expand: rank must be at most 8");
+    // Large results that stay inside the graph are broadcast as a view (stride 0 along the repeated dims).
+    if (c.may_defer(0) && prod(oshape) > HOST_MIRROR_MAX && xr->numel() > 0) {
+        Shape ps, pst, nps, npst;
+        std::vector<std::pair<int, int>> groups;
+        phys_of(*xr, ps, pst);
+        if (group_dims(xr->shape, ps, groups)) {
+            const size_t orank = oshape.size(), xrank = xr->shape.size();
+            for (size_t d = 0; d < orank; d++) {
+                if (d + xrank < orank) {
+                    push_dim(nps, npst, oshape[d], 0);
+                    continue;
+                }
+                const size_t j = d - (orank - xrank);
+                if (xr->shape[j] == oshape[d]) {
+                    for (int p = groups[j].first; p < groups[j].second; p++) push_dim(nps, npst, ps[p], pst[p]);
+                } else {
+                    push_dim(nps, npst, oshape[d], 0);
+                }
+            }
+            if (nps.size() <= RMLK_MAX_RANK) {
+                c.defer(0, *xr, oshape, nps, npst);
+                return;
+            }
+        }
+    }
+    Tensor& x = c.req(0);
     Tensor& o = c.make(0, x.dtype, oshape);
     if (o.numel() == 0) return;
     const Shape ish = kshape(x);
@@ -788,7 +1001,8 @@ void op_range(const Ctx& c) {
 // ---------------------------------------------------------------------------------------------
 // backend/reshape.rs:60-160
 void op_reshape(const Ctx& c) {
-    Tensor& x = c.req(0);
+    // a deferred view keeps its element order under Reshape, so it can stay deferred
+    Tensor& x = c.may_defer(0) && c.raw(0) ? *c.raw(0) : c.req(0);
     Tensor& sh = c.req(1);
     if (sh.dtype != RMLK_I64) unsupported_dtype(sh.dtype, "reshape shape");
     const bool allow_zero = c.attr_int("allowzero", 0) != 0;
@@ -860,7 +1074,7 @@ void op_unsqueeze(const Ctx& c) {
 
 // runtime/src/providers/cpu/flatten.rs
 void op_flatten(const Ctx& c) {
-    Tensor& x = c.req(0);
+    Tensor& x = c.may_defer(0) && c.raw(0) ? *c.raw(0) : c.req(0);
     const int64_t rank = static_cast<int64_t>(x.shape.size());
     int64_t axis = c.attr_int("axis", 1);
     if (axis < 0) axis += rank;
@@ -880,7 +1094,9 @@ void store_small_i64(const Ctx& c, Tensor& o, const std::vector<int64_t>& vals) 
 
 // backend/shape.rs:30-80
 void op_shape(const Ctx& c) {
-    Tensor& x = c.req(0);
+    Tensor* xr = c.raw(0);  // only the dims are read: a deferred view stays deferred
+    if (!xr) raise(RMLK_ERR_INVALID_ARG, "missing input 0");
+    Tensor& x = *xr;
     const int64_t rank = static_cast<int64_t>(x.shape.size());
     int64_t start = c.attr_int("start", 0), end = c.attr_int("end", rank);
     if (start < 0) start += rank;

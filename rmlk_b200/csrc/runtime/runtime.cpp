@@ -266,6 +266,23 @@ void Instance::release_value(int value_id) {
     }
 }
 
+void Instance::materialize(Tensor& t) {
+    if (!t.lazy) return;
+    Storage* base_storage = t.storage;
+    const void* base = t.data;
+    t.storage = arena->alloc(t.nbytes());
+    t.data = t.storage->ptr;
+    if (t.numel() > 0) {
+        check_rc(rmlk_b200_strided_copy(reinterpret_cast<rmlk_stream_t>(stream), static_cast<int>(dtype_size_of(t.dtype)),
+                                        static_cast<int>(t.pshape.size()), t.pshape.data(), t.pstride.data(), base, t.data));
+        launches++;
+    }
+    if (base_storage) arena->release(base_storage);
+    t.lazy = false;
+    t.pshape.clear();
+    t.pstride.clear();
+}
+
 void Instance::check_status() {
     if (!status_dirty) return;
     int code = 0;
@@ -289,6 +306,7 @@ void Instance::run() {
         values[i].present = false;
         values[i].storage = nullptr;
         values[i].data = nullptr;
+        values[i].lazy = false;
     }
     arena->reset();
     for (Binding& b : bindings) {
@@ -661,6 +679,7 @@ extern "C" int rmlk_instance_value_info(rmlk_instance* inst, const char* name, i
     if (id < 0) raise(RMLK_ERR_INVALID_ARG, std::string("unknown value `") + name + "`");
     const Tensor& t = I.values[id];
     if (!t.present) raise(RMLK_ERR_INVALID_ARG, std::string("value `") + name + "` has no data");
+    if (t.lazy && device_ptr) raise(RMLK_ERR_INVALID_ARG, std::string("value `") + name + "` is a deferred view without a buffer of its own");
     if (dtype) *dtype = t.dtype;
     if (rank) *rank = static_cast<int>(t.shape.size());
     if (dims)
@@ -678,6 +697,7 @@ extern "C" int rmlk_instance_read(rmlk_instance* inst, const char* name, void* d
     if (id < 0) raise(RMLK_ERR_INVALID_ARG, std::string("unknown value `") + name + "`");
     const Tensor& t = I.values[id];
     if (!t.present) raise(RMLK_ERR_INVALID_ARG, std::string("value `") + name + "` has no data");
+    if (t.lazy) raise(RMLK_ERR_INVALID_ARG, std::string("value `") + name + "` is a deferred view without a buffer of its own");
     if (nbytes != t.nbytes()) raise(RMLK_ERR_INVALID_ARG, std::string("read of `") + name + "`: size mismatch");
     if (nbytes) check_cuda(cudaMemcpyAsync(dst, t.data, nbytes, cudaMemcpyDeviceToHost, I.stream), "output D2H");
     check_cuda(cudaStreamSynchronize(I.stream), "cudaStreamSynchronize");

@@ -74,6 +74,16 @@ struct Tensor {
     void* data = nullptr;        // device
     Storage* storage = nullptr;  // arena ownership (null: weights, inputs, carried buffers)
     bool present = false;
+    // Deferred layout op.  When `lazy` is set, `data` is the base of another tensor's buffer (kept alive
+    // through `storage`) and element i of this tensor, in row-major order over `shape`, is element i in
+    // row-major order over `pshape`, found at the element offset sum_d index_d * pstride[d] (stride 0 =
+    // broadcast).  Expand and Transpose produce such views; Reshape and Flatten regroup `shape` and leave
+    // pshape / pstride alone.  A consumer that cannot read strides gets a dense copy on demand (one
+    // strided-copy launch for the whole chain); MatMul reads the view directly when it amounts to a
+    // transposed and / or batch-broadcast right operand.  The reference copies in every one of these ops
+    // (backend/expand.rs:49-216, backend/transpose.rs:44-178, backend/reshape.rs:27-73).
+    bool lazy = false;
+    std::vector<int64_t> pshape, pstride;
     bool mirror_valid = false;
     std::vector<int64_t> mi;  // integer / bool mirror
     std::vector<double> mf;   // float mirror
@@ -163,6 +173,8 @@ struct Instance {
     std::vector<double> host_f64(const Tensor& t);
     void run_node(const NodeDef& n);
     void release_value(int value_id);
+    // replaces a deferred view by a dense copy in arena memory (no-op for a dense tensor)
+    void materialize(Tensor& t);
     void check_status();
 };
 

@@ -191,16 +191,17 @@ def slice_(x: torch.Tensor, starts, ends, axes=None, steps=None) -> torch.Tensor
     return out
 
 
-def transpose(x: torch.Tensor, perm=None) -> torch.Tensor:
+def transpose(x: torch.Tensor, perm=None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _require_cuda(x)
     if perm is None:
         perm = list(range(x.dim()))[::-1]
-    out = torch.empty([x.shape[p] for p in perm], dtype=x.dtype, device=x.device)
+    if out is None:
+        out = torch.empty([x.shape[p] for p in perm], dtype=x.dtype, device=x.device)
     _check(lib().rmlk_b200_transpose(_stream(), x.element_size(), x.dim(), _i64(list(x.shape)), _i64(perm), _ptr(x), _ptr(out)))
     return out
 
 
-def concat(inputs: Sequence[torch.Tensor], axis: int) -> torch.Tensor:
+def concat(inputs: Sequence[torch.Tensor], axis: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _require_cuda(*inputs)
     rank = inputs[0].dim()
     axis = axis + rank if axis < 0 else axis
@@ -213,17 +214,19 @@ def concat(inputs: Sequence[torch.Tensor], axis: int) -> torch.Tensor:
         inner *= d
     dims = [t.shape[axis] for t in inputs]
     osh = sh[:axis] + [sum(dims)] + sh[axis + 1:]
-    out = torch.empty(osh, dtype=inputs[0].dtype, device=inputs[0].device)
+    if out is None:
+        out = torch.empty(osh, dtype=inputs[0].dtype, device=inputs[0].device)
     ptrs = (ctypes.c_void_p * len(inputs))(*[t.data_ptr() for t in inputs])
     _check(lib().rmlk_b200_concat(_stream(), inputs[0].element_size(), len(inputs), ctypes.c_int64(outer), ctypes.c_int64(inner),
                                   _i64(dims), ptrs, _ptr(out)))
     return out
 
 
-def expand(x: torch.Tensor, shape) -> torch.Tensor:
+def expand(x: torch.Tensor, shape, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     _require_cuda(x)
     osh = list(torch.broadcast_shapes(tuple(x.shape), tuple(int(v) for v in shape)))
-    out = torch.empty(osh, dtype=x.dtype, device=x.device)
+    if out is None:
+        out = torch.empty(osh, dtype=x.dtype, device=x.device)
     ish = _kshape(x)
     _check(lib().rmlk_b200_expand(_stream(), x.element_size(), len(ish), _i64(ish), len(osh), _i64(osh), _ptr(x), _ptr(out)))
     return out
@@ -282,4 +285,26 @@ def matmul(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None,
                                   ctypes.c_int64(k), _ptr(a), ctypes.c_int64(m * k if ba > 1 else 0), _ptr(b),
                                   ctypes.c_int64(k * n if bb > 1 else 0), _ptr(out), ctypes.c_int64(m * n), _ptr(workspace),
                                   ctypes.c_size_t(0 if workspace is None else workspace.numel() * workspace.element_size())))
+    return out
+
+
+def matmul_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """a: [batch..., m, k], b: [batch..., n, k] (row-major [n, k]) -> a x b^T: [batch..., m, n]."""
+    _require_cuda(a, b, out)
+    m, k = a.shape[-2], a.shape[-1]
+    n = b.shape[-2]
+    batch = a.numel() // (m * k) if m * k else 1
+    if out is None:
+        out = torch.empty(list(a.shape[:-2]) + [m, n], dtype=a.dtype, device=a.device)
+    _check(lib().rmlk_b200_matmul_nt(_stream(), dt.from_torch(a.dtype), ctypes.c_int64(batch), ctypes.c_int64(m), ctypes.c_int64(n),
+                                     ctypes.c_int64(k), _ptr(a), ctypes.c_int64(m * k), _ptr(b), ctypes.c_int64(n * k), _ptr(out),
+                                     ctypes.c_int64(m * n)))
+    return out
+
+
+def strided_copy(base: torch.Tensor, shape: Sequence[int], strides: Sequence[int]) -> torch.Tensor:
+    """Dense copy of the view of `base` (a contiguous buffer) with the given shape and element strides."""
+    _require_cuda(base)
+    out = torch.empty(list(shape), dtype=base.dtype, device=base.device)
+    _check(lib().rmlk_b200_strided_copy(_stream(), base.element_size(), len(shape), _i64(list(shape)), _i64(list(strides)), _ptr(base), _ptr(out)))
     return out

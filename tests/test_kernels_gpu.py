@@ -305,7 +305,10 @@ def test_softmax(shape):
 
 MM_CASES = [(1, 1, 8192, 2048), (1, 8, 8192, 2048), (1, 16, 512, 2048), (1, 64, 2048, 2048), (1, 128, 1024, 256), (1, 1, 64, 64),
             (1, 3, 5, 7), (1, 2, 2, 2), (1, 17, 33, 65), (1, 70, 130, 50), (1, 129, 257, 100), (32, 1, 641, 64), (32, 1, 64, 641),
-            (8, 128, 128, 64), (8, 128, 64, 128), (3, 5, 30, 9), (1, 1, 2048, 8192), (1, 200, 300, 4), (1, 4, 100, 1), (2, 16, 31, 1000)]
+            (8, 128, 128, 64), (8, 128, 64, 128), (3, 5, 30, 9), (1, 1, 2048, 8192), (1, 200, 300, 4), (1, 4, 100, 1), (2, 16, 31, 1000),
+            # many problems with a short K (one thread per column quad, no reduction)
+            (2048, 1, 520, 64), (600, 2, 512, 128), (300, 4, 1024, 256), (300, 3, 1024, 252), (2048, 1, 160, 4),
+            (2048, 1, 523, 64), (700, 2, 517, 128), (400, 4, 1001, 40), (400, 3, 1001, 252)]
 
 
 @pytest.mark.parametrize("case", MM_CASES)
@@ -428,7 +431,12 @@ def test_transpose_all_4d_perms(dtype):
 
 
 def test_transpose_other_ranks():
-    for sh, perm in [((7,), [0]), ((5, 9), [1, 0]), ((5, 9), None), ((2, 3, 4), [2, 0, 1]), ((1, 1, 5), [2, 1, 0]),
+    # shapes whose extents are multiples of 4 take the 64 x 64 tile kernel with 16-byte accesses
+    for sh, perm in [((3, 5, 36, 68), [0, 1, 3, 2]), ((3, 5, 36, 68), [3, 2, 1, 0]), ((3, 8, 36, 68), [3, 0, 2, 1]), ((2, 100, 260), [0, 2, 1]),
+                     ((4, 4, 4, 4), [3, 1, 2, 0]), ((1000, 520), [1, 0]), ((64, 64), [1, 0]), ((2, 8, 520, 64), [0, 1, 3, 2]),
+                     ((3, 4, 200, 12), [2, 3, 0, 1]),
+                     # only one side 16-byte aligned (rows of odd length on the other)
+                     ((2, 8, 523, 64), [0, 1, 3, 2]), ((2, 8, 64, 523), [0, 1, 3, 2]), ((130, 257), [1, 0]), ((3, 77, 68), [0, 2, 1]),((7,), [0]), ((5, 9), [1, 0]), ((5, 9), None), ((2, 3, 4), [2, 0, 1]), ((1, 1, 5), [2, 1, 0]),
                      ((2, 3, 4, 5, 6), [4, 2, 0, 3, 1]), ((1, 128, 32, 64), [0, 2, 1, 3]), ((1, 8, 640, 64), [0, 1, 3, 2]),
                      ((2, 2, 2, 2, 2, 2, 2, 2), [7, 6, 5, 4, 3, 2, 1, 0]), ((100, 1), [1, 0])]:
         x = rand(sh, np.float32, seed=6)
@@ -449,7 +457,9 @@ def test_concat(dtype):
 @pytest.mark.parametrize("dtype", [np.float32, np.int64, np.float16])
 def test_expand(dtype):
     cases = [((3, 1), [3, 4]), ((1,), [2, 3]), ((), [2, 2]), ((1, 8, 1, 5, 64), [1, 8, 4, 5, 64]), ((2, 1, 6), [1, 1, 1]),
-             ((3, 4), [2, 3, 4]), ((1, 1, 7, 12), [1, 32, 7, 12]), ((5,), [5]), ((1, 3), [4, 1, 1])]
+             ((3, 4), [2, 3, 4]), ((1, 1, 7, 12), [1, 32, 7, 12]), ((5,), [5]), ((1, 3), [4, 1, 1]),
+             # one broadcast block between dense parts: the load-once / store-R-times kernel
+             ((16, 8, 1, 37, 64), [16, 8, 4, 37, 64]), ((3, 1, 1, 8), [3, 5, 2, 8]), ((3, 1, 2, 1, 8), [3, 5, 2, 2, 8])]
     for sh, tgt in cases:
         x = rand(sh, dtype, seed=3)
         got = to_np(K.expand(dev(x), tgt))
@@ -552,3 +562,43 @@ def test_matmul_tensor_core_3xtf32(case):
     wi = torch.randint(-8, 9, (k, n), device="cuda").float()
     a, w = ai, wi
     assert torch.equal(run(None), (ai.double() @ wi.double()).float())
+
+
+NT_CASES = [(512, 4, 523, 64), (7, 1, 100, 64), (5, 2, 33, 16), (3, 3, 70, 128), (9, 8, 45, 32), (4, 4, 31, 4), (2, 4, 1000, 20),
+            # shapes outside the warp-per-32-rows kernel: K not a multiple of 4, K > 128, M > 8
+            (3, 2, 50, 30), (2, 3, 40, 300), (2, 20, 35, 64)]
+
+
+@pytest.mark.parametrize("case", NT_CASES)
+def test_matmul_nt(case):
+    """A x B^T with B stored [n, k]: equals MatMul(A, Transpose(B)) of the reference path within the MatMul bar."""
+    batch, m, n, k = case
+    a = rng(11).normal(0, 1.0, size=(batch, m, k)).astype(np.float32)
+    b = rng(12).normal(0, 1.0, size=(batch, n, k)).astype(np.float32)
+    want = np.matmul(a.astype(np.float64), np.swapaxes(b, 1, 2).astype(np.float64))
+    got = to_np(K.matmul_nt(dev(a), dev(b)))
+    assert got.shape == want.shape
+    assert max_rel_to_scale(got, want) <= 1e-4, case
+    # same numbers as the two-op path (Transpose copy, then MatMul) up to fp32 reassociation
+    two_op = to_np(K.matmul(dev(a), K.transpose(dev(b), [0, 2, 1])))
+    assert max_rel_to_scale(got, two_op.astype(np.float64)) <= 1e-5
+
+
+def test_strided_copy_views():
+    """Dense copy of strided / broadcast / permuted views of one buffer, against numpy's as_strided."""
+    from numpy.lib.stride_tricks import as_strided
+    base = rand((6 * 8 * 10 * 12,), np.float32, seed=13)
+    cases = [((6, 8, 10, 12), (960, 120, 12, 1)),            # identity
+             ((6, 8, 4, 10, 12), (960, 120, 0, 12, 1)),      # repeat a middle dim
+             ((6, 12, 10, 8), (960, 1, 12, 120)),            # permuted, inner dim moves
+             ((6, 8, 4, 12, 10), (960, 120, 0, 1, 12)),      # repeat + inner transpose
+             ((3, 6, 8), (0, 960, 120)),                     # leading broadcast, strided inner
+             ((5,), (0,)), ((), ()), ((6, 0, 3), (960, 1, 1))]
+    for shape, strides in cases:
+        got = to_np(K.strided_copy(dev(base), shape, strides))
+        want = as_strided(base, shape=shape, strides=[4 * s for s in strides]) if len(shape) else base[:1].reshape(())
+        assert got.shape == tuple(shape)
+        assert np.array_equal(got, want), (shape, strides)
+    b64 = rand((4 * 6 * 8,), np.int64, seed=14)
+    got = to_np(K.strided_copy(dev(b64), (8, 4, 6), (1, 48, 8)))
+    assert np.array_equal(got, np.ascontiguousarray(as_strided(b64, shape=(8, 4, 6), strides=(8, 384, 64))))

@@ -1,0 +1,146 @@
+"""Deferred layout ops in the host runtime: Expand / Transpose / Reshape chains that stay views.
+
+The runtime keeps the result of Expand and Transpose as a strided view of the producer's buffer and copies it
+out only when a consumer needs dense data; MatMul reads a transposed and / or batch-broadcast right operand
+straight from the view.  The reference copies in each of those ops (backend/expand.rs:49-216,
+backend/transpose.rs:44-178, backend/reshape.rs:27-73), so every graph here must give the same bytes (layout
+ops) or the same numbers within the MatMul bar (rel 1e-4) as the op-by-op CPU interpreter.
+"""
+import numpy as np
+import pytest
+
+from oracle import graph_cpu
+from rmlk_b200.graphspec import GraphSpec
+
+pytestmark = pytest.mark.gpu
+
+
+def run_both(spec, feeds):
+    from rmlk_b200.runtime import ModelInstance
+    inst = ModelInstance(spec.to_runtime())
+    for k, v in feeds.items():
+        inst.set_input(k, v)
+    inst.launch()
+    got = {o: inst.read(o) for o in spec.outputs}
+    want = graph_cpu.run_graph(spec, feeds)
+    return got, want, inst
+
+
+def i64(*v):
+    return np.array(v, dtype=np.int64)
+
+
+def gqa_graph(B, KV, G, T, D, S):
+    """scores = q x K_expanded^T, ctx = softmax(scores) x V_expanded, with the export's GQA pattern."""
+    g = GraphSpec()
+    g.input("q", np.float32, [B, KV * G, S, D])
+    g.input("k", np.float32, [B, KV, T, D])
+    g.input("v", np.float32, [B, KV, T, D])
+    g.const("ax2", i64(2))
+    g.const("five", i64(B, KV, G, T, D))
+    g.const("four", i64(B, KV * G, T, D))
+    for name in ("k", "v"):
+        u = g.op("Unsqueeze", [name, "ax2"], f"{name}_u")
+        e = g.op("Expand", [u, "five"], f"{name}_e")
+        g.op("Reshape", [e, "four"], f"{name}_r")
+    kt = g.op("Transpose", ["k_r"], "k_t", perm=[0, 1, 3, 2])
+    s = g.op("MatMul", ["q", kt], "scores")
+    p = g.op("Softmax", [s], "probs", axis=-1)
+    g.op("MatMul", [p, "v_r"], "ctx")
+    g.output("scores")
+    g.output("ctx")
+    return g
+
+
+@pytest.mark.parametrize("shape", [(2, 2, 4, 37, 16, 1), (3, 8, 4, 130, 64, 1), (2, 2, 2, 33, 64, 3), (1, 1, 8, 19, 32, 1), (2, 4, 1, 21, 8, 2),
+                                   (2, 2, 4, 40, 64, 5), (1, 2, 4, 50, 20, 1), (1, 2, 4, 64, 256, 1)])
+def test_gqa_attention_reads_the_cache_in_place(cuda, shape):
+    B, KV, G, T, D, S = shape
+    rng = np.random.default_rng(5)
+    feeds = {"q": rng.standard_normal((B, KV * G, S, D), dtype=np.float32), "k": rng.standard_normal((B, KV, T, D), dtype=np.float32),
+             "v": rng.standard_normal((B, KV, T, D), dtype=np.float32)}
+    spec = gqa_graph(B, KV, G, T, D, S)
+    got, want, inst = run_both(spec, feeds)
+    for o in ("scores", "ctx"):
+        assert got[o].shape == want[o].shape
+        assert np.max(np.abs(got[o] - want[o])) <= 1e-4 * np.max(np.abs(want[o])), (o, shape)
+    if G * S <= 8 and D <= 128 and D % 4 == 0:
+        # Unsqueeze / Expand / Reshape / Transpose launch nothing; two MatMuls and a Softmax remain
+        assert inst.last_launches == 3, inst.last_launches
+
+
+def test_views_are_copied_out_for_dense_consumers(cuda):
+    """Transpose -> Add, Expand -> Mul, Expand -> Transpose -> Reshape -> Neg: one copy per chain, exact bytes."""
+    rng = np.random.default_rng(6)
+    g = GraphSpec()
+    g.input("x", np.float32, [4, 6, 10, 12])
+    g.input("y", np.float32, [4, 1, 10, 1])
+    g.const("tgt", i64(4, 5, 10, 12))
+    g.const("flat", i64(4, -1))
+    t = g.op("Transpose", ["x"], "xt", perm=[0, 2, 3, 1])
+    g.op("Add", [t, t], "a")
+    e = g.op("Expand", ["y", "tgt"], "ye")
+    g.op("Mul", [e, e], "m")
+    et = g.op("Transpose", [e], "yet", perm=[3, 1, 0, 2])
+    r = g.op("Reshape", [et, "flat"], "yr")
+    g.op("Neg", [r], "n")
+    tt = g.op("Transpose", [t], "xtt", perm=[0, 3, 1, 2])  # back to the original order
+    g.op("Sqrt", [g.op("Mul", [tt, tt], "sq")], "back")
+    for o in ("a", "m", "n", "back"):
+        g.output(o)
+    feeds = {"x": rng.standard_normal((4, 6, 10, 12), dtype=np.float32), "y": rng.standard_normal((4, 1, 10, 1), dtype=np.float32)}
+    got, want, _ = run_both(g, feeds)
+    for o in g.outputs:
+        assert got[o].shape == want[o].shape, o
+        assert np.array_equal(got[o], want[o]), o
+
+
+def test_view_as_graph_output_and_regrouped_views(cuda):
+    """A Transpose / Expand that is itself a graph output is dense; a Reshape that cuts through the permuted
+    dims forces the copy before the next Transpose; Shape of a view needs no copy."""
+    rng = np.random.default_rng(7)
+    g = GraphSpec()
+    g.input("x", np.float32, [6, 8, 10])
+    g.const("tgt", i64(3, 6, 8, 10))
+    g.const("r1", i64(10, 4, 12))
+    g.const("r2", i64(-1, 16))
+    g.op("Transpose", ["x"], "t_out", perm=[2, 0, 1])       # graph output
+    g.op("Expand", ["x", "tgt"], "e_out")                   # graph output
+    t = g.op("Transpose", ["x"], "t", perm=[2, 1, 0])       # [10, 8, 6] view
+    r = g.op("Reshape", [t, "r1"], "r")                     # [10, 4, 12]: cuts through the permuted dims
+    g.op("Transpose", [r], "rt", perm=[1, 2, 0])            # needs the copy first
+    g.op("Reshape", ["rt", "r2"], "rt2")
+    g.op("Shape", [t], "t_shape")
+    g.op("Flatten", [t], "t_flat", axis=2)
+    g.op("Relu", ["t_flat"], "relu")
+    for o in ("t_out", "e_out", "rt", "rt2", "t_shape", "relu"):
+        g.output(o)
+    feeds = {"x": rng.standard_normal((6, 8, 10), dtype=np.float32)}
+    got, want, _ = run_both(g, feeds)
+    for o in g.outputs:
+        assert got[o].shape == want[o].shape, o
+        assert np.array_equal(got[o], want[o]), o
+
+
+def test_transposed_weight_and_broadcast_batch(cuda):
+    """MatMul(x, Transpose(W)) with a 2-D W shared by the whole batch, at sizes on both sides of the A x B^T
+    kernel's limits, and a right operand broadcast over an outer batch dim (cannot be folded: copied)."""
+    rng = np.random.default_rng(8)
+    for (b, m, k, n) in [(1, 4, 64, 300), (2, 2, 128, 77), (1, 3, 20, 50), (4, 16, 64, 200), (1, 1, 132, 40)]:
+        g = GraphSpec()
+        g.input("x", np.float32, [b, m, k])
+        g.input("w", np.float32, [n, k])
+        g.op("MatMul", ["x", g.op("Transpose", ["w"], "wt", perm=[1, 0])], "y")
+        g.output("y")
+        feeds = {"x": rng.standard_normal((b, m, k), dtype=np.float32), "w": rng.standard_normal((n, k), dtype=np.float32)}
+        got, want, _ = run_both(g, feeds)
+        assert np.max(np.abs(got["y"] - want["y"])) <= 1e-4 * np.max(np.abs(want["y"])), (b, m, k, n)
+    g = GraphSpec()
+    g.input("a", np.float32, [3, 5, 2, 40])
+    g.input("w", np.float32, [1, 5, 40, 24])
+    g.const("tgt", i64(3, 5, 40, 24))
+    g.op("MatMul", ["a", g.op("Expand", ["w", "tgt"], "we")], "y")
+    g.output("y")
+    feeds = {"a": rng.standard_normal((3, 5, 2, 40), dtype=np.float32), "w": rng.standard_normal((1, 5, 40, 24), dtype=np.float32)}
+    got, want, _ = run_both(g, feeds)
+    assert np.max(np.abs(got["y"] - want["y"])) <= 1e-4 * np.max(np.abs(want["y"]))
