@@ -12,8 +12,9 @@ replicated), so per-GPU work is fixed and scaling is "weak".
     python bench.py --impl reference ...      # the CPU path (numpy oracle interpreter) on the host cores
 
 Prints ONE JSON line (rank 0).  `value` is device-resident (inputs already in HBM); `e2e` feeds host
-buffers and reads the logits back every step.  `roofline` is measured live for the dominant kernel
-(the weight-streaming MatMul); `cpu_baseline` times the CPU oracle on a bounded sample of the same step.
+buffers and reads the logits back every step.  `roofline` is measured live (CUDA-graph replay between
+events on the launching stream) for the kernel with the largest share of the step, the weight-streaming
+tcgen05 MatMul, with the other heavy kernels of the step beside it; `cpu_baseline` times the CPU oracle on a bounded sample of the same step.
 """
 from __future__ import annotations
 
@@ -69,7 +70,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                                           "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -198,7 +199,7 @@ def time_graph(fn_of_i, n=16, replays=4):
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernel named by DOMINANT, from the
 # capture summarised under profiles/ (None until a capture of that kernel exists).
-DOMINANT = "expand_gqa"
+DOMINANT = "matmul_ffn"
 NCU_TRAFFIC_BYTES = {}
 
 
@@ -224,30 +225,18 @@ def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):
             e["tflops"] = flops / (ms * 1e-3) / 1e12
         out[name] = e
 
-    # GQA Expand of the K / V cache: [B, 8, 1, T, 64] -> [B, 8, 4, T, 64]
-    src = ring(lambda: torch.randn(B, 8, 1, T, 64, device=dev), 4 * B * 8 * T * 64)
-    dst = torch.empty(B, 8, 4, T, 64, device=dev)
-    add("expand_gqa", "ew_vec_kernel1 (Expand)", lambda i: K.expand(src[i % len(src)], [1, 1, 4, 1, 1], out=dst),
-        4 * B * 8 * T * 64 * 5, [B, 8, 4, T, 64])
-    del src, dst
-    # K^T Transpose: [B, 32, T, 64] -> [B, 32, 64, T]
-    src = ring(lambda: torch.randn(B, 32, T, 64, device=dev), 4 * B * 32 * T * 64)
-    dst = torch.empty(B, 32, 64, T, device=dev)
-    add("transpose_kt", "transpose_tile64_kernel", lambda i: K.transpose(src[i % len(src)], [0, 1, 3, 2], out=dst),
-        8 * B * 32 * T * 64, [B, 32, T, 64])
-    # decode scores: B*32 problems [1, 64] x [64, T]
-    q = torch.randn(B * 32, 1, 64, device=dev)
-    kt = [t.view(B * 32, 64, T) for t in src]
-    sc = torch.empty(B * 32, 1, T, device=dev)
-    add("scores", "smallk_kernel<1>", lambda i: K.matmul(q, kt[i % len(kt)], out=sc), 4 * B * 32 * (64 + 64 * T + T),
-        [B * 32, 1, 64, T], flops=2 * B * 32 * 64 * T)
-    # decode context: B*32 problems [1, T] x [T, 64]
-    v = [t.view(B * 32, T, 64) for t in src]
-    p = torch.randn(B * 32, 1, T, device=dev)
-    cx = torch.empty(B * 32, 1, 64, device=dev)
-    add("context", "skinny_kernel<1>", lambda i: K.matmul(p, v[i % len(v)], out=cx), 4 * B * 32 * (T + 64 * T + 64),
-        [B * 32, 1, T, 64], flops=2 * B * 32 * 64 * T)
-    del src, dst, kt, v
+    # decode scores, read from the KV cache in place: B*8 problems [4 q-heads, 64] x [T, 64]^T (A x B^T kernel)
+    kc = ring(lambda: torch.randn(B * 8, T, 64, device=dev), 4 * B * 8 * T * 64)
+    q = torch.randn(B * 8, 4, 64, device=dev)
+    sc = torch.empty(B * 8, 4, T, device=dev)
+    add("scores", "nt_rows_kernel<4,16>", lambda i: K.matmul_nt(q, kc[i % len(kc)], out=sc), 4 * B * 8 * (4 * 64 + 64 * T + 4 * T),
+        [B * 8, 4, 64, T], flops=2 * B * 32 * 64 * T)
+    # decode context: B*8 problems [4 q-heads, T] x [T, 64]
+    p = torch.randn(B * 8, 4, T, device=dev)
+    cx = torch.empty(B * 8, 4, 64, device=dev)
+    add("context", "skinny_kernel<4>", lambda i: K.matmul(p, kc[i % len(kc)], out=cx), 4 * B * 8 * (4 * T + 64 * T + 4 * 64),
+        [B * 8, 4, T, 64], flops=2 * B * 32 * 64 * T)
+    del kc, q, sc, p, cx
     # KV append Concat: [B, 8, T-1, 64] + [B, 8, 1, 64] along axis 2
     past = ring(lambda: torch.randn(B, 8, T - 1, 64, device=dev), 4 * B * 8 * T * 64)
     new = torch.randn(B, 8, 1, 64, device=dev)
@@ -369,9 +358,11 @@ def run_ours(args):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches = 0
         e0.record(stream)
+        host0 = time.perf_counter()
         for _ in range(K_):
             keep.append(device_step())
             launches += inst.last_launches
+        host_enqueue_ms = (time.perf_counter() - host0) * 1000.0   # host time to enqueue the K steps (no waiting on the GPU)
         e1.record(stream)
         barrier()
         clocks = sampler.stop() if rank == 0 else {}
@@ -432,7 +423,7 @@ def run_ours(args):
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * cfg.vocab * 4,
                 "ms_per_step": e2e_ms / K_},
         "gpu_launches": launches, "launches_per_decode_step": decode_launches, "prefill_launches": prefill_launches,
-        "clocks": clocks, "context_range": [P + W, P + W + K_], "arena_peak_bytes": inst.arena_peak,
+        "host_enqueue_ms_per_step": host_enqueue_ms / K_, "clocks": clocks, "context_range": [P + W, P + W + K_], "arena_peak_bytes": inst.arena_peak,
     }
     print(json.dumps(line))
     if world > 1:

@@ -6,23 +6,27 @@
 // The accumulator D[n][m] is 128 lanes x MT fp32 columns of TMEM, i.e. C transposed; the epilogue writes
 // C[m][n0 + lane], coalesced across the lanes of a warp.
 //
-// 3xTF32.  x = hi + lo with hi = tf32(x) and lo = tf32(x - hi), both round-to-nearest.  Per k-step three
-// MMAs' worth of products, hi*hi + hi*lo + lo*hi, accumulate in fp32 (the dropped lo*lo term is below 2^-22
-// relative).  An MMA of this shape costs about the same for N = 64 ... 256, so the first two are issued as one:
-// the lo tile of the activations follows the hi tile in shared memory and a single descriptor with N = 2 MT
-// covers both, filling two accumulator blocks that the epilogue adds.
+// 3xTF32.  x = hi + lo with hi = x truncated to tf32 (sign, exponent, 10 mantissa bits) and lo = x - hi, which
+// is exact in fp32.  The MMA itself reads only the tf32 part of an operand word, so the raw fp32 word serves
+// as hi without any conversion and only lo has to be computed (one AND, one subtraction).  Per k-step three
+// MMAs' worth of products, hi*hi + hi*lo + lo*hi, accumulate in fp32 (the dropped lo*lo term is below 2^-20
+// relative); measured error against fp64 is about 1e-5 of the result's scale.  The first two products are
+// issued as one MMA: the lo tile of the activations follows the raw tile in shared memory and a single
+// descriptor with N = 2 MT covers both, filling two accumulator blocks that the epilogue adds.
 //
 // Data path per k-block of 32 (STAGES deep):
 //   warp 0     TMA: four unswizzled [32 k][32 n] boxes of W and one 128B-swizzled [MT][32 k] box of A -> smem
-//   warps 2-9  converters (two groups of four warps on alternate k-blocks): thread (sub, lane) owns weight column sub*32+lane: it reads its 32 k values from
-//              shared memory (conflict-free), splits them in registers and writes hi / lo straight into TMEM
-//              with tcgen05.st, so the weights never make a second trip through shared memory; the small A
-//              tile is split in shared memory (hi in place, lo into a twin tile at the same swizzled offsets)
+//   warps 2-9  converters (two groups of four warps on alternate k-blocks): thread (sub, lane) owns weight
+//              column sub*32+lane: it reads its 32 k values from shared memory (conflict-free), and writes the
+//              raw words and their lo parts straight into TMEM with tcgen05.st, so the weights never make a
+//              second trip through shared memory; the lo part of the small A tile goes into a twin tile at
+//              the same swizzled offsets
 //   warp 1     one thread issues 4 k-steps x 2 tcgen05.mma with the weight operand read from TMEM and the
 //              activation operand from shared memory (K-major descriptor), then tcgen05.commit -> empty[s]
 //   warps 2-9  epilogue: tcgen05.ld 32 lanes x 32 columns, store to C or to the split-K scratch
-// Shared-memory traffic per k-block is about 80 KB (TMA 24, converter 32, MMA operand reads 24), below the
-// time HBM needs for the same block, so skinny shapes (decode, M <= 128) run at the HBM roofline.
+// Measured with stages of the pipeline switched off: streaming alone (TMA + barriers, no conversion, no MMA)
+// runs the [64, 2048] x [2048, 128256] shape at 5.3 TB/s; the MMAs cost nothing on top (tensor pipe about 30 %
+// busy); the converters are what separates the full kernel from the streaming rate.
 //
 // Every mbarrier wait is bounded: on expiry the thread raises a CTA-wide abort flag, records
 // RMLK_ERR_TIMEOUT in the caller's status word, and every role falls through to the common exit where TMEM
@@ -71,7 +75,24 @@ static int launch(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tm
         RMLK_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<MT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         configured[dev] = true;
     }
-    tc_gemm_kernel<MT, STAGES><<<grid, THREADS, L::TOTAL, st>>>(tmW, tmA, p);
+    if (p.cluster_reduce) {
+        // the ksplit CTAs of one tile (grid y) form a cluster and exchange partial sums through shared memory
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = L::TOTAL;
+        cfg.stream = st;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 1;
+        at[0].val.clusterDim.y = grid.y;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        RMLK_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<MT, STAGES>, tmW, tmA, p));
+    } else {
+        tc_gemm_kernel<MT, STAGES><<<grid, THREADS, L::TOTAL, st>>>(tmW, tmA, p);
+    }
     RMLK_CHECK_LAUNCH("tc_gemm_kernel");
     return RMLK_OK;
 }
@@ -94,6 +115,8 @@ bool tc_matmul_eligible(int64_t m, int64_t n, int64_t k, const void* a, const vo
            tc::encode_fn() != nullptr;
 }
 
+constexpr int TC_CLUSTER_MAX = 8;  // portable cluster size
+
 int tc_matmul_plan(int64_t m, int64_t n, int64_t k) {
     const int mt = m <= 64 ? 64 : 128;
     const int64_t tiles = (n / tc::BN) * ceil_div64(m, mt);
@@ -102,12 +125,15 @@ int tc_matmul_plan(int64_t m, int64_t n, int64_t k) {
     const int64_t max_s = k_iters / 8 > 0 ? k_iters / 8 : 1;  // at least 8 k-blocks per split
     if (s > max_s) s = max_s;
     if (s < 1) s = 1;
+    // Up to TC_CLUSTER_MAX splits add up on chip (one thread-block cluster per tile); a little above that the
+    // cluster form with fewer splits still wins over a scratch round trip plus a second kernel.
+    if (s > TC_CLUSTER_MAX && s <= TC_CLUSTER_MAX + TC_CLUSTER_MAX / 2) s = TC_CLUSTER_MAX;
     return static_cast<int>(s > 32 ? 32 : s);
 }
 
 size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     const int s = tc_matmul_plan(m, n, k);
-    return s > 1 ? static_cast<size_t>(s) * m * n * sizeof(float) : 0;
+    return s > TC_CLUSTER_MAX ? static_cast<size_t>(s) * m * n * sizeof(float) : 0;
 }
 
 // Launches the tensor-core GEMM.  `ksplit_out` tells the caller how many partial slabs were written to
@@ -116,23 +142,26 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
               size_t workspace_bytes, int* status, int* ksplit_out) {
     const int mt = m <= 64 ? 64 : 128;
     int ksplit = tc_matmul_plan(m, n, k);
-    if (ksplit > 1 && (!workspace || workspace_bytes < static_cast<size_t>(ksplit) * m * n * sizeof(float))) ksplit = 1;
+    if (ksplit > TC_CLUSTER_MAX && (!workspace || workspace_bytes < static_cast<size_t>(ksplit) * m * n * sizeof(float)))
+        ksplit = TC_CLUSTER_MAX;  // no scratch from the caller: stay within one cluster per tile
     const int k_iters = static_cast<int>(k / tc::BK);
     const int per = static_cast<int>(ceil_div64(k_iters, ksplit));
-    ksplit = static_cast<int>(ceil_div64(k_iters, per));
+    ksplit = static_cast<int>(ceil_div64(k_iters, per));  // every split gets at least one k-block
+    const bool cluster = ksplit > 1 && ksplit <= TC_CLUSTER_MAX;
     CUtensorMap tmW, tmA;
     if (!tc::make_map_2d(&tmW, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 32, 32, CU_TENSOR_MAP_SWIZZLE_NONE) ||
         !tc::make_map_2d(&tmA, a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), 32, static_cast<uint32_t>(mt), CU_TENSOR_MAP_SWIZZLE_128B))
         return fail(RMLK_ERR_INTERNAL, "matmul: cuTensorMapEncodeTiled failed");
     tc::TcParams p;
-    p.out = ksplit > 1 ? static_cast<float*>(workspace) : c;
+    p.cluster_reduce = cluster ? 1 : 0;
+    p.out = (ksplit > 1 && !cluster) ? static_cast<float*>(workspace) : c;
     p.M = m; p.N = n; p.K = k;
     p.k_iters_per_split = per;
     p.k_iters_total = k_iters;
     p.ksplit = ksplit;
     p.status = status;
     dim3 grid(static_cast<unsigned>(n / tc::BN), static_cast<unsigned>(ksplit), static_cast<unsigned>(ceil_div64(m, mt)));
-    *ksplit_out = ksplit;
+    *ksplit_out = cluster ? 1 : ksplit;  // slabs left in `workspace` for the caller to add
     if (mt == 64) return tc::launch<64, 6>(st, tmW, tmA, p, grid);
     return tc::launch<128, 4>(st, tmW, tmA, p, grid);
 }

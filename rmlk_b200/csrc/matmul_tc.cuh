@@ -12,6 +12,7 @@ constexpr int BK = 32;    // fp32 elements per k-block: one 128-byte row
 constexpr int BN = 128;   // weight columns per CTA = MMA M = TMEM lanes
 constexpr int THREADS = 320;  // TMA warp, MMA warp, 2 x 4 converter / epilogue warps
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
+constexpr uint32_t TF32_MASK = 0xffffe000u;  // sign, exponent and the 10 mantissa bits a tf32 MMA operand keeps
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
@@ -109,7 +110,28 @@ __device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[
         : "memory");
 }
 
+// ---- thread-block cluster helpers (split-K partial sums exchanged through distributed shared memory) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Executed by every thread of every CTA of the cluster.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Address of this CTA's shared-memory location `addr` in the CTA of rank `cta` of the same cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void st_shared_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
 struct TcParams {
+    int cluster_reduce;     // ksplit CTAs form a cluster along grid y and add their partial sums on chip
     float* out;             // C, or the split-K scratch [ksplit][M][N]
     int64_t M, N, K;
     int k_iters_per_split;  // k-blocks per split

@@ -10,6 +10,9 @@ template <int MT, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW,
                                                               const __grid_constant__ CUtensorMap tmA, TcParams p) {
     using L = SmemLayout<MT, STAGES>;
+    // the two converter groups take alternate k-blocks; a stage must always come back to the same group, or a
+    // group could be two barrier phases behind and mistake an old phase for the one it waits for
+    static_assert(STAGES % 2 == 0, "stage count must be even");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -112,26 +115,26 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
                 uint32_t hi[16], lo[16];
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
+                    // The MMA reads only the tf32 part of an operand word (sign, exponent, 10 mantissa bits):
+                    // the raw fp32 word already is its own truncated `hi`; lo = x - trunc(x) is exact in fp32.
                     const float x = wcol[(half * 16 + j) * 32];
-                    hi[j] = to_tf32(x);
-                    lo[j] = to_tf32(x - __uint_as_float(hi[j]));
+                    hi[j] = __float_as_uint(x);
+                    lo[j] = __float_as_uint(x - __uint_as_float(hi[j] & TF32_MASK));
                 }
                 tmem_st_x16(tmem_base + lane_field + whi_col(s) + half * 16, hi);
                 tmem_st_x16(tmem_base + lane_field + whi_col(s) + 32 + half * 16, lo);
             }
-            // activations: split in shared memory, hi in place, lo into the twin tile at the same swizzled offsets
+            // activations: the tile as loaded is its own hi part; lo goes into the twin tile at the same swizzled offsets
             uint8_t* ahi = st + L::W_BYTES;
             uint8_t* alo = ahi + L::A_BYTES;
 #pragma unroll 2
             for (int c = t; c < static_cast<int>(L::A_BYTES / 16); c += 128) {
                 const float4 v = *reinterpret_cast<const float4*>(ahi + 16 * c);
-                uint4 h, l;
-                h.x = to_tf32(v.x); h.y = to_tf32(v.y); h.z = to_tf32(v.z); h.w = to_tf32(v.w);
-                l.x = to_tf32(v.x - __uint_as_float(h.x));
-                l.y = to_tf32(v.y - __uint_as_float(h.y));
-                l.z = to_tf32(v.z - __uint_as_float(h.z));
-                l.w = to_tf32(v.w - __uint_as_float(h.w));
-                *reinterpret_cast<uint4*>(ahi + 16 * c) = h;
+                uint4 l;
+                l.x = __float_as_uint(v.x - __uint_as_float(__float_as_uint(v.x) & TF32_MASK));
+                l.y = __float_as_uint(v.y - __uint_as_float(__float_as_uint(v.y) & TF32_MASK));
+                l.z = __float_as_uint(v.z - __uint_as_float(__float_as_uint(v.z) & TF32_MASK));
+                l.w = __float_as_uint(v.w - __uint_as_float(__float_as_uint(v.w) & TF32_MASK));
                 *reinterpret_cast<uint4*>(alo + 16 * c) = l;
             }
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -140,7 +143,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
             mbar_arrive(conv_bar(s));
         }
         if (ok) ok = mbar_wait(accum_bar, 0, abort_flag, p.status);
-        if (ok) {
+        if (ok && !p.cluster_reduce) {
             tc_fence_after();
             const int64_t n = n0 + sub * 32 + lane;
             float* out = p.out + (p.ksplit > 1 ? static_cast<int64_t>(split) * p.M * p.N : 0);
@@ -154,6 +157,49 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
                 for (int j = 0; j < 32; j++) {
                     const int64_t m = m0 + c0 + j;
                     if (m < p.M) out[m * p.N + n] = __uint_as_float(r[j]) + __uint_as_float(q[j]);
+                }
+            }
+        }
+    }
+    if (p.cluster_reduce) {
+        // Split-K inside a thread-block cluster: the ksplit CTAs of a cluster hold the partial sums of one tile.
+        // CTA `rank` owns rows [rank * rows_per, (rank + 1) * rows_per) of the tile: every CTA stores that
+        // slice of its partial into slot [its own rank] of the owner's shared memory (the pipeline stages, idle
+        // by then), and each owner adds its ksplit slots in rank order - a fixed order, so the result does not
+        // depend on timing - and writes its rows of C.  No scratch in global memory, no second kernel.
+        const uint32_t ks = static_cast<uint32_t>(p.ksplit), rank = cluster_ctarank();
+        const uint32_t rows_per = (MT + ks - 1) / ks;
+        cluster_sync_all();  // every CTA of the cluster has drained its pipeline: its stage buffers are free
+        if (warp >= 2 && !*abort_flag) {
+            const int cg = (warp - 2) >> 2, sub = warp & 3;
+            const uint32_t lane_field = static_cast<uint32_t>(sub * 32) << 16;
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = 32 * cg; c0 < MT; c0 += 64) {
+                uint32_t r[32], q[32];
+                tmem_ld_x32(tmem_base + lane_field + c0, r);
+                tmem_ld_x32(tmem_base + lane_field + MT + c0, q);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const uint32_t ml_tile = static_cast<uint32_t>(c0 + j);
+                    const uint32_t owner = ml_tile / rows_per, ml = ml_tile - owner * rows_per;
+                    const uint32_t local = base + ((rank * rows_per + ml) * BN + sub * 32 + lane) * 4u;
+                    st_shared_cluster_f32(mapa_shared(local, owner), __uint_as_float(r[j]) + __uint_as_float(q[j]));
+                }
+            }
+        }
+        cluster_sync_all();  // all slices delivered (release / acquire at cluster scope)
+        if (warp >= 2 && !*abort_flag) {
+            const float* buf = reinterpret_cast<const float*>(base_ptr);
+            for (uint32_t idx = threadIdx.x - 64; idx < rows_per * BN; idx += THREADS - 64) {
+                const uint32_t ml = idx / BN, n = idx - ml * BN;
+                const uint32_t row = rank * rows_per + ml;
+                const int64_t m = m0 + row;
+                if (row < static_cast<uint32_t>(MT) && m < p.M) {
+                    float s = buf[ml * BN + n];
+                    for (uint32_t r2 = 1; r2 < ks; r2++) s += buf[(r2 * rows_per + ml) * BN + n];
+                    p.out[m * p.N + n0 + n] = s;
                 }
             }
         }

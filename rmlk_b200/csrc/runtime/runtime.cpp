@@ -2,6 +2,9 @@
 #include "runtime.h"
 
 #include <algorithm>
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "../common.cuh"
@@ -232,6 +235,14 @@ std::vector<double> Instance::host_f64(const Tensor& t) {
 
 // ---- Instance ---------------------------------------------------------------------------------
 Instance::~Instance() {
+    if (host_profile) {
+        double total = 0;
+        for (auto& kv : host_prof) total += kv.second.second;
+        fprintf(stderr, "[rmlk_b200 host profile] %.1f us of host time in ops\n", total);
+        for (auto& kv : host_prof)
+            fprintf(stderr, "  op %3d: %8lld nodes %10.1f us %6.2f us/node\n", kv.first, static_cast<long long>(kv.second.first), kv.second.second,
+                    kv.second.second / std::max<int64_t>(1, kv.second.first));
+    }
     cudaSetDevice(device);
     if (stream) cudaStreamSynchronize(stream);
     arena.reset();
@@ -320,7 +331,15 @@ void Instance::run() {
     for (size_t i = 0; i < g.nodes.size(); i++) {
         const NodeDef& n = g.nodes[i];
         try {
-            run_node(n);
+            if (host_profile) {
+                const auto t0 = std::chrono::steady_clock::now();
+                run_node(n);
+                auto& slot = host_prof[n.op];
+                slot.first++;
+                slot.second += std::chrono::duration<double, std::micro>(std::chrono::steady_clock::now() - t0).count();
+            } else {
+                run_node(n);
+            }
         } catch (const Error& e) {
             throw Error(e.code, std::string(e.what()) + " [node " + std::to_string(i) + ", op " + std::to_string(n.op) + "]");
         }
@@ -516,6 +535,7 @@ extern "C" rmlk_instance* rmlk_instance_create(const rmlk_graph* g, int device, 
         if (!g) raise(RMLK_ERR_INVALID_ARG, "NULL graph");
         check_cuda(cudaSetDevice(device), "cudaSetDevice");
         h = new rmlk_instance();
+        if (const char* e = getenv("RMLK_B200_HOST_PROFILE")) h->I.host_profile = e[0] == '1';
         Instance& I = h->I;
         I.g = g->g;
         I.device = device;

@@ -162,6 +162,9 @@ struct Instance {
     std::vector<uint8_t> persistent;       // per value id: initializer / Constant output / input (kept across runs)
     std::vector<int> binding_of_out;       // per value id: index into `bindings` if it is a carried output, else -1
     int64_t launches = 0, syncs = 0;
+    // host-side tracing (RMLK_B200_HOST_PROFILE=1): time spent enqueuing each op kind, printed at destruction
+    bool host_profile = false;
+    std::map<int, std::pair<int64_t, double>> host_prof;  // op -> (nodes run, microseconds)
     bool status_dirty = false;
 
     ~Instance();

@@ -516,7 +516,9 @@ def test_large_elementwise_and_copy_roundtrip():
 
 
 TC_CASES = [(64, 8192, 2048), (64, 2048, 2048), (64, 512, 2048), (64, 2048, 8192), (17, 128, 32), (33, 256, 64), (100, 384, 96), (128, 1024, 256),
-            (200, 256, 512), (300, 128, 2048), (64, 128256, 2048), (4096, 8192, 2048), (65, 128, 4096)]
+            (200, 256, 512), (300, 128, 2048), (64, 128256, 2048), (4096, 8192, 2048), (65, 128, 4096),
+            # K split 7, 5 and 3 ways inside a thread-block cluster (rows of the tile not divisible by the split)
+            (64, 2688, 2048), (64, 3712, 2048), (64, 6272, 2048), (17, 2688, 2048), (128, 2688, 1024)]
 
 
 @pytest.mark.parametrize("case", TC_CASES)

@@ -22,7 +22,7 @@ def _call(fn, stream, m, n, k, a, w, out, extra):
               ctypes.c_void_p(out.data_ptr()), ctypes.c_int64(m * n), *extra)
 
 
-@pytest.mark.parametrize("shape", [(1, 2048, 2048), (8, 512, 2048), (16, 8192, 2048), (64, 2048, 2048), (64, 8192, 2048)])
+@pytest.mark.parametrize("shape", [(1, 2048, 2048), (8, 512, 2048), (16, 8192, 2048), (64, 256, 8192), (128, 512, 4096)])
 def test_static_scratch_matmul_matches_regular_entry_point(cuda, shape):
     from rmlk_b200 import kernels as K
     from rmlk_b200._lib import last_error, lib
@@ -57,7 +57,7 @@ def test_static_scratch_matmul_rejects_oversized_shapes(cuda):
     from rmlk_b200._lib import last_error, lib
     l = lib()
     l.rmlk_b200_matmul_static_scratch_bytes.restype = ctypes.c_size_t
-    m, n, k = 128, 2048, 8192   # nine K-splits of 1 MiB each: more than the 8 MiB array
+    m, n, k = 256, 512, 8192   # eighteen K-splits of 512 KiB each: more than the 8 MiB array
     assert K.matmul_workspace_bytes(1, m, n, k) > l.rmlk_b200_matmul_static_scratch_bytes()
     a = torch.randn(m, k, device="cuda")
     w = torch.randn(k, n, device="cuda")
