@@ -200,7 +200,7 @@ def time_graph(fn_of_i, n=16, replays=4):
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernel named by DOMINANT, from the
 # capture summarised under profiles/ (None until a capture of that kernel exists).
 DOMINANT = "matmul_ffn"
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {"matmul_ffn": 67_684_352 + 1_249_792}   # profiles/tc_gemm_kernel_ffn_m64.md
 
 
 def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):

@@ -115,7 +115,20 @@ bool tc_matmul_eligible(int64_t m, int64_t n, int64_t k, const void* a, const vo
            tc::encode_fn() != nullptr;
 }
 
-constexpr int TC_CLUSTER_MAX = 8;  // portable cluster size
+// Largest split-K that is added up inside one thread-block cluster.  Each CTA needs a whole SM (198 KB of
+// shared memory), and clusters of 8 such CTAs did not all become resident at once on a B200 (128 CTAs ran as
+// two waves, twice the time), while clusters of up to 4 did; wider splits go through the scratch buffer.
+// RMLK_B200_TC_CLUSTER_MAX=1..8 overrides the limit; 1 sends every split through the scratch buffer.
+static int tc_cluster_max() {
+    static int v = 0;
+    if (v == 0) {
+        const char* e = getenv("RMLK_B200_TC_CLUSTER_MAX");
+        int x = e ? atoi(e) : 4;
+        v = x < 1 ? 1 : x > 8 ? 8 : x;
+    }
+    return v;
+}
+#define TC_CLUSTER_MAX (tc_cluster_max())
 
 int tc_matmul_plan(int64_t m, int64_t n, int64_t k) {
     const int mt = m <= 64 ? 64 : 128;
