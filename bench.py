@@ -119,6 +119,13 @@ def cpu_decode_sample(cfg, batch, context, steps, seed=0):
     from oracle import graph_cpu
     from rmlk_b200 import llama
     threads = os.cpu_count() or 1
+    # use every host core even when a launcher exported OMP_NUM_THREADS=1 (torchrun does)
+    torch.set_num_threads(threads)
+    try:
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=threads)
+    except Exception:
+        pass
     torch.manual_seed(seed)
     w = {}
     for name, shape in llama.weight_shapes(cfg).items():

@@ -49,21 +49,24 @@ def _init():
     _ctx_ready = True
 
 
-def _function(module: str, symbol: str):
+def _function(module: str, symbol: str, ptx_dir: str):
     d = _drv()
     _init()
-    if module not in _modules:
-        with open(os.path.join(PTX_DIR, module + ".ptx"), "rb") as f:
+    key = (ptx_dir, module)
+    if key not in _modules:
+        with open(os.path.join(ptx_dir, module + ".ptx"), "rb") as f:
             ptx = f.read() + b"\0"
-        _modules[module] = _chk(d.cuModuleLoadData(ptx))
-    return _chk(d.cuModuleGetFunction(_modules[module], symbol.encode()))
+        _modules[key] = _chk(d.cuModuleLoadData(ptx))
+    return _chk(d.cuModuleGetFunction(_modules[key], symbol.encode()))
 
 
-def run(plan, time_iters: int = 0):
+def run(plan, time_iters: int = 0, ptx_dir: str = None):
     """Execute one plan on the GPU; returns plan.out.  With time_iters > 0 also returns the mean
-    launch time in milliseconds (CUDA events on the default stream)."""
+    launch time in milliseconds (CUDA events on the default stream).  `ptx_dir` selects another set of
+    PTX modules with the same entry points (the symbol-compatible kernels of rmlk_b200/tier1) to be driven
+    through the same launch contract."""
     d = _drv()
-    fn = _function(plan.module, plan.symbol)
+    fn = _function(plan.module, plan.symbol, ptx_dir or PTX_DIR)
     dev_bufs = []
     holders = []
     ptr_vals = []

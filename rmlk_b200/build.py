@@ -72,5 +72,34 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+TIER1 = os.path.join(HERE, "tier1")
+TIER1_PTX = os.path.join(TIER1, "ptx")
+
+
+def build_tier1(force: bool = False) -> str:
+    """PTX of the symbol-compatible kernels (rmlk_b200/tier1/*.cu), one module per reference module, built the
+    way the reference's cuda/build.rs builds its own files: plain nvcc, compute capability 10.0, include
+    path = the headers directory, no extra flags."""
+    os.makedirs(TIER1_PTX, exist_ok=True)
+    hdr = max(os.path.getmtime(h) for h in glob.glob(os.path.join(TIER1, "headers", "*.cuh")))
+    todo = []
+    for src in sorted(glob.glob(os.path.join(TIER1, "*.cu"))):
+        out = os.path.join(TIER1_PTX, os.path.basename(src)[:-3] + ".ptx")
+        if force or not os.path.exists(out) or os.path.getmtime(out) < max(os.path.getmtime(src), hdr):
+            todo.append((src, out))
+
+    def one(job):
+        src, out = job
+        r = subprocess.run([NVCC, "-ptx", "-arch=sm_100", "-I", os.path.join(TIER1, "headers"), src, "-o", out], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"nvcc -ptx failed for {src}:\n{r.stdout}\n{r.stderr}")
+
+    if todo:
+        with cf.ThreadPoolExecutor(max_workers=min(len(todo), os.cpu_count() or 4)) as ex:
+            list(ex.map(one, todo))
+    return TIER1_PTX
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_tier1(force="--force" in sys.argv))

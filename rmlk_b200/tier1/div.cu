@@ -1,0 +1,18 @@
+// Tier-1 (symbol-compatible) kernels: entry points of the reference module cuda/src/ptx/div.cu.
+#include "t1_common.cuh"
+// Integer division by zero has no defined result in the reference either; these kernels return 0.
+
+#define T1_BINARY(T, O, NAME, EXPR)                                                                                  \
+    struct NAME##_op {                                                                                               \
+        __device__ __forceinline__ O operator()(T x, T y) const { return EXPR; }                                     \
+    };                                                                                                               \
+    extern "C" __global__ void NAME(const size_t num_elems, const size_t rank, const size_t* info, const T* a, const T* b, \
+                                    O* out) {                                                                        \
+        t1::binary_body(num_elems, rank, info, a, b, out, NAME##_op());                                              \
+    }
+
+T1_BINARY(__half, __half, div_fwd_f16, x / y)
+T1_BINARY(float, float, div_fwd_f32, x / y)
+T1_BINARY(double, double, div_fwd_f64, x / y)
+T1_BINARY(int32_t, int32_t, div_fwd_i32, y == 0 ? 0 : x / y)
+T1_BINARY(int64_t, int64_t, div_fwd_i64, y == 0 ? 0 : x / y)
