@@ -273,6 +273,35 @@ RMLK_API int rmlk_b200_matmul_static(rmlk_stream_t stream, int dtype, int64_t ba
 RMLK_API size_t rmlk_b200_matmul_static_scratch_bytes(void);
 RMLK_API size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k);
 
+/* ---- op chains as one launch ----------------------------------------------------------------------------------
+ * The reference has no fused ops: an exported decoder graph reaches it as single ops, each dispatched to its own
+ * backend (runtime/src/providers/cuda/backend/mod.rs:121-161).  The four entry points below compute exactly what
+ * those chains compute (same fp32 expressions in the same order; the row sums may associate differently), f32 only.
+ * The host runtime substitutes them when it recognises the chain; callers may also use them directly. */
+
+/* RMSNorm as exported: Pow(x, exponent) -> ReduceMean(last axis, keepdims) -> Add(eps) -> Sqrt -> Div(x, .) -> Mul(., w).
+ * x, out: [rows, cols] dense; weight: [cols].  Replaces one launch each of backend/pow.rs:123-132,
+ * reduce_mean.rs:47-310, add.rs, sqrt.rs, div.rs, mul.rs. */
+RMLK_API int rmlk_b200_rmsnorm(rmlk_stream_t stream, int dtype, int64_t rows, int64_t cols, const void* x, float exponent, float eps,
+                      const void* weight, void* out);
+
+/* Rotary embedding as exported: Add(Mul(x, cos), Mul(Concat(Neg(x[..., D/2:]), x[..., :D/2]), sin)).  shape4 = output dims
+ * [d0, d1, d2, D] (dense output); *_strides = element strides of x / cos / sin per output dim, 0 to broadcast (x may be
+ * a permuted view).  Replaces backend/mul.rs (x2), slice.rs:49-464 (x2), neg.rs, concat.rs:28-198, add.rs. */
+RMLK_API int rmlk_b200_rope(rmlk_stream_t stream, int dtype, const int64_t* shape4, const int64_t* x_strides,
+                   const int64_t* cos_strides, const int64_t* sin_strides, const void* x, const void* cosv, const void* sinv,
+                   void* out);
+
+/* SwiGLU gate as exported: Mul(Mul(gate, Sigmoid(gate)), up), n elements each.  Replaces backend/sigmoid.rs (cuDNN
+ * activation, kernels/activation.rs:6-39) and backend/mul.rs (x2). */
+RMLK_API int rmlk_b200_swiglu(rmlk_stream_t stream, int dtype, int64_t n, const void* gate, const void* up, void* out);
+
+/* Attention probabilities as exported: Softmax(Add(Mul(scores, scale), mask), last axis).  scores / out: [d0, d1, d2, cols]
+ * dense (lead3 = d0, d1, d2); mask rows are dense, mask_strides3 = its element strides over d0, d1, d2 (0 = broadcast);
+ * cols <= 2048.  Replaces backend/mul.rs, add.rs and softmax.rs:31-158 (cudnnSoftmaxForward). */
+RMLK_API int rmlk_b200_scale_mask_softmax(rmlk_stream_t stream, int dtype, const int64_t* lead3, int64_t cols,
+                                 const int64_t* mask_strides3, float scale, const void* scores, const void* mask, void* out);
+
 #ifdef __cplusplus
 }
 #endif

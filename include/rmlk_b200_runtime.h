@@ -100,6 +100,14 @@ RMLK_API int rmlk_instance_read(rmlk_instance* inst, const char* name, void* dst
  * the device (0 when all small operands had host mirrors). */
 RMLK_API int64_t rmlk_instance_last_launches(const rmlk_instance* inst);
 RMLK_API int64_t rmlk_instance_last_syncs(const rmlk_instance* inst);
+/* Op chains that run as one launch (RMSNorm, rotary embedding, SwiGLU gate, scale + mask + softmax; see
+ * rmlk_b200_rmsnorm ... in rmlk_b200.h): chains recognised in the graph, and, since the instance was created, how
+ * often a chain ran fused / fell back to its single ops because a run's tensors did not meet the fused kernel's
+ * conditions.  The reference executes every node on its own (runtime/src/core/instance.rs:100-112).
+ * RMLK_B200_NO_FUSION=1 in the environment turns the substitution off. */
+RMLK_API int64_t rmlk_instance_fused_chains(const rmlk_instance* inst);
+RMLK_API int64_t rmlk_instance_fused_runs(const rmlk_instance* inst);
+RMLK_API int64_t rmlk_instance_fused_fallbacks(const rmlk_instance* inst);
 /* High-water mark of the intermediate arena, in bytes. */
 RMLK_API size_t rmlk_instance_arena_peak(const rmlk_instance* inst);
 

@@ -1,0 +1,240 @@
+// Fused forms of op chains that an exported decoder graph spells out op by op.  Each kernel evaluates the same
+// fp32 expressions, in the same order, as the chain of single-op kernels it stands for (same libm calls, no
+// FMA contraction across op boundaries), so results agree with the op-by-op path to the last bit except for
+// the summation order inside the row reductions.  The host runtime substitutes them when it recognises the
+// chain (runtime/ops.cpp); the single-op entry points stay the reference-facing interface.
+//
+//   rmsnorm             Pow(x, 2) -> ReduceMean(last axis, keepdims) -> Add(eps) -> Sqrt -> Div(x, .) -> Mul(., w)
+//   rope                Mul(x, cos) + Mul(Concat(Neg(x[..., D/2:]), x[..., :D/2]), sin)
+//   swiglu              Mul(Mul(g, Sigmoid(g)), u)
+//   scale_mask_softmax  Softmax(Add(Mul(s, scale), mask), last axis)
+//
+// Reference backends replaced per launch: backend/pow.rs, reduce_mean.rs, add.rs, sqrt.rs, div.rs, mul.rs;
+// mul.rs, slice.rs (x2), neg.rs, concat.rs, add.rs; sigmoid.rs, mul.rs (x2); mul.rs, add.rs, softmax.rs
+// (all under runtime/src/providers/cuda/backend/).
+#include "common.cuh"
+
+namespace rmlk {
+
+__device__ __forceinline__ double warp_sum_d(double v) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_sum_f(float v) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max_f(float v) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// One CTA of 256 threads per row.  The squares are summed in double, as the ReduceMean kernel does.
+__global__ void __launch_bounds__(256) rmsnorm_f32_kernel(int64_t cols, float exponent, float eps, const float* __restrict__ x,
+                                                         const float* __restrict__ w, float* __restrict__ out) {
+    __shared__ double part[8];
+    const float* row = x + static_cast<int64_t>(blockIdx.x) * cols;
+    float* dst = out + static_cast<int64_t>(blockIdx.x) * cols;
+    double acc = 0.0;
+    for (int64_t c = threadIdx.x; c < cols; c += 256) acc += static_cast<double>(powf(row[c], exponent));
+    acc = warp_sum_d(acc);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    double total = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) total += part[i];
+    const float mean = static_cast<float>(total / static_cast<double>(cols));
+    const float sd = sqrtf(__fadd_rn(mean, eps));
+    for (int64_t c = threadIdx.x; c < cols; c += 256) dst[c] = __fmul_rn(__fdiv_rn(row[c], sd), w[c]);
+}
+
+struct RopeParams {
+    int64_t d[4];         // output dims, row-major; d[3] = head dim D
+    int64_t xs[4], cs[4], ss[4];  // element strides of x, cos, sin per output dim (0 = broadcast)
+};
+
+__global__ void __launch_bounds__(256) rope_f32_kernel(RopeParams p, int64_t total, const float* __restrict__ x, const float* __restrict__ cosv,
+                                                      const float* __restrict__ sinv, float* __restrict__ out) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= total) return;
+    const int64_t D = p.d[3], half = D / 2;
+    int64_t t = i;
+    const int64_t j = t % D;
+    t /= D;
+    const int64_t i2 = t % p.d[2];
+    t /= p.d[2];
+    const int64_t i1 = t % p.d[1];
+    const int64_t i0 = t / p.d[1];
+    const int64_t xb = i0 * p.xs[0] + i1 * p.xs[1] + i2 * p.xs[2];
+    const int64_t cb = i0 * p.cs[0] + i1 * p.cs[1] + i2 * p.cs[2] + j * p.cs[3];
+    const int64_t sb = i0 * p.ss[0] + i1 * p.ss[1] + i2 * p.ss[2] + j * p.ss[3];
+    const float xv = x[xb + j * p.xs[3]];
+    // rotate_half: Concat(Neg(x[half:]), x[:half]); Neg is x * -1
+    const float rot = j < half ? __fmul_rn(x[xb + (j + half) * p.xs[3]], -1.0f) : x[xb + (j - half) * p.xs[3]];
+    out[i] = __fadd_rn(__fmul_rn(xv, cosv[cb]), __fmul_rn(rot, sinv[sb]));
+}
+
+__global__ void __launch_bounds__(256) swiglu_f32_kernel(int64_t n, const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ out) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= n) return;
+    const float gv = g[i];
+    const float sg = 1.0f / (1.0f + expf(-gv));
+    out[i] = __fmul_rn(__fmul_rn(gv, sg), u[i]);
+}
+
+__global__ void __launch_bounds__(256) swiglu_f32_vec_kernel(int64_t packs, const float4* __restrict__ g, const float4* __restrict__ u,
+                                                            float4* __restrict__ out) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= packs) return;
+    const float4 a = g[i], b = u[i];
+    float4 r;
+    r.x = __fmul_rn(__fmul_rn(a.x, 1.0f / (1.0f + expf(-a.x))), b.x);
+    r.y = __fmul_rn(__fmul_rn(a.y, 1.0f / (1.0f + expf(-a.y))), b.y);
+    r.z = __fmul_rn(__fmul_rn(a.z, 1.0f / (1.0f + expf(-a.z))), b.z);
+    r.w = __fmul_rn(__fmul_rn(a.w, 1.0f / (1.0f + expf(-a.w))), b.w);
+    out[i] = r;
+}
+
+struct MaskParams {
+    int64_t d[3];   // leading dims of the scores [d0, d1, d2, cols]
+    int64_t ms[3];  // mask element strides for those dims (0 = broadcast); mask rows are dense
+};
+
+// One warp per row of up to 32 * PER columns, the row held in registers.
+template <int PER>
+__global__ void __launch_bounds__(256) scale_mask_softmax_f32_kernel(MaskParams p, int64_t rows, int cols, float scale, const float* __restrict__ s,
+                                                                    const float* __restrict__ mask, float* __restrict__ out) {
+    const int64_t row = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 5;
+    if (row >= rows) return;
+    const int lane = threadIdx.x & 31;
+    int64_t t = row;
+    const int64_t i2 = t % p.d[2];
+    t /= p.d[2];
+    const int64_t i1 = t % p.d[1];
+    const int64_t i0 = t / p.d[1];
+    const float* src = s + row * cols;
+    const float* mrow = mask + i0 * p.ms[0] + i1 * p.ms[1] + i2 * p.ms[2];
+    float v[PER];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+        const int c = lane + 32 * k;
+        v[k] = -INFINITY;
+        if (c < cols) {
+            v[k] = __fadd_rn(__fmul_rn(src[c], scale), mrow[c]);
+            mx = fmaxf(mx, v[k]);
+        }
+    }
+    mx = warp_max_f(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+        const int c = lane + 32 * k;
+        if (c < cols) {
+            v[k] = expf(v[k] - mx);
+            sum += v[k];
+        }
+    }
+    sum = warp_sum_f(sum);
+    float* dst = out + row * cols;
+#pragma unroll
+    for (int k = 0; k < PER; k++) {
+        const int c = lane + 32 * k;
+        if (c < cols) dst[c] = v[k] / sum;
+    }
+}
+
+}  // namespace rmlk
+
+using namespace rmlk;
+
+extern "C" int rmlk_b200_rmsnorm(rmlk_stream_t stream, int dtype, int64_t rows, int64_t cols, const void* x, float exponent, float eps,
+                                 const void* weight, void* out) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for rmsnorm (f32 only)");
+    if (rows < 0 || cols < 0) return fail(RMLK_ERR_INVALID_ARG, "rmsnorm: negative extent");
+    if (rows == 0 || cols == 0) return RMLK_OK;
+    if (!x || !weight || !out) return fail(RMLK_ERR_INVALID_ARG, "rmsnorm: NULL tensor pointer");
+    if (rows > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "rmsnorm: too many rows");
+    rmsnorm_f32_kernel<<<static_cast<unsigned>(rows), 256, 0, as_stream(stream)>>>(cols, exponent, eps, static_cast<const float*>(x),
+                                                                                   static_cast<const float*>(weight), static_cast<float*>(out));
+    RMLK_CHECK_LAUNCH("rmsnorm_f32_kernel");
+    return RMLK_OK;
+}
+
+extern "C" int rmlk_b200_rope(rmlk_stream_t stream, int dtype, const int64_t* shape4, const int64_t* x_strides, const int64_t* cos_strides,
+                              const int64_t* sin_strides, const void* x, const void* cosv, const void* sinv, void* out) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for rope (f32 only)");
+    if (!shape4 || !x_strides || !cos_strides || !sin_strides) return fail(RMLK_ERR_INVALID_ARG, "rope: NULL shape / strides");
+    RopeParams p;
+    int64_t total = 1;
+    for (int d = 0; d < 4; d++) {
+        if (shape4[d] < 0) return fail(RMLK_ERR_INVALID_ARG, "rope: negative extent");
+        p.d[d] = shape4[d];
+        p.xs[d] = x_strides[d];
+        p.cs[d] = cos_strides[d];
+        p.ss[d] = sin_strides[d];
+        total *= shape4[d];
+    }
+    if (total == 0) return RMLK_OK;
+    if (shape4[3] % 2) return fail(RMLK_ERR_INVALID_ARG, "rope: head dim must be even");
+    if (!x || !cosv || !sinv || !out) return fail(RMLK_ERR_INVALID_ARG, "rope: NULL tensor pointer");
+    if (ceil_div64(total, 256) > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "rope: tensor too large");
+    rope_f32_kernel<<<static_cast<unsigned>(ceil_div64(total, 256)), 256, 0, as_stream(stream)>>>(
+        p, total, static_cast<const float*>(x), static_cast<const float*>(cosv), static_cast<const float*>(sinv), static_cast<float*>(out));
+    RMLK_CHECK_LAUNCH("rope_f32_kernel");
+    return RMLK_OK;
+}
+
+extern "C" int rmlk_b200_swiglu(rmlk_stream_t stream, int dtype, int64_t n, const void* gate, const void* up, void* out) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for swiglu (f32 only)");
+    if (n < 0) return fail(RMLK_ERR_INVALID_ARG, "swiglu: negative extent");
+    if (n == 0) return RMLK_OK;
+    if (!gate || !up || !out) return fail(RMLK_ERR_INVALID_ARG, "swiglu: NULL tensor pointer");
+    cudaStream_t st = as_stream(stream);
+    if (n % 4 == 0 && aligned_to(gate, 16) && aligned_to(up, 16) && aligned_to(out, 16) && ceil_div64(n / 4, 256) <= 0x7fffffffll) {
+        swiglu_f32_vec_kernel<<<static_cast<unsigned>(ceil_div64(n / 4, 256)), 256, 0, st>>>(n / 4, static_cast<const float4*>(gate),
+                                                                                             static_cast<const float4*>(up), static_cast<float4*>(out));
+    } else {
+        if (ceil_div64(n, 256) > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "swiglu: tensor too large");
+        swiglu_f32_kernel<<<static_cast<unsigned>(ceil_div64(n, 256)), 256, 0, st>>>(n, static_cast<const float*>(gate), static_cast<const float*>(up),
+                                                                                     static_cast<float*>(out));
+    }
+    RMLK_CHECK_LAUNCH("swiglu_f32_kernel");
+    return RMLK_OK;
+}
+
+extern "C" int rmlk_b200_scale_mask_softmax(rmlk_stream_t stream, int dtype, const int64_t* lead3, int64_t cols, const int64_t* mask_strides3,
+                                            float scale, const void* scores, const void* mask, void* out) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for scale_mask_softmax (f32 only)");
+    if (!lead3 || !mask_strides3) return fail(RMLK_ERR_INVALID_ARG, "scale_mask_softmax: NULL dims / strides");
+    MaskParams p;
+    int64_t rows = 1;
+    for (int d = 0; d < 3; d++) {
+        if (lead3[d] < 0) return fail(RMLK_ERR_INVALID_ARG, "scale_mask_softmax: negative extent");
+        p.d[d] = lead3[d];
+        p.ms[d] = mask_strides3[d];
+        rows *= lead3[d];
+    }
+    if (cols < 0) return fail(RMLK_ERR_INVALID_ARG, "scale_mask_softmax: negative extent");
+    if (rows == 0 || cols == 0) return RMLK_OK;
+    if (cols > 2048) return fail(RMLK_ERR_INVALID_ARG, "scale_mask_softmax: rows longer than 2048 are not supported");
+    if (!scores || !mask || !out) return fail(RMLK_ERR_INVALID_ARG, "scale_mask_softmax: NULL tensor pointer");
+    const int64_t blocks = ceil_div64(rows, 8);
+    if (blocks > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "scale_mask_softmax: too many rows");
+    cudaStream_t st = as_stream(stream);
+    const float* s = static_cast<const float*>(scores);
+    const float* m = static_cast<const float*>(mask);
+    float* o = static_cast<float*>(out);
+    const unsigned grid = static_cast<unsigned>(blocks);
+    const int c = static_cast<int>(cols);
+    if (cols <= 128) scale_mask_softmax_f32_kernel<4><<<grid, 256, 0, st>>>(p, rows, c, scale, s, m, o);
+    else if (cols <= 256) scale_mask_softmax_f32_kernel<8><<<grid, 256, 0, st>>>(p, rows, c, scale, s, m, o);
+    else if (cols <= 512) scale_mask_softmax_f32_kernel<16><<<grid, 256, 0, st>>>(p, rows, c, scale, s, m, o);
+    else if (cols <= 1024) scale_mask_softmax_f32_kernel<32><<<grid, 256, 0, st>>>(p, rows, c, scale, s, m, o);
+    else scale_mask_softmax_f32_kernel<64><<<grid, 256, 0, st>>>(p, rows, c, scale, s, m, o);
+    RMLK_CHECK_LAUNCH("scale_mask_softmax_f32_kernel");
+    return RMLK_OK;
+}

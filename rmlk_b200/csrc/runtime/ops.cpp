@@ -1151,6 +1151,307 @@ void op_constant_of_shape(const Ctx& c) {
 
 size_t dtype_size_of(int dt) { return rmlk_b200_dtype_size(dt); }
 
+// ---------------------------------------------------------------------------------------------
+// fused chains
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+struct Matcher {
+    const Graph& g;
+    std::vector<int> producer, uses;
+    const std::vector<int>& group_of_node;
+    Matcher(const Graph& gr, const std::vector<int>& gon) : g(gr), producer(gr.values.size(), -1), uses(gr.values.size(), 0), group_of_node(gon) {
+        for (size_t i = 0; i < g.nodes.size(); i++) {
+            for (int v : g.nodes[i].outputs)
+                if (v >= 0) producer[v] = static_cast<int>(i);
+            for (int v : g.nodes[i].inputs)
+                if (v >= 0) uses[v]++;
+        }
+    }
+    // node producing `v` if it has the given op, `v` feeds exactly one node and never leaves the graph
+    int inner(int v, int op) const {
+        if (v < 0) return -1;
+        const int p = producer[v];
+        if (p < 0 || g.nodes[p].op != op || group_of_node[p] >= 0) return -1;
+        const ValueDef& d = g.values[v];
+        if (uses[v] != 1 || d.is_output || d.is_input || d.is_const) return -1;
+        return p;
+    }
+    bool is_const(int v) const { return v >= 0 && g.values[v].is_const; }
+    int in(int node, size_t i) const { return i < g.nodes[node].inputs.size() ? g.nodes[node].inputs[i] : -1; }
+    size_t n_in(int node) const {
+        size_t n = g.nodes[node].inputs.size();
+        while (n > 0 && g.nodes[node].inputs[n - 1] < 0) n--;
+        return n;
+    }
+};
+
+bool scalar_f32(const Tensor& t, float& v) {
+    if (t.dtype != RMLK_F32 || t.numel() != 1 || !t.mirror_valid || t.mf.empty()) return false;
+    v = static_cast<float>(t.mf[0]);
+    return true;
+}
+
+// Element strides of `t` (dense) when broadcast to `shape` (same rank or lower, right-aligned); false if not broadcastable.
+bool bcast_strides(const Tensor& t, const Shape& shape, int64_t* out) {
+    if (t.shape.size() > shape.size()) return false;
+    const Shape st = dense_strides(t.shape);
+    const size_t lead = shape.size() - t.shape.size();
+    for (size_t d = 0; d < shape.size(); d++) {
+        if (d < lead) {
+            out[d] = 0;
+            continue;
+        }
+        const int64_t n = t.shape[d - lead];
+        if (n == shape[d]) out[d] = n == 1 ? 0 : st[d - lead];
+        else if (n == 1) out[d] = 0;
+        else return false;
+    }
+    return true;
+}
+
+}  // namespace
+
+void Instance::find_fusions() {
+    group_of_node.assign(g.nodes.size(), -1);
+    groups.clear();
+    if (!fusion) return;
+    Matcher m(g, group_of_node);
+    auto commit = [&](FusedGroup& fg) {
+        std::sort(fg.members.begin(), fg.members.end());
+        fg.root = fg.members.back();
+        for (int n : fg.members) group_of_node[n] = static_cast<int>(groups.size());
+        groups.push_back(fg);
+    };
+    for (size_t r = 0; r < g.nodes.size(); r++) {
+        const NodeDef& root = g.nodes[r];
+        if (group_of_node[r] >= 0) continue;
+        const int ri = static_cast<int>(r);
+        if (root.op == RMLK_OP_MUL && m.n_in(ri) == 2) {
+            bool done = false;
+            for (int side = 0; side < 2 && !done; side++) {
+                // RMSNorm: Mul(Div(x, Sqrt(Add(ReduceMean(Pow(x, c)), eps))), w)
+                const int dv = m.in(ri, side), w = m.in(ri, 1 - side);
+                const int n_div = m.inner(dv, RMLK_OP_DIV);
+                if (n_div >= 0) {
+                    const int x = m.in(n_div, 0), n_sqrt = m.inner(m.in(n_div, 1), RMLK_OP_SQRT);
+                    const int n_add = n_sqrt >= 0 ? m.inner(m.in(n_sqrt, 0), RMLK_OP_ADD) : -1;
+                    for (int s2 = 0; s2 < 2 && n_add >= 0 && !done; s2++) {
+                        const int var = m.in(n_add, s2), eps = m.in(n_add, 1 - s2);
+                        const int n_mean = m.inner(var, RMLK_OP_REDUCE_MEAN);
+                        if (n_mean < 0 || !m.is_const(eps) || m.n_in(n_mean) != 1) continue;
+                        const NodeDef& mean = g.nodes[n_mean];
+                        auto ax = mean.attrs.find("axes");
+                        auto kd = mean.attrs.find("keepdims");
+                        if (ax == mean.attrs.end() || ax->second.kind != Attr::INTS || ax->second.ints.size() != 1 || ax->second.ints[0] != -1) continue;
+                        if (kd != mean.attrs.end() && kd->second.i != 1) continue;
+                        const int n_pow = m.inner(m.in(n_mean, 0), RMLK_OP_POW);
+                        if (n_pow < 0 || m.in(n_pow, 0) != x || !m.is_const(m.in(n_pow, 1))) continue;
+                        FusedGroup fg;
+                        fg.kind = FusedGroup::RMSNORM;
+                        fg.members = {n_pow, n_mean, n_add, n_sqrt, n_div, ri};
+                        fg.v[0] = x; fg.v[1] = w; fg.v[2] = eps; fg.v[3] = m.in(n_pow, 1);
+                        commit(fg);
+                        done = true;
+                    }
+                }
+                if (done) break;
+                // SwiGLU gate: Mul(Mul(g, Sigmoid(g)), u)
+                const int n_silu = m.inner(m.in(ri, side), RMLK_OP_MUL);
+                if (n_silu >= 0 && m.n_in(n_silu) == 2) {
+                    for (int s2 = 0; s2 < 2 && !done; s2++) {
+                        const int gate = m.in(n_silu, s2), n_sig = m.inner(m.in(n_silu, 1 - s2), RMLK_OP_SIGMOID);
+                        if (n_sig < 0 || m.in(n_sig, 0) != gate) continue;
+                        FusedGroup fg;
+                        fg.kind = FusedGroup::SWIGLU;
+                        fg.members = {n_sig, n_silu, ri};
+                        fg.v[0] = gate; fg.v[1] = m.in(ri, 1 - side);
+                        commit(fg);
+                        done = true;
+                    }
+                }
+            }
+        } else if (root.op == RMLK_OP_ADD && m.n_in(ri) == 2) {
+            // rotary embedding: Add(Mul(x, cos), Mul(Concat(Neg(Slice(x, hi)), Slice(x, lo)), sin))
+            bool done = false;
+            for (int side = 0; side < 2 && !done; side++) {
+                const int n_xc = m.inner(m.in(ri, side), RMLK_OP_MUL), n_xs = m.inner(m.in(ri, 1 - side), RMLK_OP_MUL);
+                if (n_xc < 0 || n_xs < 0 || n_xc == n_xs || m.n_in(n_xc) != 2 || m.n_in(n_xs) != 2) continue;
+                for (int s2 = 0; s2 < 2 && !done; s2++) {
+                    const int n_cat = m.inner(m.in(n_xs, s2), RMLK_OP_CONCAT), sinv = m.in(n_xs, 1 - s2);
+                    if (n_cat < 0 || m.n_in(n_cat) != 2) continue;
+                    const int n_neg = m.inner(m.in(n_cat, 0), RMLK_OP_NEG), n_lo = m.inner(m.in(n_cat, 1), RMLK_OP_SLICE);
+                    const int n_hi = n_neg >= 0 ? m.inner(m.in(n_neg, 0), RMLK_OP_SLICE) : -1;
+                    if (n_lo < 0 || n_hi < 0 || n_lo == n_hi) continue;
+                    const int x = m.in(n_lo, 0);
+                    if (m.in(n_hi, 0) != x) continue;
+                    bool consts = true;
+                    for (int sl : {n_lo, n_hi})
+                        for (size_t k = 1; k < m.n_in(sl); k++) consts = consts && m.is_const(m.in(sl, k));
+                    if (!consts || m.n_in(n_lo) < 4 || m.n_in(n_hi) < 4) continue;
+                    int cosv = -1;
+                    if (m.in(n_xc, 0) == x) cosv = m.in(n_xc, 1);
+                    else if (m.in(n_xc, 1) == x) cosv = m.in(n_xc, 0);
+                    if (cosv < 0) continue;
+                    FusedGroup fg;
+                    fg.kind = FusedGroup::ROPE;
+                    fg.members = {n_xc, n_lo, n_hi, n_neg, n_cat, n_xs, ri};
+                    fg.v[0] = x; fg.v[1] = cosv; fg.v[2] = sinv; fg.v[3] = n_lo; fg.v[4] = n_hi; fg.v[5] = n_cat;  // v[3..5]: node ids
+                    commit(fg);
+                    done = true;
+                }
+            }
+        } else if (root.op == RMLK_OP_SOFTMAX) {
+            // Softmax(Add(Mul(scores, scale), mask))
+            const int n_add = m.inner(m.in(ri, 0), RMLK_OP_ADD);
+            bool done = false;
+            for (int side = 0; side < 2 && n_add >= 0 && !done; side++) {
+                const int n_mul = m.inner(m.in(n_add, side), RMLK_OP_MUL), mask = m.in(n_add, 1 - side);
+                if (n_mul < 0 || m.n_in(n_mul) != 2) continue;
+                for (int s2 = 0; s2 < 2 && !done; s2++) {
+                    const int scores = m.in(n_mul, s2), scale = m.in(n_mul, 1 - s2);
+                    if (!m.is_const(scale) || m.is_const(scores)) continue;
+                    FusedGroup fg;
+                    fg.kind = FusedGroup::SCALE_MASK_SOFTMAX;
+                    fg.members = {n_mul, n_add, ri};
+                    fg.v[0] = scores; fg.v[1] = scale; fg.v[2] = mask;
+                    commit(fg);
+                    done = true;
+                }
+            }
+        }
+    }
+    // a skipped member's inputs are read when the root runs: they stay alive until then
+    last_use.assign(g.values.size(), -1);
+    for (size_t i = 0; i < g.nodes.size(); i++) {
+        const int at = group_of_node[i] >= 0 ? groups[group_of_node[i]].root : static_cast<int>(i);
+        for (int v : g.nodes[i].inputs)
+            if (v >= 0) last_use[v] = std::max(last_use[v], at);
+    }
+}
+
+// Runs the fused kernel of `fg` if the tensors of this run meet its conditions.  False: nothing was launched and no
+// output was touched; the caller runs the member nodes instead.
+bool Instance::run_fused(const FusedGroup& fg) {
+    const NodeDef& root = g.nodes[fg.root];
+    Ctx c{*this, root};
+    auto val = [&](int id) -> Tensor* {
+        if (id < 0) return nullptr;
+        Tensor& t = values[id];
+        return t.present ? &t : nullptr;
+    };
+    rmlk_stream_t st = reinterpret_cast<rmlk_stream_t>(stream);
+    switch (fg.kind) {
+        case FusedGroup::RMSNORM: {
+            Tensor *x = val(fg.v[0]), *w = val(fg.v[1]), *eps = val(fg.v[2]), *ex = val(fg.v[3]);
+            float e = 0.f, p = 0.f;
+            if (!x || !w || !eps || !ex || x->dtype != RMLK_F32 || w->dtype != RMLK_F32 || x->shape.empty() || w->lazy) return false;
+            if (!scalar_f32(*eps, e) || !scalar_f32(*ex, p)) return false;
+            const int64_t cols = x->shape.back();
+            if (cols == 0 || w->numel() != cols || w->shape.empty() || w->shape.back() != cols || w->shape.size() > x->shape.size()) return false;
+            if (x->lazy) materialize(*x);
+            const Shape oshape = x->shape;
+            Tensor& o = c.make(0, RMLK_F32, oshape);
+            check_rc(rmlk_b200_rmsnorm(st, RMLK_F32, x->numel() / cols, cols, x->data, p, e, w->data, o.data));
+            launches++;
+            return true;
+        }
+        case FusedGroup::SWIGLU: {
+            Tensor *gt = val(fg.v[0]), *up = val(fg.v[1]);
+            if (!gt || !up || gt->dtype != RMLK_F32 || up->dtype != RMLK_F32 || gt->shape != up->shape) return false;
+            if (gt->lazy) materialize(*gt);
+            if (up->lazy) materialize(*up);
+            const Shape oshape = gt->shape;
+            Tensor& o = c.make(0, RMLK_F32, oshape);
+            check_rc(rmlk_b200_swiglu(st, RMLK_F32, gt->numel(), gt->data, up->data, o.data));
+            launches++;
+            return true;
+        }
+        case FusedGroup::SCALE_MASK_SOFTMAX: {
+            Tensor *s = val(fg.v[0]), *sc = val(fg.v[1]), *mk = val(fg.v[2]);
+            float scale = 0.f;
+            if (!s || !sc || !mk || s->dtype != RMLK_F32 || mk->dtype != RMLK_F32 || !scalar_f32(*sc, scale)) return false;
+            const size_t rank = s->shape.size();
+            if (rank < 1 || rank > 4 || mk->shape.size() > rank || mk->shape.empty()) return false;
+            const int64_t axis = c.attr_int("axis", -1);
+            if (axis != -1 && axis != static_cast<int64_t>(rank) - 1) return false;
+            const int64_t cols = s->shape.back();
+            if (cols == 0 || cols > 2048 || mk->shape.back() != cols) return false;
+            if (mk->lazy) materialize(*mk);
+            int64_t ms[4];
+            if (!bcast_strides(*mk, s->shape, ms) || ms[rank - 1] != 1) return false;
+            int64_t lead3[3] = {1, 1, 1}, mstr3[3] = {0, 0, 0};
+            for (size_t d = 0; d + 1 < rank; d++) {
+                lead3[3 - (rank - 1) + d] = s->shape[d];
+                mstr3[3 - (rank - 1) + d] = ms[d];
+            }
+            if (s->lazy) materialize(*s);
+            const Shape oshape = s->shape;
+            Tensor& o = c.make(0, RMLK_F32, oshape);
+            if (o.numel() == 0) return true;
+            check_rc(rmlk_b200_scale_mask_softmax(st, RMLK_F32, lead3, cols, mstr3, scale, s->data, mk->data, o.data));
+            launches++;
+            return true;
+        }
+        case FusedGroup::ROPE: {
+            Tensor *x = val(fg.v[0]), *cs = val(fg.v[1]), *sn = val(fg.v[2]);
+            if (!x || !cs || !sn || x->dtype != RMLK_F32 || cs->dtype != RMLK_F32 || sn->dtype != RMLK_F32 || x->shape.size() != 4) return false;
+            const int64_t D = x->shape[3];
+            if (D < 2 || D % 2) return false;
+            // the two Slice nodes must cut [0, D/2) and [D/2, D) of the last axis with step 1; the Concat joins on it
+            auto slice_ok = [&](int node, int64_t lo, int64_t hi) {
+                const NodeDef& n = g.nodes[node];
+                Tensor *s0 = val(n.inputs[1]), *e0 = val(n.inputs[2]), *a0 = val(n.inputs[3]);
+                Tensor* p0 = n.inputs.size() > 4 ? val(n.inputs[4]) : nullptr;
+                if (!s0 || !e0 || !a0 || !small_mirrored(*s0) || !small_mirrored(*e0) || !small_mirrored(*a0)) return false;
+                if (s0->mi.size() != 1 || e0->mi.size() != 1 || a0->mi.size() != 1) return false;
+                if (p0 && (!small_mirrored(*p0) || p0->mi.size() != 1 || p0->mi[0] != 1)) return false;
+                if (n.inputs.size() > 4 && n.inputs[4] >= 0 && !p0) return false;
+                const int64_t ax = a0->mi[0];
+                return (ax == 3 || ax == -1) && s0->mi[0] == lo && (e0->mi[0] == hi || (hi == D && e0->mi[0] >= D));
+            };
+            if (!slice_ok(fg.v[3], 0, D / 2) || !slice_ok(fg.v[4], D / 2, D)) return false;
+            const int64_t cat_axis = Ctx{*this, g.nodes[fg.v[5]]}.attr_int("axis", 0);
+            if (cat_axis != 3 && cat_axis != -1) return false;
+            if (cs->lazy) materialize(*cs);
+            if (sn->lazy) materialize(*sn);
+            int64_t cstr[4], sstr[4], xstr[4];
+            if (!bcast_strides(*cs, x->shape, cstr) || !bcast_strides(*sn, x->shape, sstr)) return false;
+            // x may be a permuted view: one physical dim (or none) per logical dim, else copy it out first
+            bool strided_ok = false;
+            if (x->lazy) {
+                std::vector<std::pair<int, int>> groups_;
+                if (group_dims(x->shape, x->pshape, groups_)) {
+                    strided_ok = true;
+                    for (int d = 0; d < 4 && strided_ok; d++) {
+                        int cnt = 0;
+                        xstr[d] = 0;
+                        for (int p = groups_[d].first; p < groups_[d].second; p++)
+                            if (x->pshape[p] != 1) {
+                                cnt++;
+                                xstr[d] = x->pstride[p];
+                            }
+                        strided_ok = cnt <= 1;
+                    }
+                }
+                if (!strided_ok) materialize(*x);
+            }
+            if (!strided_ok) {
+                const Shape st4 = dense_strides(x->shape);
+                for (int d = 0; d < 4; d++) xstr[d] = st4[d];
+            }
+            const Shape oshape = x->shape;
+            const void* xdata = x->data;
+            Tensor& o = c.make(0, RMLK_F32, oshape);
+            if (o.numel() == 0) return true;
+            check_rc(rmlk_b200_rope(st, RMLK_F32, oshape.data(), xstr, cstr, sstr, xdata, cs->data, sn->data, o.data));
+            launches++;
+            return true;
+        }
+    }
+    return false;
+}
+
 void Instance::run_node(const NodeDef& n) {
     Ctx c{*this, n};
     switch (n.op) {

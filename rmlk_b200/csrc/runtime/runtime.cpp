@@ -330,6 +330,29 @@ void Instance::run() {
         if (g.values[i].is_input && !input_fed[i]) raise(RMLK_ERR_INVALID_ARG, "graph input `" + g.values[i].name + "` was not fed");
     for (size_t i = 0; i < g.nodes.size(); i++) {
         const NodeDef& n = g.nodes[i];
+        const int gi = group_of_node.empty() ? -1 : group_of_node[i];
+        if (gi >= 0) {
+            // member of a fused chain: everything happens when the chain's last node comes up
+            const FusedGroup& fg = groups[gi];
+            if (fg.root != static_cast<int>(i)) continue;
+            try {
+                if (run_fused(fg)) {
+                    fused_runs++;
+                } else {
+                    fused_fallbacks++;
+                    for (int m : fg.members) run_node(g.nodes[m]);
+                }
+            } catch (const Error& e) {
+                throw Error(e.code, std::string(e.what()) + " [fused chain ending at node " + std::to_string(i) + "]");
+            }
+            for (int m : fg.members) {
+                for (int v : g.nodes[m].inputs)
+                    if (v >= 0 && last_use[v] == static_cast<int>(i) && !g.values[v].is_output) release_value(v);
+                for (int v : g.nodes[m].outputs)
+                    if (v >= 0 && last_use[v] < 0 && !g.values[v].is_output) release_value(v);
+            }
+            continue;
+        }
         try {
             if (host_profile) {
                 const auto t0 = std::chrono::steady_clock::now();
@@ -559,6 +582,8 @@ extern "C" rmlk_instance* rmlk_instance_create(const rmlk_graph* g, int device, 
         for (size_t i = 0; i < I.g.nodes.size(); i++)
             for (int v : I.g.nodes[i].inputs)
                 if (v >= 0) I.last_use[v] = static_cast<int>(i);
+        if (const char* e = getenv("RMLK_B200_NO_FUSION")) I.fusion = e[0] != '1';
+        I.find_fusions();  // recognise RMSNorm / rotary / SwiGLU / scale-mask-softmax chains; re-derives last_use
         // one weight arena, one pass of uploads (the reference allocates and copies per tensor through a
         // 4 KiB bump allocator, runtime/src/providers/cuda/store.rs:95-262)
         size_t total = 0;
@@ -728,4 +753,7 @@ extern "C" int rmlk_instance_read(rmlk_instance* inst, const char* name, void* d
 
 extern "C" int64_t rmlk_instance_last_launches(const rmlk_instance* inst) { return inst ? inst->I.launches : 0; }
 extern "C" int64_t rmlk_instance_last_syncs(const rmlk_instance* inst) { return inst ? inst->I.syncs : 0; }
+extern "C" int64_t rmlk_instance_fused_chains(const rmlk_instance* inst) { return inst ? static_cast<int64_t>(inst->I.groups.size()) : 0; }
+extern "C" int64_t rmlk_instance_fused_runs(const rmlk_instance* inst) { return inst ? inst->I.fused_runs : 0; }
+extern "C" int64_t rmlk_instance_fused_fallbacks(const rmlk_instance* inst) { return inst ? inst->I.fused_fallbacks : 0; }
 extern "C" size_t rmlk_instance_arena_peak(const rmlk_instance* inst) { return inst && inst->I.arena ? inst->I.arena->peak() : 0; }

@@ -144,8 +144,26 @@ struct Binding {  // output value -> input value, double-buffered
     bool have = false;
 };
 
+// A chain of single-op nodes that one fused launch can stand for (RMSNorm, rotary embedding, SwiGLU gate,
+// scale + mask + softmax).  Found once per instance by matching the graph; the members other than the last one
+// (`root`) are skipped when their turn comes, and at the root either the fused kernel runs or - when the
+// tensors of this run do not meet its conditions - the members run one by one, as if nothing had been matched.
+// Member outputs other than the root's are used only inside the chain, so running them late changes nothing.
+struct FusedGroup {
+    enum Kind { RMSNORM = 1, ROPE, SWIGLU, SCALE_MASK_SOFTMAX } kind;
+    int root = -1;
+    std::vector<int> members;  // node indices in execution order, root last
+    int v[8] = {-1, -1, -1, -1, -1, -1, -1, -1};  // value ids by role (per kind, see ops.cpp)
+};
+
 struct Instance {
     Graph g;
+    std::vector<FusedGroup> groups;
+    std::vector<int> group_of_node;  // per node: index into `groups`, or -1
+    bool fusion = true;              // RMLK_B200_NO_FUSION=1 turns the substitution off
+    void find_fusions();
+    bool run_fused(const FusedGroup& fg);
+    int64_t fused_runs = 0, fused_fallbacks = 0;
     int device = 0;
     cudaStream_t stream = nullptr;
     bool own_stream = false;

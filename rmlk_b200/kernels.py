@@ -308,3 +308,45 @@ def strided_copy(base: torch.Tensor, shape: Sequence[int], strides: Sequence[int
     out = torch.empty(list(shape), dtype=base.dtype, device=base.device)
     _check(lib().rmlk_b200_strided_copy(_stream(), base.element_size(), len(shape), _i64(list(shape)), _i64(list(strides)), _ptr(base), _ptr(out)))
     return out
+
+
+# ---- op chains as one launch (f32) ------------------------------------------------------------------------------
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, exponent: float = 2.0) -> torch.Tensor:
+    """Pow(x, exponent) -> ReduceMean(-1, keepdims) -> Add(eps) -> Sqrt -> Div(x, .) -> Mul(., weight)."""
+    _require_cuda(x, weight)
+    out = torch.empty_like(x)
+    cols = x.shape[-1]
+    _check(lib().rmlk_b200_rmsnorm(_stream(), dt.from_torch(x.dtype), ctypes.c_int64(x.numel() // cols if cols else 0), ctypes.c_int64(cols),
+                                   _ptr(x), ctypes.c_float(exponent), ctypes.c_float(eps), _ptr(weight), _ptr(out)))
+    return out
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x * cos + rotate_half(x) * sin for x [d0, d1, d2, D] (any strides) and cos / sin broadcastable to it."""
+    _require_cuda(cos, sin)
+    assert x.dim() == 4 and x.is_cuda   # x may be a permuted (non-contiguous) view: its strides are passed on
+    out = torch.empty(list(x.shape), dtype=x.dtype, device=x.device)
+    cs = cos.expand(x.shape).stride() if cos.dim() == 4 else cos.reshape([1] * (4 - cos.dim()) + list(cos.shape)).expand(x.shape).stride()
+    ss = sin.expand(x.shape).stride() if sin.dim() == 4 else sin.reshape([1] * (4 - sin.dim()) + list(sin.shape)).expand(x.shape).stride()
+    _check(lib().rmlk_b200_rope(_stream(), dt.from_torch(x.dtype), _i64(list(x.shape)), _i64(list(x.stride())), _i64(list(cs)), _i64(list(ss)),
+                                _ptr(x), _ptr(cos), _ptr(sin), _ptr(out)))
+    return out
+
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """(gate * sigmoid(gate)) * up."""
+    _require_cuda(gate, up)
+    out = torch.empty_like(gate)
+    _check(lib().rmlk_b200_swiglu(_stream(), dt.from_torch(gate.dtype), ctypes.c_int64(gate.numel()), _ptr(gate), _ptr(up), _ptr(out)))
+    return out
+
+
+def scale_mask_softmax(scores: torch.Tensor, scale: float, mask: torch.Tensor) -> torch.Tensor:
+    """softmax(scores * scale + mask, -1) for scores [d0, d1, d2, T] and a mask broadcastable over d0..d2 with dense rows."""
+    _require_cuda(scores, mask)
+    assert scores.dim() == 4 and mask.shape[-1] == scores.shape[-1]
+    out = torch.empty_like(scores)
+    m4 = mask.reshape([1] * (4 - mask.dim()) + list(mask.shape)).expand(scores.shape)
+    _check(lib().rmlk_b200_scale_mask_softmax(_stream(), dt.from_torch(scores.dtype), _i64(list(scores.shape[:3])), ctypes.c_int64(scores.shape[3]),
+                                              _i64(list(m4.stride()[:3])), ctypes.c_float(scale), _ptr(scores), _ptr(mask), _ptr(out)))
+    return out

@@ -116,6 +116,9 @@ def _setup(l):
     l.rmlk_instance_last_launches.argtypes = [ctypes.c_void_p]
     l.rmlk_instance_last_syncs.restype = ctypes.c_int64
     l.rmlk_instance_last_syncs.argtypes = [ctypes.c_void_p]
+    for fn in (l.rmlk_instance_fused_chains, l.rmlk_instance_fused_runs, l.rmlk_instance_fused_fallbacks):
+        fn.restype = ctypes.c_int64
+        fn.argtypes = [ctypes.c_void_p]
     l.rmlk_instance_arena_peak.restype = ctypes.c_size_t
     l.rmlk_instance_arena_peak.argtypes = [ctypes.c_void_p]
     l.rmlk_graph_input.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p]
@@ -304,6 +307,12 @@ class ModelInstance:
     @property
     def last_syncs(self) -> int:
         return int(_rt().rmlk_instance_last_syncs(self._h))
+
+    @property
+    def fused(self) -> tuple:
+        """(chains recognised in the graph, fused launches so far, fallbacks to single ops so far)."""
+        r = _rt()
+        return (int(r.rmlk_instance_fused_chains(self._h)), int(r.rmlk_instance_fused_runs(self._h)), int(r.rmlk_instance_fused_fallbacks(self._h)))
 
     @property
     def arena_peak(self) -> int:

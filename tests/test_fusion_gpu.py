@@ -1,0 +1,183 @@
+"""Op chains that run as one launch: RMSNorm, rotary embedding, SwiGLU gate, scale + mask + softmax.
+
+The reference runs every node of these chains through its own backend.  The fused kernels must give what the chain
+of single-op kernels gives: bit-identical where the chain has no reduction (rotary, SwiGLU), within the
+ReduceMean / Softmax bar (rel 1e-5) where the row sums may associate differently.  The runtime substitutes a fused
+kernel only when it recognises the whole chain and the run's tensors fit; otherwise the single ops run.
+"""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import graph_cpu
+from rmlk_b200.graphspec import GraphSpec
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def K(cuda):
+    from rmlk_b200 import kernels
+    return kernels
+
+
+def test_fused_kernels_equal_the_single_op_chain(K):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    r = lambda *s: torch.randn(*s, device="cuda", generator=g)  # noqa: E731
+    # RMSNorm
+    for rows, cols in [(64, 2048), (3, 7), (1, 4097), (130, 64)]:
+        x, w = r(rows, cols) * 3, r(cols)
+        two, eps = torch.tensor(2.0, device="cuda"), torch.tensor(1e-5, device="cuda")
+        var = K.reduce_mean(K.pow_(x, two), [-1], True)
+        want = K.binary("mul", K.binary("div", x, K.unary("sqrt", K.binary("add", var, eps))), w)
+        got = K.rmsnorm(x, w, 1e-5)
+        assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max()), (rows, cols)
+        ref = x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + 1e-5) * w.double()
+        assert float((got.double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
+    # SwiGLU: no reduction, so the same bits as Sigmoid -> Mul -> Mul
+    for n in [(64, 8192), (5, 7), (1,), (4099,)]:
+        a, b = r(*n) * 4, r(*n)
+        want = K.binary("mul", K.binary("mul", a, K.unary("sigmoid", a)), b)
+        assert torch.equal(K.swiglu(a, b), want), n
+    # rotary embedding: same bits as Mul, Slice x2, Neg, Concat, Mul, Add; x given as a permuted view too
+    for (B, H, S, D) in [(4, 8, 1, 64), (2, 3, 5, 16), (1, 1, 7, 2), (3, 4, 2, 128)]:
+        xb = r(B, S, H, D)
+        cos, sin = r(B, 1, S, D), r(B, 1, S, D)
+        for x in (xb.permute(0, 2, 1, 3), xb.permute(0, 2, 1, 3).contiguous()):
+            xc = x.contiguous()
+            lo = K.slice_(xc, [0], [D // 2], [3], None)
+            hi = K.slice_(xc, [D // 2], [D], [3], None)
+            rot = K.concat([K.unary("neg", hi), lo], -1)
+            want = K.binary("add", K.binary("mul", xc, cos), K.binary("mul", rot, sin))
+            assert torch.equal(K.rope(x, cos, sin), want), (B, H, S, D)
+    # scale + mask + softmax
+    for (B, H, S, T) in [(4, 8, 1, 523), (2, 3, 5, 33), (1, 2, 3, 1030), (2, 2, 2, 2048), (3, 1, 4, 7)]:
+        s = r(B, H, S, T) * 5
+        mask = torch.where(torch.rand(B, 1, S, T, device="cuda", generator=g) > 0.8, torch.tensor(float(np.finfo(np.float32).min), device="cuda"),
+                           torch.tensor(0.0, device="cuda"))
+        mask[..., 0] = 0.0
+        scale = 0.125
+        want = K.softmax(K.binary("add", K.binary("mul", s, torch.tensor(scale, device="cuda")), mask))
+        got = K.scale_mask_softmax(s, scale, mask)
+        assert float((got - want).abs().max()) <= 1e-6, (B, H, S, T)
+        assert float((got.sum(-1) - 1).abs().max()) <= 1e-5
+
+
+def i64(*v):
+    return np.array(v, dtype=np.int64)
+
+
+def block_graph(hidden, heads, D, exact_names=True):
+    """RMSNorm -> projections -> rotary on q -> scores with scale and mask -> softmax; SwiGLU on the side."""
+    g = GraphSpec()
+    g.input("x", np.float32, [0, 0, hidden])
+    g.input("cos", np.float32, [0, 1, 0, D])
+    g.input("sin", np.float32, [0, 1, 0, D])
+    g.input("mask", np.float32, [0, 1, 0, 0])
+    g.input("k", np.float32, [0, heads, 0, D])
+    rng = np.random.default_rng(0)
+    g.const("w_norm", rng.standard_normal(hidden).astype(np.float32))
+    g.const("wq", (rng.standard_normal((hidden, heads * D)) * 0.1).astype(np.float32))
+    g.const("wg", (rng.standard_normal((hidden, 3 * hidden)) * 0.1).astype(np.float32))
+    g.const("wu", (rng.standard_normal((hidden, 3 * hidden)) * 0.1).astype(np.float32))
+    g.const("two", np.array(2.0, np.float32))
+    g.const("eps", np.array(1e-5, np.float32))
+    g.const("scale", np.array(1.0 / np.sqrt(D), np.float32))
+    g.const("shape_q", i64(0, 0, heads, D))
+    g.const("z", i64(0)); g.const("h", i64(D // 2)); g.const("d", i64(D)); g.const("ax", i64(3))
+    x2 = g.op("Pow", ["x", "two"])
+    var = g.op("ReduceMean", [x2], axes=[-1], keepdims=1)
+    sd = g.op("Sqrt", [g.op("Add", [var, "eps"])])
+    hn = g.op("Mul", [g.op("Div", ["x", sd]), "w_norm"], "normed")
+    q = g.op("Transpose", [g.op("Reshape", [g.op("MatMul", [hn, "wq"]), "shape_q"])], perm=[0, 2, 1, 3])
+    xc = g.op("Mul", [q, "cos"])
+    lo = g.op("Slice", [q, "z", "h", "ax"])
+    hi = g.op("Slice", [q, "h", "d", "ax"])
+    rot = g.op("Concat", [g.op("Neg", [hi]), lo], axis=-1)
+    qr = g.op("Add", [xc, g.op("Mul", [rot, "sin"])], "q_rot")
+    sc = g.op("MatMul", [qr, g.op("Transpose", ["k"], perm=[0, 1, 3, 2])])
+    pr = g.op("Softmax", [g.op("Add", [g.op("Mul", [sc, "scale"]), "mask"])], "probs", axis=-1)
+    ga, up = g.op("MatMul", [hn, "wg"]), g.op("MatMul", [hn, "wu"])
+    g.op("Mul", [g.op("Mul", [ga, g.op("Sigmoid", [ga])]), up], "gated")
+    for o in ("normed", "q_rot", "probs", "gated"):
+        g.output(o)
+    return g
+
+
+@pytest.mark.parametrize("B,S,T", [(3, 1, 37), (2, 5, 5), (1, 4, 20)])
+def test_runtime_recognises_the_chains(cuda, B, S, T):
+    from rmlk_b200.runtime import ModelInstance
+    hidden, heads, D = 64, 4, 16
+    spec = block_graph(hidden, heads, D)
+    rng = np.random.default_rng(1)
+    feeds = {"x": rng.standard_normal((B, S, hidden), dtype=np.float32), "cos": rng.standard_normal((B, 1, S, D), dtype=np.float32),
+             "sin": rng.standard_normal((B, 1, S, D), dtype=np.float32), "k": rng.standard_normal((B, heads, T, D), dtype=np.float32),
+             "mask": np.where(rng.random((B, 1, S, T)) > 0.7, np.finfo(np.float32).min, 0.0).astype(np.float32)}
+    feeds["mask"][..., 0] = 0.0
+    want = graph_cpu.run_graph(spec, feeds)
+
+    def run(no_fusion):
+        if no_fusion:
+            os.environ["RMLK_B200_NO_FUSION"] = "1"
+        try:
+            inst = ModelInstance(spec.to_runtime())
+        finally:
+            os.environ.pop("RMLK_B200_NO_FUSION", None)
+        for k, v in feeds.items():
+            inst.set_input(k, v)
+        inst.launch()
+        return {o: inst.read(o) for o in spec.outputs}, inst.fused, inst.last_launches
+
+    fused, counts, n_fused = run(False)
+    plain, counts0, n_plain = run(True)
+    assert counts == (4, 4, 0), counts          # RMSNorm, rotary, softmax and SwiGLU chains, all ran fused
+    assert counts0 == (0, 0, 0)
+    assert n_fused == n_plain - (5 + 6 + 2 + 2) - 1, (n_fused, n_plain)   # launches saved (rotary also reads q as a view: one copy less)
+    for o in spec.outputs:
+        scale = np.max(np.abs(want[o]))
+        assert np.max(np.abs(fused[o] - want[o])) <= 1e-4 * scale, o
+        assert np.max(np.abs(fused[o] - plain[o])) <= 2e-6 * scale, o
+
+
+def test_chain_falls_back_when_tensors_do_not_fit(cuda):
+    """Same node pattern as RMSNorm, but the last Mul broadcasts the result up ([1, cols] * [rows, cols]): the fused
+    kernel does not cover that, so the single ops run and the result is still right."""
+    from rmlk_b200.runtime import ModelInstance
+    g = GraphSpec()
+    g.input("x", np.float32, [1, 0])
+    g.input("w", np.float32, [0, 0])
+    g.const("two", np.array(2.0, np.float32))
+    g.const("eps", np.array(1e-5, np.float32))
+    var = g.op("ReduceMean", [g.op("Pow", ["x", "two"])], axes=[-1], keepdims=1)
+    g.op("Mul", [g.op("Div", ["x", g.op("Sqrt", [g.op("Add", [var, "eps"])])]), "w"], "y")
+    g.output("y")
+    rng = np.random.default_rng(2)
+    feeds = {"x": rng.standard_normal((1, 40), dtype=np.float32), "w": rng.standard_normal((6, 40), dtype=np.float32)}
+    inst = ModelInstance(g.to_runtime())
+    for k, v in feeds.items():
+        inst.set_input(k, v)
+    inst.launch()
+    got = inst.read("y")
+    want = graph_cpu.run_graph(g, feeds)["y"]
+    assert inst.fused == (1, 0, 1)
+    assert got.shape == want.shape == (6, 40)
+    assert np.max(np.abs(got - want)) <= 1e-5 * np.max(np.abs(want))
+    # a value of the chain that is also a graph output keeps the chain from being matched at all
+    g2 = GraphSpec()
+    g2.input("x", np.float32, [0, 0])
+    g2.const("w", rng.standard_normal(40).astype(np.float32))
+    g2.const("two", np.array(2.0, np.float32))
+    g2.const("eps", np.array(1e-5, np.float32))
+    var = g2.op("ReduceMean", [g2.op("Pow", ["x", "two"])], "var", axes=[-1], keepdims=1)
+    g2.op("Mul", [g2.op("Div", ["x", g2.op("Sqrt", [g2.op("Add", [var, "eps"])])]), "w"], "y")
+    g2.output("y")
+    g2.output("var")
+    inst2 = ModelInstance(g2.to_runtime())
+    inst2.set_input("x", feeds["x"])
+    inst2.launch()
+    assert inst2.fused == (0, 0, 0)
+    w2 = graph_cpu.run_graph(g2, {"x": feeds["x"]})
+    assert np.max(np.abs(inst2.read("y") - w2["y"])) <= 1e-5 * np.max(np.abs(w2["y"]))
+    assert np.max(np.abs(inst2.read("var") - w2["var"])) <= 1e-5 * np.max(np.abs(w2["var"]))
