@@ -91,7 +91,11 @@ RMLK_API int rmlk_instance_bind(rmlk_instance* inst, const char* output, const c
  * returns when everything is enqueued, unless an op needed a device value on the host. */
 RMLK_API int rmlk_instance_run(rmlk_instance* inst);
 RMLK_API int rmlk_instance_synchronize(rmlk_instance* inst);
-/* Shape / dtype / device address of a graph output (or any named value) after a run. */
+/* Shape / dtype / device address of a graph output (or any named value) after a run.  *device_ptr is NULL for an
+ * output kept as a strided view: a bound output that is Concat(bound input, new rows) - a KV cache - lives in a
+ * buffer with spare room along the concat axis and is appended in place (rmlk_instance_bind); rmlk_instance_read
+ * still returns it dense.  RMLK_B200_NO_INPLACE_APPEND=1 in the environment keeps such outputs dense (one copy of
+ * the whole cache per run, as the reference's Concat does, backend/concat.rs:28-76). */
 RMLK_API int rmlk_instance_value_info(rmlk_instance* inst, const char* name, int* dtype, int* rank, int64_t* dims,
                                       void** device_ptr);
 /* Copies a value to host memory and waits for it (get_outputs, runtime/src/core/instance.rs:58-82). */

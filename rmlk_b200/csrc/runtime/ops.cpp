@@ -806,8 +806,81 @@ void op_transpose(const Ctx& c) {
     c.launched();
 }
 
+// Concat(cache, new rows) whose result is carried to the next run as the cache (a bound output, see Binding): the
+// cache lives in one buffer with spare room along the axis, only the new rows are copied in behind the old ones,
+// and the result is a strided view of that buffer.  False: conditions not met, the general Concat runs.
+bool concat_append(const Ctx& c) {
+    if (c.n.outputs.empty() || c.n.inputs.size() != 2) return false;
+    const int vid = c.n.outputs[0];
+    const int bi = c.I.binding_of_out[vid];
+    if (bi < 0 || !c.I.bindings[bi].appendable) return false;
+    Binding& b = c.I.bindings[bi];
+    Tensor* past = c.raw(0);
+    Tensor* add = c.raw(1);
+    if (!past || !add || past->dtype != add->dtype || past->shape.size() != add->shape.size() || past->shape.empty()) return false;
+    const int64_t rank = static_cast<int64_t>(past->shape.size());
+    const int64_t axis = b.axis < 0 ? b.axis + rank : b.axis;
+    if (axis < 0 || axis >= rank) return false;
+    for (int64_t d = 0; d < rank; d++)
+        if (d != axis && past->shape[d] != add->shape[d]) return false;
+    const size_t elem = dtype_size_of(past->dtype);
+    const int64_t outer = prod(past->shape, 0, axis), inner = prod(past->shape, axis + 1);
+    const int64_t tp = past->shape[axis], tn = add->shape[axis], total = tp + tn;
+    if (elem == 0 || outer <= 0 || inner <= 0) return false;
+    if (add->lazy) c.I.materialize(*add);
+    const size_t row = static_cast<size_t>(inner) * elem;  // bytes of one entry along the axis
+    const bool ours = b.store.ptr && past->data == b.store.ptr && b.cap >= tp;  // the view handed out by the previous run
+    if (past->lazy && !ours) c.I.materialize(*past);
+    if (!(ours && b.cap >= total)) {
+        // first run, a cache fed from outside, or out of room: move to a larger buffer (old rows copied once)
+        const int64_t ncap = total + std::max<int64_t>(64, total / 2);
+        void* np = nullptr;
+        check_cuda(cudaMalloc(&np, std::max<size_t>(static_cast<size_t>(outer) * ncap * row, 256)), "cache cudaMalloc");
+        if (tp > 0) {
+            const size_t spitch = (ours ? static_cast<size_t>(b.cap) : static_cast<size_t>(tp)) * row;
+            check_cuda(cudaMemcpy2DAsync(np, static_cast<size_t>(ncap) * row, past->data, spitch, static_cast<size_t>(tp) * row, static_cast<size_t>(outer),
+                                         cudaMemcpyDeviceToDevice, c.I.stream), "cache move");
+            c.launched();
+        }
+        if (b.store.ptr) {
+            check_cuda(cudaStreamSynchronize(c.I.stream), "cudaStreamSynchronize");  // the old buffer is still being read
+            cudaFree(b.store.ptr);
+        }
+        b.store.ptr = np;
+        b.store.cap = static_cast<size_t>(outer) * ncap * row;
+        b.cap = ncap;
+    }
+    if (tn > 0) {
+        check_cuda(cudaMemcpy2DAsync(static_cast<char*>(b.store.ptr) + static_cast<size_t>(tp) * row, static_cast<size_t>(b.cap) * row, add->data,
+                                     static_cast<size_t>(tn) * row, static_cast<size_t>(tn) * row, static_cast<size_t>(outer), cudaMemcpyDeviceToDevice,
+                                     c.I.stream), "cache append");
+        c.launched();
+    }
+    Tensor& o = c.out(0);
+    o.dtype = past->dtype;
+    o.shape = past->shape;
+    o.shape[axis] = total;
+    o.mirror_valid = false;
+    o.mi.clear();
+    o.mf.clear();
+    o.data = b.store.ptr;
+    o.storage = nullptr;
+    o.pshape.clear();
+    o.pstride.clear();
+    o.lazy = outer > 1 && b.cap != total;  // otherwise the rows are contiguous: an ordinary dense tensor
+    if (o.lazy) {
+        // dims before the axis step over `cap` entries, the rest is dense
+        Shape st(rank, 1);
+        for (int64_t d = rank - 2; d >= 0; d--) st[d] = st[d + 1] * (d + 1 == axis ? b.cap : o.shape[d + 1]);
+        for (int64_t d = 0; d < rank; d++) push_dim(o.pshape, o.pstride, o.shape[d], st[d]);
+    }
+    o.present = true;
+    return true;
+}
+
 // backend/concat.rs:28-198
 void op_concat(const Ctx& c) {
+    if (concat_append(c)) return;
     Tensor& first = c.req(0);
     if (!in_set(first.dtype, {RMLK_F16, RMLK_F32, RMLK_F64, RMLK_I32, RMLK_U32, RMLK_I64, RMLK_U64})) unsupported_dtype(first.dtype, "concat");
     if (first.is_scalar()) raise(RMLK_ERR_INVALID_ARG, "scalars are not allowed");
@@ -1044,7 +1117,8 @@ void op_reshape(const Ctx& c) {
 
 // backend/unsqueeze.rs:60-130
 void op_unsqueeze(const Ctx& c) {
-    Tensor& x = c.req(0);
+    // inserting size-1 dims does not change the element order: a deferred view stays deferred
+    Tensor& x = c.may_defer(0) && c.raw(0) ? *c.raw(0) : c.req(0);
     std::vector<int64_t> axes;
     if (Tensor* at = c.in(1)) {
         if (at->shape.size() != 1) raise(RMLK_ERR_INVALID_ARG, "InvalidAxesRank");

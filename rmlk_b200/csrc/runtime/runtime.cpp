@@ -249,10 +249,12 @@ Instance::~Instance() {
     weights.release();
     status_word.release();
     matmul_ws.release();
+    read_staging.release();
     for (DeviceBuffer& b : input_bufs) b.release();
     for (Binding& b : bindings) {
         b.buf[0].release();
         b.buf[1].release();
+        b.store.release();
     }
     if (own_stream && stream) cudaStreamDestroy(stream);
 }
@@ -693,6 +695,17 @@ extern "C" int rmlk_instance_bind(rmlk_instance* inst, const char* output, const
     Binding b;
     b.out_id = o;
     b.in_id = i;
+    // output = Concat(input, something) along a fixed axis: a growing cache that can be appended in place
+    if (!getenv("RMLK_B200_NO_INPLACE_APPEND"))
+        for (const NodeDef& n : I.g.nodes) {
+            if (n.outputs.empty() || n.outputs[0] != o) continue;
+            auto ax = n.attrs.find("axis");
+            if (n.op == RMLK_OP_CONCAT && n.inputs.size() == 2 && n.inputs[0] == i && n.inputs[1] >= 0 && ax != n.attrs.end() &&
+                ax->second.kind == Attr::INT) {
+                b.appendable = true;
+                b.axis = static_cast<int>(ax->second.i);
+            }
+        }
     I.bindings.push_back(b);
     I.binding_of_out[o] = static_cast<int>(I.bindings.size()) - 1;
     return RMLK_OK;
@@ -724,12 +737,11 @@ extern "C" int rmlk_instance_value_info(rmlk_instance* inst, const char* name, i
     if (id < 0) raise(RMLK_ERR_INVALID_ARG, std::string("unknown value `") + name + "`");
     const Tensor& t = I.values[id];
     if (!t.present) raise(RMLK_ERR_INVALID_ARG, std::string("value `") + name + "` has no data");
-    if (t.lazy && device_ptr) raise(RMLK_ERR_INVALID_ARG, std::string("value `") + name + "` is a deferred view without a buffer of its own");
     if (dtype) *dtype = t.dtype;
     if (rank) *rank = static_cast<int>(t.shape.size());
     if (dims)
         for (size_t i = 0; i < t.shape.size() && i < RMLK_MAX_RANK; i++) dims[i] = t.shape[i];
-    if (device_ptr) *device_ptr = t.data;
+    if (device_ptr) *device_ptr = t.lazy ? nullptr : t.data;  // a strided view (growing cache) has no dense buffer to hand out
     return RMLK_OK;
     RT_CATCH
 }
@@ -742,9 +754,16 @@ extern "C" int rmlk_instance_read(rmlk_instance* inst, const char* name, void* d
     if (id < 0) raise(RMLK_ERR_INVALID_ARG, std::string("unknown value `") + name + "`");
     const Tensor& t = I.values[id];
     if (!t.present) raise(RMLK_ERR_INVALID_ARG, std::string("value `") + name + "` has no data");
-    if (t.lazy) raise(RMLK_ERR_INVALID_ARG, std::string("value `") + name + "` is a deferred view without a buffer of its own");
     if (nbytes != t.nbytes()) raise(RMLK_ERR_INVALID_ARG, std::string("read of `") + name + "`: size mismatch");
-    if (nbytes) check_cuda(cudaMemcpyAsync(dst, t.data, nbytes, cudaMemcpyDeviceToHost, I.stream), "output D2H");
+    const void* src = t.data;
+    if (t.lazy && nbytes) {
+        // a strided view (a cache kept in a buffer with spare room): gather it into a dense staging buffer first
+        void* tmp = I.read_staging.ensure(nbytes);
+        check_rc(rmlk_b200_strided_copy(reinterpret_cast<rmlk_stream_t>(I.stream), static_cast<int>(dtype_size_of(t.dtype)),
+                                        static_cast<int>(t.pshape.size()), t.pshape.data(), t.pstride.data(), t.data, tmp));
+        src = tmp;
+    }
+    if (nbytes) check_cuda(cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, I.stream), "output D2H");
     check_cuda(cudaStreamSynchronize(I.stream), "cudaStreamSynchronize");
     I.check_status();
     return RMLK_OK;

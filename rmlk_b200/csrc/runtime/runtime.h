@@ -142,6 +142,14 @@ struct Binding {  // output value -> input value, double-buffered
     int cur = 0;  // buffer the NEXT run writes
     Tensor carried;  // what the next run reads as the input
     bool have = false;
+    // Growing cache: the bound output is Concat(bound input, new rows) along `axis` (a KV cache append).  The data
+    // then lives in ONE buffer with room for `cap` entries along that axis; a run writes only the new rows behind
+    // the old ones and hands out a strided view (Tensor::lazy, row pitch = cap), so nothing of the old cache is
+    // copied.  The reference's Concat re-copies the whole cache every step (backend/concat.rs:28-76).
+    bool appendable = false;
+    int axis = 0;
+    int64_t cap = 0;
+    DeviceBuffer store;
 };
 
 // A chain of single-op nodes that one fused launch can stand for (RMSNorm, rotary embedding, SwiGLU gate,
@@ -173,6 +181,7 @@ struct Instance {
     std::unique_ptr<Arena> arena;
     DeviceBuffer status_word;   // device int for gather / scatter_nd diagnostics
     DeviceBuffer matmul_ws;     // split-K scratch
+    DeviceBuffer read_staging;  // dense copy of a strided output while it is read back
     std::vector<Binding> bindings;
     std::vector<Tensor> const_nodes;       // per node: the materialised `value` of a Constant op
     std::vector<int> last_use;             // per value id: index of the last node reading it (-1: never)

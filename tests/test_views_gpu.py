@@ -144,3 +144,64 @@ def test_transposed_weight_and_broadcast_batch(cuda):
     feeds = {"a": rng.standard_normal((3, 5, 2, 40), dtype=np.float32), "w": rng.standard_normal((1, 5, 40, 24), dtype=np.float32)}
     got, want, _ = run_both(g, feeds)
     assert np.max(np.abs(got["y"] - want["y"])) <= 1e-4 * np.max(np.abs(want["y"]))
+
+
+def test_bound_cache_is_appended_in_place(cuda):
+    """present = Concat(past, new, axis=2) carried to the next run: only the new rows are written, the result is a
+    strided view of a buffer with spare room; reading it back, attention over it, growth past the spare room and a
+    cache fed from outside must all behave like the copying Concat."""
+    import os
+    from rmlk_b200.runtime import ModelInstance
+    B, KV, G, D = 2, 2, 4, 16
+    g = GraphSpec()
+    g.input("q", np.float32, [B, KV * G, 1, D])
+    g.input("new", np.float32, [B, KV, 0, D])
+    g.input("past", np.float32, [B, KV, 0, D])
+    g.const("ax2", i64(2))
+    g.const("rep", i64(1, 1, G, 1, 1))
+    g.const("heads", i64(0, KV * G, -1, D))
+    g.op("Concat", ["past", "new"], "present", axis=2)
+    e = g.op("Expand", [g.op("Unsqueeze", ["present", "ax2"]), "rep"])
+    kt = g.op("Transpose", [g.op("Reshape", [e, "heads"])], perm=[0, 1, 3, 2])
+    g.op("MatMul", ["q", kt], "scores")
+    g.output("present")
+    g.output("scores")
+    rng = np.random.default_rng(11)
+
+    def drive(no_append):
+        if no_append:
+            os.environ["RMLK_B200_NO_INPLACE_APPEND"] = "1"
+        try:
+            inst = ModelInstance(g.to_runtime())
+            inst.bind("present", "past")
+        finally:
+            os.environ.pop("RMLK_B200_NO_INPLACE_APPEND", None)
+        return inst
+
+    inst, plain = drive(False), drive(True)
+    cache = np.zeros((B, KV, 0, D), np.float32)
+    r = np.random.default_rng(12)
+    launches = []
+    for step in range(75):
+        n_new = 3 if step == 0 else 1
+        new = r.standard_normal((B, KV, n_new, D), dtype=np.float32)
+        q = r.standard_normal((B, KV * G, 1, D), dtype=np.float32)
+        if step == 40:   # a cache handed in from outside replaces the carried one
+            cache = r.standard_normal((B, KV, 5, D), dtype=np.float32)
+        for m in (inst, plain):
+            m.set_input("q", q)
+            m.set_input("new", new)
+            if step == 0 or step == 40:
+                m.set_input("past", cache)
+            m.launch()
+        cache = np.concatenate([cache, new], axis=2)
+        launches.append(inst.last_launches)
+        want = np.matmul(q.astype(np.float64), np.repeat(cache, G, axis=1).transpose(0, 1, 3, 2).astype(np.float64))
+        got = inst.read("scores")
+        assert np.max(np.abs(got - want)) <= 1e-4 * np.max(np.abs(want)), step
+        assert np.array_equal(got, plain.read("scores")), step
+        if step in (0, 1, 39, 40, 41, 66, 67, 68, 74):
+            assert np.array_equal(inst.read("present"), cache), step
+            assert np.array_equal(plain.read("present"), cache), step
+    assert launches[5] == 2, launches[:8]    # one small copy of the new rows + the MatMul: the cache itself is not copied
+    assert plain.last_launches == 2          # (the copying Concat is one launch too, but moves the whole cache)
