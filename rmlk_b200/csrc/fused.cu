@@ -51,6 +51,51 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(int64_t cols, float ex
     for (int64_t c = threadIdx.x; c < cols; c += 256) dst[c] = __fmul_rn(__fdiv_rn(row[c], sd), w[c]);
 }
 
+// Same, for rows of up to 256 * 4 * NP elements with 16-byte alignment: the row is read once and held in registers.
+template <int NP>
+__global__ void __launch_bounds__(256) rmsnorm_f32_regs_kernel(int cols, float exponent, float eps, const float* __restrict__ x,
+                                                              const float* __restrict__ w, float* __restrict__ out) {
+    __shared__ double part[8];
+    const float4* row = reinterpret_cast<const float4*>(x + static_cast<int64_t>(blockIdx.x) * cols);
+    float4* dst = reinterpret_cast<float4*>(out + static_cast<int64_t>(blockIdx.x) * cols);
+    const float4* wv = reinterpret_cast<const float4*>(w);
+    const int packs = cols / 4;
+    float4 v[NP];
+    double acc = 0.0;
+#pragma unroll
+    for (int i = 0; i < NP; i++) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < packs) {
+            v[i] = row[c];
+            acc += static_cast<double>(powf(v[i].x, exponent));
+            acc += static_cast<double>(powf(v[i].y, exponent));
+            acc += static_cast<double>(powf(v[i].z, exponent));
+            acc += static_cast<double>(powf(v[i].w, exponent));
+        }
+    }
+    acc = warp_sum_d(acc);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    double total = 0.0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) total += part[i];
+    const float mean = static_cast<float>(total / static_cast<double>(cols));
+    const float sd = sqrtf(__fadd_rn(mean, eps));
+#pragma unroll
+    for (int i = 0; i < NP; i++) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < packs) {
+            const float4 g = wv[c];
+            float4 r;
+            r.x = __fmul_rn(__fdiv_rn(v[i].x, sd), g.x);
+            r.y = __fmul_rn(__fdiv_rn(v[i].y, sd), g.y);
+            r.z = __fmul_rn(__fdiv_rn(v[i].z, sd), g.z);
+            r.w = __fmul_rn(__fdiv_rn(v[i].w, sd), g.w);
+            dst[c] = r;
+        }
+    }
+}
+
 struct RopeParams {
     int64_t d[4];         // output dims, row-major; d[3] = head dim D
     int64_t xs[4], cs[4], ss[4];  // element strides of x, cos, sin per output dim (0 = broadcast)
@@ -158,8 +203,19 @@ extern "C" int rmlk_b200_rmsnorm(rmlk_stream_t stream, int dtype, int64_t rows, 
     if (rows == 0 || cols == 0) return RMLK_OK;
     if (!x || !weight || !out) return fail(RMLK_ERR_INVALID_ARG, "rmsnorm: NULL tensor pointer");
     if (rows > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "rmsnorm: too many rows");
-    rmsnorm_f32_kernel<<<static_cast<unsigned>(rows), 256, 0, as_stream(stream)>>>(cols, exponent, eps, static_cast<const float*>(x),
-                                                                                   static_cast<const float*>(weight), static_cast<float*>(out));
+    const float* xp = static_cast<const float*>(x);
+    const float* wp = static_cast<const float*>(weight);
+    float* op = static_cast<float*>(out);
+    cudaStream_t st = as_stream(stream);
+    const unsigned grid = static_cast<unsigned>(rows);
+    if (cols % 4 == 0 && cols <= 4096 && aligned_to(x, 16) && aligned_to(weight, 16) && aligned_to(out, 16)) {
+        const int c = static_cast<int>(cols);
+        if (cols <= 1024) rmsnorm_f32_regs_kernel<1><<<grid, 256, 0, st>>>(c, exponent, eps, xp, wp, op);
+        else if (cols <= 2048) rmsnorm_f32_regs_kernel<2><<<grid, 256, 0, st>>>(c, exponent, eps, xp, wp, op);
+        else rmsnorm_f32_regs_kernel<4><<<grid, 256, 0, st>>>(c, exponent, eps, xp, wp, op);
+    } else {
+        rmsnorm_f32_kernel<<<grid, 256, 0, st>>>(cols, exponent, eps, xp, wp, op);
+    }
     RMLK_CHECK_LAUNCH("rmsnorm_f32_kernel");
     return RMLK_OK;
 }

@@ -302,6 +302,104 @@ __global__ void __launch_bounds__(256) nt_rows_kernel(SkinnyParams p, uint32_t c
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Few rows of A against a narrow B (N <= 128), many problems, any K: decode attention context
+// ([4 heads, T] x [T, head_dim] per KV head).  One CTA per problem; LPR = N / 4 lanes cover one row of B (a
+// warp-wide load reads 32 / LPR whole rows, contiguous in memory), the 8 warps take successive row groups, A is
+// staged per k-chunk in shared memory as [k][m] so that one 16-byte shared load feeds the FMAs of four rows of A.
+// The k-lanes are added at the end: inside a warp by shuffles, across warps through shared memory in warp order.
+// ---------------------------------------------------------------------------------------------
+constexpr int NN_KC = 512;  // k-chunk of A staged in shared memory
+
+template <int MB, int LPR>
+__global__ void __launch_bounds__(256) nn_narrow_kernel(SkinnyParams p) {
+    constexpr int RPI = 32 / LPR;      // rows of B per warp-wide load
+    constexpr int ROWS = 8 * RPI;      // rows of B per CTA-wide load
+    constexpr int SA = MB < 4 ? MB : ((MB + 3) / 4) * 4;
+    __shared__ __align__(16) float sA[NN_KC * SA];
+    __shared__ __align__(16) float sRed[8 * MB * LPR * 4];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPR, rsel = lane / LPR;
+    const int64_t batch = blockIdx.x;
+    const float* __restrict__ A = p.a + batch * p.sa;
+    const float* __restrict__ B = p.b + batch * p.sb + 4 * sub;
+    const bool nin = 4 * sub < p.N;
+    float acc[MB][4];
+#pragma unroll
+    for (int m = 0; m < MB; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[m][j] = 0.f;
+    for (int64_t kc = 0; kc < p.K; kc += NN_KC) {
+        const int kn = static_cast<int>(p.K - kc < NN_KC ? p.K - kc : NN_KC);
+        __syncthreads();
+        for (int i = threadIdx.x; i < NN_KC * MB; i += 256) {
+            const int m = i / NN_KC, k = i - m * NN_KC;  // consecutive threads read consecutive k
+            sA[k * SA + m] = (m < p.M && k < kn) ? A[static_cast<int64_t>(m) * p.K + kc + k] : 0.f;
+        }
+        __syncthreads();
+        for (int k0 = warp * RPI + rsel; k0 < kn; k0 += 8 * ROWS) {
+            uint4 bv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int k = k0 + u * ROWS;
+                bv[u] = make_uint4(0, 0, 0, 0);
+                if (nin && k < kn) bv[u] = ld_stream_u4(B + (kc + k) * p.N);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int k = k0 + u * ROWS;
+                if (k < kn) {
+                    const float bx = __uint_as_float(bv[u].x), by = __uint_as_float(bv[u].y), bz = __uint_as_float(bv[u].z), bw = __uint_as_float(bv[u].w);
+                    float av[SA];
+                    if constexpr (SA % 4 == 0) {
+#pragma unroll
+                        for (int m = 0; m < SA; m += 4) {
+                            const float4 t = *reinterpret_cast<const float4*>(sA + k * SA + m);
+                            av[m] = t.x; av[m + 1] = t.y; av[m + 2] = t.z; av[m + 3] = t.w;
+                        }
+                    } else {
+#pragma unroll
+                        for (int m = 0; m < SA; m++) av[m] = sA[k * SA + m];
+                    }
+#pragma unroll
+                    for (int m = 0; m < MB; m++) {
+                        acc[m][0] = fmaf(av[m], bx, acc[m][0]);
+                        acc[m][1] = fmaf(av[m], by, acc[m][1]);
+                        acc[m][2] = fmaf(av[m], bz, acc[m][2]);
+                        acc[m][3] = fmaf(av[m], bw, acc[m][3]);
+                    }
+                }
+            }
+        }
+    }
+    // add the row groups of a warp, then the 8 warps in order
+#pragma unroll
+    for (int m = 0; m < MB; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float v = acc[m][j];
+#pragma unroll
+            for (int off = LPR; off < 32; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+            acc[m][j] = v;
+        }
+    if (rsel == 0) {
+#pragma unroll
+        for (int m = 0; m < MB; m++)
+            *reinterpret_cast<float4*>(sRed + ((warp * MB + m) * LPR + sub) * 4) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+    }
+    __syncthreads();
+    float* __restrict__ C = p.c + batch * p.sc;
+    for (int i = threadIdx.x; i < MB * LPR * 4; i += 256) {
+        const int m = i / (LPR * 4), n = i - m * (LPR * 4);
+        if (m < p.M && n < p.N) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) s += sRed[(w * MB + m) * LPR * 4 + n];
+            C[static_cast<int64_t>(m) * p.N + n] = s;
+        }
+    }
+}
+
 // Any other shape: one thread per output element, sequential fp32 dot product.
 __global__ void __launch_bounds__(256) nt_generic_kernel(SkinnyParams p, int64_t total) {
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
@@ -581,6 +679,23 @@ extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batc
                 else smallk1_kernel<4><<<grid, 256, 0, st>>>(p, total_cols, static_cast<uint32_t>(n));
             }
             RMLK_CHECK_LAUNCH("smallk_kernel");
+            return RMLK_OK;
+        }
+        // many problems with a narrow B: one CTA per problem reading whole rows of B
+        if (m <= 4 && n <= 128 && b_rows_aligned && batch >= sm_count() && batch <= 0x7fffffffll) {
+            p.ksplit = 1;
+            p.k_per_split = k;
+            p.c = static_cast<float*>(c);
+            const unsigned grid = static_cast<unsigned>(batch);
+#define RMLK_NN_NARROW(MB)                                                            \
+    if (n <= 32) nn_narrow_kernel<MB, 8><<<grid, 256, 0, st>>>(p);                    \
+    else if (n <= 64) nn_narrow_kernel<MB, 16><<<grid, 256, 0, st>>>(p);              \
+    else nn_narrow_kernel<MB, 32><<<grid, 256, 0, st>>>(p);
+            if (m == 1) { RMLK_NN_NARROW(1) }
+            else if (m == 2) { RMLK_NN_NARROW(2) }
+            else { RMLK_NN_NARROW(4) }
+#undef RMLK_NN_NARROW
+            RMLK_CHECK_LAUNCH("nn_narrow_kernel");
             return RMLK_OK;
         }
         int ksplit = skinny_plan(batch, n, k);

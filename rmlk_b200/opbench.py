@@ -161,6 +161,11 @@ def cases():
         bmm("matmul batched 2048x[1,64]x[64,520] (decode scores)", 2048, 1, 64, T),
         bmm("matmul batched 2048x[1,520]x[520,64] (decode context)", 2048, 1, T, 64),
         bmm("matmul batched 256x[512,64]x[64,512] (prefill scores)", 256, 512, 64, 512),
+        # grouped-query attention read from the KV cache in place: 4 query heads per KV head are 4 rows of one problem
+        generic("matmul_nt 512x[4,64]x[523,64]^T (decode scores, cache in place)", lambda: (rnd(512, 4, 64), rnd(512, 523, 64)),
+                lambda q, k: K.matmul_nt(q, k), flops=2 * 512 * 4 * 64 * 523),
+        generic("matmul 512x[4,523]x[523,64] (decode context, cache in place)", lambda: (rnd(512, 4, 523), rnd(512, 523, 64)),
+                lambda p, v: K.matmul(p, v), flops=2 * 512 * 4 * 64 * 523),
     ]
     return cs
 

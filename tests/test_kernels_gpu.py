@@ -308,7 +308,9 @@ MM_CASES = [(1, 1, 8192, 2048), (1, 8, 8192, 2048), (1, 16, 512, 2048), (1, 64, 
             (8, 128, 128, 64), (8, 128, 64, 128), (3, 5, 30, 9), (1, 1, 2048, 8192), (1, 200, 300, 4), (1, 4, 100, 1), (2, 16, 31, 1000),
             # many problems with a short K (one thread per column quad, no reduction)
             (2048, 1, 520, 64), (600, 2, 512, 128), (300, 4, 1024, 256), (300, 3, 1024, 252), (2048, 1, 160, 4),
-            (2048, 1, 523, 64), (700, 2, 517, 128), (400, 4, 1001, 40), (400, 3, 1001, 252)]
+            (2048, 1, 523, 64), (700, 2, 517, 128), (400, 4, 1001, 40), (400, 3, 1001, 252),
+            # many problems with a narrow right operand (one CTA per problem, whole rows of B per load)
+            (512, 4, 64, 523), (300, 1, 32, 100), (200, 3, 128, 77), (160, 2, 20, 1500), (150, 4, 4, 9)]
 
 
 @pytest.mark.parametrize("case", MM_CASES)
