@@ -295,6 +295,10 @@ RMLK_API int rmlk_b200_rope(rmlk_stream_t stream, int dtype, const int64_t* shap
 /* SwiGLU gate as exported: Mul(Mul(gate, Sigmoid(gate)), up), n elements each.  Replaces backend/sigmoid.rs (cuDNN
  * activation, kernels/activation.rs:6-39) and backend/mul.rs (x2). */
 RMLK_API int rmlk_b200_swiglu(rmlk_stream_t stream, int dtype, int64_t n, const void* gate, const void* up, void* out);
+/* Same with gate and up given as [rows, cols] blocks of wider matrices (row pitches in elements; e.g. the two halves of
+ * one MatMul against the concatenated gate and up weights); out is dense [rows, cols].  cols, pitches: multiples of 4. */
+RMLK_API int rmlk_b200_swiglu_pitched(rmlk_stream_t stream, int dtype, int64_t rows, int64_t cols, const void* gate,
+                             int64_t gate_pitch, const void* up, int64_t up_pitch, void* out);
 
 /* Attention probabilities as exported: Softmax(Add(Mul(scores, scale), mask), last axis).  scores / out: [d0, d1, d2, cols]
  * dense (lead3 = d0, d1, d2); mask rows are dense, mask_strides3 = its element strides over d0, d1, d2 (0 = broadcast);

@@ -143,6 +143,23 @@ __global__ void __launch_bounds__(256) swiglu_f32_vec_kernel(int64_t packs, cons
     out[i] = r;
 }
 
+// gate and up as [rows, cols] matrices with row pitches (columns of a wider matrix), out dense
+__global__ void __launch_bounds__(256) swiglu_f32_pitched_kernel(int64_t rows, int64_t cols, const float* __restrict__ g, int64_t ldg,
+                                                                const float* __restrict__ u, int64_t ldu, float* __restrict__ out) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    const int64_t packs = cols / 4;
+    if (i >= rows * packs) return;
+    const int64_t r = i / packs, c = (i - r * packs) * 4;
+    const float4 a = *reinterpret_cast<const float4*>(g + r * ldg + c);
+    const float4 b = *reinterpret_cast<const float4*>(u + r * ldu + c);
+    float4 o;
+    o.x = __fmul_rn(__fmul_rn(a.x, 1.0f / (1.0f + expf(-a.x))), b.x);
+    o.y = __fmul_rn(__fmul_rn(a.y, 1.0f / (1.0f + expf(-a.y))), b.y);
+    o.z = __fmul_rn(__fmul_rn(a.z, 1.0f / (1.0f + expf(-a.z))), b.z);
+    o.w = __fmul_rn(__fmul_rn(a.w, 1.0f / (1.0f + expf(-a.w))), b.w);
+    *reinterpret_cast<float4*>(out + r * cols + c) = o;
+}
+
 struct MaskParams {
     int64_t d[3];   // leading dims of the scores [d0, d1, d2, cols]
     int64_t ms[3];  // mask element strides for those dims (0 = broadcast); mask rows are dense
@@ -259,6 +276,22 @@ extern "C" int rmlk_b200_swiglu(rmlk_stream_t stream, int dtype, int64_t n, cons
                                                                                      static_cast<float*>(out));
     }
     RMLK_CHECK_LAUNCH("swiglu_f32_kernel");
+    return RMLK_OK;
+}
+
+extern "C" int rmlk_b200_swiglu_pitched(rmlk_stream_t stream, int dtype, int64_t rows, int64_t cols, const void* gate, int64_t gate_pitch,
+                                        const void* up, int64_t up_pitch, void* out) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for swiglu (f32 only)");
+    if (rows < 0 || cols < 0) return fail(RMLK_ERR_INVALID_ARG, "swiglu: negative extent");
+    if (rows == 0 || cols == 0) return RMLK_OK;
+    if (!gate || !up || !out) return fail(RMLK_ERR_INVALID_ARG, "swiglu: NULL tensor pointer");
+    if (cols % 4 || gate_pitch % 4 || up_pitch % 4 || !aligned_to(gate, 16) || !aligned_to(up, 16) || !aligned_to(out, 16))
+        return fail(RMLK_ERR_INVALID_ARG, "swiglu_pitched: columns, pitches and pointers must be multiples of 4 elements / 16 bytes");
+    const int64_t blocks = ceil_div64(rows * (cols / 4), 256);
+    if (blocks > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "swiglu: tensor too large");
+    swiglu_f32_pitched_kernel<<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(rows, cols, static_cast<const float*>(gate), gate_pitch,
+                                                                                            static_cast<const float*>(up), up_pitch, static_cast<float*>(out));
+    RMLK_CHECK_LAUNCH("swiglu_f32_pitched_kernel");
     return RMLK_OK;
 }
 

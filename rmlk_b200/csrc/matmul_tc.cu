@@ -141,6 +141,8 @@ int tc_matmul_plan(int64_t m, int64_t n, int64_t k) {
     // Up to TC_CLUSTER_MAX splits add up on chip (one thread-block cluster per tile); a little above that the
     // cluster form with fewer splits still wins over a scratch round trip plus a second kernel.
     if (s > TC_CLUSTER_MAX && s <= TC_CLUSTER_MAX + TC_CLUSTER_MAX / 2) s = TC_CLUSTER_MAX;
+    // (Capping a wider split at the cluster size for short K was measured and did not pay: [64,2048]x[2048,2048]
+    // took 13.9 us as 4-CTA clusters against 11.0 us + a 2-3 us reduction as an 8-way scratch split.)
     return static_cast<int>(s > 32 ? 32 : s);
 }
 

@@ -249,6 +249,54 @@ void push_dim(Shape& ps, Shape& pst, int64_t size, int64_t stride) {
     pst.push_back(stride);
 }
 
+// Splits physical dims where an edge of a logical dim falls inside one and divides it evenly (a dim of size
+// a * b and stride s is the two dims (a, s * b), (b, s)), so that afterwards every logical dim is a run of whole
+// physical dims.  False (ps / pst untouched) when some edge does not divide.
+bool refine_dims(const Shape& logical, Shape& ps, Shape& pst) {
+    Shape nps, npst;
+    size_t p = 0;
+    int64_t rem = 1, rstride = 0;
+    auto next = [&]() {
+        if (p >= ps.size()) return false;
+        rem = ps[p];
+        rstride = pst[p];
+        p++;
+        return true;
+    };
+    for (int64_t n : logical) {
+        if (n <= 0) return false;
+        int64_t need = n;
+        while (need > 1) {
+            if (rem == 1 && !next()) return false;
+            if (rem == 1) continue;
+            if (need >= rem) {
+                if (need % rem) return false;
+                push_dim(nps, npst, rem, rstride);
+                need /= rem;
+                rem = 1;
+            } else {
+                if (rem % need) return false;
+                push_dim(nps, npst, need, rstride * (rem / need));
+                rem /= need;
+                need = 1;
+            }
+        }
+    }
+    if (rem != 1) return false;
+    for (; p < ps.size(); p++)
+        if (ps[p] != 1) return false;
+    ps = nps;
+    pst = npst;
+    return true;
+}
+
+// Physical dims of `t`, refined to its logical shape, and the run of physical dims behind each logical dim.
+bool dims_of(const Tensor& t, Shape& ps, Shape& pst, std::vector<std::pair<int, int>>& groups) {
+    phys_of(t, ps, pst);
+    if (t.lazy) refine_dims(t.shape, ps, pst);
+    return group_dims(t.shape, ps, groups);
+}
+
 // A deferred right operand of MatMul that is a dense [k, n] (or, transposed, a dense [n, k]) matrix per
 // batch entry, whose batch dims are `outer` entries `sb` elements apart followed by `fold` entries that
 // all read the same matrix (stride 0: a broadcast such as grouped-query attention's repeated KV heads).
@@ -260,14 +308,15 @@ bool analyze_lazy_b(const Tensor& b, int64_t k, int64_t n, LazyB& r) {
     const size_t br = b.shape.size();
     if (br < 2) return false;
     std::vector<std::pair<int, int>> groups;
-    if (!group_dims(b.shape, b.pshape, groups)) return false;
+    Shape ps, pst;
+    if (!dims_of(b, ps, pst, groups)) return false;
     auto single = [&](const std::pair<int, int>& g, int64_t& stride) {
         int cnt = 0;
         stride = 0;
         for (int p = g.first; p < g.second; p++)
-            if (b.pshape[p] != 1) {
+            if (ps[p] != 1) {
                 cnt++;
-                stride = b.pstride[p];
+                stride = pst[p];
             }
         return cnt <= 1;
     };
@@ -279,7 +328,7 @@ bool analyze_lazy_b(const Tensor& b, int64_t k, int64_t n, LazyB& r) {
     r.transposed = !nn;
     Shape bd, bs;
     for (size_t d = 0; d + 2 < br; d++)
-        for (int p = groups[d].first; p < groups[d].second; p++) push_dim(bd, bs, b.pshape[p], b.pstride[p]);
+        for (int p = groups[d].first; p < groups[d].second; p++) push_dim(bd, bs, ps[p], pst[p]);
     r.fold = 1;
     while (!bd.empty() && bs.back() == 0) {
         r.fold *= bd.back();
@@ -767,8 +816,7 @@ void op_transpose(const Ctx& c) {
         }
         Shape ps, pst;
         std::vector<std::pair<int, int>> groups;
-        phys_of(*xr, ps, pst);
-        if (ok && group_dims(xr->shape, ps, groups)) {
+        if (ok && dims_of(*xr, ps, pst, groups)) {
             Shape oshape(rank), nps, npst;
             for (int d = 0; d < rank; d++) {
                 oshape[d] = xr->shape[perm[d]];
@@ -947,8 +995,7 @@ void op_expand(const Ctx& c) {
     if (c.may_defer(0) && prod(oshape) > HOST_MIRROR_MAX && xr->numel() > 0) {
         Shape ps, pst, nps, npst;
         std::vector<std::pair<int, int>> groups;
-        phys_of(*xr, ps, pst);
-        if (group_dims(xr->shape, ps, groups)) {
+        if (dims_of(*xr, ps, pst, groups)) {
             const size_t orank = oshape.size(), xrank = xr->shape.size();
             for (size_t d = 0; d < orank; d++) {
                 if (d + xrank < orank) {
@@ -1433,11 +1480,41 @@ bool Instance::run_fused(const FusedGroup& fg) {
         case FusedGroup::SWIGLU: {
             Tensor *gt = val(fg.v[0]), *up = val(fg.v[1]);
             if (!gt || !up || gt->dtype != RMLK_F32 || up->dtype != RMLK_F32 || gt->shape != up->shape) return false;
-            if (gt->lazy) materialize(*gt);
-            if (up->lazy) materialize(*up);
+            // a view that is a block of columns of a wider matrix (one MatMul against concatenated weights) is read in place
+            auto as_rows = [&](const Tensor& t, int64_t& pitch) {
+                if (t.shape.empty()) return false;
+                const int64_t cols = t.shape.back();
+                if (!t.lazy) {
+                    pitch = cols;
+                    return true;
+                }
+                if (t.pshape.size() == 2 && t.pshape[1] == cols && t.pstride[1] == 1 && t.pshape[0] * cols == t.numel()) {
+                    pitch = t.pstride[0];
+                    return true;
+                }
+                if (t.pshape.size() == 1 && t.pshape[0] == cols && t.pstride[0] == 1 && t.numel() == cols) {
+                    pitch = cols;
+                    return true;
+                }
+                return false;
+            };
+            int64_t pg = 0, pu = 0;
+            const bool pitched = (gt->lazy || up->lazy) && !gt->shape.empty() && gt->shape.back() % 4 == 0 && as_rows(*gt, pg) && as_rows(*up, pu) &&
+                                 pg % 4 == 0 && pu % 4 == 0 && reinterpret_cast<uintptr_t>(gt->data) % 16 == 0 && reinterpret_cast<uintptr_t>(up->data) % 16 == 0;
+            if (!pitched) {
+                if (gt->lazy) materialize(*gt);
+                if (up->lazy) materialize(*up);
+            }
             const Shape oshape = gt->shape;
+            const void *gd = gt->data, *ud = up->data;
             Tensor& o = c.make(0, RMLK_F32, oshape);
-            check_rc(rmlk_b200_swiglu(st, RMLK_F32, gt->numel(), gt->data, up->data, o.data));
+            if (o.numel() == 0) return true;
+            if (pitched) {
+                const int64_t cols = oshape.back();
+                check_rc(rmlk_b200_swiglu_pitched(st, RMLK_F32, o.numel() / cols, cols, gd, pg, ud, pu, o.data));
+            } else {
+                check_rc(rmlk_b200_swiglu(st, RMLK_F32, o.numel(), gd, ud, o.data));
+            }
             launches++;
             return true;
         }
@@ -1495,15 +1572,16 @@ bool Instance::run_fused(const FusedGroup& fg) {
             bool strided_ok = false;
             if (x->lazy) {
                 std::vector<std::pair<int, int>> groups_;
-                if (group_dims(x->shape, x->pshape, groups_)) {
+                Shape xps, xpst;
+                if (dims_of(*x, xps, xpst, groups_)) {
                     strided_ok = true;
                     for (int d = 0; d < 4 && strided_ok; d++) {
                         int cnt = 0;
                         xstr[d] = 0;
                         for (int p = groups_[d].first; p < groups_[d].second; p++)
-                            if (x->pshape[p] != 1) {
+                            if (xps[p] != 1) {
                                 cnt++;
-                                xstr[d] = x->pstride[p];
+                                xstr[d] = xpst[p];
                             }
                         strided_ok = cnt <= 1;
                     }
@@ -1526,7 +1604,99 @@ bool Instance::run_fused(const FusedGroup& fg) {
     return false;
 }
 
+// ---------------------------------------------------------------------------------------------
+// MatMul nodes sharing their left operand, against constant weights: one MatMul on concatenated weights
+// ---------------------------------------------------------------------------------------------
+void Instance::find_merged_matmuls() {
+    merged.clear();
+    merged_of_node.assign(g.nodes.size(), -1);
+    if (getenv("RMLK_B200_NO_MATMUL_MERGE")) return;
+    std::map<std::pair<int, int64_t>, std::vector<int>> by_input;  // (left operand, K) -> nodes
+    for (size_t i = 0; i < g.nodes.size(); i++) {
+        const NodeDef& n = g.nodes[i];
+        if (n.op != RMLK_OP_MATMUL || n.inputs.size() < 2 || n.outputs.empty() || n.inputs[0] < 0 || n.inputs[1] < 0) continue;
+        const ValueDef& w = g.values[n.inputs[1]];
+        const ValueDef& o = g.values[n.outputs[0]];
+        if (!w.is_const || w.dtype != RMLK_F32 || w.dims.size() != 2 || w.dims[0] <= 0 || w.dims[1] <= 0 || w.dims[1] % 4) continue;
+        if (o.is_output || g.values[n.inputs[0]].is_const) continue;
+        by_input[{n.inputs[0], w.dims[0]}].push_back(static_cast<int>(i));
+    }
+    for (auto& kv : by_input) {
+        if (kv.second.size() < 2) continue;
+        MergedMatMul mm;
+        mm.nodes = kv.second;
+        mm.a_value = kv.first.first;
+        mm.k = kv.first.second;
+        for (int node : mm.nodes) {
+            const int64_t n = g.values[g.nodes[node].inputs[1]].dims[1];
+            mm.col0.push_back(mm.n_total);
+            mm.n.push_back(n);
+            mm.n_total += n;
+        }
+        for (int node : mm.nodes) merged_of_node[node] = static_cast<int>(merged.size());
+        merged.push_back(std::move(mm));
+    }
+}
+
+// Called for a member node.  True: the node's output is in place (produced now, or earlier in this run by the
+// group's first member).  False: the tensors of this run do not fit; the node runs as an ordinary MatMul.
+bool Instance::run_merged_matmul(int node_index) {
+    MergedMatMul& mm = merged[merged_of_node[node_index]];
+    if (mm.done_in_run == run_counter) return node_index != mm.nodes.front() ? values[g.nodes[node_index].outputs[0]].present : false;
+    if (node_index != mm.nodes.front()) return false;  // the first member decided against it for this run
+    Tensor& a = values[mm.a_value];
+    if (!a.present || a.dtype != RMLK_F32 || a.shape.empty() || a.shape.back() != mm.k || a.numel() == 0) return false;
+    for (size_t j = 0; j < mm.nodes.size(); j++) {
+        const Tensor& w = values[g.nodes[mm.nodes[j]].inputs[1]];
+        if (!w.present || w.lazy || w.dtype != RMLK_F32 || w.shape.size() != 2 || w.shape[0] != mm.k || w.shape[1] != mm.n[j]) return false;
+    }
+    if (a.lazy) materialize(a);
+    if (!mm.ready) {
+        char* dst = static_cast<char*>(mm.w.ensure(static_cast<size_t>(mm.k) * mm.n_total * sizeof(float)));
+        for (size_t j = 0; j < mm.nodes.size(); j++) {
+            const Tensor& w = values[g.nodes[mm.nodes[j]].inputs[1]];
+            check_cuda(cudaMemcpy2DAsync(dst + mm.col0[j] * sizeof(float), mm.n_total * sizeof(float), w.data, mm.n[j] * sizeof(float),
+                                         mm.n[j] * sizeof(float), static_cast<size_t>(mm.k), cudaMemcpyDeviceToDevice, stream), "weight concatenation");
+        }
+        mm.ready = true;
+    }
+    const int64_t rows = a.numel() / mm.k;
+    Storage* y = arena->alloc(static_cast<size_t>(rows) * mm.n_total * sizeof(float));
+    const size_t need = rmlk_b200_matmul_workspace_bytes(RMLK_F32, 1, rows, mm.n_total, mm.k);
+    void* ws = need ? matmul_ws.ensure(need) : nullptr;
+    check_rc(rmlk_b200_matmul_ex(reinterpret_cast<rmlk_stream_t>(stream), RMLK_F32, 1, rows, mm.n_total, mm.k, a.data, 0, mm.w.ptr, 0, y->ptr,
+                                 rows * mm.n_total, ws, need, static_cast<int*>(status_word.ptr)));
+    status_dirty = true;
+    launches += need ? 2 : 1;
+    for (size_t j = 0; j < mm.nodes.size(); j++) {
+        Tensor& o = values[g.nodes[mm.nodes[j]].outputs[0]];
+        o.dtype = RMLK_F32;
+        o.shape.assign(a.shape.begin(), a.shape.end() - 1);  // [..., M, K] x [K, N_j] -> [..., M, N_j]
+        o.shape.push_back(mm.n[j]);
+        o.mirror_valid = false;
+        o.mi.clear();
+        o.mf.clear();
+        o.data = static_cast<char*>(y->ptr) + mm.col0[j] * sizeof(float);
+        o.storage = y;
+        if (j > 0) y->refs++;
+        o.pshape.clear();
+        o.pstride.clear();
+        o.lazy = rows > 1;
+        if (o.lazy) {
+            push_dim(o.pshape, o.pstride, rows, mm.n_total);
+            push_dim(o.pshape, o.pstride, mm.n[j], 1);
+        }
+        o.present = true;
+    }
+    mm.done_in_run = run_counter;
+    return true;
+}
+
 void Instance::run_node(const NodeDef& n) {
+    if (!merged_of_node.empty()) {
+        const int idx = static_cast<int>(&n - g.nodes.data());
+        if (idx >= 0 && idx < static_cast<int>(g.nodes.size()) && merged_of_node[idx] >= 0 && run_merged_matmul(idx)) return;
+    }
     Ctx c{*this, n};
     switch (n.op) {
         case RMLK_OP_NOOP: case RMLK_OP_CONST: return;

@@ -251,6 +251,7 @@ Instance::~Instance() {
     matmul_ws.release();
     read_staging.release();
     for (DeviceBuffer& b : input_bufs) b.release();
+    for (MergedMatMul& m : merged) m.w.release();
     for (Binding& b : bindings) {
         b.buf[0].release();
         b.buf[1].release();
@@ -313,6 +314,7 @@ void Instance::run() {
     check_cuda(cudaSetDevice(device), "cudaSetDevice");
     launches = 0;
     syncs = 0;
+    run_counter++;
     // hand back last run's intermediates
     for (size_t i = 0; i < values.size(); i++) {
         if (persistent[i]) continue;
@@ -586,6 +588,7 @@ extern "C" rmlk_instance* rmlk_instance_create(const rmlk_graph* g, int device, 
                 if (v >= 0) I.last_use[v] = static_cast<int>(i);
         if (const char* e = getenv("RMLK_B200_NO_FUSION")) I.fusion = e[0] != '1';
         I.find_fusions();  // recognise RMSNorm / rotary / SwiGLU / scale-mask-softmax chains; re-derives last_use
+        I.find_merged_matmuls();  // q / k / v and gate / up projections: one MatMul per shared left operand
         // one weight arena, one pass of uploads (the reference allocates and copies per tensor through a
         // 4 KiB bump allocator, runtime/src/providers/cuda/store.rs:95-262)
         size_t total = 0;

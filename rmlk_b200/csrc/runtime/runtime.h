@@ -164,8 +164,27 @@ struct FusedGroup {
     int v[8] = {-1, -1, -1, -1, -1, -1, -1, -1};  // value ids by role (per kind, see ops.cpp)
 };
 
+// MatMul nodes that multiply the SAME left operand by constant [K, N_i] weights (q / k / v projections, gate / up
+// projections) run as one MatMul against the weights laid side by side ([K, sum N_i], built once on the device);
+// each node's output is a block of columns of the product, handed out as a strided view.  One launch streams the
+// activations once and gives the weight-streaming kernel a wide N instead of several narrow ones.
+struct MergedMatMul {
+    std::vector<int> nodes;     // member node indices, in execution order
+    std::vector<int64_t> n, col0;
+    int a_value = -1;
+    int64_t k = 0, n_total = 0;
+    DeviceBuffer w;             // the concatenated weights
+    bool ready = false;
+    int64_t done_in_run = -1;   // run counter of the run in which the first member produced every output
+};
+
 struct Instance {
     Graph g;
+    std::vector<MergedMatMul> merged;
+    std::vector<int> merged_of_node;  // per node: index into `merged`, or -1
+    int64_t run_counter = 0;
+    void find_merged_matmuls();
+    bool run_merged_matmul(int node_index);
     std::vector<FusedGroup> groups;
     std::vector<int> group_of_node;  // per node: index into `groups`, or -1
     bool fusion = true;              // RMLK_B200_NO_FUSION=1 turns the substitution off
