@@ -206,8 +206,8 @@ def time_graph(fn_of_i, n=16, replays=4):
 
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernel named by DOMINANT, from the
 # capture summarised under profiles/ (None until a capture of that kernel exists).
-DOMINANT = "matmul_ffn"
-NCU_TRAFFIC_BYTES = {"matmul_ffn": 67_684_352 + 1_249_792}   # profiles/tc_gemm_kernel_ffn_m64.md
+DOMINANT = "matmul_gate_up"
+NCU_TRAFFIC_BYTES = {}   # filled from the ncu capture summarised under profiles/ (dram read + write bytes per launch)
 
 
 def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):
@@ -251,7 +251,9 @@ def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):
     add("concat_kv", "concat_kernel", lambda i: K.concat([past[i % len(past)], new], 2, out=dst), 8 * B * 8 * T * 64, [B, 8, T, 64])
     del past, dst
     # weight-streaming MatMul at the FFN gate/up shape and at the lm_head
-    for name, (m, k, n) in (("matmul_ffn", (B, 2048, 8192)), ("matmul_lm_head", (B, 2048, 128256))):
+    # gate | up projections as the runtime runs them (one MatMul on the concatenated weights), the down projection, the lm_head
+    for name, (m, k, n) in (("matmul_gate_up", (B, 2048, 16384)), ("matmul_qkv", (B, 2048, 3072)), ("matmul_down", (B, 8192, 2048)),
+                            ("matmul_lm_head", (B, 2048, 128256))):
         w = ring(lambda: torch.randn(k, n, device=dev) * 0.02, 4 * k * n)
         x = torch.randn(m, k, device=dev)
         y = torch.empty(m, n, device=dev)

@@ -154,6 +154,8 @@ def cases():
         matmul("matmul GEMV M=1 K=2048 N=8192", 1, 2048, 8192),
         matmul("matmul M=8 K=2048 N=8192", 8, 2048, 8192),
         matmul("matmul M=64 K=2048 N=8192", 64, 2048, 8192),
+        matmul("matmul M=64 K=2048 N=16384 (gate|up merged)", 64, 2048, 16384),
+        matmul("matmul M=64 K=2048 N=3072 (q|k|v merged)", 64, 2048, 3072),
         matmul("matmul M=64 K=8192 N=2048", 64, 8192, 2048),
         matmul("matmul M=64 K=2048 N=2048", 64, 2048, 2048),
         matmul("matmul M=64 K=2048 N=128256 (lm_head)", 64, 2048, 128256),
