@@ -1,7 +1,7 @@
-"""Headline benchmark: decode tok/s of a Llama-3.2-1B-shaped fp32 model run as un-fused ONNX-style ops.
+"""Headline benchmark: decode tok/s of a Llama-3.2-1B-shaped fp32 model given as an exported (un-fused) op graph.
 
-Workload (BASELINE config 3): 16 layers, hidden 2048, 32 q / 8 kv heads, head_dim 64, FFN 8192, vocab 128256,
-random-init weights; 64 independent requests per GPU decoded as one batch, 512-token uniform-random prompts,
+Workload (the full-model decode configuration of the benchmark plan): 16 layers, hidden 2048, 32 q / 8 kv heads,
+head_dim 64, FFN 8192, vocab 128256, random-init weights; 64 independent requests per GPU decoded as one batch, 512-token uniform-random prompts,
 then greedy-style decode steps of one token per request (context 512 + step).  A "step" is one decode
 step over the 64 requests = one pass of the op graph through the host runtime and kernels of
 librmlk_b200.so.  Requests are sharded across GPUs with no collective (one process per GPU, weights
@@ -60,7 +60,9 @@ def workload_config(cfg, batch, prompt):
 # clocks
 # ---------------------------------------------------------------------------------------------------
 class ClockSampler:
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+    """nvidia-smi polled every 20 ms in the background; stop(windows) keeps the samples whose timestamp falls inside
+    one of the (start, end) wall-clock windows, i.e. the samples taken under load during the timed regions."""
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
@@ -75,7 +77,8 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, windows=None):
+        import datetime
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if not self.proc:
             return out
@@ -84,17 +87,22 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
-        sm, mx, reasons = [], [], set()
+        sm, mx, reasons, total = [], [], set(), 0
         try:
             for line in open(self.path):
                 f = [x.strip() for x in line.split(",")]
                 if len(f) < 9:
                     continue
                 try:
-                    sm.append(float(f[1]))
-                    mx.append(float(f[2]))
+                    ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                    clk, cmax = float(f[1]), float(f[2])
                 except ValueError:
                     continue
+                total += 1
+                if windows and not any(w0 <= ts <= w1 for w0, w1 in windows):
+                    continue
+                sm.append(clk)
+                mx.append(cmax)
                 for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
                     if v.lower().startswith("active"):
                         reasons.add(name)
@@ -105,6 +113,7 @@ class ClockSampler:
             out["sm_mhz"] = statistics.median(sm)
             out["sm_max_mhz"] = max(mx)
             out["samples"] = len(sm)
+        out["samples_total"] = total
         out["reasons"] = sorted(reasons)
         return out
 
@@ -207,7 +216,7 @@ def time_graph(fn_of_i, n=16, replays=4):
 # ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernel named by DOMINANT, from the
 # capture summarised under profiles/ (None until a capture of that kernel exists).
 DOMINANT = "matmul_gate_up"
-NCU_TRAFFIC_BYTES = {}   # filled from the ncu capture summarised under profiles/ (dram read + write bytes per launch)
+NCU_TRAFFIC_BYTES = {"matmul_gate_up": 134_793_472 + 3_464_448}   # profiles/tc_gemm_kernel_ffn_m64.md
 
 
 def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):
@@ -357,15 +366,19 @@ def run_ours(args):
 
     # ---- device-resident timing -----------------------------------------------------------------
     with torch.cuda.stream(stream):
+        # the clock sampler starts before the warm-up (nvidia-smi takes a moment to come up); only samples that
+        # fall inside the two timed regions are kept
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        windows = []
         keep = []
         for _ in range(W):
             keep.append(device_step())
         barrier()
-        sampler = ClockSampler(local)
-        if rank == 0:
-            sampler.start()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches = 0
+        win0 = time.time()
         e0.record(stream)
         host0 = time.perf_counter()
         for _ in range(K_):
@@ -374,7 +387,7 @@ def run_ours(args):
         host_enqueue_ms = (time.perf_counter() - host0) * 1000.0   # host time to enqueue the K steps (no waiting on the GPU)
         e1.record(stream)
         barrier()
-        clocks = sampler.stop() if rank == 0 else {}
+        windows.append((win0, time.time()))
         dev_ms = max_over_ranks(e0.elapsed_time(e1))
         decode_launches = inst.last_launches
         inst.synchronize()
@@ -387,6 +400,7 @@ def run_ours(args):
         h2d = 0
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
+        win0 = time.time()
         t0.record(stream)
         wall0 = time.perf_counter()
         for _ in range(K_):
@@ -394,6 +408,8 @@ def run_ours(args):
         t1.record(stream)
         barrier()
         wall_ms = (time.perf_counter() - wall0) * 1000.0
+        windows.append((win0, time.time()))
+        clocks = sampler.stop(windows) if rank == 0 else {}
         e2e_ms = max_over_ranks(max(t0.elapsed_time(t1), wall_ms))
 
     value = world * B * K_ / (dev_ms * 1e-3)
@@ -442,7 +458,7 @@ def run_ours(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=32)
+    ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--requests", type=int, default=REQUESTS_PER_GPU)

@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(256) nt_rows_kernel(SkinnyParams p, uint32_t c
     }
     const float* __restrict__ B = p.b + batch * p.sb + 4 * sub;
     float* __restrict__ C = p.c + batch * p.sc;
-    constexpr int UN = LPR < 8 ? LPR : 8;
+    constexpr int UN = LPR < 16 ? LPR : 16;  // a warp keeps up to 16 row loads (8 KB) in flight
     for (int it0 = 0; it0 < LPR; it0 += UN) {
         uint4 bv[UN];
 #pragma unroll

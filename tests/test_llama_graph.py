@@ -3,7 +3,7 @@
 CPU: the op list of rmlk_b200.llama.build_graph, walked by the numpy interpreter (oracle/graph_cpu.py), must
 equal an independently written dense numpy decoder (float64) for prefill and for incremental decode with a
 KV cache.  GPU: the same graphs through librmlk_b200.so must match the interpreter — end-to-end logits at
-rel 1e-4 (the path's stated bar), including BASELINE config 2 (one Llama-3.2-1B-shaped layer, 128-token prefill
+rel 1e-4 (the path's stated bar), including the single-layer configuration of the benchmark plan (one Llama-3.2-1B-shaped layer, 128-token prefill
 then 32 decode steps).
 """
 import numpy as np
@@ -148,7 +148,7 @@ def test_tiny_decoder_gpu_vs_oracle(cuda):
 
 @pytest.mark.gpu
 def test_one_1b_shaped_layer_prefill_128_decode_32(cuda):
-    """BASELINE config 2: hidden 2048, 32 q heads, 8 kv heads, head_dim 64, FFN 8192, fp32, N(0, 0.02) init;
+    """Single-layer configuration of the benchmark plan: hidden 2048, 32 q heads, 8 kv heads, head_dim 64, FFN 8192, fp32, N(0, 0.02) init;
     batch 1, 128-token prefill then 32 decode steps; every step's output against the CPU interpreter."""
     cfg = llama.LLAMA_1B_ONE_LAYER
     w = llama.make_weights_host(cfg, seed=0, with_embedding=False)
