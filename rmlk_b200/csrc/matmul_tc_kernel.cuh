@@ -42,6 +42,17 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
         mbar_init(accum_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // The first STAGES loads need nothing but their barriers: they go out now, while TMEM is being allocated
+        // and the other warps arrive, instead of after the CTA-wide sync (the start-up latency of a CTA is a
+        // large part of a launch with few k-blocks).
+        for (int it = 0; it < n_iters && it < STAGES; it++) {
+            const uint32_t st = base + it * L::STAGE_BYTES;
+            const int k0 = (it_begin + it) * BK;
+            mbar_expect_tx(full_bar(it), L::W_BYTES + L::A_BYTES);
+#pragma unroll
+            for (int j = 0; j < 4; j++) tma_load_2d(st + j * 4096, &tmW, n0 + 32 * j, k0, full_bar(it));
+            tma_load_2d(st + L::W_BYTES, &tmA, k0, m0, full_bar(it));
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(L::TMEM_COLS) : "memory");
@@ -57,9 +68,9 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (lane == 0) {
-            for (int it = 0; it < n_iters; it++) {
+            for (int it = STAGES; it < n_iters; it++) {  // the first STAGES loads were issued before the CTA-wide sync
                 const int s = it % STAGES;
-                if (it >= STAGES && !mbar_wait(empty_bar(s), ((it / STAGES) - 1) & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(empty_bar(s), ((it / STAGES) - 1) & 1, abort_flag, p.status)) break;
                 const uint32_t st = base + s * L::STAGE_BYTES;
                 const int k0 = (it_begin + it) * BK;
                 mbar_expect_tx(full_bar(s), L::W_BYTES + L::A_BYTES);
