@@ -200,6 +200,12 @@ RMLK_API int rmlk_b200_transpose(rmlk_stream_t stream, int elem_size, int rank, 
  * (cuda/src/kernels/transpose.rs:38-80) - when the host runtime has kept the chain as a view. */
 RMLK_API int rmlk_b200_strided_copy(rmlk_stream_t stream, int elem_size, int rank, const int64_t* shape,
                            const int64_t* strides, const void* in, void* out);
+/* Strided view -> strided view in one launch: element i (row-major over `shape`) is read at sum idx_d * in_strides[d]
+ * and written at sum idx_d * out_strides[d] (strides in elements; the views must not overlap; fewer than 2^31 units).
+ * Used to put rows that exist only as a view straight into their slot of a carried cache, where the reference runs
+ * Transpose (backend/transpose.rs:44-178) and then Concat over the whole cache (backend/concat.rs:28-198). */
+RMLK_API int rmlk_b200_strided_copy_to(rmlk_stream_t stream, int elem_size, int rank, const int64_t* shape, const int64_t* in_strides,
+                              const int64_t* out_strides, const void* in, void* out);
 
 /* Concat of n_inputs tensors along an axis; every input is viewed as [outer, axis_dims[i] * inner].
  * Replaces the nested cuMemcpyDtoD loops of runtime/src/providers/cuda/backend/concat.rs:28-76.
@@ -245,6 +251,24 @@ RMLK_API int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, in
 RMLK_API int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                         const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
                         int64_t c_batch_stride, void* workspace, size_t workspace_bytes, int* status);
+/* Same, with hints.  RMLK_MATMUL_B_STATIC: nothing still in flight on the device writes B (model weights).  The
+ * kernels of this library let the next kernel of a stream be scheduled while the previous one drains, each waiting for
+ * its predecessor before it touches memory; with this flag the tensor-core kernel requests its first tiles of B
+ * before that wait, so the weight stream starts under the tail of the previous kernel.  flags = 0: as _ex. */
+#define RMLK_MATMUL_B_STATIC 1
+RMLK_API int rmlk_b200_matmul_flags(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                           const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
+                           int64_t c_batch_stride, void* workspace, size_t workspace_bytes, int* status, int flags);
+/* Unbatched MatMul for a caller that adds split-K partial sums in its own next kernel (rmlk_b200_add_rmsnorm does).
+ * When the kernel plan for the shape splits K through the workspace, the [*parts][m*n] slabs are left in `workspace`
+ * (to be added in slab order starting from 0.f - the order rmlk_b200_matmul uses) and c is NOT written; otherwise c
+ * holds the result and *parts = 1.  Same kernels as rmlk_b200_matmul_ex (cuda/src/kernels/gemm.rs:206-231 in the
+ * reference has no such form: cuBLAS reduces internally). */
+RMLK_API int rmlk_b200_matmul_parts(rmlk_stream_t stream, int dtype, int64_t m, int64_t n, int64_t k, const void* a, const void* b,
+                           void* c, void* workspace, size_t workspace_bytes, int* status, int flags, int* parts);
+/* dst[i] = 0.f + src[0][i] + ... + src[parts-1][i] (slabs of n floats, dense): the split-K reduction that
+ * rmlk_b200_matmul runs after a workspace split, for callers of rmlk_b200_matmul_parts that need the plain result. */
+RMLK_API int rmlk_b200_sum_parts(rmlk_stream_t stream, int dtype, int parts, int64_t n, const void* src, void* dst);
 /* C[b] = A[b] x B[b]^T with B stored [n,k] row-major: what MatMul(A, Transpose(B, swap of the last two dims))
  * computes in the reference through a Transpose copy (cuda/src/kernels/transpose.rs:38-80) followed by
  * cublasGemmStridedBatchedEx (cuda/src/kernels/gemm.rs:206-231), without the copy.  A is [m,k], C is [m,n],
@@ -285,12 +309,26 @@ RMLK_API size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int64
 RMLK_API int rmlk_b200_rmsnorm(rmlk_stream_t stream, int dtype, int64_t rows, int64_t cols, const void* x, float exponent, float eps,
                       const void* weight, void* out);
 
+/* Residual Add followed by RMSNorm: sum_out = a + b, norm_out = RMSNorm(sum_out) as above, one launch.  b may be the
+ * b_parts >= 1 split-K slabs left by rmlk_b200_matmul_parts (slab stride b_part_stride elements), added in slab order
+ * before the Add, so the values equal MatMul -> Add -> RMSNorm run op by op.  a, b slabs, sum_out, norm_out: [rows, cols]
+ * dense; sum_out must not overlap a or b.  Replaces backend/add.rs plus the RMSNorm chain's launches. */
+RMLK_API int rmlk_b200_add_rmsnorm(rmlk_stream_t stream, int dtype, int64_t rows, int64_t cols, const void* a, const void* b, int b_parts,
+                          int64_t b_part_stride, float exponent, float eps, const void* weight, void* sum_out, void* norm_out);
+
 /* Rotary embedding as exported: Add(Mul(x, cos), Mul(Concat(Neg(x[..., D/2:]), x[..., :D/2]), sin)).  shape4 = output dims
  * [d0, d1, d2, D] (dense output); *_strides = element strides of x / cos / sin per output dim, 0 to broadcast (x may be
  * a permuted view).  Replaces backend/mul.rs (x2), slice.rs:49-464 (x2), neg.rs, concat.rs:28-198, add.rs. */
 RMLK_API int rmlk_b200_rope(rmlk_stream_t stream, int dtype, const int64_t* shape4, const int64_t* x_strides,
                    const int64_t* cos_strides, const int64_t* sin_strides, const void* x, const void* cosv, const void* sinv,
                    void* out);
+
+/* Same, with the output placed by the caller: out_strides = element strides of the output per dim (NULL = dense).
+ * Lets the rotated keys of a decode step be written straight into their slot of a carried KV cache instead of being
+ * copied there by Concat (backend/concat.rs:28-198 re-copies the whole cache). */
+RMLK_API int rmlk_b200_rope_to(rmlk_stream_t stream, int dtype, const int64_t* shape4, const int64_t* x_strides,
+                      const int64_t* cos_strides, const int64_t* sin_strides, const void* x, const void* cosv, const void* sinv,
+                      void* out, const int64_t* out_strides);
 
 /* SwiGLU gate as exported: Mul(Mul(gate, Sigmoid(gate)), up), n elements each.  Replaces backend/sigmoid.rs (cuDNN
  * activation, kernels/activation.rs:6-39) and backend/mul.rs (x2). */

@@ -36,6 +36,43 @@ int cuda_fail(cudaError_t e, const char* what);
 // Number of SMs of the current device (cached per device; an immutable capability table).
 int sm_count();
 
+// ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Consecutive kernels of one stream normally run strictly one after the other:
+// the next grid is scheduled only when the previous one has drained, and each small launch pays that gap.
+// A kernel launched through launch_dep may be scheduled as soon as every CTA of the previous kernel has called
+// dep_trigger() (or exited); it must then call dep_wait() before its first access to global memory, which blocks
+// until the previous grid has completed and its writes are visible.  Kernels here call both at their very top,
+// so that only scheduling and launch latency overlap, never memory accesses: ordering is exactly stream order.
+// Both calls do nothing for a kernel launched the ordinary way.  RMLK_B200_NO_PDL=1 launches everything the
+// ordinary way.
+// ---------------------------------------------------------------------------------------------
+bool dep_launch_enabled();
+
+#ifdef __CUDACC__
+__device__ __forceinline__ void dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dep_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// the usual opening of a kernel: let the next kernel be scheduled, then wait for the previous one
+__device__ __forceinline__ void dep_sync() {
+    dep_trigger();
+    dep_wait();
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dep(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = dep_launch_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 inline size_t dtype_size(int dt) {
     switch (dt) {
         case RMLK_F16: case RMLK_U16: case RMLK_I16: return 2;

@@ -1,6 +1,7 @@
 // Library-wide helpers: thread-local error text, device capability cache, version.
 #include "common.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace rmlk {
@@ -30,6 +31,15 @@ int sm_count() {
         counts[dev] = n;
     }
     return counts[dev];
+}
+
+bool dep_launch_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("RMLK_B200_NO_PDL");
+        v = (e && e[0] == '1') ? 0 : 1;
+    }
+    return v == 1;
 }
 
 }  // namespace rmlk

@@ -180,6 +180,7 @@ extern "C" int rmlk_b200_where(rmlk_stream_t stream, int dtype, int rank, const 
 // per R stores.
 __global__ void __launch_bounds__(256) expand_repeat_kernel(uint64_t in_packs, uint32_t inner_packs, FastDiv inner_div, uint32_t repeat,
                                                             const uint4* __restrict__ in, uint4* __restrict__ out) {
+    dep_sync();
     const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (idx >= in_packs) return;
     uint64_t o;
@@ -241,7 +242,7 @@ extern "C" int rmlk_b200_expand(rmlk_stream_t stream, int elem_size, int in_rank
             const uint64_t in_packs = static_cast<uint64_t>(outer) * inner_packs;
             if (in_packs == 0) return RMLK_OK;
             if (in_packs / 256 < 0x7fffffffull) {
-                expand_repeat_kernel<<<static_cast<unsigned>((in_packs + 255) / 256), 256, 0, st>>>(
+                launch_dep(expand_repeat_kernel, dim3(static_cast<unsigned>((in_packs + 255) / 256)), dim3(256), 0, st, 
                     in_packs, static_cast<uint32_t>(inner_packs), FastDiv(static_cast<uint32_t>(inner_packs)), static_cast<uint32_t>(repeat),
                     static_cast<const uint4*>(in), static_cast<uint4*>(out));
                 RMLK_CHECK_LAUNCH("expand_repeat_kernel");

@@ -152,6 +152,7 @@ constexpr int EW_BLOCK = 256;
 // ---- one input ------------------------------------------------------------------------------
 template <int E, typename F, typename TO, typename T0>
 __global__ void __launch_bounds__(EW_BLOCK) ew_vec_kernel1(EwParams<1> p, TO* __restrict__ out, const T0* __restrict__ a) {
+    dep_sync();
     const uint64_t item = static_cast<uint64_t>(blockIdx.x) * EW_BLOCK + threadIdx.x;
     if (item >= p.n_items) return;
     uint64_t ii;
@@ -166,6 +167,7 @@ __global__ void __launch_bounds__(EW_BLOCK) ew_vec_kernel1(EwParams<1> p, TO* __
 
 template <bool WIDE, typename F, typename TO, typename T0>
 __global__ void __launch_bounds__(EW_BLOCK) ew_scalar_kernel1(EwParams<1> p, TO* __restrict__ out, const T0* __restrict__ a) {
+    dep_sync();
     const uint64_t item = static_cast<uint64_t>(blockIdx.x) * EW_BLOCK + threadIdx.x;
     if (item >= p.n_items) return;
     uint64_t ii;
@@ -178,6 +180,7 @@ __global__ void __launch_bounds__(EW_BLOCK) ew_scalar_kernel1(EwParams<1> p, TO*
 template <int E, typename F, typename TO, typename T0, typename T1>
 __global__ void __launch_bounds__(EW_BLOCK)
     ew_vec_kernel2(EwParams<2> p, TO* __restrict__ out, const T0* __restrict__ a, const T1* __restrict__ b) {
+    dep_sync();
     const uint64_t item = static_cast<uint64_t>(blockIdx.x) * EW_BLOCK + threadIdx.x;
     if (item >= p.n_items) return;
     uint64_t ii;
@@ -194,6 +197,7 @@ __global__ void __launch_bounds__(EW_BLOCK)
 template <bool WIDE, typename F, typename TO, typename T0, typename T1>
 __global__ void __launch_bounds__(EW_BLOCK)
     ew_scalar_kernel2(EwParams<2> p, TO* __restrict__ out, const T0* __restrict__ a, const T1* __restrict__ b) {
+    dep_sync();
     const uint64_t item = static_cast<uint64_t>(blockIdx.x) * EW_BLOCK + threadIdx.x;
     if (item >= p.n_items) return;
     uint64_t ii;
@@ -207,6 +211,7 @@ __global__ void __launch_bounds__(EW_BLOCK)
 template <int E, typename F, typename TO, typename T0, typename T1, typename T2>
 __global__ void __launch_bounds__(EW_BLOCK) ew_vec_kernel3(EwParams<3> p, TO* __restrict__ out, const T0* __restrict__ a,
                                                            const T1* __restrict__ b, const T2* __restrict__ c) {
+    dep_sync();
     const uint64_t item = static_cast<uint64_t>(blockIdx.x) * EW_BLOCK + threadIdx.x;
     if (item >= p.n_items) return;
     uint64_t ii;
@@ -224,6 +229,7 @@ __global__ void __launch_bounds__(EW_BLOCK) ew_vec_kernel3(EwParams<3> p, TO* __
 template <bool WIDE, typename F, typename TO, typename T0, typename T1, typename T2>
 __global__ void __launch_bounds__(EW_BLOCK) ew_scalar_kernel3(EwParams<3> p, TO* __restrict__ out, const T0* __restrict__ a,
                                                               const T1* __restrict__ b, const T2* __restrict__ c) {
+    dep_sync();
     const uint64_t item = static_cast<uint64_t>(blockIdx.x) * EW_BLOCK + threadIdx.x;
     if (item >= p.n_items) return;
     uint64_t ii;
@@ -284,7 +290,7 @@ int ew_launch1(cudaStream_t st, int rank, const int64_t* shape, const int64_t* s
         if (d.rank == 1) dv.shape[0] = d.shape[0] - d.shape[0] % E;
         EwParams<1> p = ew_params<1>(dv, E);
         if (p.n_items <= EW_NARROW_LIMIT) {
-            ew_vec_kernel1<E, F, TO, T0><<<EW_GRID(p.n_items), EW_BLOCK, 0, st>>>(p, out, a);
+            launch_dep(ew_vec_kernel1<E, F, TO, T0>, dim3(EW_GRID(p.n_items)), dim3(EW_BLOCK), 0, st, p, out, a);
             RMLK_CHECK_LAUNCH("ew_vec_kernel1");
             if (d.rank > 1 || dv.shape[0] == d.shape[0]) return RMLK_OK;
             done = dv.shape[0];
@@ -298,9 +304,9 @@ int ew_launch1(cudaStream_t st, int rank, const int64_t* shape, const int64_t* s
     }
     EwParams<1> p = ew_params<1>(ds, 1);
     if (p.n_items <= EW_NARROW_LIMIT)
-        ew_scalar_kernel1<false, F, TO, T0><<<EW_GRID(p.n_items), EW_BLOCK, 0, st>>>(p, out + done, a2);
+        launch_dep(ew_scalar_kernel1<false, F, TO, T0>, dim3(EW_GRID(p.n_items)), dim3(EW_BLOCK), 0, st, p, out + done, a2);
     else
-        ew_scalar_kernel1<true, F, TO, T0><<<EW_GRID(p.n_items), EW_BLOCK, 0, st>>>(p, out + done, a2);
+        launch_dep(ew_scalar_kernel1<true, F, TO, T0>, dim3(EW_GRID(p.n_items)), dim3(EW_BLOCK), 0, st, p, out + done, a2);
     RMLK_CHECK_LAUNCH("ew_scalar_kernel1");
     return RMLK_OK;
 }
@@ -320,7 +326,7 @@ int ew_launch2(cudaStream_t st, int rank, const int64_t* shape, const int64_t* s
         if (d.rank == 1) dv.shape[0] = d.shape[0] - d.shape[0] % E;
         EwParams<2> p = ew_params<2>(dv, E);
         if (p.n_items <= EW_NARROW_LIMIT) {
-            ew_vec_kernel2<E, F, TO, T0, T1><<<EW_GRID(p.n_items), EW_BLOCK, 0, st>>>(p, out, a, b);
+            launch_dep(ew_vec_kernel2<E, F, TO, T0, T1>, dim3(EW_GRID(p.n_items)), dim3(EW_BLOCK), 0, st, p, out, a, b);
             RMLK_CHECK_LAUNCH("ew_vec_kernel2");
             if (d.rank > 1 || dv.shape[0] == d.shape[0]) return RMLK_OK;
             done = dv.shape[0];
@@ -336,9 +342,9 @@ int ew_launch2(cudaStream_t st, int rank, const int64_t* shape, const int64_t* s
     }
     EwParams<2> p = ew_params<2>(ds, 1);
     if (p.n_items <= EW_NARROW_LIMIT)
-        ew_scalar_kernel2<false, F, TO, T0, T1><<<EW_GRID(p.n_items), EW_BLOCK, 0, st>>>(p, out + done, a2, b2);
+        launch_dep(ew_scalar_kernel2<false, F, TO, T0, T1>, dim3(EW_GRID(p.n_items)), dim3(EW_BLOCK), 0, st, p, out + done, a2, b2);
     else
-        ew_scalar_kernel2<true, F, TO, T0, T1><<<EW_GRID(p.n_items), EW_BLOCK, 0, st>>>(p, out + done, a2, b2);
+        launch_dep(ew_scalar_kernel2<true, F, TO, T0, T1>, dim3(EW_GRID(p.n_items)), dim3(EW_BLOCK), 0, st, p, out + done, a2, b2);
     RMLK_CHECK_LAUNCH("ew_scalar_kernel2");
     return RMLK_OK;
 }
@@ -358,7 +364,7 @@ int ew_launch3(cudaStream_t st, int rank, const int64_t* shape, const int64_t* s
         if (d.rank == 1) dv.shape[0] = d.shape[0] - d.shape[0] % E;
         EwParams<3> p = ew_params<3>(dv, E);
         if (p.n_items <= EW_NARROW_LIMIT) {
-            ew_vec_kernel3<E, F, TO, T0, T1, T2><<<EW_GRID(p.n_items), EW_BLOCK, 0, st>>>(p, out, a, b, c);
+            launch_dep(ew_vec_kernel3<E, F, TO, T0, T1, T2>, dim3(EW_GRID(p.n_items)), dim3(EW_BLOCK), 0, st, p, out, a, b, c);
             RMLK_CHECK_LAUNCH("ew_vec_kernel3");
             if (d.rank > 1 || dv.shape[0] == d.shape[0]) return RMLK_OK;
             done = dv.shape[0];
@@ -376,9 +382,9 @@ int ew_launch3(cudaStream_t st, int rank, const int64_t* shape, const int64_t* s
     }
     EwParams<3> p = ew_params<3>(ds, 1);
     if (p.n_items <= EW_NARROW_LIMIT)
-        ew_scalar_kernel3<false, F, TO, T0, T1, T2><<<EW_GRID(p.n_items), EW_BLOCK, 0, st>>>(p, out + done, a2, b2, c2);
+        launch_dep(ew_scalar_kernel3<false, F, TO, T0, T1, T2>, dim3(EW_GRID(p.n_items)), dim3(EW_BLOCK), 0, st, p, out + done, a2, b2, c2);
     else
-        ew_scalar_kernel3<true, F, TO, T0, T1, T2><<<EW_GRID(p.n_items), EW_BLOCK, 0, st>>>(p, out + done, a2, b2, c2);
+        launch_dep(ew_scalar_kernel3<true, F, TO, T0, T1, T2>, dim3(EW_GRID(p.n_items)), dim3(EW_BLOCK), 0, st, p, out + done, a2, b2, c2);
     RMLK_CHECK_LAUNCH("ew_scalar_kernel3");
     return RMLK_OK;
 }

@@ -5,6 +5,7 @@
 // chain (runtime/ops.cpp); the single-op entry points stay the reference-facing interface.
 //
 //   rmsnorm             Pow(x, 2) -> ReduceMean(last axis, keepdims) -> Add(eps) -> Sqrt -> Div(x, .) -> Mul(., w)
+//   add_rmsnorm         the same on x = Add(a, b), x written out as well; b may still be split-K slabs of a MatMul
 //   rope                Mul(x, cos) + Mul(Concat(Neg(x[..., D/2:]), x[..., :D/2]), sin)
 //   swiglu              Mul(Mul(g, Sigmoid(g)), u)
 //   scale_mask_softmax  Softmax(Add(Mul(s, scale), mask), last axis)
@@ -32,14 +33,47 @@ __device__ __forceinline__ float warp_max_f(float v) {
     return v;
 }
 
+// Optional producer of the row in front of RMSNorm: x = a + b (the residual Add of a decoder layer), where b may
+// still be the `parts` split-K slabs of the MatMul that made it.  The slabs are added in slab order starting from
+// 0.f, exactly as the stand-alone split-K reduction does, then a + b as the Add kernel does, and x is written to
+// `sum` for the later consumers of the Add.  b == nullptr: the row is read from a as it is.
+struct RowAdd {
+    const float* b;
+    float* sum;
+    int parts;
+    int64_t part_stride;
+};
+
+__device__ __forceinline__ float row_add_value(const RowAdd& r, float a, int64_t i) {
+    float y;
+    if (r.parts == 1) {
+        y = r.b[i];
+    } else {
+        y = 0.f;
+        for (int k = 0; k < r.parts; k++) y += r.b[k * r.part_stride + i];
+    }
+    return __fadd_rn(a, y);
+}
+
 // One CTA of 256 threads per row.  The squares are summed in double, as the ReduceMean kernel does.
 __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(int64_t cols, float exponent, float eps, const float* __restrict__ x,
-                                                         const float* __restrict__ w, float* __restrict__ out) {
+                                                         const float* __restrict__ w, float* __restrict__ out, RowAdd ra) {
+    dep_sync();
     __shared__ double part[8];
-    const float* row = x + static_cast<int64_t>(blockIdx.x) * cols;
-    float* dst = out + static_cast<int64_t>(blockIdx.x) * cols;
+    const int64_t r0 = static_cast<int64_t>(blockIdx.x) * cols;
+    const float* row = x + r0;
+    float* dst = out + r0;
     double acc = 0.0;
-    for (int64_t c = threadIdx.x; c < cols; c += 256) acc += static_cast<double>(powf(row[c], exponent));
+    if (ra.b) {
+        for (int64_t c = threadIdx.x; c < cols; c += 256) {
+            const float v = row_add_value(ra, row[c], r0 + c);
+            ra.sum[r0 + c] = v;
+            acc += static_cast<double>(powf(v, exponent));
+        }
+        row = ra.sum + r0;  // each thread reads back only what it wrote itself
+    } else {
+        for (int64_t c = threadIdx.x; c < cols; c += 256) acc += static_cast<double>(powf(row[c], exponent));
+    }
     acc = warp_sum_d(acc);
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = acc;
     __syncthreads();
@@ -54,10 +88,12 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(int64_t cols, float ex
 // Same, for rows of up to 256 * 4 * NP elements with 16-byte alignment: the row is read once and held in registers.
 template <int NP>
 __global__ void __launch_bounds__(256) rmsnorm_f32_regs_kernel(int cols, float exponent, float eps, const float* __restrict__ x,
-                                                              const float* __restrict__ w, float* __restrict__ out) {
+                                                              const float* __restrict__ w, float* __restrict__ out, RowAdd ra) {
+    dep_sync();
     __shared__ double part[8];
-    const float4* row = reinterpret_cast<const float4*>(x + static_cast<int64_t>(blockIdx.x) * cols);
-    float4* dst = reinterpret_cast<float4*>(out + static_cast<int64_t>(blockIdx.x) * cols);
+    const int64_t r0 = static_cast<int64_t>(blockIdx.x) * cols;
+    const float4* row = reinterpret_cast<const float4*>(x + r0);
+    float4* dst = reinterpret_cast<float4*>(out + r0);
     const float4* wv = reinterpret_cast<const float4*>(w);
     const int packs = cols / 4;
     float4 v[NP];
@@ -67,6 +103,30 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_regs_kernel(int cols, float e
         const int c = threadIdx.x + 256 * i;
         if (c < packs) {
             v[i] = row[c];
+            if (ra.b) {
+                float4 y;
+                if (ra.parts == 1) {
+                    y = *reinterpret_cast<const float4*>(ra.b + r0 + 4 * c);
+                } else {
+                    y = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int k0 = 0; k0 < ra.parts; k0 += 8) {  // eight slab loads in flight, added in slab order
+                        float4 q[8];
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            if (k0 + j < ra.parts) q[j] = *reinterpret_cast<const float4*>(ra.b + (k0 + j) * ra.part_stride + r0 + 4 * c);
+#pragma unroll
+                        for (int j = 0; j < 8; j++)
+                            if (k0 + j < ra.parts) {
+                                y.x += q[j].x; y.y += q[j].y; y.z += q[j].z; y.w += q[j].w;
+                            }
+                    }
+                }
+                v[i].x = __fadd_rn(v[i].x, y.x);
+                v[i].y = __fadd_rn(v[i].y, y.y);
+                v[i].z = __fadd_rn(v[i].z, y.z);
+                v[i].w = __fadd_rn(v[i].w, y.w);
+                *reinterpret_cast<float4*>(ra.sum + r0 + 4 * c) = v[i];
+            }
             acc += static_cast<double>(powf(v[i].x, exponent));
             acc += static_cast<double>(powf(v[i].y, exponent));
             acc += static_cast<double>(powf(v[i].z, exponent));
@@ -99,10 +159,12 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_regs_kernel(int cols, float e
 struct RopeParams {
     int64_t d[4];         // output dims, row-major; d[3] = head dim D
     int64_t xs[4], cs[4], ss[4];  // element strides of x, cos, sin per output dim (0 = broadcast)
+    int64_t os[4];                // element strides of the output (dense, or a slot inside a larger buffer)
 };
 
 __global__ void __launch_bounds__(256) rope_f32_kernel(RopeParams p, int64_t total, const float* __restrict__ x, const float* __restrict__ cosv,
                                                       const float* __restrict__ sinv, float* __restrict__ out) {
+    dep_sync();
     const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= total) return;
     const int64_t D = p.d[3], half = D / 2;
@@ -119,10 +181,11 @@ __global__ void __launch_bounds__(256) rope_f32_kernel(RopeParams p, int64_t tot
     const float xv = x[xb + j * p.xs[3]];
     // rotate_half: Concat(Neg(x[half:]), x[:half]); Neg is x * -1
     const float rot = j < half ? __fmul_rn(x[xb + (j + half) * p.xs[3]], -1.0f) : x[xb + (j - half) * p.xs[3]];
-    out[i] = __fadd_rn(__fmul_rn(xv, cosv[cb]), __fmul_rn(rot, sinv[sb]));
+    out[i0 * p.os[0] + i1 * p.os[1] + i2 * p.os[2] + j * p.os[3]] = __fadd_rn(__fmul_rn(xv, cosv[cb]), __fmul_rn(rot, sinv[sb]));
 }
 
 __global__ void __launch_bounds__(256) swiglu_f32_kernel(int64_t n, const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ out) {
+    dep_sync();
     const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= n) return;
     const float gv = g[i];
@@ -132,6 +195,7 @@ __global__ void __launch_bounds__(256) swiglu_f32_kernel(int64_t n, const float*
 
 __global__ void __launch_bounds__(256) swiglu_f32_vec_kernel(int64_t packs, const float4* __restrict__ g, const float4* __restrict__ u,
                                                             float4* __restrict__ out) {
+    dep_sync();
     const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= packs) return;
     const float4 a = g[i], b = u[i];
@@ -146,6 +210,7 @@ __global__ void __launch_bounds__(256) swiglu_f32_vec_kernel(int64_t packs, cons
 // gate and up as [rows, cols] matrices with row pitches (columns of a wider matrix), out dense
 __global__ void __launch_bounds__(256) swiglu_f32_pitched_kernel(int64_t rows, int64_t cols, const float* __restrict__ g, int64_t ldg,
                                                                 const float* __restrict__ u, int64_t ldu, float* __restrict__ out) {
+    dep_sync();
     const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     const int64_t packs = cols / 4;
     if (i >= rows * packs) return;
@@ -169,6 +234,7 @@ struct MaskParams {
 template <int PER>
 __global__ void __launch_bounds__(256) scale_mask_softmax_f32_kernel(MaskParams p, int64_t rows, int cols, float scale, const float* __restrict__ s,
                                                                     const float* __restrict__ mask, float* __restrict__ out) {
+    dep_sync();
     const int64_t row = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 5;
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
@@ -213,6 +279,26 @@ __global__ void __launch_bounds__(256) scale_mask_softmax_f32_kernel(MaskParams 
 
 using namespace rmlk;
 
+static int launch_rmsnorm(rmlk_stream_t stream, int64_t rows, int64_t cols, const void* x, float exponent, float eps, const void* weight,
+                          void* out, const RowAdd& ra) {
+    const float* xp = static_cast<const float*>(x);
+    const float* wp = static_cast<const float*>(weight);
+    float* op = static_cast<float*>(out);
+    cudaStream_t st = as_stream(stream);
+    const unsigned grid = static_cast<unsigned>(rows);
+    const bool add_ok = !ra.b || (aligned_to(ra.b, 16) && aligned_to(ra.sum, 16) && ra.part_stride % 4 == 0);
+    if (cols % 4 == 0 && cols <= 4096 && aligned_to(x, 16) && aligned_to(weight, 16) && aligned_to(out, 16) && add_ok) {
+        const int c = static_cast<int>(cols);
+        if (cols <= 1024) launch_dep(rmsnorm_f32_regs_kernel<1>, dim3(grid), dim3(256), 0, st, c, exponent, eps, xp, wp, op, ra);
+        else if (cols <= 2048) launch_dep(rmsnorm_f32_regs_kernel<2>, dim3(grid), dim3(256), 0, st, c, exponent, eps, xp, wp, op, ra);
+        else launch_dep(rmsnorm_f32_regs_kernel<4>, dim3(grid), dim3(256), 0, st, c, exponent, eps, xp, wp, op, ra);
+    } else {
+        launch_dep(rmsnorm_f32_kernel, dim3(grid), dim3(256), 0, st, cols, exponent, eps, xp, wp, op, ra);
+    }
+    RMLK_CHECK_LAUNCH("rmsnorm_f32_kernel");
+    return RMLK_OK;
+}
+
 extern "C" int rmlk_b200_rmsnorm(rmlk_stream_t stream, int dtype, int64_t rows, int64_t cols, const void* x, float exponent, float eps,
                                  const void* weight, void* out) {
     if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for rmsnorm (f32 only)");
@@ -220,25 +306,31 @@ extern "C" int rmlk_b200_rmsnorm(rmlk_stream_t stream, int dtype, int64_t rows, 
     if (rows == 0 || cols == 0) return RMLK_OK;
     if (!x || !weight || !out) return fail(RMLK_ERR_INVALID_ARG, "rmsnorm: NULL tensor pointer");
     if (rows > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "rmsnorm: too many rows");
-    const float* xp = static_cast<const float*>(x);
-    const float* wp = static_cast<const float*>(weight);
-    float* op = static_cast<float*>(out);
-    cudaStream_t st = as_stream(stream);
-    const unsigned grid = static_cast<unsigned>(rows);
-    if (cols % 4 == 0 && cols <= 4096 && aligned_to(x, 16) && aligned_to(weight, 16) && aligned_to(out, 16)) {
-        const int c = static_cast<int>(cols);
-        if (cols <= 1024) rmsnorm_f32_regs_kernel<1><<<grid, 256, 0, st>>>(c, exponent, eps, xp, wp, op);
-        else if (cols <= 2048) rmsnorm_f32_regs_kernel<2><<<grid, 256, 0, st>>>(c, exponent, eps, xp, wp, op);
-        else rmsnorm_f32_regs_kernel<4><<<grid, 256, 0, st>>>(c, exponent, eps, xp, wp, op);
-    } else {
-        rmsnorm_f32_kernel<<<grid, 256, 0, st>>>(cols, exponent, eps, xp, wp, op);
-    }
-    RMLK_CHECK_LAUNCH("rmsnorm_f32_kernel");
-    return RMLK_OK;
+    RowAdd ra = {nullptr, nullptr, 0, 0};
+    return launch_rmsnorm(stream, rows, cols, x, exponent, eps, weight, out, ra);
+}
+
+extern "C" int rmlk_b200_add_rmsnorm(rmlk_stream_t stream, int dtype, int64_t rows, int64_t cols, const void* a, const void* b, int b_parts,
+                                     int64_t b_part_stride, float exponent, float eps, const void* weight, void* sum_out, void* norm_out) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for add_rmsnorm (f32 only)");
+    if (rows < 0 || cols < 0) return fail(RMLK_ERR_INVALID_ARG, "add_rmsnorm: negative extent");
+    if (b_parts < 1 || b_parts > 64) return fail(RMLK_ERR_INVALID_ARG, "add_rmsnorm: b_parts must be 1..64");
+    if (b_parts > 1 && b_part_stride < rows * cols) return fail(RMLK_ERR_INVALID_ARG, "add_rmsnorm: slabs of b overlap");
+    if (rows == 0 || cols == 0) return RMLK_OK;
+    if (!a || !b || !weight || !sum_out || !norm_out) return fail(RMLK_ERR_INVALID_ARG, "add_rmsnorm: NULL tensor pointer");
+    if (rows > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "add_rmsnorm: too many rows");
+    RowAdd ra = {static_cast<const float*>(b), static_cast<float*>(sum_out), b_parts, b_part_stride};
+    return launch_rmsnorm(stream, rows, cols, a, exponent, eps, weight, norm_out, ra);
 }
 
 extern "C" int rmlk_b200_rope(rmlk_stream_t stream, int dtype, const int64_t* shape4, const int64_t* x_strides, const int64_t* cos_strides,
                               const int64_t* sin_strides, const void* x, const void* cosv, const void* sinv, void* out) {
+    return rmlk_b200_rope_to(stream, dtype, shape4, x_strides, cos_strides, sin_strides, x, cosv, sinv, out, nullptr);
+}
+
+extern "C" int rmlk_b200_rope_to(rmlk_stream_t stream, int dtype, const int64_t* shape4, const int64_t* x_strides, const int64_t* cos_strides,
+                                 const int64_t* sin_strides, const void* x, const void* cosv, const void* sinv, void* out,
+                                 const int64_t* out_strides) {
     if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for rope (f32 only)");
     if (!shape4 || !x_strides || !cos_strides || !sin_strides) return fail(RMLK_ERR_INVALID_ARG, "rope: NULL shape / strides");
     RopeParams p;
@@ -251,11 +343,16 @@ extern "C" int rmlk_b200_rope(rmlk_stream_t stream, int dtype, const int64_t* sh
         p.ss[d] = sin_strides[d];
         total *= shape4[d];
     }
+    int64_t run = 1;
+    for (int d = 3; d >= 0; d--) {  // dense output unless the caller places it
+        p.os[d] = out_strides ? out_strides[d] : run;
+        run *= shape4[d] > 0 ? shape4[d] : 1;
+    }
     if (total == 0) return RMLK_OK;
     if (shape4[3] % 2) return fail(RMLK_ERR_INVALID_ARG, "rope: head dim must be even");
     if (!x || !cosv || !sinv || !out) return fail(RMLK_ERR_INVALID_ARG, "rope: NULL tensor pointer");
     if (ceil_div64(total, 256) > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "rope: tensor too large");
-    rope_f32_kernel<<<static_cast<unsigned>(ceil_div64(total, 256)), 256, 0, as_stream(stream)>>>(
+    launch_dep(rope_f32_kernel, dim3(static_cast<unsigned>(ceil_div64(total, 256))), dim3(256), 0, as_stream(stream), 
         p, total, static_cast<const float*>(x), static_cast<const float*>(cosv), static_cast<const float*>(sinv), static_cast<float*>(out));
     RMLK_CHECK_LAUNCH("rope_f32_kernel");
     return RMLK_OK;
@@ -268,11 +365,11 @@ extern "C" int rmlk_b200_swiglu(rmlk_stream_t stream, int dtype, int64_t n, cons
     if (!gate || !up || !out) return fail(RMLK_ERR_INVALID_ARG, "swiglu: NULL tensor pointer");
     cudaStream_t st = as_stream(stream);
     if (n % 4 == 0 && aligned_to(gate, 16) && aligned_to(up, 16) && aligned_to(out, 16) && ceil_div64(n / 4, 256) <= 0x7fffffffll) {
-        swiglu_f32_vec_kernel<<<static_cast<unsigned>(ceil_div64(n / 4, 256)), 256, 0, st>>>(n / 4, static_cast<const float4*>(gate),
+        launch_dep(swiglu_f32_vec_kernel, dim3(static_cast<unsigned>(ceil_div64(n / 4, 256))), dim3(256), 0, st, n / 4, static_cast<const float4*>(gate),
                                                                                              static_cast<const float4*>(up), static_cast<float4*>(out));
     } else {
         if (ceil_div64(n, 256) > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "swiglu: tensor too large");
-        swiglu_f32_kernel<<<static_cast<unsigned>(ceil_div64(n, 256)), 256, 0, st>>>(n, static_cast<const float*>(gate), static_cast<const float*>(up),
+        launch_dep(swiglu_f32_kernel, dim3(static_cast<unsigned>(ceil_div64(n, 256))), dim3(256), 0, st, n, static_cast<const float*>(gate), static_cast<const float*>(up),
                                                                                      static_cast<float*>(out));
     }
     RMLK_CHECK_LAUNCH("swiglu_f32_kernel");
@@ -289,7 +386,7 @@ extern "C" int rmlk_b200_swiglu_pitched(rmlk_stream_t stream, int dtype, int64_t
         return fail(RMLK_ERR_INVALID_ARG, "swiglu_pitched: columns, pitches and pointers must be multiples of 4 elements / 16 bytes");
     const int64_t blocks = ceil_div64(rows * (cols / 4), 256);
     if (blocks > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "swiglu: tensor too large");
-    swiglu_f32_pitched_kernel<<<static_cast<unsigned>(blocks), 256, 0, as_stream(stream)>>>(rows, cols, static_cast<const float*>(gate), gate_pitch,
+    launch_dep(swiglu_f32_pitched_kernel, dim3(static_cast<unsigned>(blocks)), dim3(256), 0, as_stream(stream), rows, cols, static_cast<const float*>(gate), gate_pitch,
                                                                                             static_cast<const float*>(up), up_pitch, static_cast<float*>(out));
     RMLK_CHECK_LAUNCH("swiglu_f32_pitched_kernel");
     return RMLK_OK;
@@ -319,11 +416,11 @@ extern "C" int rmlk_b200_scale_mask_softmax(rmlk_stream_t stream, int dtype, con
     float* o = static_cast<float*>(out);
     const unsigned grid = static_cast<unsigned>(blocks);
     const int c = static_cast<int>(cols);
-    if (cols <= 128) scale_mask_softmax_f32_kernel<4><<<grid, 256, 0, st>>>(p, rows, c, scale, s, m, o);
-    else if (cols <= 256) scale_mask_softmax_f32_kernel<8><<<grid, 256, 0, st>>>(p, rows, c, scale, s, m, o);
-    else if (cols <= 512) scale_mask_softmax_f32_kernel<16><<<grid, 256, 0, st>>>(p, rows, c, scale, s, m, o);
-    else if (cols <= 1024) scale_mask_softmax_f32_kernel<32><<<grid, 256, 0, st>>>(p, rows, c, scale, s, m, o);
-    else scale_mask_softmax_f32_kernel<64><<<grid, 256, 0, st>>>(p, rows, c, scale, s, m, o);
+    if (cols <= 128) launch_dep(scale_mask_softmax_f32_kernel<4>, dim3(grid), dim3(256), 0, st, p, rows, c, scale, s, m, o);
+    else if (cols <= 256) launch_dep(scale_mask_softmax_f32_kernel<8>, dim3(grid), dim3(256), 0, st, p, rows, c, scale, s, m, o);
+    else if (cols <= 512) launch_dep(scale_mask_softmax_f32_kernel<16>, dim3(grid), dim3(256), 0, st, p, rows, c, scale, s, m, o);
+    else if (cols <= 1024) launch_dep(scale_mask_softmax_f32_kernel<32>, dim3(grid), dim3(256), 0, st, p, rows, c, scale, s, m, o);
+    else launch_dep(scale_mask_softmax_f32_kernel<64>, dim3(grid), dim3(256), 0, st, p, rows, c, scale, s, m, o);
     RMLK_CHECK_LAUNCH("scale_mask_softmax_f32_kernel");
     return RMLK_OK;
 }

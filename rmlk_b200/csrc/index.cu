@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(256) gather_kernel(uint64_t total_units, uint3
                                                      FastDiv idx_div, int64_t axis_dim, uint64_t in_outer_units,
                                                      const U* __restrict__ data, const I* __restrict__ indices,
                                                      U* __restrict__ out, int* __restrict__ status) {
+    dep_sync();
     const uint64_t u = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (u >= total_units) return;
     uint32_t row, c, o, j;
@@ -63,10 +64,10 @@ static int gather_units(cudaStream_t st, int idx_dtype, uint64_t total, uint32_t
     const unsigned grid = static_cast<unsigned>((total + 255) / 256);
     const uint64_t in_outer = static_cast<uint64_t>(axis_dim) * row_units;
     if (idx_dtype == RMLK_I64)
-        gather_kernel<U, int64_t><<<grid, 256, 0, st>>>(total, row_units, FastDiv(row_units), n_idx, FastDiv(n_idx), axis_dim, in_outer,
+        launch_dep(gather_kernel<U, int64_t>, dim3(grid), dim3(256), 0, st, total, row_units, FastDiv(row_units), n_idx, FastDiv(n_idx), axis_dim, in_outer,
                                                         static_cast<const U*>(data), static_cast<const int64_t*>(indices), static_cast<U*>(out), status);
     else
-        gather_kernel<U, int32_t><<<grid, 256, 0, st>>>(total, row_units, FastDiv(row_units), n_idx, FastDiv(n_idx), axis_dim, in_outer,
+        launch_dep(gather_kernel<U, int32_t>, dim3(grid), dim3(256), 0, st, total, row_units, FastDiv(row_units), n_idx, FastDiv(n_idx), axis_dim, in_outer,
                                                         static_cast<const U*>(data), static_cast<const int32_t*>(indices), static_cast<U*>(out), status);
     RMLK_CHECK_LAUNCH("gather_kernel");
     return RMLK_OK;
@@ -88,6 +89,7 @@ struct ConcatTable {
 
 template <typename U>
 __global__ void __launch_bounds__(256) concat_kernel(ConcatTable t, U* __restrict__ out) {
+    dep_sync();
     const int i = blockIdx.y;
     const uint64_t ru = t.row_units[i];
     const uint64_t total = ru * t.outer;
@@ -124,6 +126,7 @@ struct TileParams {
 
 template <typename U>
 __global__ void __launch_bounds__(256) transpose_tile_kernel(TileParams p, const U* __restrict__ in, U* __restrict__ out) {
+    dep_sync();
     __shared__ U tile[32][33];
     const uint32_t tiles_x = (p.nx + 31) / 32;
     const uint32_t tiles_y = (p.ny + 31) / 32;
@@ -171,6 +174,7 @@ __device__ __forceinline__ uint32_t tile64_col(uint32_t x, uint32_t y) { return 
 
 template <bool VIN, bool VOUT>
 __global__ void __launch_bounds__(256) transpose_tile64_kernel(TileParams p, const uint32_t* __restrict__ in, uint32_t* __restrict__ out) {
+    dep_sync();
     __shared__ __align__(16) uint32_t tile[64 * 64];
     const uint32_t tiles_x = (p.nx + 63) / 64;
     const uint32_t tiles_y = (p.ny + 63) / 64;
@@ -267,6 +271,7 @@ template <typename T, int V>
 __global__ void __launch_bounds__(256) trilu_kernel(uint64_t total_packs, uint32_t col_packs, FastDiv col_div, uint32_t rows,
                                                     FastDiv row_div, int upper, int64_t k, const T* __restrict__ in,
                                                     T* __restrict__ out) {
+    dep_sync();
     const uint64_t u = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (u >= total_packs) return;
     uint32_t rowlin, cp, b, r;
@@ -301,11 +306,11 @@ static int trilu_typed(cudaStream_t st, int64_t batch, int64_t rows, int64_t col
     if (packs > EW_NARROW_LIMIT) return fail(RMLK_ERR_INVALID_ARG, "trilu: tensor too large");
     const unsigned grid = static_cast<unsigned>((packs + 255) / 256);
     if (vec)
-        trilu_kernel<T, VMAX><<<grid, 256, 0, st>>>(packs, static_cast<uint32_t>(cols / VMAX), FastDiv(static_cast<uint32_t>(cols / VMAX)),
+        launch_dep(trilu_kernel<T, VMAX>, dim3(grid), dim3(256), 0, st, packs, static_cast<uint32_t>(cols / VMAX), FastDiv(static_cast<uint32_t>(cols / VMAX)),
                                                     static_cast<uint32_t>(rows), FastDiv(static_cast<uint32_t>(rows)), upper, k,
                                                     static_cast<const T*>(in), static_cast<T*>(out));
     else
-        trilu_kernel<T, 1><<<grid, 256, 0, st>>>(packs, static_cast<uint32_t>(cols), FastDiv(static_cast<uint32_t>(cols)),
+        launch_dep(trilu_kernel<T, 1>, dim3(grid), dim3(256), 0, st, packs, static_cast<uint32_t>(cols), FastDiv(static_cast<uint32_t>(cols)),
                                                  static_cast<uint32_t>(rows), FastDiv(static_cast<uint32_t>(rows)), upper, k,
                                                  static_cast<const T*>(in), static_cast<T*>(out));
     RMLK_CHECK_LAUNCH("trilu_kernel");
@@ -334,17 +339,20 @@ template <> struct RangeOp<__half> {
 
 template <typename T>
 __global__ void __launch_bounds__(256) range_kernel(uint64_t n, T start, T delta, T* __restrict__ out) {
+    dep_sync();
     const uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i < n) out[i] = RangeOp<T>::at(start, delta, i);
 }
 
 template <typename U>
 __global__ void __launch_bounds__(256) fill_kernel(uint64_t n, U value, U* __restrict__ out) {
+    dep_sync();
     for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < n; i += static_cast<uint64_t>(gridDim.x) * 256) out[i] = value;
 }
 
 struct SmallWords { uint64_t w[32]; };
 __global__ void store_small_kernel(SmallWords v, int n, uint64_t* __restrict__ out) {
+    dep_sync();
     if (threadIdx.x < n) out[threadIdx.x] = v.w[threadIdx.x];
 }
 
@@ -371,6 +379,7 @@ __device__ __forceinline__ T scatter_apply(T in, T outv) {
 template <int RED, typename T>
 __global__ void __launch_bounds__(256) scatter_nd_kernel(ScatterParams p, const int64_t* __restrict__ indices,
                                                          const T* __restrict__ updates, T* __restrict__ out, int* __restrict__ status) {
+    dep_sync();
     const uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= p.total) return;
     const uint64_t t = i / p.slice_len;
@@ -400,11 +409,11 @@ static int scatter_typed(cudaStream_t st, int reduction, const ScatterParams& p,
     const T* up = static_cast<const T*>(updates);
     T* o = static_cast<T*>(out);
     switch (reduction) {
-        case RMLK_SCATTER_NONE: scatter_nd_kernel<RMLK_SCATTER_NONE, T><<<grid, 256, 0, st>>>(p, ix, up, o, status); break;
-        case RMLK_SCATTER_ADD: scatter_nd_kernel<RMLK_SCATTER_ADD, T><<<grid, 256, 0, st>>>(p, ix, up, o, status); break;
-        case RMLK_SCATTER_MUL: scatter_nd_kernel<RMLK_SCATTER_MUL, T><<<grid, 256, 0, st>>>(p, ix, up, o, status); break;
-        case RMLK_SCATTER_MAX: scatter_nd_kernel<RMLK_SCATTER_MAX, T><<<grid, 256, 0, st>>>(p, ix, up, o, status); break;
-        case RMLK_SCATTER_MIN: scatter_nd_kernel<RMLK_SCATTER_MIN, T><<<grid, 256, 0, st>>>(p, ix, up, o, status); break;
+        case RMLK_SCATTER_NONE: launch_dep(scatter_nd_kernel<RMLK_SCATTER_NONE, T>, dim3(grid), dim3(256), 0, st, p, ix, up, o, status); break;
+        case RMLK_SCATTER_ADD: launch_dep(scatter_nd_kernel<RMLK_SCATTER_ADD, T>, dim3(grid), dim3(256), 0, st, p, ix, up, o, status); break;
+        case RMLK_SCATTER_MUL: launch_dep(scatter_nd_kernel<RMLK_SCATTER_MUL, T>, dim3(grid), dim3(256), 0, st, p, ix, up, o, status); break;
+        case RMLK_SCATTER_MAX: launch_dep(scatter_nd_kernel<RMLK_SCATTER_MAX, T>, dim3(grid), dim3(256), 0, st, p, ix, up, o, status); break;
+        case RMLK_SCATTER_MIN: launch_dep(scatter_nd_kernel<RMLK_SCATTER_MIN, T>, dim3(grid), dim3(256), 0, st, p, ix, up, o, status); break;
         default: return fail(RMLK_ERR_INVALID_ARG, "scatter_nd: unknown reduction");
     }
     RMLK_CHECK_LAUNCH("scatter_nd_kernel");
@@ -490,11 +499,11 @@ extern "C" int rmlk_b200_concat(rmlk_stream_t stream, int elem_size, int n_input
         t.narrow = max_units <= EW_NARROW_LIMIT ? 1 : 0;
         dim3 grid(flat_grid(static_cast<int64_t>(max_units), 256, 16), cnt);
         switch (unit) {
-            case 16: concat_kernel<uint4><<<grid, 256, 0, st>>>(t, static_cast<uint4*>(out)); break;
-            case 8: concat_kernel<uint64_t><<<grid, 256, 0, st>>>(t, static_cast<uint64_t*>(out)); break;
-            case 4: concat_kernel<uint32_t><<<grid, 256, 0, st>>>(t, static_cast<uint32_t*>(out)); break;
-            case 2: concat_kernel<uint16_t><<<grid, 256, 0, st>>>(t, static_cast<uint16_t*>(out)); break;
-            default: concat_kernel<uint8_t><<<grid, 256, 0, st>>>(t, static_cast<uint8_t*>(out)); break;
+            case 16: launch_dep(concat_kernel<uint4>, dim3(grid), dim3(256), 0, st, t, static_cast<uint4*>(out)); break;
+            case 8: launch_dep(concat_kernel<uint64_t>, dim3(grid), dim3(256), 0, st, t, static_cast<uint64_t*>(out)); break;
+            case 4: launch_dep(concat_kernel<uint32_t>, dim3(grid), dim3(256), 0, st, t, static_cast<uint32_t*>(out)); break;
+            case 2: launch_dep(concat_kernel<uint16_t>, dim3(grid), dim3(256), 0, st, t, static_cast<uint16_t*>(out)); break;
+            default: launch_dep(concat_kernel<uint8_t>, dim3(grid), dim3(256), 0, st, t, static_cast<uint8_t*>(out)); break;
         }
         RMLK_CHECK_LAUNCH("concat_kernel");
     }
@@ -599,6 +608,104 @@ extern "C" int rmlk_b200_strided_copy(rmlk_stream_t stream, int elem_size, int r
     return view_copy(as_stream(stream), elem_size, n, oshape, ostr_in, in, out);
 }
 
+// Strided view -> strided view, one launch: element i (row-major over `shape`) is read at sum idx_d * in_strides[d]
+// and written at sum idx_d * out_strides[d].  The host runtime uses it to put rows that exist only as a view (a
+// block of columns of a wider MatMul result, permuted) straight into their slot of a carried cache, where the
+// reference copies twice (backend/transpose.rs:44-178, then backend/concat.rs:28-198 over the whole cache).
+struct Copy2Params {
+    int rank;
+    FastDiv div[RMLK_MAX_RANK];
+    int64_t is[RMLK_MAX_RANK], os[RMLK_MAX_RANK];
+};
+
+template <typename U>
+__global__ void __launch_bounds__(256) strided_copy2_kernel(Copy2Params p, uint32_t total, const U* __restrict__ in, U* __restrict__ out) {
+    dep_sync();
+    for (uint32_t i = blockIdx.x * 256u + threadIdx.x; i < total; i += gridDim.x * 256u) {
+        uint32_t t = i;
+        int64_t io = 0, oo = 0;
+        for (int d = p.rank - 1; d >= 0; d--) {
+            uint32_t q, r;
+            p.div[d].divmod(t, q, r);
+            t = q;
+            io += static_cast<int64_t>(r) * p.is[d];
+            oo += static_cast<int64_t>(r) * p.os[d];
+        }
+        out[oo] = in[io];
+    }
+}
+
+extern "C" int rmlk_b200_strided_copy_to(rmlk_stream_t stream, int elem_size, int rank, const int64_t* shape, const int64_t* in_strides,
+                                         const int64_t* out_strides, const void* in, void* out) {
+    if (rank < 0 || rank > RMLK_MAX_RANK || (rank > 0 && (!shape || !in_strides || !out_strides)))
+        return fail(RMLK_ERR_INVALID_ARG, "strided_copy_to: rank must be in [0, 8]");
+    if (elem_size != 1 && elem_size != 2 && elem_size != 4 && elem_size != 8) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "strided_copy_to: element size must be 1, 2, 4 or 8");
+    for (int d = 0; d < rank; d++) {
+        if (shape[d] < 0) return fail(RMLK_ERR_INVALID_ARG, "strided_copy_to: negative extent");
+        if (shape[d] == 0) return RMLK_OK;
+    }
+    if (!in || !out) return fail(RMLK_ERR_INVALID_ARG, "strided_copy_to: NULL tensor pointer");
+    // drop dims of size 1, merge neighbours that are contiguous on both sides
+    int64_t dim[RMLK_MAX_RANK], is[RMLK_MAX_RANK], os[RMLK_MAX_RANK];
+    int n = 0;
+    for (int d = 0; d < rank; d++) {
+        if (shape[d] == 1) continue;
+        if (n > 0 && is[n - 1] == in_strides[d] * shape[d] && os[n - 1] == out_strides[d] * shape[d]) {
+            dim[n - 1] *= shape[d];
+            is[n - 1] = in_strides[d];
+            os[n - 1] = out_strides[d];
+        } else {
+            dim[n] = shape[d];
+            is[n] = in_strides[d];
+            os[n++] = out_strides[d];
+        }
+    }
+    if (n == 0) {
+        dim[0] = 1; is[0] = 1; os[0] = 1;
+        n = 1;
+    }
+    // 16-byte units when both sides walk the innermost dim contiguously and everything else keeps the alignment
+    int unit = elem_size;
+    if (is[n - 1] == 1 && os[n - 1] == 1) {
+        for (int v = 16 / elem_size; v > 1; v /= 2) {
+            bool ok = dim[n - 1] % v == 0 && reinterpret_cast<uintptr_t>(in) % (v * elem_size) == 0 && reinterpret_cast<uintptr_t>(out) % (v * elem_size) == 0;
+            for (int d = 0; d + 1 < n && ok; d++) ok = is[d] % v == 0 && os[d] % v == 0;
+            if (ok) {
+                dim[n - 1] /= v;
+                for (int d = 0; d + 1 < n; d++) {
+                    is[d] /= v;
+                    os[d] /= v;
+                }
+                unit = v * elem_size;
+                break;
+            }
+        }
+    }
+    int64_t total = 1;
+    Copy2Params p;
+    p.rank = n;
+    for (int d = 0; d < n; d++) {
+        if (dim[d] > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "strided_copy_to: more than 2^31 units");
+        total *= dim[d];
+        if (total > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "strided_copy_to: more than 2^31 units");
+        p.div[d] = FastDiv(static_cast<uint32_t>(dim[d]));
+        p.is[d] = is[d];
+        p.os[d] = os[d];
+    }
+    cudaStream_t st = as_stream(stream);
+    const unsigned grid = flat_grid(total, 256, 16);
+    const uint32_t tot = static_cast<uint32_t>(total);
+    switch (unit) {
+        case 1: launch_dep(strided_copy2_kernel<uint8_t>, dim3(grid), dim3(256), 0, st, p, tot, static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out)); break;
+        case 2: launch_dep(strided_copy2_kernel<uint16_t>, dim3(grid), dim3(256), 0, st, p, tot, static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out)); break;
+        case 4: launch_dep(strided_copy2_kernel<uint32_t>, dim3(grid), dim3(256), 0, st, p, tot, static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out)); break;
+        case 8: launch_dep(strided_copy2_kernel<uint64_t>, dim3(grid), dim3(256), 0, st, p, tot, static_cast<const uint64_t*>(in), static_cast<uint64_t*>(out)); break;
+        default: launch_dep(strided_copy2_kernel<uint4>, dim3(grid), dim3(256), 0, st, p, tot, static_cast<const uint4*>(in), static_cast<uint4*>(out)); break;
+    }
+    RMLK_CHECK_LAUNCH("strided_copy2_kernel");
+    return RMLK_OK;
+}
+
 extern "C" int rmlk_b200_transpose(rmlk_stream_t stream, int elem_size, int rank, const int64_t* in_shape, const int64_t* perm,
                                    const void* in, void* out) {
     if (rank < 1 || rank > RMLK_MAX_RANK || !in_shape || !perm) return fail(RMLK_ERR_INVALID_ARG, "transpose: rank must be in [1, 8]");
@@ -682,20 +789,20 @@ static int view_copy(cudaStream_t st, int elem_size, int n, int64_t* oshape, int
         const unsigned grid64 = static_cast<unsigned>(tiles64 < (1u << 30) ? tiles64 : (1u << 30));
         const uint32_t* src = static_cast<const uint32_t*>(in);
         uint32_t* dst = static_cast<uint32_t*>(out);
-        if (vin && vout) transpose_tile64_kernel<true, true><<<grid64, 256, 0, st>>>(p, src, dst);
-        else if (vin) transpose_tile64_kernel<true, false><<<grid64, 256, 0, st>>>(p, src, dst);
-        else if (vout) transpose_tile64_kernel<false, true><<<grid64, 256, 0, st>>>(p, src, dst);
-        else transpose_tile64_kernel<false, false><<<grid64, 256, 0, st>>>(p, src, dst);
+        if (vin && vout) launch_dep(transpose_tile64_kernel<true, true>, dim3(grid64), dim3(256), 0, st, p, src, dst);
+        else if (vin) launch_dep(transpose_tile64_kernel<true, false>, dim3(grid64), dim3(256), 0, st, p, src, dst);
+        else if (vout) launch_dep(transpose_tile64_kernel<false, true>, dim3(grid64), dim3(256), 0, st, p, src, dst);
+        else launch_dep(transpose_tile64_kernel<false, false>, dim3(grid64), dim3(256), 0, st, p, src, dst);
         RMLK_CHECK_LAUNCH("transpose_tile64_kernel");
         return RMLK_OK;
     }
     const uint64_t tiles = static_cast<uint64_t>((p.nx + 31) / 32) * ((p.ny + 31) / 32) * p.n_batches;
     const unsigned grid = static_cast<unsigned>(tiles < (1u << 30) ? tiles : (1u << 30));
     switch (elem_size) {
-        case 1: transpose_tile_kernel<uint8_t><<<grid, 256, 0, st>>>(p, static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out)); break;
-        case 2: transpose_tile_kernel<uint16_t><<<grid, 256, 0, st>>>(p, static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out)); break;
-        case 4: transpose_tile_kernel<uint32_t><<<grid, 256, 0, st>>>(p, static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out)); break;
-        default: transpose_tile_kernel<uint64_t><<<grid, 256, 0, st>>>(p, static_cast<const uint64_t*>(in), static_cast<uint64_t*>(out)); break;
+        case 1: launch_dep(transpose_tile_kernel<uint8_t>, dim3(grid), dim3(256), 0, st, p, static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out)); break;
+        case 2: launch_dep(transpose_tile_kernel<uint16_t>, dim3(grid), dim3(256), 0, st, p, static_cast<const uint16_t*>(in), static_cast<uint16_t*>(out)); break;
+        case 4: launch_dep(transpose_tile_kernel<uint32_t>, dim3(grid), dim3(256), 0, st, p, static_cast<const uint32_t*>(in), static_cast<uint32_t*>(out)); break;
+        default: launch_dep(transpose_tile_kernel<uint64_t>, dim3(grid), dim3(256), 0, st, p, static_cast<const uint64_t*>(in), static_cast<uint64_t*>(out)); break;
     }
     RMLK_CHECK_LAUNCH("transpose_tile_kernel");
     return RMLK_OK;
@@ -725,7 +832,7 @@ extern "C" int rmlk_b200_range(rmlk_stream_t stream, int dtype, int64_t n, const
     const unsigned grid = static_cast<unsigned>((static_cast<uint64_t>(n) + 255) / 256);
 #define RMLK_CASE(DT, T)                                                                                                   \
     case DT:                                                                                                               \
-        range_kernel<T><<<grid, 256, 0, st>>>(static_cast<uint64_t>(n), *static_cast<const T*>(start), *static_cast<const T*>(delta), static_cast<T*>(out)); \
+        launch_dep(range_kernel<T>, dim3(grid), dim3(256), 0, st, static_cast<uint64_t>(n), *static_cast<const T*>(start), *static_cast<const T*>(delta), static_cast<T*>(out)); \
         break;
     switch (dtype) {
         RMLK_CASE(RMLK_F16, __half)
@@ -747,10 +854,10 @@ extern "C" int rmlk_b200_fill(rmlk_stream_t stream, int elem_size, int64_t n, co
     cudaStream_t st = as_stream(stream);
     const unsigned grid = flat_grid(n, 256, 16);
     switch (elem_size) {
-        case 1: { uint8_t v; memcpy(&v, value, 1); fill_kernel<uint8_t><<<grid, 256, 0, st>>>(static_cast<uint64_t>(n), v, static_cast<uint8_t*>(out)); break; }
-        case 2: { uint16_t v; memcpy(&v, value, 2); fill_kernel<uint16_t><<<grid, 256, 0, st>>>(static_cast<uint64_t>(n), v, static_cast<uint16_t*>(out)); break; }
-        case 4: { uint32_t v; memcpy(&v, value, 4); fill_kernel<uint32_t><<<grid, 256, 0, st>>>(static_cast<uint64_t>(n), v, static_cast<uint32_t*>(out)); break; }
-        case 8: { uint64_t v; memcpy(&v, value, 8); fill_kernel<uint64_t><<<grid, 256, 0, st>>>(static_cast<uint64_t>(n), v, static_cast<uint64_t*>(out)); break; }
+        case 1: { uint8_t v; memcpy(&v, value, 1); launch_dep(fill_kernel<uint8_t>, dim3(grid), dim3(256), 0, st, static_cast<uint64_t>(n), v, static_cast<uint8_t*>(out)); break; }
+        case 2: { uint16_t v; memcpy(&v, value, 2); launch_dep(fill_kernel<uint16_t>, dim3(grid), dim3(256), 0, st, static_cast<uint64_t>(n), v, static_cast<uint16_t*>(out)); break; }
+        case 4: { uint32_t v; memcpy(&v, value, 4); launch_dep(fill_kernel<uint32_t>, dim3(grid), dim3(256), 0, st, static_cast<uint64_t>(n), v, static_cast<uint32_t*>(out)); break; }
+        case 8: { uint64_t v; memcpy(&v, value, 8); launch_dep(fill_kernel<uint64_t>, dim3(grid), dim3(256), 0, st, static_cast<uint64_t>(n), v, static_cast<uint64_t*>(out)); break; }
         default: return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "fill: element size must be 1, 2, 4 or 8");
     }
     RMLK_CHECK_LAUNCH("fill_kernel");
@@ -804,7 +911,7 @@ extern "C" int rmlk_b200_store_small(rmlk_stream_t stream, int n_words, const ui
     if (!words || !out || !aligned_to(out, 8)) return fail(RMLK_ERR_INVALID_ARG, "store_small: bad pointer");
     SmallWords v;
     for (int i = 0; i < 32; i++) v.w[i] = i < n_words ? words[i] : 0;
-    store_small_kernel<<<1, 32, 0, as_stream(stream)>>>(v, n_words, static_cast<uint64_t*>(out));
+    launch_dep(store_small_kernel, dim3(1), dim3(32), 0, as_stream(stream), v, n_words, static_cast<uint64_t*>(out));
     RMLK_CHECK_LAUNCH("store_small_kernel");
     return RMLK_OK;
 }

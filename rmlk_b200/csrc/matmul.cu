@@ -39,6 +39,7 @@ struct SkinnyParams {
 
 template <int MB>
 __global__ void __launch_bounds__(SK_THREADS) skinny_kernel(SkinnyParams p) {
+    dep_sync();
     constexpr int SA = MB >= 8 ? MB + 4 : MB;  // padded row stride: fewer bank conflicts while staging
     __shared__ __align__(16) float sA[SK_KC * SA];
     __shared__ __align__(16) float sRed[8 * MB * SK_COLS];
@@ -150,6 +151,7 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_kernel(SkinnyParams p) {
 // 16-byte aligned operands and batch strides.
 template <int MB>
 __global__ void __launch_bounds__(256) smallk_kernel(SkinnyParams p, int64_t total_quads, uint32_t nq) {
+    dep_sync();
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (idx >= total_quads) return;
     const int64_t batch = idx / nq;
@@ -193,6 +195,7 @@ __global__ void __launch_bounds__(256) smallk_kernel(SkinnyParams p, int64_t tot
 // flight per thread.  A still needs K % 4 == 0 and 16-byte alignment.
 template <int MB>
 __global__ void __launch_bounds__(256) smallk1_kernel(SkinnyParams p, int64_t total_cols, uint32_t n32) {
+    dep_sync();
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (idx >= total_cols) return;
     const int64_t batch = idx / n32;
@@ -244,6 +247,7 @@ __global__ void __launch_bounds__(256) smallk1_kernel(SkinnyParams p, int64_t to
 // exchange halves of the four partial sums instead of all of them (5 shuffles per row instead of 16).
 template <int MB, int LPR>
 __global__ void __launch_bounds__(256) nt_rows_kernel(SkinnyParams p, uint32_t chunks_per_batch, int64_t total_chunks) {
+    dep_sync();
     const int64_t wid = (static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x) >> 5;
     if (wid >= total_chunks) return;
     const int lane = threadIdx.x & 31;
@@ -313,6 +317,7 @@ constexpr int NN_KC = 512;  // k-chunk of A staged in shared memory
 
 template <int MB, int LPR>
 __global__ void __launch_bounds__(256) nn_narrow_kernel(SkinnyParams p) {
+    dep_sync();
     constexpr int RPI = 32 / LPR;      // rows of B per warp-wide load
     constexpr int ROWS = 8 * RPI;      // rows of B per CTA-wide load
     constexpr int SA = MB < 4 ? MB : ((MB + 3) / 4) * 4;
@@ -402,6 +407,7 @@ __global__ void __launch_bounds__(256) nn_narrow_kernel(SkinnyParams p) {
 
 // Any other shape: one thread per output element, sequential fp32 dot product.
 __global__ void __launch_bounds__(256) nt_generic_kernel(SkinnyParams p, int64_t total) {
+    dep_sync();
     const int64_t idx = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (idx >= total) return;
     const int64_t mn = p.M * p.N;
@@ -417,6 +423,7 @@ __global__ void __launch_bounds__(256) nt_generic_kernel(SkinnyParams p, int64_t
 // Sum the split-K partials [ksplit][batch][M*N] in split order.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part, float* __restrict__ c, int ksplit,
                                                             int64_t batch, int64_t mn, int64_t sc) {
+    dep_sync();
     const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= batch * mn) return;
     const int64_t b = i / mn, e = i - b * mn;
@@ -441,6 +448,7 @@ struct GemmParams {
 
 template <int BM, int BN>
 __global__ void __launch_bounds__(256) gemm_kernel(GemmParams p) {
+    dep_sync();
     constexpr int TM = BM / 16, TN = BN / 16;
     __shared__ __align__(16) float As[2][GM_BK][BM + 4];
     __shared__ __align__(16) float Bs[2][GM_BK][BN + 4];
@@ -580,7 +588,7 @@ __global__ void __launch_bounds__(256) gemm_kernel(GemmParams p) {
 
 template <int MB>
 static void skinny_launch(cudaStream_t st, const SkinnyParams& p, dim3 grid) {
-    skinny_kernel<MB><<<grid, SK_THREADS, 0, st>>>(p);
+    launch_dep(skinny_kernel<MB>, dim3(grid), dim3(SK_THREADS), 0, st, p);
 }
 
 static int skinny_plan(int64_t batch, int64_t n, int64_t k) {
@@ -604,7 +612,7 @@ namespace rmlk {
 bool tc_matmul_eligible(int64_t m, int64_t n, int64_t k, const void* a, const void* w, const void* c);
 size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, const float* w, float* c, void* workspace,
-              size_t workspace_bytes, int* status, int* ksplit_out);
+              size_t workspace_bytes, int* status, int* ksplit_out, int flags);
 bool tc_enabled();
 }  // namespace rmlk
 
@@ -623,9 +631,47 @@ extern "C" int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, 
                                workspace_bytes, nullptr);
 }
 
+// dst[i] = 0.f + src[0][i] + src[1][i] + ... : the split-K reduction as an entry point of its own.
+extern "C" int rmlk_b200_sum_parts(rmlk_stream_t stream, int dtype, int parts, int64_t n, const void* src, void* dst) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for sum_parts (f32 only)");
+    if (parts < 1 || n < 0) return fail(RMLK_ERR_INVALID_ARG, "sum_parts: bad extent");
+    if (n == 0) return RMLK_OK;
+    if (!src || !dst) return fail(RMLK_ERR_INVALID_ARG, "sum_parts: NULL pointer");
+    if (ceil_div64(n, 256) > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "sum_parts: tensor too large");
+    launch_dep(splitk_reduce_kernel, dim3(static_cast<unsigned>(ceil_div64(n, 256))), dim3(256), 0, as_stream(stream), static_cast<const float*>(src),
+                                                                                                  static_cast<float*>(dst), parts, 1, n, n);
+    RMLK_CHECK_LAUNCH("splitk_reduce_kernel");
+    return RMLK_OK;
+}
+
+// C[m,n] = A x B for a caller that adds the split-K partial sums itself (in its next kernel): when the plan for this
+// shape splits K through the workspace, the slabs are left there ([*parts][m*n] floats, to be added in slab order
+// starting from 0.f) and C is not written; otherwise C is complete and *parts = 1.
+extern "C" int rmlk_b200_matmul_parts(rmlk_stream_t stream, int dtype, int64_t m, int64_t n, int64_t k, const void* a, const void* b, void* c,
+                                      void* workspace, size_t workspace_bytes, int* status, int flags, int* parts) {
+    if (!parts) return fail(RMLK_ERR_INVALID_ARG, "matmul_parts: NULL parts");
+    *parts = 1;
+    if (dtype == RMLK_F32 && m > 0 && n > 0 && k > 0 && a && b && c && tc_matmul_eligible(m, n, k, a, b, c)) {
+        int ksplit = 1;
+        if (int rc = tc_matmul(as_stream(stream), m, n, k, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c),
+                               workspace, workspace_bytes, status, &ksplit, flags))
+            return rc;
+        *parts = ksplit;
+        return RMLK_OK;
+    }
+    return rmlk_b200_matmul_flags(stream, dtype, 1, m, n, k, a, 0, b, 0, c, 0, workspace, workspace_bytes, status, flags);
+}
+
 extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                                    const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
                                    int64_t c_batch_stride, void* workspace, size_t workspace_bytes, int* status) {
+    return rmlk_b200_matmul_flags(stream, dtype, batch, m, n, k, a, a_batch_stride, b, b_batch_stride, c, c_batch_stride, workspace,
+                                  workspace_bytes, status, 0);
+}
+
+extern "C" int rmlk_b200_matmul_flags(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
+                                      const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
+                                      int64_t c_batch_stride, void* workspace, size_t workspace_bytes, int* status, int flags) {
     if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for matmul (f32 only)");
     if (batch < 0 || m < 0 || n < 0 || k < 0) return fail(RMLK_ERR_INVALID_ARG, "matmul: negative extent");
     if (batch == 0 || m == 0 || n == 0) return RMLK_OK;
@@ -642,11 +688,11 @@ extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batc
     if (batch == 1 && tc_matmul_eligible(m, n, k, a, b, c)) {
         int ksplit = 1;
         if (int rc = tc_matmul(st, m, n, k, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c), workspace,
-                               workspace_bytes, status, &ksplit))
+                               workspace_bytes, status, &ksplit, flags))
             return rc;
         if (ksplit > 1) {
             const int64_t total = m * n;
-            splitk_reduce_kernel<<<static_cast<unsigned>(ceil_div64(total, 256)), 256, 0, st>>>(static_cast<const float*>(workspace),
+            launch_dep(splitk_reduce_kernel, dim3(static_cast<unsigned>(ceil_div64(total, 256))), dim3(256), 0, st, static_cast<const float*>(workspace),
                                                                                                   static_cast<float*>(c), ksplit, 1, total, total);
             RMLK_CHECK_LAUNCH("splitk_reduce_kernel");
         }
@@ -668,15 +714,15 @@ extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batc
             if (b_rows_aligned && aligned_to(c, 16) && c_batch_stride % 4 == 0) {
                 const int64_t total_quads = batch * (n / 4);
                 const unsigned grid = static_cast<unsigned>(ceil_div64(total_quads, 256));
-                if (m == 1) smallk_kernel<1><<<grid, 256, 0, st>>>(p, total_quads, static_cast<uint32_t>(n / 4));
-                else if (m == 2) smallk_kernel<2><<<grid, 256, 0, st>>>(p, total_quads, static_cast<uint32_t>(n / 4));
-                else smallk_kernel<4><<<grid, 256, 0, st>>>(p, total_quads, static_cast<uint32_t>(n / 4));
+                if (m == 1) launch_dep(smallk_kernel<1>, dim3(grid), dim3(256), 0, st, p, total_quads, static_cast<uint32_t>(n / 4));
+                else if (m == 2) launch_dep(smallk_kernel<2>, dim3(grid), dim3(256), 0, st, p, total_quads, static_cast<uint32_t>(n / 4));
+                else launch_dep(smallk_kernel<4>, dim3(grid), dim3(256), 0, st, p, total_quads, static_cast<uint32_t>(n / 4));
             } else {
                 const int64_t total_cols = batch * n;
                 const unsigned grid = static_cast<unsigned>(ceil_div64(total_cols, 256));
-                if (m == 1) smallk1_kernel<1><<<grid, 256, 0, st>>>(p, total_cols, static_cast<uint32_t>(n));
-                else if (m == 2) smallk1_kernel<2><<<grid, 256, 0, st>>>(p, total_cols, static_cast<uint32_t>(n));
-                else smallk1_kernel<4><<<grid, 256, 0, st>>>(p, total_cols, static_cast<uint32_t>(n));
+                if (m == 1) launch_dep(smallk1_kernel<1>, dim3(grid), dim3(256), 0, st, p, total_cols, static_cast<uint32_t>(n));
+                else if (m == 2) launch_dep(smallk1_kernel<2>, dim3(grid), dim3(256), 0, st, p, total_cols, static_cast<uint32_t>(n));
+                else launch_dep(smallk1_kernel<4>, dim3(grid), dim3(256), 0, st, p, total_cols, static_cast<uint32_t>(n));
             }
             RMLK_CHECK_LAUNCH("smallk_kernel");
             return RMLK_OK;
@@ -688,9 +734,9 @@ extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batc
             p.c = static_cast<float*>(c);
             const unsigned grid = static_cast<unsigned>(batch);
 #define RMLK_NN_NARROW(MB)                                                            \
-    if (n <= 32) nn_narrow_kernel<MB, 8><<<grid, 256, 0, st>>>(p);                    \
-    else if (n <= 64) nn_narrow_kernel<MB, 16><<<grid, 256, 0, st>>>(p);              \
-    else nn_narrow_kernel<MB, 32><<<grid, 256, 0, st>>>(p);
+    if (n <= 32) launch_dep(nn_narrow_kernel<MB, 8>, dim3(grid), dim3(256), 0, st, p);                    \
+    else if (n <= 64) launch_dep(nn_narrow_kernel<MB, 16>, dim3(grid), dim3(256), 0, st, p);              \
+    else launch_dep(nn_narrow_kernel<MB, 32>, dim3(grid), dim3(256), 0, st, p);
             if (m == 1) { RMLK_NN_NARROW(1) }
             else if (m == 2) { RMLK_NN_NARROW(2) }
             else { RMLK_NN_NARROW(4) }
@@ -714,7 +760,7 @@ extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batc
         RMLK_CHECK_LAUNCH("skinny_kernel");
         if (ksplit > 1) {
             const int64_t total = batch * m * n;
-            splitk_reduce_kernel<<<static_cast<unsigned>(ceil_div64(total, 256)), 256, 0, st>>>(
+            launch_dep(splitk_reduce_kernel, dim3(static_cast<unsigned>(ceil_div64(total, 256))), dim3(256), 0, st, 
                 static_cast<const float*>(workspace), static_cast<float*>(c), ksplit, batch, m * n, c_batch_stride);
             RMLK_CHECK_LAUNCH("splitk_reduce_kernel");
         }
@@ -731,10 +777,10 @@ extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batc
     const int64_t tiles128 = ceil_div64(m, 128) * ceil_div64(n, 128) * batch;
     if (m > 64 && tiles128 >= sm_count()) {
         dim3 grid(static_cast<unsigned>(ceil_div64(n, 128)), static_cast<unsigned>(ceil_div64(m, 128)), static_cast<unsigned>(batch));
-        gemm_kernel<128, 128><<<grid, 256, 0, st>>>(g);
+        launch_dep(gemm_kernel<128, 128>, dim3(grid), dim3(256), 0, st, g);
     } else {
         dim3 grid(static_cast<unsigned>(ceil_div64(n, 64)), static_cast<unsigned>(ceil_div64(m, 64)), static_cast<unsigned>(batch));
-        gemm_kernel<64, 64><<<grid, 256, 0, st>>>(g);
+        launch_dep(gemm_kernel<64, 64>, dim3(grid), dim3(256), 0, st, g);
     }
     RMLK_CHECK_LAUNCH("gemm_kernel");
     return RMLK_OK;
@@ -745,10 +791,10 @@ static void nt_rows_launch(cudaStream_t st, const SkinnyParams& p, int64_t batch
     const int64_t chunks = ceil_div64(p.N, 32);
     const int64_t total = chunks * batch;
     const unsigned grid = static_cast<unsigned>(ceil_div64(total, 8));
-    if (p.K <= 16) nt_rows_kernel<MB, 4><<<grid, 256, 0, st>>>(p, static_cast<uint32_t>(chunks), total);
-    else if (p.K <= 32) nt_rows_kernel<MB, 8><<<grid, 256, 0, st>>>(p, static_cast<uint32_t>(chunks), total);
-    else if (p.K <= 64) nt_rows_kernel<MB, 16><<<grid, 256, 0, st>>>(p, static_cast<uint32_t>(chunks), total);
-    else nt_rows_kernel<MB, 32><<<grid, 256, 0, st>>>(p, static_cast<uint32_t>(chunks), total);
+    if (p.K <= 16) launch_dep(nt_rows_kernel<MB, 4>, dim3(grid), dim3(256), 0, st, p, static_cast<uint32_t>(chunks), total);
+    else if (p.K <= 32) launch_dep(nt_rows_kernel<MB, 8>, dim3(grid), dim3(256), 0, st, p, static_cast<uint32_t>(chunks), total);
+    else if (p.K <= 64) launch_dep(nt_rows_kernel<MB, 16>, dim3(grid), dim3(256), 0, st, p, static_cast<uint32_t>(chunks), total);
+    else launch_dep(nt_rows_kernel<MB, 32>, dim3(grid), dim3(256), 0, st, p, static_cast<uint32_t>(chunks), total);
 }
 
 extern "C" int rmlk_b200_matmul_nt(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k, const void* a,
@@ -786,7 +832,7 @@ extern "C" int rmlk_b200_matmul_nt(rmlk_stream_t stream, int dtype, int64_t batc
     const int64_t total = batch * m * n;
     if (total / 256 >= 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "matmul_nt: output too large");
     p.ksplit = 1;
-    nt_generic_kernel<<<static_cast<unsigned>(ceil_div64(total, 256)), 256, 0, st>>>(p, total);
+    launch_dep(nt_generic_kernel, dim3(static_cast<unsigned>(ceil_div64(total, 256))), dim3(256), 0, st, p, total);
     RMLK_CHECK_LAUNCH("nt_generic_kernel");
     return RMLK_OK;
 }

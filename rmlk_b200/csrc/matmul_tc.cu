@@ -75,24 +75,30 @@ static int launch(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tm
         RMLK_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<MT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         configured[dev] = true;
     }
+    // launched so that it may be scheduled while the previous kernel of the stream drains (the kernel waits, see
+    // dep_wait); with split-K inside a cluster the ksplit CTAs of one tile (grid y) form the cluster
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = L::TOTAL;
+    cfg.stream = st;
+    cudaLaunchAttribute at[2];
+    unsigned na = 0;
     if (p.cluster_reduce) {
-        // the ksplit CTAs of one tile (grid y) form a cluster and exchange partial sums through shared memory
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = grid;
-        cfg.blockDim = dim3(THREADS);
-        cfg.dynamicSmemBytes = L::TOTAL;
-        cfg.stream = st;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeClusterDimension;
-        at[0].val.clusterDim.x = 1;
-        at[0].val.clusterDim.y = grid.y;
-        at[0].val.clusterDim.z = 1;
-        cfg.attrs = at;
-        cfg.numAttrs = 1;
-        RMLK_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<MT, STAGES>, tmW, tmA, p));
-    } else {
-        tc_gemm_kernel<MT, STAGES><<<grid, THREADS, L::TOTAL, st>>>(tmW, tmA, p);
+        at[na].id = cudaLaunchAttributeClusterDimension;
+        at[na].val.clusterDim.x = 1;
+        at[na].val.clusterDim.y = grid.y;
+        at[na].val.clusterDim.z = 1;
+        na++;
     }
+    if (dep_launch_enabled()) {
+        at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    cfg.attrs = at;
+    cfg.numAttrs = na;
+    RMLK_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<MT, STAGES>, tmW, tmA, p));
     RMLK_CHECK_LAUNCH("tc_gemm_kernel");
     return RMLK_OK;
 }
@@ -154,7 +160,7 @@ size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k) {
 // Launches the tensor-core GEMM.  `ksplit_out` tells the caller how many partial slabs were written to
 // `workspace` (1 = the result is already in c).
 int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, const float* w, float* c, void* workspace,
-              size_t workspace_bytes, int* status, int* ksplit_out) {
+              size_t workspace_bytes, int* status, int* ksplit_out, int flags) {
     const int mt = m <= 64 ? 64 : 128;
     int ksplit = tc_matmul_plan(m, n, k);
     if (ksplit > TC_CLUSTER_MAX && (!workspace || workspace_bytes < static_cast<size_t>(ksplit) * m * n * sizeof(float)))
@@ -175,6 +181,7 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
     p.k_iters_total = k_iters;
     p.ksplit = ksplit;
     p.status = status;
+    p.w_static = (flags & RMLK_MATMUL_B_STATIC) ? 1 : 0;
     dim3 grid(static_cast<unsigned>(n / tc::BN), static_cast<unsigned>(ksplit), static_cast<unsigned>(ceil_div64(m, mt)));
     *ksplit_out = cluster ? 1 : ksplit;  // slabs left in `workspace` for the caller to add
     if (mt == 64) return tc::launch<64, 6>(st, tmW, tmA, p, grid);

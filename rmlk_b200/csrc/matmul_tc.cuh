@@ -138,6 +138,7 @@ struct TcParams {
     int k_iters_total;
     int ksplit;
     int* status;
+    int w_static;           // the weights are not written by work still in flight: their loads need not wait for the previous kernel
 };
 
 template <int MT, int STAGES>

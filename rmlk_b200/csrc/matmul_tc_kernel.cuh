@@ -10,6 +10,7 @@ template <int MT, int STAGES>
 __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW,
                                                               const __grid_constant__ CUtensorMap tmA, TcParams p) {
     using L = SmemLayout<MT, STAGES>;
+    dep_trigger();  // the next kernel of the stream may be scheduled; it waits for this grid before touching memory
     // the two converter groups take alternate k-blocks; a stage must always come back to the same group, or a
     // group could be two barrier phases behind and mistake an old phase for the one it waits for
     static_assert(STAGES % 2 == 0, "stage count must be even");
@@ -44,20 +45,26 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // The first STAGES loads need nothing but their barriers: they go out now, while TMEM is being allocated
         // and the other warps arrive, instead of after the CTA-wide sync (the start-up latency of a CTA is a
-        // large part of a launch with few k-blocks).
+        // large part of a launch with few k-blocks).  Weights that nothing in flight writes are requested even
+        // before the previous kernel of the stream has finished (this grid may have been scheduled early, see
+        // dep_wait); the activations, which that kernel may be producing, only after it.
+        if (!p.w_static) dep_wait();
         for (int it = 0; it < n_iters && it < STAGES; it++) {
             const uint32_t st = base + it * L::STAGE_BYTES;
             const int k0 = (it_begin + it) * BK;
             mbar_expect_tx(full_bar(it), L::W_BYTES + L::A_BYTES);
 #pragma unroll
             for (int j = 0; j < 4; j++) tma_load_2d(st + j * 4096, &tmW, n0 + 32 * j, k0, full_bar(it));
-            tma_load_2d(st + L::W_BYTES, &tmA, k0, m0, full_bar(it));
         }
+        if (p.w_static) dep_wait();
+        for (int it = 0; it < n_iters && it < STAGES; it++)
+            tma_load_2d(base + it * L::STAGE_BYTES + L::W_BYTES, &tmA, (it_begin + it) * BK, m0, full_bar(it));
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(L::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    dep_wait();  // every thread: nothing below reads or writes global memory before the previous grid is complete
     tc_fence_before();
     __syncthreads();
     tc_fence_after();

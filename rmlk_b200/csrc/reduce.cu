@@ -97,6 +97,7 @@ __device__ __forceinline__ int64_t rm_offset(uint64_t idx, int n, const uint64_t
 // Innermost group reduced and contiguous: G threads per output, V elements per load.
 template <typename T, int G, int V, int BLOCK>
 __global__ void __launch_bounds__(BLOCK) reduce_mean_row_kernel(RmParams p, const T* __restrict__ in, T* __restrict__ out) {
+    dep_sync();
     using Acc = typename RmAcc<T>::type;
     __shared__ Acc smem[BLOCK / 32];
     constexpr int ROWS = BLOCK / G;
@@ -129,6 +130,7 @@ __global__ void __launch_bounds__(BLOCK) reduce_mean_row_kernel(RmParams p, cons
 // Innermost group kept: one thread per output, coalesced across threads, serial over the reduction.
 template <typename T>
 __global__ void __launch_bounds__(256) reduce_mean_col_kernel(RmParams p, const T* __restrict__ in, T* __restrict__ out) {
+    dep_sync();
     using Acc = typename RmAcc<T>::type;
     const uint64_t o = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (o >= p.n_out) return;
@@ -147,6 +149,7 @@ __global__ void __launch_bounds__(256) reduce_mean_col_kernel(RmParams p, const 
 // Any layout, few outputs: G threads per output with strided (non-vector) loads.
 template <typename T, int G, int BLOCK>
 __global__ void __launch_bounds__(BLOCK) reduce_mean_generic_kernel(RmParams p, const T* __restrict__ in, T* __restrict__ out) {
+    dep_sync();
     using Acc = typename RmAcc<T>::type;
     __shared__ Acc smem[BLOCK / 32];
     constexpr int ROWS = BLOCK / G;
@@ -228,7 +231,7 @@ static int reduce_mean_typed(cudaStream_t st, int rank, const int64_t* shape, in
     do {                                                                                              \
         constexpr int ROWS = 256 / (G);                                                               \
         const unsigned grid = static_cast<unsigned>((p.n_out + ROWS - 1) / ROWS);                     \
-        reduce_mean_row_kernel<T, G, VV, 256><<<grid, 256, 0, st>>>(p, in, out);                      \
+        launch_dep(reduce_mean_row_kernel<T, G, VV, 256>, dim3(grid), dim3(256), 0, st, p, in, out);                      \
     } while (0)
         if (work <= 256 || (work <= 2048 && many_rows)) {
             if (vec) RM_LAUNCH(32, V); else RM_LAUNCH(32, 1);
@@ -242,12 +245,12 @@ static int reduce_mean_typed(cudaStream_t st, int rank, const int64_t* shape, in
     // innermost group kept
     if (p.n_out >= static_cast<uint64_t>(sm_count()) * 256 || p.n_red_total <= 32) {
         const unsigned grid = static_cast<unsigned>((p.n_out + 255) / 256);
-        reduce_mean_col_kernel<T><<<grid, 256, 0, st>>>(p, in, out);
+        launch_dep(reduce_mean_col_kernel<T>, dim3(grid), dim3(256), 0, st, p, in, out);
         RMLK_CHECK_LAUNCH("reduce_mean_col_kernel");
     } else {
         constexpr int G = 32;
         const unsigned grid = static_cast<unsigned>((p.n_out + (256 / G) - 1) / (256 / G));
-        reduce_mean_generic_kernel<T, G, 256><<<grid, 256, 0, st>>>(p, in, out);
+        launch_dep(reduce_mean_generic_kernel<T, G, 256>, dim3(grid), dim3(256), 0, st, p, in, out);
         RMLK_CHECK_LAUNCH("reduce_mean_generic_kernel");
     }
     return RMLK_OK;
@@ -263,6 +266,7 @@ __device__ __forceinline__ double sm_exp(double x) { return exp(x); }
 template <int G, int NP, int BLOCK>
 __global__ void __launch_bounds__(BLOCK) softmax_f32_regs_kernel(uint64_t rows, uint32_t cols, const float* __restrict__ in,
                                                                 float* __restrict__ out) {
+    dep_sync();
     __shared__ float smem[BLOCK / 32];
     constexpr int ROWS = BLOCK / G;
     const int g = threadIdx.x / G;
@@ -311,6 +315,7 @@ __global__ void __launch_bounds__(BLOCK) softmax_f32_regs_kernel(uint64_t rows, 
 template <typename T, typename C, int G, int BLOCK>
 __global__ void __launch_bounds__(BLOCK) softmax_generic_kernel(uint64_t rows, uint64_t cols, const T* __restrict__ in,
                                                                T* __restrict__ out) {
+    dep_sync();
     __shared__ C smem[BLOCK / 32];
     constexpr int ROWS = BLOCK / G;
     const int g = threadIdx.x / G;
@@ -338,6 +343,7 @@ __global__ void __launch_bounds__(BLOCK) softmax_generic_kernel(uint64_t rows, u
 // along `inner`, three passes over C (the column stays in L1/L2).
 __global__ void __launch_bounds__(256) softmax_strided_kernel(uint64_t outer, uint64_t C, uint64_t inner, const float* __restrict__ in,
                                                               float* __restrict__ out) {
+    dep_sync();
     const uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
     if (i >= outer * inner) return;
     const uint64_t o = i / inner, r = i - o * inner;
@@ -354,7 +360,7 @@ template <int G, int NP>
 static void softmax_regs_launch(cudaStream_t st, uint64_t rows, uint32_t cols, const float* in, float* out) {
     constexpr int ROWS = 256 / G;
     const unsigned grid = static_cast<unsigned>((rows + ROWS - 1) / ROWS);
-    softmax_f32_regs_kernel<G, NP, 256><<<grid, 256, 0, st>>>(rows, cols, in, out);
+    launch_dep(softmax_f32_regs_kernel<G, NP, 256>, dim3(grid), dim3(256), 0, st, rows, cols, in, out);
 }
 
 }  // namespace rmlk
@@ -404,21 +410,21 @@ extern "C" int rmlk_b200_softmax(rmlk_stream_t stream, int dtype, int64_t rows, 
             return RMLK_OK;
         }
         if (C <= 1024) {
-            softmax_generic_kernel<float, float, 32, 256><<<static_cast<unsigned>((R + 7) / 8), 256, 0, st>>>(R, C, src, dst);
+            launch_dep(softmax_generic_kernel<float, float, 32, 256>, dim3(static_cast<unsigned>((R + 7) / 8)), dim3(256), 0, st, R, C, src, dst);
         } else {
-            softmax_generic_kernel<float, float, 256, 256><<<static_cast<unsigned>(R), 256, 0, st>>>(R, C, src, dst);
+            launch_dep(softmax_generic_kernel<float, float, 256, 256>, dim3(static_cast<unsigned>(R)), dim3(256), 0, st, R, C, src, dst);
         }
         RMLK_CHECK_LAUNCH("softmax_generic_kernel<float>");
         return RMLK_OK;
     }
     if (dtype == RMLK_F16) {
-        softmax_generic_kernel<__half, float, 256, 256><<<static_cast<unsigned>(R), 256, 0, st>>>(
+        launch_dep(softmax_generic_kernel<__half, float, 256, 256>, dim3(static_cast<unsigned>(R)), dim3(256), 0, st, 
             R, C, static_cast<const __half*>(in), static_cast<__half*>(out));
         RMLK_CHECK_LAUNCH("softmax_generic_kernel<half>");
         return RMLK_OK;
     }
     if (dtype == RMLK_F64) {
-        softmax_generic_kernel<double, double, 256, 256><<<static_cast<unsigned>(R), 256, 0, st>>>(
+        launch_dep(softmax_generic_kernel<double, double, 256, 256>, dim3(static_cast<unsigned>(R)), dim3(256), 0, st, 
             R, C, static_cast<const double*>(in), static_cast<double*>(out));
         RMLK_CHECK_LAUNCH("softmax_generic_kernel<double>");
         return RMLK_OK;
@@ -434,7 +440,7 @@ extern "C" int rmlk_b200_softmax_strided(rmlk_stream_t stream, int dtype, int64_
     if (!in || !out) return fail(RMLK_ERR_INVALID_ARG, "softmax: NULL tensor pointer");
     if (inner == 1) return rmlk_b200_softmax(stream, dtype, outer, channels, in, out);
     const uint64_t n = static_cast<uint64_t>(outer) * inner;
-    softmax_strided_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, as_stream(stream)>>>(
+    launch_dep(softmax_strided_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, as_stream(stream), 
         static_cast<uint64_t>(outer), static_cast<uint64_t>(channels), static_cast<uint64_t>(inner), static_cast<const float*>(in),
         static_cast<float*>(out));
     RMLK_CHECK_LAUNCH("softmax_strided_kernel");

@@ -89,6 +89,7 @@ struct Ctx {
         if (i >= n.inputs.size() || n.inputs[i] < 0) return nullptr;
         Tensor& t = I.values[n.inputs[i]];
         if (!t.present) raise(RMLK_ERR_INVALID_ARG, "input value `" + I.g.values[n.inputs[i]].name + "` has no data");
+        if (t.parts > 1) I.settle_parts(n.inputs[i]);
         return &t;
     }
     // Input i as a dense tensor; a deferred view is copied out first.
@@ -128,6 +129,7 @@ struct Ctx {
         o.mi.clear();
         o.mf.clear();
         o.lazy = false;
+        o.parts = 0;
         I.alloc_output(n.outputs[i], o);
         o.present = true;
         return o;
@@ -142,6 +144,7 @@ struct Ctx {
         o.mirror_valid = src.mirror_valid;
         o.mi = src.mi;
         o.mf = src.mf;
+        o.parts = 0;
         if (bound) {  // a carried output must own its storage
             I.alloc_output(vid, o);
             if (o.nbytes()) check_cuda(cudaMemcpyAsync(o.data, src.data, o.nbytes(), cudaMemcpyDeviceToDevice, I.stream), "view copy");
@@ -166,12 +169,27 @@ struct Ctx {
         o.mirror_valid = false;
         o.mi.clear();
         o.mf.clear();
+        o.parts = 0;
         o.data = base.data;
         o.storage = base.storage;
         if (o.storage) o.storage->refs++;
-        o.lazy = true;
-        o.pshape = pshape;
-        o.pstride = pstride;
+        // a permutation that only moves dims of size 1 (a [B, heads, 1, D] -> [B, 1, heads, D] transpose of one
+        // decoded token) enumerates the buffer in its own order: that is an ordinary dense tensor, nothing deferred
+        bool dense = true;
+        int64_t expect = 1;
+        for (size_t d = pshape.size(); d-- > 0 && dense;) {
+            if (pshape[d] == 1) continue;
+            dense = pstride[d] == expect;
+            expect *= pshape[d];
+        }
+        o.lazy = !dense;
+        if (dense) {
+            o.pshape.clear();
+            o.pstride.clear();
+        } else {
+            o.pshape = pshape;
+            o.pstride = pstride;
+        }
         o.present = true;
         return o;
     }
@@ -668,9 +686,28 @@ void op_matmul(const Ctx& c) {
         sc = em * n;
     }
     const size_t need = rmlk_b200_matmul_workspace_bytes(a.dtype, eb, em, n, ka);
+    const int ovid = c.n.outputs[0];
+    // initializers were uploaded before the first run: nothing in flight writes them
+    const int flags = c.I.g.values[c.n.inputs[1]].is_const ? RMLK_MATMUL_B_STATIC : 0;
+    if (need && eb == 1 && c.I.parts_owner < 0 && ovid < static_cast<int>(c.I.parts_ok_value.size()) && c.I.parts_ok_value[ovid]) {
+        // The only reader is a residual Add + RMSNorm chain whose kernel adds split-K slabs itself: leave them unreduced.
+        void* slabs = c.I.parts_ws.ensure(need);
+        int parts = 1;
+        check_rc(rmlk_b200_matmul_parts(c.stream(), a.dtype, em, n, ka, a.data, b.data, o.data, slabs, need, static_cast<int*>(c.I.status_word.ptr),
+                                        flags, &parts));
+        c.I.status_dirty = true;
+        c.launched();
+        if (parts > 1) {
+            c.I.release_value(ovid);  // the dense buffer is not needed unless the chain falls back (settle_parts)
+            o.data = slabs;
+            o.parts = parts;
+            c.I.parts_owner = ovid;
+        }
+        return;
+    }
     void* ws = need ? c.I.matmul_ws.ensure(need) : nullptr;
-    check_rc(rmlk_b200_matmul_ex(c.stream(), a.dtype, eb, em, n, ka, a.data, sa, b.data, sb, o.data, sc, ws, need,
-                                 static_cast<int*>(c.I.status_word.ptr)));
+    check_rc(rmlk_b200_matmul_flags(c.stream(), a.dtype, eb, em, n, ka, a.data, sa, b.data, sb, o.data, sc, ws, need,
+                                    static_cast<int*>(c.I.status_word.ptr), flags));
     c.I.status_dirty = true;
     c.launched(need ? 2 : 1);
 }
@@ -857,6 +894,114 @@ void op_transpose(const Ctx& c) {
 // Concat(cache, new rows) whose result is carried to the next run as the cache (a bound output, see Binding): the
 // cache lives in one buffer with spare room along the axis, only the new rows are copied in behind the old ones,
 // and the result is a strided view of that buffer.  False: conditions not met, the general Concat runs.
+struct AppendPlan;
+Shape cache_strides(const AppendPlan& ap, const Shape& shape, int64_t cap);
+void set_strided(Tensor& t, void* data, const Shape& shape, const Shape& st);
+
+// Geometry of appending `add_shape` rows behind `past` along a binding's axis.
+struct AppendPlan {
+    int64_t rank = 0, axis = 0, outer = 0, inner = 0, tp = 0, tn = 0, total = 0;
+    size_t elem = 0, row = 0;  // row: bytes of one entry along the axis
+};
+
+bool append_plan(const Binding& b, const Tensor& past, int add_dtype, const Shape& add_shape, AppendPlan& ap) {
+    if (past.dtype != add_dtype || past.shape.size() != add_shape.size() || past.shape.empty()) return false;
+    ap.rank = static_cast<int64_t>(past.shape.size());
+    ap.axis = b.axis < 0 ? b.axis + ap.rank : b.axis;
+    if (ap.axis < 0 || ap.axis >= ap.rank) return false;
+    for (int64_t d = 0; d < ap.rank; d++)
+        if (d != ap.axis && past.shape[d] != add_shape[d]) return false;
+    ap.elem = dtype_size_of(past.dtype);
+    ap.outer = prod(past.shape, 0, ap.axis);
+    ap.inner = prod(past.shape, ap.axis + 1);
+    ap.tp = past.shape[ap.axis];
+    ap.tn = add_shape[ap.axis];
+    ap.total = ap.tp + ap.tn;
+    if (ap.elem == 0 || ap.outer <= 0 || ap.inner <= 0) return false;
+    ap.row = static_cast<size_t>(ap.inner) * ap.elem;
+    return true;
+}
+
+// Makes sure the binding's buffer holds the old rows and has room for the new ones.  Runs once per run and cache:
+// the producer of the new rows may reserve their slot before the Concat node comes up.
+void append_reserve(Instance& I, Binding& b, Tensor& past, const AppendPlan& ap) {
+    if (b.reserved_run == I.run_counter && b.reserved_tp == ap.tp && b.cap >= ap.total) return;
+    const bool ours = b.store.ptr && past.data == b.store.ptr && b.cap >= ap.tp;  // the view handed out by the previous run
+    if (past.lazy && !ours) I.materialize(past);
+    if (!(ours && b.cap >= ap.total)) {
+        // first run, a cache fed from outside, or out of room: move to a larger buffer (old rows copied once)
+        const int64_t ncap = ap.total + std::max<int64_t>(64, ap.total / 2);
+        void* np = nullptr;
+        check_cuda(cudaMalloc(&np, std::max<size_t>(static_cast<size_t>(ap.outer) * ncap * ap.row, 256)), "cache cudaMalloc");
+        if (ap.tp > 0) {
+            const size_t spitch = (ours ? static_cast<size_t>(b.cap) : static_cast<size_t>(ap.tp)) * ap.row;
+            check_cuda(cudaMemcpy2DAsync(np, static_cast<size_t>(ncap) * ap.row, past.data, spitch, static_cast<size_t>(ap.tp) * ap.row,
+                                         static_cast<size_t>(ap.outer), cudaMemcpyDeviceToDevice, I.stream), "cache move");
+            I.launches++;
+        }
+        if (b.store.ptr) {
+            check_cuda(cudaStreamSynchronize(I.stream), "cudaStreamSynchronize");  // the old buffer is still being read
+            cudaFree(b.store.ptr);
+        }
+        b.store.ptr = np;
+        b.store.cap = static_cast<size_t>(ap.outer) * ncap * ap.row;
+        b.cap = ncap;
+        // the old rows now live in the new buffer: later readers of `past` must not follow the freed pointer
+        if (past.storage == nullptr) set_strided(past, np, past.shape, cache_strides(ap, past.shape, ncap));
+    }
+    b.reserved_run = I.run_counter;
+    b.reserved_tp = ap.tp;
+}
+
+// Element strides, per logical dim, of a tensor of `shape` laid out in the binding's buffer (dims before the axis
+// step over `cap` entries, the rest is dense).
+Shape cache_strides(const AppendPlan& ap, const Shape& shape, int64_t cap) {
+    Shape st(ap.rank, 1);
+    for (int64_t d = ap.rank - 2; d >= 0; d--) st[d] = st[d + 1] * (d + 1 == ap.axis ? cap : shape[d + 1]);
+    return st;
+}
+
+// Turns `t` into a view of `shape` at `data` with the given per-dim element strides (an ordinary dense tensor when
+// the strides happen to be the dense ones).
+void set_strided(Tensor& t, void* data, const Shape& shape, const Shape& st) {
+    t.data = data;
+    t.storage = nullptr;
+    t.pshape.clear();
+    t.pstride.clear();
+    for (size_t d = 0; d < shape.size(); d++) push_dim(t.pshape, t.pstride, shape[d], st[d]);
+    bool dense = true;
+    int64_t expect = 1;
+    for (size_t d = t.pshape.size(); d-- > 0 && dense;) {
+        dense = t.pstride[d] == expect;
+        expect *= t.pshape[d];
+    }
+    t.lazy = !dense;
+    if (dense) {
+        t.pshape.clear();
+        t.pstride.clear();
+    }
+}
+
+// For the producer of the rows that node `concat_node` will append to a carried cache: reserves the slot and
+// returns where the rows go (pointer + per-dim element strides).  False: that Concat is not an in-place append in
+// this run, produce the rows the ordinary way.
+bool append_slot_for(Instance& I, int concat_node, int dtype, const Shape& rows_shape, void*& ptr, Shape& strides) {
+    if (!I.inplace_append_to) return false;
+    const NodeDef& cn = I.g.nodes[concat_node];
+    if (cn.outputs.empty() || cn.inputs.size() != 2 || cn.inputs[0] < 0) return false;
+    const int bi = I.binding_of_out[cn.outputs[0]];
+    if (bi < 0 || !I.bindings[bi].appendable) return false;
+    Binding& b = I.bindings[bi];
+    Tensor& past = I.values[cn.inputs[0]];
+    if (!past.present || past.parts > 1) return false;
+    AppendPlan ap;
+    if (!append_plan(b, past, dtype, rows_shape, ap) || ap.tn <= 0) return false;
+    append_reserve(I, b, past, ap);
+    ptr = static_cast<char*>(b.store.ptr) + static_cast<size_t>(ap.tp) * ap.row;
+    strides = cache_strides(ap, rows_shape, b.cap);
+    return true;
+}
+
 bool concat_append(const Ctx& c) {
     if (c.n.outputs.empty() || c.n.inputs.size() != 2) return false;
     const int vid = c.n.outputs[0];
@@ -865,63 +1010,54 @@ bool concat_append(const Ctx& c) {
     Binding& b = c.I.bindings[bi];
     Tensor* past = c.raw(0);
     Tensor* add = c.raw(1);
-    if (!past || !add || past->dtype != add->dtype || past->shape.size() != add->shape.size() || past->shape.empty()) return false;
-    const int64_t rank = static_cast<int64_t>(past->shape.size());
-    const int64_t axis = b.axis < 0 ? b.axis + rank : b.axis;
-    if (axis < 0 || axis >= rank) return false;
-    for (int64_t d = 0; d < rank; d++)
-        if (d != axis && past->shape[d] != add->shape[d]) return false;
-    const size_t elem = dtype_size_of(past->dtype);
-    const int64_t outer = prod(past->shape, 0, axis), inner = prod(past->shape, axis + 1);
-    const int64_t tp = past->shape[axis], tn = add->shape[axis], total = tp + tn;
-    if (elem == 0 || outer <= 0 || inner <= 0) return false;
-    if (add->lazy) c.I.materialize(*add);
-    const size_t row = static_cast<size_t>(inner) * elem;  // bytes of one entry along the axis
-    const bool ours = b.store.ptr && past->data == b.store.ptr && b.cap >= tp;  // the view handed out by the previous run
-    if (past->lazy && !ours) c.I.materialize(*past);
-    if (!(ours && b.cap >= total)) {
-        // first run, a cache fed from outside, or out of room: move to a larger buffer (old rows copied once)
-        const int64_t ncap = total + std::max<int64_t>(64, total / 2);
-        void* np = nullptr;
-        check_cuda(cudaMalloc(&np, std::max<size_t>(static_cast<size_t>(outer) * ncap * row, 256)), "cache cudaMalloc");
-        if (tp > 0) {
-            const size_t spitch = (ours ? static_cast<size_t>(b.cap) : static_cast<size_t>(tp)) * row;
-            check_cuda(cudaMemcpy2DAsync(np, static_cast<size_t>(ncap) * row, past->data, spitch, static_cast<size_t>(tp) * row, static_cast<size_t>(outer),
-                                         cudaMemcpyDeviceToDevice, c.I.stream), "cache move");
+    AppendPlan ap;
+    if (!past || !add || !append_plan(b, *past, add->dtype, add->shape, ap)) return false;
+    append_reserve(c.I, b, *past, ap);
+    if (ap.tn > 0) {
+        char* slot = static_cast<char*>(b.store.ptr) + static_cast<size_t>(ap.tp) * ap.row;
+        const Shape dst = cache_strides(ap, add->shape, b.cap);
+        Tensor placed;
+        set_strided(placed, slot, add->shape, dst);
+        if (add->data == slot && add->storage == nullptr && add->lazy == placed.lazy && add->pshape == placed.pshape &&
+            add->pstride == placed.pstride) {
+            // the producer of the rows wrote them into the slot already (append_slot_for)
+        } else if (add->lazy) {
+            // rows that exist only as a view (a block of columns of a wider MatMul result, permuted): one strided ->
+            // strided launch instead of a dense copy followed by the append
+            Shape ps, pst;
+            std::vector<std::pair<int, int>> groups;
+            if (c.I.inplace_append_to && dims_of(*add, ps, pst, groups) && ps.size() <= RMLK_MAX_RANK) {
+                Shape ost(ps.size(), 0);
+                for (int64_t d = 0; d < ap.rank; d++) {
+                    int64_t run = dst[d];
+                    for (int p2 = groups[d].second - 1; p2 >= groups[d].first; p2--) {
+                        ost[p2] = run;
+                        run *= ps[p2];
+                    }
+                }
+                check_rc(rmlk_b200_strided_copy_to(c.stream(), static_cast<int>(ap.elem), static_cast<int>(ps.size()), ps.data(), pst.data(), ost.data(),
+                                                   add->data, slot));
+                c.launched();
+            } else {
+                c.I.materialize(*add);
+            }
+        }
+        if (!add->lazy && add->data != slot) {
+            check_cuda(cudaMemcpy2DAsync(slot, static_cast<size_t>(b.cap) * ap.row, add->data, static_cast<size_t>(ap.tn) * ap.row,
+                                         static_cast<size_t>(ap.tn) * ap.row, static_cast<size_t>(ap.outer), cudaMemcpyDeviceToDevice, c.I.stream),
+                       "cache append");
             c.launched();
         }
-        if (b.store.ptr) {
-            check_cuda(cudaStreamSynchronize(c.I.stream), "cudaStreamSynchronize");  // the old buffer is still being read
-            cudaFree(b.store.ptr);
-        }
-        b.store.ptr = np;
-        b.store.cap = static_cast<size_t>(outer) * ncap * row;
-        b.cap = ncap;
-    }
-    if (tn > 0) {
-        check_cuda(cudaMemcpy2DAsync(static_cast<char*>(b.store.ptr) + static_cast<size_t>(tp) * row, static_cast<size_t>(b.cap) * row, add->data,
-                                     static_cast<size_t>(tn) * row, static_cast<size_t>(tn) * row, static_cast<size_t>(outer), cudaMemcpyDeviceToDevice,
-                                     c.I.stream), "cache append");
-        c.launched();
     }
     Tensor& o = c.out(0);
     o.dtype = past->dtype;
     o.shape = past->shape;
-    o.shape[axis] = total;
+    o.shape[ap.axis] = ap.total;
     o.mirror_valid = false;
     o.mi.clear();
     o.mf.clear();
-    o.data = b.store.ptr;
-    o.storage = nullptr;
-    o.pshape.clear();
-    o.pstride.clear();
-    o.lazy = outer > 1 && b.cap != total;  // otherwise the rows are contiguous: an ordinary dense tensor
-    if (o.lazy) {
-        // dims before the axis step over `cap` entries, the rest is dense
-        Shape st(rank, 1);
-        for (int64_t d = rank - 2; d >= 0; d--) st[d] = st[d + 1] * (d + 1 == axis ? b.cap : o.shape[d + 1]);
-        for (int64_t d = 0; d < rank; d++) push_dim(o.pshape, o.pstride, o.shape[d], st[d]);
-    }
+    o.parts = 0;
+    set_strided(o, b.store.ptr, o.shape, cache_strides(ap, o.shape, b.cap));
     o.present = true;
     return true;
 }
@@ -1336,8 +1472,17 @@ bool bcast_strides(const Tensor& t, const Shape& shape, int64_t* out) {
 void Instance::find_fusions() {
     group_of_node.assign(g.nodes.size(), -1);
     groups.clear();
+    parts_ok_value.assign(g.values.size(), 0);
+    append_consumer.assign(g.values.size(), -1);
     if (!fusion) return;
     Matcher m(g, group_of_node);
+    for (size_t i = 0; i < g.nodes.size(); i++) {
+        const NodeDef& n = g.nodes[i];
+        if (n.op != RMLK_OP_CONCAT || m.n_in(static_cast<int>(i)) != 2) continue;
+        const int v = n.inputs[1];
+        const ValueDef& d = g.values[v];
+        if (v >= 0 && m.uses[v] == 1 && !d.is_output && !d.is_input && !d.is_const) append_consumer[v] = static_cast<int>(i);
+    }
     auto commit = [&](FusedGroup& fg) {
         std::sort(fg.members.begin(), fg.members.end());
         fg.root = fg.members.back();
@@ -1372,6 +1517,30 @@ void Instance::find_fusions() {
                         fg.kind = FusedGroup::RMSNORM;
                         fg.members = {n_pow, n_mean, n_add, n_sqrt, n_div, ri};
                         fg.v[0] = x; fg.v[1] = w; fg.v[2] = eps; fg.v[3] = m.in(n_pow, 1);
+                        // x = Add(a, b) made just for this chain and for readers that come after it (the residual
+                        // stream of a decoder layer): the Add joins the chain, whose kernel then writes x as well
+                        const int n_res = x >= 0 ? m.producer[x] : -1;
+                        const ValueDef* xd = x >= 0 ? &g.values[x] : nullptr;
+                        if (add_norm && n_res >= 0 && g.nodes[n_res].op == RMLK_OP_ADD && group_of_node[n_res] < 0 && m.n_in(n_res) == 2 &&
+                            !xd->is_output && !xd->is_input && !xd->is_const) {
+                            bool later = true;
+                            for (size_t j = 0; j < g.nodes.size() && later; j++) {
+                                const int ji = static_cast<int>(j);
+                                if (ji > ri || ji == n_res || std::find(fg.members.begin(), fg.members.end(), ji) != fg.members.end()) continue;
+                                for (int v : g.nodes[j].inputs) later = later && v != x;
+                            }
+                            if (later) {
+                                int a_in = m.in(n_res, 0), b_in = m.in(n_res, 1);
+                                auto sole_matmul = [&](int v) {
+                                    const int pn = v >= 0 ? m.producer[v] : -1;
+                                    return pn >= 0 && g.nodes[pn].op == RMLK_OP_MATMUL && m.uses[v] == 1 && !g.values[v].is_output;
+                                };
+                                if (!sole_matmul(b_in) && sole_matmul(a_in)) std::swap(a_in, b_in);
+                                if (sole_matmul(b_in)) parts_ok_value[b_in] = 1;
+                                fg.members.push_back(n_res);
+                                fg.v[4] = a_in; fg.v[5] = b_in;
+                            }
+                        }
                         commit(fg);
                         done = true;
                     }
@@ -1465,16 +1634,47 @@ bool Instance::run_fused(const FusedGroup& fg) {
     switch (fg.kind) {
         case FusedGroup::RMSNORM: {
             Tensor *x = val(fg.v[0]), *w = val(fg.v[1]), *eps = val(fg.v[2]), *ex = val(fg.v[3]);
+            Tensor *ra = val(fg.v[4]), *rb = val(fg.v[5]);  // the residual Add in front of the chain, if it joined
+            const bool with_add = fg.v[4] >= 0;
             float e = 0.f, p = 0.f;
+            if (with_add) {
+                if (!ra || !rb || ra->dtype != RMLK_F32 || rb->dtype != RMLK_F32 || ra->shape != rb->shape || ra->parts > 1) return false;
+                x = ra;  // same dtype and shape as the sum
+            }
             if (!x || !w || !eps || !ex || x->dtype != RMLK_F32 || w->dtype != RMLK_F32 || x->shape.empty() || w->lazy) return false;
             if (!scalar_f32(*eps, e) || !scalar_f32(*ex, p)) return false;
             const int64_t cols = x->shape.back();
             if (cols == 0 || w->numel() != cols || w->shape.empty() || w->shape.back() != cols || w->shape.size() > x->shape.size()) return false;
             if (x->lazy) materialize(*x);
             const Shape oshape = x->shape;
+            const int64_t rows = x->numel() / cols;
+            if (!with_add) {
+                Tensor& o = c.make(0, RMLK_F32, oshape);
+                check_rc(rmlk_b200_rmsnorm(st, RMLK_F32, rows, cols, x->data, p, e, w->data, o.data));
+                launches++;
+                return true;
+            }
+            if (rb->lazy) materialize(*rb);
+            Tensor& sum = values[fg.v[0]];
+            sum.dtype = RMLK_F32;
+            sum.shape = oshape;
+            sum.mirror_valid = false;
+            sum.mi.clear();
+            sum.mf.clear();
+            sum.lazy = false;
+            sum.parts = 0;
+            alloc_output(fg.v[0], sum);
+            sum.present = true;
             Tensor& o = c.make(0, RMLK_F32, oshape);
-            check_rc(rmlk_b200_rmsnorm(st, RMLK_F32, x->numel() / cols, cols, x->data, p, e, w->data, o.data));
+            const int parts = rb->parts > 1 ? rb->parts : 1;
+            check_rc(rmlk_b200_add_rmsnorm(st, RMLK_F32, rows, cols, ra->data, rb->data, parts, rows * cols, p, e, w->data, sum.data, o.data));
             launches++;
+            if (rb->parts > 1) {  // the slabs have been consumed
+                rb->parts = 0;
+                rb->data = nullptr;
+                rb->present = false;
+                if (parts_owner == fg.v[5]) parts_owner = -1;
+            }
             return true;
         }
         case FusedGroup::SWIGLU: {
@@ -1594,6 +1794,25 @@ bool Instance::run_fused(const FusedGroup& fg) {
             }
             const Shape oshape = x->shape;
             const void* xdata = x->data;
+            // rotated keys that are only ever appended to a carried cache are written straight into their slot
+            const int ov = root.outputs[0];
+            const int cnode = ov < static_cast<int>(append_consumer.size()) ? append_consumer[ov] : -1;
+            void* slot = nullptr;
+            Shape ost;
+            if (cnode >= 0 && x->numel() > 0 && append_slot_for(*this, cnode, RMLK_F32, oshape, slot, ost)) {
+                Tensor& o = c.out(0);
+                o.dtype = RMLK_F32;
+                o.shape = oshape;
+                o.mirror_valid = false;
+                o.mi.clear();
+                o.mf.clear();
+                o.parts = 0;
+                set_strided(o, slot, oshape, ost);
+                o.present = true;
+                check_rc(rmlk_b200_rope_to(st, RMLK_F32, oshape.data(), xstr, cstr, sstr, xdata, cs->data, sn->data, slot, ost.data()));
+                launches++;
+                return true;
+            }
             Tensor& o = c.make(0, RMLK_F32, oshape);
             if (o.numel() == 0) return true;
             check_rc(rmlk_b200_rope(st, RMLK_F32, oshape.data(), xstr, cstr, sstr, xdata, cs->data, sn->data, o.data));
@@ -1651,6 +1870,7 @@ bool Instance::run_merged_matmul(int node_index) {
         if (!w.present || w.lazy || w.dtype != RMLK_F32 || w.shape.size() != 2 || w.shape[0] != mm.k || w.shape[1] != mm.n[j]) return false;
     }
     if (a.lazy) materialize(a);
+    const int flags = mm.ready ? RMLK_MATMUL_B_STATIC : 0;  // from the second run on nothing in flight writes the weights
     if (!mm.ready) {
         char* dst = static_cast<char*>(mm.w.ensure(static_cast<size_t>(mm.k) * mm.n_total * sizeof(float)));
         for (size_t j = 0; j < mm.nodes.size(); j++) {
@@ -1664,8 +1884,8 @@ bool Instance::run_merged_matmul(int node_index) {
     Storage* y = arena->alloc(static_cast<size_t>(rows) * mm.n_total * sizeof(float));
     const size_t need = rmlk_b200_matmul_workspace_bytes(RMLK_F32, 1, rows, mm.n_total, mm.k);
     void* ws = need ? matmul_ws.ensure(need) : nullptr;
-    check_rc(rmlk_b200_matmul_ex(reinterpret_cast<rmlk_stream_t>(stream), RMLK_F32, 1, rows, mm.n_total, mm.k, a.data, 0, mm.w.ptr, 0, y->ptr,
-                                 rows * mm.n_total, ws, need, static_cast<int*>(status_word.ptr)));
+    check_rc(rmlk_b200_matmul_flags(reinterpret_cast<rmlk_stream_t>(stream), RMLK_F32, 1, rows, mm.n_total, mm.k, a.data, 0, mm.w.ptr, 0, y->ptr,
+                                    rows * mm.n_total, ws, need, static_cast<int*>(status_word.ptr), flags));
     status_dirty = true;
     launches += need ? 2 : 1;
     for (size_t j = 0; j < mm.nodes.size(); j++) {

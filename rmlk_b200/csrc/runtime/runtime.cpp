@@ -297,6 +297,21 @@ void Instance::materialize(Tensor& t) {
     t.pstride.clear();
 }
 
+// Adds up the split-K slabs a MatMul left behind (Tensor::parts) into an ordinary dense tensor: the path taken when
+// the value is read by anything but the fused Add + RMSNorm kernel (that chain falling back to single ops).
+void Instance::settle_parts(int value_id) {
+    Tensor& t = values[value_id];
+    if (t.parts <= 1) return;
+    const void* slabs = t.data;
+    const int parts = t.parts;
+    t.parts = 0;
+    t.storage = nullptr;
+    alloc_output(value_id, t);
+    check_rc(rmlk_b200_sum_parts(reinterpret_cast<rmlk_stream_t>(stream), t.dtype, parts, t.numel(), slabs, t.data));
+    launches++;
+    if (parts_owner == value_id) parts_owner = -1;
+}
+
 void Instance::check_status() {
     if (!status_dirty) return;
     int code = 0;
@@ -322,7 +337,9 @@ void Instance::run() {
         values[i].storage = nullptr;
         values[i].data = nullptr;
         values[i].lazy = false;
+        values[i].parts = 0;
     }
+    parts_owner = -1;
     arena->reset();
     for (Binding& b : bindings) {
         if (b.have && !input_fed[b.in_id]) {
@@ -587,6 +604,8 @@ extern "C" rmlk_instance* rmlk_instance_create(const rmlk_graph* g, int device, 
             for (int v : I.g.nodes[i].inputs)
                 if (v >= 0) I.last_use[v] = static_cast<int>(i);
         if (const char* e = getenv("RMLK_B200_NO_FUSION")) I.fusion = e[0] != '1';
+        if (const char* e = getenv("RMLK_B200_NO_ADD_NORM")) I.add_norm = e[0] != '1';
+        if (const char* e = getenv("RMLK_B200_NO_APPEND_TO")) I.inplace_append_to = e[0] != '1';
         I.find_fusions();  // recognise RMSNorm / rotary / SwiGLU / scale-mask-softmax chains; re-derives last_use
         I.find_merged_matmuls();  // q / k / v and gate / up projections: one MatMul per shared left operand
         // one weight arena, one pass of uploads (the reference allocates and copies per tensor through a

@@ -84,6 +84,10 @@ struct Tensor {
     // (backend/expand.rs:49-216, backend/transpose.rs:44-178, backend/reshape.rs:27-73).
     bool lazy = false;
     std::vector<int64_t> pshape, pstride;
+    // > 1: a MatMul result still in `parts` split-K slabs ([parts][numel] floats at `data`, to be added in slab
+    // order); only ever set on a value whose single reader is the residual Add in front of an RMSNorm chain, which
+    // adds the slabs itself.  Any other access goes through Instance::settle_parts first.
+    int parts = 0;
     bool mirror_valid = false;
     std::vector<int64_t> mi;  // integer / bool mirror
     std::vector<double> mf;   // float mirror
@@ -150,6 +154,7 @@ struct Binding {  // output value -> input value, double-buffered
     int axis = 0;
     int64_t cap = 0;
     DeviceBuffer store;
+    int64_t reserved_run = -1, reserved_tp = -1;  // run (and old length) for which room for the new rows was made
 };
 
 // A chain of single-op nodes that one fused launch can stand for (RMSNorm, rotary embedding, SwiGLU gate,
@@ -200,6 +205,15 @@ struct Instance {
     std::unique_ptr<Arena> arena;
     DeviceBuffer status_word;   // device int for gather / scatter_nd diagnostics
     DeviceBuffer matmul_ws;     // split-K scratch
+    DeviceBuffer parts_ws;      // split-K slabs that outlive their MatMul (Tensor::parts)
+    int parts_owner = -1;       // value id whose slabs are in parts_ws, -1: free
+    std::vector<uint8_t> parts_ok_value;  // per value id: MatMul output read only by a residual Add + RMSNorm chain
+    // per value id: the Concat node that appends this value (its only reader) to its first input, or -1.  The
+    // producer of such rows may write them straight into the cache slot (rotary embedding of the keys does).
+    std::vector<int> append_consumer;
+    bool inplace_append_to = true;  // RMLK_B200_NO_APPEND_TO=1: new rows are made dense first, then copied in
+    bool add_norm = true;       // RMLK_B200_NO_ADD_NORM=1: keep the residual Add (and the split-K sum) as launches of their own
+    void settle_parts(int value_id);
     DeviceBuffer read_staging;  // dense copy of a strided output while it is read back
     std::vector<Binding> bindings;
     std::vector<Tensor> const_nodes;       // per node: the materialised `value` of a Constant op

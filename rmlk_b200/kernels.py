@@ -302,12 +302,45 @@ def matmul_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = No
     return out
 
 
+def matmul_parts(a: torch.Tensor, b: torch.Tensor):
+    """a [m, k] x b [k, n] with the split-K partial sums left to the caller: returns (c, slabs, parts).  parts == 1: `c`
+    holds the product; parts > 1: `slabs[:parts]` ([parts, m, n]) are to be added in order and `c` was not written."""
+    _require_cuda(a, b)
+    m, k = a.shape
+    n = b.shape[1]
+    need = lib().rmlk_b200_matmul_workspace_bytes(dt.from_torch(a.dtype), ctypes.c_int64(1), ctypes.c_int64(m), ctypes.c_int64(n), ctypes.c_int64(k))
+    ws = torch.empty(max(need // 4, 1), dtype=torch.float32, device=a.device)
+    c = torch.empty(m, n, dtype=a.dtype, device=a.device)
+    parts = ctypes.c_int(0)
+    _check(lib().rmlk_b200_matmul_parts(_stream(), dt.from_torch(a.dtype), ctypes.c_int64(m), ctypes.c_int64(n), ctypes.c_int64(k), _ptr(a), _ptr(b),
+                                        _ptr(c), _ptr(ws), ctypes.c_size_t(need), None, ctypes.c_int(0), ctypes.byref(parts)))
+    slabs = ws[:parts.value * m * n].view(parts.value, m, n) if parts.value > 1 else None
+    return c, slabs, parts.value
+
+
+def sum_parts(slabs: torch.Tensor) -> torch.Tensor:
+    """0.f + slabs[0] + slabs[1] + ... (the split-K reduction of matmul)."""
+    _require_cuda(slabs)
+    out = torch.empty(list(slabs.shape[1:]), dtype=slabs.dtype, device=slabs.device)
+    _check(lib().rmlk_b200_sum_parts(_stream(), dt.from_torch(slabs.dtype), ctypes.c_int(slabs.shape[0]), ctypes.c_int64(out.numel()), _ptr(slabs),
+                                     _ptr(out)))
+    return out
+
+
 def strided_copy(base: torch.Tensor, shape: Sequence[int], strides: Sequence[int]) -> torch.Tensor:
     """Dense copy of the view of `base` (a contiguous buffer) with the given shape and element strides."""
     _require_cuda(base)
     out = torch.empty(list(shape), dtype=base.dtype, device=base.device)
     _check(lib().rmlk_b200_strided_copy(_stream(), base.element_size(), len(shape), _i64(list(shape)), _i64(list(strides)), _ptr(base), _ptr(out)))
     return out
+
+
+def strided_copy_to(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    """dst[...] = src[...] for two views of equal shape with arbitrary strides (views of CUDA buffers; no overlap)."""
+    assert src.is_cuda and dst.is_cuda and src.shape == dst.shape and src.dtype == dst.dtype
+    _check(lib().rmlk_b200_strided_copy_to(_stream(), src.element_size(), src.dim(), _i64(list(src.shape)), _i64(list(src.stride())),
+                                           _i64(list(dst.stride())), ctypes.c_void_p(src.data_ptr()), ctypes.c_void_p(dst.data_ptr())))
+    return dst
 
 
 # ---- op chains as one launch (f32) ------------------------------------------------------------------------------
@@ -321,10 +354,31 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, exponent: float =
     return out
 
 
-def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """x * cos + rotate_half(x) * sin for x [d0, d1, d2, D] (any strides) and cos / sin broadcastable to it."""
+def add_rmsnorm(a: torch.Tensor, b: torch.Tensor, weight: torch.Tensor, eps: float, exponent: float = 2.0, parts: int = 1):
+    """(a + b, rmsnorm(a + b)) in one launch; with parts > 1, b is [parts, *a.shape] split-K slabs added in order first."""
+    _require_cuda(a, b, weight)
+    total = torch.empty_like(a)
+    out = torch.empty_like(a)
+    cols = a.shape[-1]
+    rows = a.numel() // cols if cols else 0
+    _check(lib().rmlk_b200_add_rmsnorm(_stream(), dt.from_torch(a.dtype), ctypes.c_int64(rows), ctypes.c_int64(cols), _ptr(a), _ptr(b),
+                                       ctypes.c_int(parts), ctypes.c_int64(a.numel()), ctypes.c_float(exponent), ctypes.c_float(eps), _ptr(weight),
+                                       _ptr(total), _ptr(out)))
+    return total, out
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x * cos + rotate_half(x) * sin for x [d0, d1, d2, D] (any strides) and cos / sin broadcastable to it.  `out` may
+    be a strided view of a larger buffer (a slot of a cache): the result is written there."""
     _require_cuda(cos, sin)
     assert x.dim() == 4 and x.is_cuda   # x may be a permuted (non-contiguous) view: its strides are passed on
+    if out is not None:
+        assert out.is_cuda and out.shape == x.shape and out.dtype == x.dtype
+        cs = cos.expand(x.shape).stride() if cos.dim() == 4 else cos.reshape([1] * (4 - cos.dim()) + list(cos.shape)).expand(x.shape).stride()
+        ss = sin.expand(x.shape).stride() if sin.dim() == 4 else sin.reshape([1] * (4 - sin.dim()) + list(sin.shape)).expand(x.shape).stride()
+        _check(lib().rmlk_b200_rope_to(_stream(), dt.from_torch(x.dtype), _i64(list(x.shape)), _i64(list(x.stride())), _i64(list(cs)), _i64(list(ss)),
+                                       ctypes.c_void_p(x.data_ptr()), _ptr(cos), _ptr(sin), ctypes.c_void_p(out.data_ptr()), _i64(list(out.stride()))))
+        return out
     out = torch.empty(list(x.shape), dtype=x.dtype, device=x.device)
     cs = cos.expand(x.shape).stride() if cos.dim() == 4 else cos.reshape([1] * (4 - cos.dim()) + list(cos.shape)).expand(x.shape).stride()
     ss = sin.expand(x.shape).stride() if sin.dim() == 4 else sin.reshape([1] * (4 - sin.dim()) + list(sin.shape)).expand(x.shape).stride()

@@ -6,11 +6,9 @@
 //
 // What differs from the reference's bodies, inside that contract:
 //  * 64-bit element indices throughout (the reference's `unsigned int` loop counters wrap at 2^32 elements);
-//  * operands that are dense or fully broadcast are recognised once per thread and indexed directly - the
-//    per-element divide / modulo chain over `rank` dims runs only for genuinely strided operands, and then
-//    with 32-bit arithmetic when the tensor is small enough;
-//  * dense same-width elementwise calls are processed in 16-byte packs by the first n / V threads (the other
-//    threads of the caller's fixed grid exit);
+//  * the per-element index decode is one loop shared by all operands, in 32-bit arithmetic when the tensor has
+//    fewer than 2^32 elements, and stops once the remaining index is zero (the reference divides 64-bit values
+//    for every operand and every dim);
 //  * ReduceMean decodes an output's base offset once and walks the reduced dims with an odometer instead of
 //    re-deriving every coordinate for every element;
 //  * Trilu writes zeros to masked elements (the reference leaves them unwritten and relies on fresh memory);
@@ -30,93 +28,57 @@ constexpr int MAX_RANK = 32;  // the reference's reduce kernel sizes its coordin
 __device__ __forceinline__ size_t global_tid() { return static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; }
 __device__ __forceinline__ size_t grid_threads() { return static_cast<size_t>(blockDim.x) * gridDim.x; }
 
-// How one operand of a broadcast op is laid out relative to the output dims.
-enum Layout { DENSE, SCALAR, STRIDED };
-
-__device__ __forceinline__ Layout classify(const size_t* dims, const size_t* strides, int rank) {
-    bool dense = true, zero = true;
-    size_t run = 1;
-    for (int d = rank - 1; d >= 0; d--) {
-        if (dims[d] != 1) {
-            dense = dense && strides[d] == run;
-            zero = zero && strides[d] == 0;
-        }
-        run *= dims[d];
-    }
-    return dense ? DENSE : zero ? SCALAR : STRIDED;
-}
-
-// Offset of output element i in an operand with the given strides (row-major decode over dims).
-__device__ __forceinline__ size_t offset_of(size_t i, const size_t* dims, const size_t* strides, int rank, bool small) {
-    size_t off = 0;
+// Offsets of output element i in up to three operands at once: one row-major decode over dims shared by all of
+// them (32-bit arithmetic when the tensor has fewer than 2^32 elements, which a 64-bit divide costs several
+// times over), stopping as soon as the remaining index is zero.
+template <int NOPS>
+__device__ __forceinline__ void offsets_of(size_t i, const size_t* dims, const size_t* const (&strides)[NOPS], int rank, bool small, size_t (&off)[NOPS]) {
+#pragma unroll
+    for (int o = 0; o < NOPS; o++) off[o] = 0;
     if (small) {
         uint32_t t = static_cast<uint32_t>(i);
-        for (int d = rank - 1; d >= 0; d--) {
+        for (int d = rank - 1; d >= 0 && t != 0; d--) {
             const uint32_t n = static_cast<uint32_t>(dims[d]);
-            const uint32_t q = t / n;
-            off += static_cast<size_t>(t - q * n) * strides[d];
+            const uint32_t q = t / n, c = t - q * n;
             t = q;
+#pragma unroll
+            for (int o = 0; o < NOPS; o++) off[o] += static_cast<size_t>(c) * strides[o][d];
         }
     } else {
-        for (int d = rank - 1; d >= 0; d--) {
-            const size_t q = i / dims[d];
-            off += (i - q * dims[d]) * strides[d];
+        for (int d = rank - 1; d >= 0 && i != 0; d--) {
+            const size_t q = i / dims[d], c = i - q * dims[d];
             i = q;
+#pragma unroll
+            for (int o = 0; o < NOPS; o++) off[o] += c * strides[o][d];
         }
     }
-    return off;
 }
-
-__device__ __forceinline__ size_t pick(Layout l, size_t i, const size_t* dims, const size_t* strides, int rank, bool small) {
-    return l == DENSE ? i : l == SCALAR ? 0 : offset_of(i, dims, strides, rank, small);
-}
-
-template <typename T>
-__device__ __forceinline__ bool aligned16(const T* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
-
-template <typename T, int V>
-struct alignas(sizeof(T) * V) Pack {
-    T v[V];
-};
 
 // ---- broadcast binary: info = [dims | a strides | b strides] ------------------------------------------------
 template <typename X, typename Y, typename O, typename F>
 __device__ __forceinline__ void binary_body(size_t n, size_t rank_, const size_t* info, const X* a, const Y* b, O* out, F f) {
     const int rank = static_cast<int>(rank_);
-    const size_t *dims = info, *as = info + rank, *bs = info + 2 * rank;
-    const Layout la = classify(dims, as, rank), lb = classify(dims, bs, rank);
-    const size_t tid = global_tid(), step = grid_threads();
-    if constexpr (sizeof(X) == sizeof(Y) && sizeof(X) == sizeof(O) && sizeof(X) <= 8) {
-        constexpr int V = 16 / sizeof(X);
-        if (la == DENSE && lb == DENSE && n % V == 0 && aligned16(a) && aligned16(b) && aligned16(out)) {
-            const Pack<X, V>* pa = reinterpret_cast<const Pack<X, V>*>(a);
-            const Pack<Y, V>* pb = reinterpret_cast<const Pack<Y, V>*>(b);
-            Pack<O, V>* po = reinterpret_cast<Pack<O, V>*>(out);
-            for (size_t p = tid; p < n / V; p += step) {
-                const Pack<X, V> xa = pa[p];
-                const Pack<Y, V> xb = pb[p];
-                Pack<O, V> r;
-#pragma unroll
-                for (int j = 0; j < V; j++) r.v[j] = f(xa.v[j], xb.v[j]);
-                po[p] = r;
-            }
-            return;
-        }
-    }
+    const size_t* dims = info;
+    const size_t* const strides[2] = {info + rank, info + 2 * rank};
     const bool small = n <= 0xffffffffull;
-    for (size_t i = tid; i < n; i += step) out[i] = f(a[pick(la, i, dims, as, rank, small)], b[pick(lb, i, dims, bs, rank, small)]);
+    for (size_t i = global_tid(); i < n; i += grid_threads()) {
+        size_t off[2];
+        offsets_of<2>(i, dims, strides, rank, small, off);
+        out[i] = f(a[off[0]], b[off[1]]);
+    }
 }
 
 // in-place b = f(alpha, a, beta, b): info = [dims | a strides | b strides]
 template <typename T, typename F>
 __device__ __forceinline__ void binary_inplace_body(T alpha, T beta, size_t n, size_t rank_, const size_t* info, const T* a, T* b, F f) {
     const int rank = static_cast<int>(rank_);
-    const size_t *dims = info, *as = info + rank, *bs = info + 2 * rank;
-    const Layout la = classify(dims, as, rank), lb = classify(dims, bs, rank);
+    const size_t* dims = info;
+    const size_t* const strides[2] = {info + rank, info + 2 * rank};
     const bool small = n <= 0xffffffffull;
     for (size_t i = global_tid(); i < n; i += grid_threads()) {
-        const size_t bi = pick(lb, i, dims, bs, rank, small);
-        b[bi] = f(alpha, a[pick(la, i, dims, as, rank, small)], beta, b[bi]);
+        size_t off[2];
+        offsets_of<2>(i, dims, strides, rank, small, off);
+        b[off[1]] = f(alpha, a[off[0]], beta, b[off[1]]);
     }
 }
 
@@ -124,36 +86,22 @@ __device__ __forceinline__ void binary_inplace_body(T alpha, T beta, size_t n, s
 template <typename T, typename Z>
 __device__ __forceinline__ void where_body(size_t n, size_t rank_, const size_t* info, const T* x, const T* y, const Z* z, T* out) {
     const int rank = static_cast<int>(rank_);
-    const size_t *dims = info, *xs = info + rank, *ys = info + 2 * rank, *zs = info + 3 * rank;
-    const Layout lx = classify(dims, xs, rank), ly = classify(dims, ys, rank), lz = classify(dims, zs, rank);
+    const size_t* dims = info;
+    const size_t* const strides[3] = {info + rank, info + 2 * rank, info + 3 * rank};
     const bool small = n <= 0xffffffffull;
     for (size_t i = global_tid(); i < n; i += grid_threads()) {
-        const T xv = x[pick(lx, i, dims, xs, rank, small)];
-        const T yv = y[pick(ly, i, dims, ys, rank, small)];
-        out[i] = z[pick(lz, i, dims, zs, rank, small)] ? xv : yv;
+        size_t off[3];
+        offsets_of<3>(i, dims, strides, rank, small, off);
+        const T xv = x[off[0]];
+        const T yv = y[off[1]];
+        out[i] = z[off[2]] ? xv : yv;
     }
 }
 
 // ---- contiguous unary / cast ------------------------------------------------------------------------------------
 template <typename I, typename O, typename F>
 __device__ __forceinline__ void unary_body(size_t n, const I* in, O* out, F f) {
-    const size_t tid = global_tid(), step = grid_threads();
-    if constexpr (sizeof(I) == sizeof(O) && sizeof(I) <= 8) {
-        constexpr int V = 16 / sizeof(I);
-        if (n % V == 0 && aligned16(in) && aligned16(out)) {
-            const Pack<I, V>* pi = reinterpret_cast<const Pack<I, V>*>(in);
-            Pack<O, V>* po = reinterpret_cast<Pack<O, V>*>(out);
-            for (size_t p = tid; p < n / V; p += step) {
-                const Pack<I, V> x = pi[p];
-                Pack<O, V> r;
-#pragma unroll
-                for (int j = 0; j < V; j++) r.v[j] = f(x.v[j]);
-                po[p] = r;
-            }
-            return;
-        }
-    }
-    for (size_t i = tid; i < n; i += step) out[i] = f(in[i]);
+    for (size_t i = global_tid(); i < n; i += grid_threads()) out[i] = f(in[i]);
 }
 
 // static_cast between arithmetic types, through float for f16, `x != 0` into bool

@@ -36,6 +36,31 @@ def test_fused_kernels_equal_the_single_op_chain(K):
         assert float((got - want).abs().max()) <= 1e-5 * float(want.abs().max()), (rows, cols)
         ref = x.double() / torch.sqrt((x.double() ** 2).mean(-1, keepdim=True) + 1e-5) * w.double()
         assert float((got.double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
+    # residual Add in front of RMSNorm, with the second operand whole or as split-K slabs: the same bits as
+    # (split-K sum ->) Add -> the RMSNorm kernel
+    for rows, cols, parts in [(64, 2048, 1), (64, 2048, 9), (3, 7, 1), (3, 7, 4), (2, 4097, 11), (130, 64, 2), (5, 4096, 8)]:
+        a, w = r(rows, cols) * 3, r(cols)
+        slabs = r(parts, rows, cols)
+        b = K.sum_parts(slabs) if parts > 1 else slabs[0]
+        if parts > 1:
+            ref = torch.zeros(rows, cols, device="cuda")
+            for k in range(parts):
+                ref = ref + slabs[k]
+            assert torch.equal(b, ref)
+        want_sum = K.binary("add", a, b)
+        want = K.rmsnorm(want_sum, w, 1e-5)
+        got_sum, got = K.add_rmsnorm(a, slabs if parts > 1 else b, w, 1e-5, parts=parts)
+        assert torch.equal(got_sum, want_sum), (rows, cols, parts)
+        assert torch.equal(got, want), (rows, cols, parts)
+    # MatMul that leaves its split-K slabs to the caller: their sum is the MatMul's own result
+    for (m, k, n) in [(64, 2048, 2048), (64, 8192, 2048), (64, 2048, 8192), (8, 512, 256)]:
+        a, b = r(m, k), r(k, n) * 0.05
+        c, slabs, parts = K.matmul_parts(a, b)
+        want = K.matmul(a, b, workspace=torch.empty(16 << 20, device="cuda"))   # with scratch: the same K split as above
+        got = K.sum_parts(slabs) if parts > 1 else c
+        assert torch.equal(got, want), (m, k, n, parts)
+        if (m, k, n) == (64, 8192, 2048):
+            assert parts > 4      # this shape splits K through the workspace
     # SwiGLU: no reduction, so the same bits as Sigmoid -> Mul -> Mul
     for n in [(64, 8192), (5, 7), (1,), (4099,)]:
         a, b = r(*n) * 4, r(*n)
@@ -232,3 +257,85 @@ def test_matmuls_sharing_their_left_operand_run_as_one(cuda):
             scale = np.max(np.abs(want[o]))
             assert np.max(np.abs(got[o] - want[o])) <= 1e-4 * scale, o
             assert np.max(np.abs(got[o] - ref[o])) <= 1e-5 * scale, o
+
+
+def residual_graph(hidden, ffn, broadcast_add=False):
+    """x -> MatMul -> residual Add -> RMSNorm -> MatMul -> residual Add (reads the first sum again) -> RMSNorm."""
+    g = GraphSpec()
+    g.input("x", np.float32, [0, hidden])
+    g.input("y", np.float32, [0, ffn])
+    rng = np.random.default_rng(5)
+    g.const("w1", (rng.standard_normal((ffn, hidden)) * 0.05).astype(np.float32))
+    g.const("w2", (rng.standard_normal((hidden, hidden)) * 0.05).astype(np.float32))
+    g.const("n1", rng.standard_normal(hidden).astype(np.float32))
+    g.const("n2", rng.standard_normal(hidden).astype(np.float32))
+    g.const("two", np.array(2.0, np.float32))
+    g.const("eps", np.array(1e-5, np.float32))
+    if broadcast_add:
+        g.input("x1", np.float32, [1, hidden])
+
+    def norm(x, w, name):
+        var = g.op("ReduceMean", [g.op("Pow", [x, "two"])], axes=[-1], keepdims=1)
+        return g.op("Mul", [g.op("Div", [x, g.op("Sqrt", [g.op("Add", [var, "eps"])])]), w], name)
+
+    r1 = g.op("Add", ["x1" if broadcast_add else "x", g.op("MatMul", ["y", "w1"])], "res1")
+    h1 = norm(r1, "n1", "h1")
+    r2 = g.op("Add", [g.op("MatMul", [h1, "w2"]), r1], "res2")
+    norm(r2, "n2", "h2")
+    g.output("h2")
+    return g
+
+
+@pytest.mark.parametrize("rows,hidden,ffn", [(64, 2048, 8192), (24, 256, 512), (3, 40, 72)])
+def test_residual_add_joins_the_rmsnorm_chain(cuda, rows, hidden, ffn):
+    """The Add that feeds an RMSNorm chain (and later readers) runs inside the chain's kernel, and a MatMul read only by
+    that Add hands over its split-K slabs unreduced.  Same bits as with the Add and the split-K sum as launches of
+    their own."""
+    from rmlk_b200.runtime import ModelInstance
+    spec = residual_graph(hidden, ffn)
+    rng = np.random.default_rng(6)
+    feeds = {"x": rng.standard_normal((rows, hidden), dtype=np.float32), "y": rng.standard_normal((rows, ffn), dtype=np.float32)}
+
+    def run(env):
+        os.environ.update(env)
+        try:
+            inst = ModelInstance(spec.to_runtime())
+        finally:
+            for k in env:
+                os.environ.pop(k, None)
+        for k, v in feeds.items():
+            inst.set_input(k, v)
+        inst.launch()
+        first = inst.read("h2")
+        inst.set_input("x", feeds["x"])
+        inst.set_input("y", feeds["y"])
+        inst.launch()                       # a second run reuses the slab buffer
+        assert np.array_equal(inst.read("h2"), first)
+        return first, inst.fused, inst.last_launches
+
+    joined, counts, n_joined = run({})
+    apart, counts0, n_apart = run({"RMLK_B200_NO_ADD_NORM": "1"})
+    assert counts[0] == 2 and counts[2] == 0 and counts0[0] == 2
+    assert np.array_equal(joined, apart)
+    # two Adds fewer; on the large shape both MatMuls split K through the workspace: two reductions fewer as well
+    assert n_apart - n_joined == (4 if rows == 64 else 2), (n_joined, n_apart)
+    want = graph_cpu.run_graph(spec, feeds)["h2"]
+    assert np.max(np.abs(joined - want)) <= 1e-4 * np.max(np.abs(want))
+
+
+def test_residual_add_that_broadcasts_falls_back(cuda):
+    """An Add in front of the chain whose operands differ in shape is outside the fused kernel: the members run one
+    by one, and the MatMul's slabs are summed on the way."""
+    from rmlk_b200.runtime import ModelInstance
+    spec = residual_graph(2048, 8192, broadcast_add=True)
+    rng = np.random.default_rng(7)
+    feeds = {"x": rng.standard_normal((64, 2048), dtype=np.float32), "y": rng.standard_normal((64, 8192), dtype=np.float32),
+             "x1": rng.standard_normal((1, 2048), dtype=np.float32)}
+    inst = ModelInstance(spec.to_runtime())
+    for k, v in feeds.items():
+        inst.set_input(k, v)
+    inst.launch()
+    got = inst.read("h2")
+    assert inst.fused[2] == 1 and inst.fused[1] == 1     # first chain fell back, second ran fused
+    want = graph_cpu.run_graph(spec, feeds)["h2"]
+    assert np.max(np.abs(got - want)) <= 1e-4 * np.max(np.abs(want))

@@ -606,3 +606,50 @@ def test_strided_copy_views():
     b64 = rand((4 * 6 * 8,), np.int64, seed=14)
     got = to_np(K.strided_copy(dev(b64), (8, 4, 6), (1, 48, 8)))
     assert np.array_equal(got, np.ascontiguousarray(as_strided(b64, shape=(8, 4, 6), strides=(8, 384, 64))))
+
+
+def test_strided_copy_to_places_views_inside_a_larger_buffer():
+    """View -> view copy in one launch (new rows of a KV cache going into their slot): against torch's own copy_."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(21)
+    # rows [B, KV, S, D] that exist as a permuted block of columns of a wider matrix, into [B, KV, cap, D] at row T
+    for (B, KV, S, D, cap, T, wide, col0) in [(64, 8, 1, 64, 700, 523, 3072, 2560), (3, 2, 5, 16, 40, 7, 200, 33), (2, 4, 1, 6, 9, 8, 31, 3),
+                                              (1, 1, 1, 64, 64, 63, 64, 0)]:
+        src_buf = torch.randn(B * S, wide, device="cuda", generator=g)
+        src = src_buf[:, col0:col0 + KV * D].view(B, S, KV, D).permute(0, 2, 1, 3)
+        for dtype in (torch.float32, torch.int64, torch.float16):
+            sb = (src_buf * 100).to(dtype)
+            sv = sb[:, col0:col0 + KV * D].view(B, S, KV, D).permute(0, 2, 1, 3)
+            cache = torch.zeros(B, KV, cap, D, device="cuda", dtype=dtype)
+            want = cache.clone()
+            want[:, :, T:T + S, :].copy_(sv)
+            K.strided_copy_to(sv, cache[:, :, T:T + S, :])
+            assert torch.equal(cache, want), (B, KV, S, D, dtype)
+    # broadcast source, scalar, inner-dim transposes on both sides
+    a = torch.randn(7, device="cuda", generator=g)
+    out = torch.zeros(5, 7, 3, device="cuda")
+    K.strided_copy_to(a.view(1, 7, 1).expand(5, 7, 3), out)
+    assert torch.equal(out, a.view(1, 7, 1).expand(5, 7, 3).contiguous())
+    m = torch.randn(33, 65, device="cuda", generator=g)
+    outT = torch.zeros(65, 40, device="cuda")
+    K.strided_copy_to(m.t(), outT[:, 2:35])
+    assert torch.equal(outT[:, 2:35], m.t()) and float(outT[:, :2].abs().sum()) == 0.0 and float(outT[:, 35:].abs().sum()) == 0.0
+    s0 = torch.tensor(3.5, device="cuda")
+    d0 = torch.zeros((), device="cuda")
+    K.strided_copy_to(s0, d0)
+    assert float(d0) == 3.5
+
+
+def test_rope_writes_into_a_cache_slot():
+    """The rotary kernel with a placed output: same bits as the dense result, nothing outside the slot touched."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(22)
+    for (B, KV, S, D, cap, T) in [(64, 8, 1, 64, 600, 523), (2, 3, 4, 16, 20, 5), (1, 1, 1, 2, 3, 2)]:
+        xb = torch.randn(B, S, KV, D, device="cuda", generator=g)
+        x = xb.permute(0, 2, 1, 3)
+        cos, sin = torch.randn(B, 1, S, D, device="cuda", generator=g), torch.randn(B, 1, S, D, device="cuda", generator=g)
+        want = K.rope(x, cos, sin)
+        cache = torch.full((B, KV, cap, D), 7.0, device="cuda")
+        K.rope(x, cos, sin, out=cache[:, :, T:T + S, :])
+        assert torch.equal(cache[:, :, T:T + S, :], want)
+        assert float((cache[:, :, :T, :] - 7.0).abs().sum()) == 0.0 and float((cache[:, :, T + S:, :] - 7.0).abs().sum()) == 0.0

@@ -205,3 +205,82 @@ def test_bound_cache_is_appended_in_place(cuda):
             assert np.array_equal(plain.read("present"), cache), step
     assert launches[5] == 2, launches[:8]    # one small copy of the new rows + the MatMul: the cache itself is not copied
     assert plain.last_launches == 2          # (the copying Concat is one launch too, but moves the whole cache)
+
+
+def test_new_rows_go_straight_into_the_cache(cuda):
+    """Decode-style K / V append: keys = rotary(MatMul) and values = MatMul, both reshaped and permuted, appended to
+    carried caches.  The rotary kernel writes its result into the cache slot and the value rows (a view of the merged
+    k|v MatMul result) are copied there by one strided launch - no dense intermediate, no second copy.  Results equal
+    the path that makes the rows dense first, over growth of the cache and a multi-token first step."""
+    import os
+    from rmlk_b200.runtime import ModelInstance
+    B, KV, G, D, hidden = 3, 2, 2, 16, 48
+    g = GraphSpec()
+    g.input("x", np.float32, [B, 0, hidden])
+    g.input("q", np.float32, [B, KV * G, 0, D])
+    g.input("cos", np.float32, [B, 1, 0, D])
+    g.input("sin", np.float32, [B, 1, 0, D])
+    g.input("past_k", np.float32, [B, KV, 0, D])
+    g.input("past_v", np.float32, [B, KV, 0, D])
+    rng = np.random.default_rng(31)
+    g.const("wk", (rng.standard_normal((hidden, KV * D)) * 0.2).astype(np.float32))
+    g.const("wv", (rng.standard_normal((hidden, KV * D)) * 0.2).astype(np.float32))
+    g.const("shape_kv", i64(0, 0, KV, D))
+    g.const("z", i64(0)); g.const("h", i64(D // 2)); g.const("d", i64(D)); g.const("ax", i64(3))
+    g.const("ax2", i64(2))
+    g.const("rep", i64(1, 1, G, 1, 1))
+    g.const("heads", i64(0, KV * G, -1, D))
+    k4 = g.op("Transpose", [g.op("Reshape", [g.op("MatMul", ["x", "wk"]), "shape_kv"])], perm=[0, 2, 1, 3])
+    v4 = g.op("Transpose", [g.op("Reshape", [g.op("MatMul", ["x", "wv"]), "shape_kv"])], perm=[0, 2, 1, 3])
+    lo = g.op("Slice", [k4, "z", "h", "ax"])
+    hi = g.op("Slice", [k4, "h", "d", "ax"])
+    rot = g.op("Concat", [g.op("Neg", [hi]), lo], axis=-1)
+    kr = g.op("Add", [g.op("Mul", [k4, "cos"]), g.op("Mul", [rot, "sin"])])
+    g.op("Concat", ["past_k", kr], "present_k", axis=2)
+    g.op("Concat", ["past_v", v4], "present_v", axis=2)
+
+    def heads(c):
+        return g.op("Reshape", [g.op("Expand", [g.op("Unsqueeze", [c, "ax2"]), "rep"]), "heads"])
+
+    sc = g.op("MatMul", ["q", g.op("Transpose", [heads("present_k")], perm=[0, 1, 3, 2])], "scores")
+    g.op("MatMul", [sc, heads("present_v")], "ctx")
+    for o in ("present_k", "present_v", "scores", "ctx"):
+        g.output(o)
+
+    def drive(env):
+        os.environ.update(env)
+        try:
+            inst = ModelInstance(g.to_runtime())
+            inst.bind("present_k", "past_k")
+            inst.bind("present_v", "past_v")
+        finally:
+            for k in env:
+                os.environ.pop(k, None)
+        return inst
+
+    direct, staged = drive({}), drive({"RMLK_B200_NO_APPEND_TO": "1"})
+    r = np.random.default_rng(32)
+    T = 0
+    saved = []
+    for step in range(80):
+        S = 5 if step == 0 else 1
+        feeds = {"x": r.standard_normal((B, S, hidden), dtype=np.float32), "q": r.standard_normal((B, KV * G, S, D), dtype=np.float32),
+                 "cos": r.standard_normal((B, 1, S, D), dtype=np.float32), "sin": r.standard_normal((B, 1, S, D), dtype=np.float32)}
+        for m in (direct, staged):
+            for k, v in feeds.items():
+                m.set_input(k, v)
+            if step == 0:
+                m.set_input("past_k", np.zeros((B, KV, 0, D), np.float32))
+                m.set_input("past_v", np.zeros((B, KV, 0, D), np.float32))
+            m.launch()
+        T += S
+        for o in ("scores", "ctx"):
+            assert np.array_equal(direct.read(o), staged.read(o)), (step, o)
+        if step in (0, 1, 2, 60, 79):
+            for o in ("present_k", "present_v"):
+                a = direct.read(o)
+                assert a.shape == (B, KV, T, D)
+                assert np.array_equal(a, staged.read(o)), (step, o)
+        saved.append(staged.last_launches - direct.last_launches)
+    # per decode step: the keys' append copy is gone, and the values' dense copy + append copy became one launch
+    assert saved[10] == 2, saved[:12]
