@@ -15,7 +15,8 @@
 // descriptor with N = 2 MT covers both, filling two accumulator blocks that the epilogue adds.
 //
 // Data path per k-block of 32 (STAGES deep):
-//   warp 0     TMA: four unswizzled [32 k][32 n] boxes of W and one 128B-swizzled [MT][32 k] box of A -> smem
+//   warp 0     TMA: one unswizzled [32 k][128 n] box of W (512-byte row pieces; four 32-wide boxes streamed a fifth
+//              slower) and one 128B-swizzled [MT][32 k] box of A -> smem
 //   warps 2-9  converters (two groups of four warps on alternate k-blocks): thread (sub, lane) owns weight
 //              column sub*32+lane: it reads its 32 k values from shared memory (conflict-free), and writes the
 //              raw words and their lo parts straight into TMEM with tcgen05.st, so the weights never make a
@@ -170,7 +171,7 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
     ksplit = static_cast<int>(ceil_div64(k_iters, per));  // every split gets at least one k-block
     const bool cluster = ksplit > 1 && ksplit <= TC_CLUSTER_MAX;
     CUtensorMap tmW, tmA;
-    if (!tc::make_map_2d(&tmW, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), 32, 32, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+    if (!tc::make_map_2d(&tmW, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), tc::BN, tc::BK, CU_TENSOR_MAP_SWIZZLE_NONE) ||
         !tc::make_map_2d(&tmA, a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), 32, static_cast<uint32_t>(mt), CU_TENSOR_MAP_SWIZZLE_128B))
         return fail(RMLK_ERR_INTERNAL, "matmul: cuTensorMapEncodeTiled failed");
     tc::TcParams p;

@@ -143,7 +143,7 @@ struct TcParams {
 
 template <int MT, int STAGES>
 struct SmemLayout {
-    static constexpr uint32_t W_BYTES = BK * BN * 4;   // 16 KB raw weights: 4 slabs of [32 k][32 n], unswizzled
+    static constexpr uint32_t W_BYTES = BK * BN * 4;   // 16 KB raw weights: [32 k][128 n] row-major, unswizzled
     static constexpr uint32_t A_BYTES = MT * BK * 4;   // activations [MT rows][32 k], 128-byte swizzled
     static constexpr uint32_t STAGE_BYTES = W_BYTES + 2 * A_BYTES;
     static constexpr uint32_t TILE_BYTES = STAGES * STAGE_BYTES;

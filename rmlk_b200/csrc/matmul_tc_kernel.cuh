@@ -53,8 +53,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
             const uint32_t st = base + it * L::STAGE_BYTES;
             const int k0 = (it_begin + it) * BK;
             mbar_expect_tx(full_bar(it), L::W_BYTES + L::A_BYTES);
-#pragma unroll
-            for (int j = 0; j < 4; j++) tma_load_2d(st + j * 4096, &tmW, n0 + 32 * j, k0, full_bar(it));
+            tma_load_2d(st, &tmW, n0, k0, full_bar(it));
         }
         if (p.w_static) dep_wait();
         for (int it = 0; it < n_iters && it < STAGES; it++)
@@ -81,8 +80,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
                 const uint32_t st = base + s * L::STAGE_BYTES;
                 const int k0 = (it_begin + it) * BK;
                 mbar_expect_tx(full_bar(s), L::W_BYTES + L::A_BYTES);
-#pragma unroll
-                for (int j = 0; j < 4; j++) tma_load_2d(st + j * 4096, &tmW, n0 + 32 * j, k0, full_bar(s));
+                tma_load_2d(st, &tmW, n0, k0, full_bar(s));
                 tma_load_2d(st + L::W_BYTES, &tmA, k0, m0, full_bar(s));
             }
         }
@@ -125,9 +123,10 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
             ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag, p.status);
             if (!ok) break;
             uint8_t* st = base_ptr + s * L::STAGE_BYTES;
-            // weights: this thread owns column n0 + sub*32 + lane = TMEM lane sub*32 + lane; slab `sub` holds it.
-            // 32 k values go to TMEM as tf32 hi and lo (16 columns per store)
-            const float* wcol = reinterpret_cast<const float*>(st + sub * 4096) + lane;
+            // weights: this thread owns column n0 + sub*32 + lane = TMEM lane sub*32 + lane of the [32 k][128 n] block
+            // (a warp reads 32 consecutive floats of a row: conflict-free).  32 k values go to TMEM as tf32 hi and lo
+            // (16 columns per store)
+            const float* wcol = reinterpret_cast<const float*>(st) + sub * 32 + lane;
 #pragma unroll
             for (int half = 0; half < 2; half++) {
                 uint32_t hi[16], lo[16];
@@ -135,7 +134,7 @@ __global__ void __launch_bounds__(THREADS, 1) tc_gemm_kernel(const __grid_consta
                 for (int j = 0; j < 16; j++) {
                     // The MMA reads only the tf32 part of an operand word (sign, exponent, 10 mantissa bits):
                     // the raw fp32 word already is its own truncated `hi`; lo = x - trunc(x) is exact in fp32.
-                    const float x = wcol[(half * 16 + j) * 32];
+                    const float x = wcol[(half * 16 + j) * BN];
                     hi[j] = __float_as_uint(x);
                     lo[j] = __float_as_uint(x - __uint_as_float(hi[j] & TF32_MASK));
                 }
