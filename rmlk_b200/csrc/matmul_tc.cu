@@ -14,20 +14,26 @@
 // issued as one MMA: the lo tile of the activations follows the raw tile in shared memory and a single
 // descriptor with N = 2 MT covers both, filling two accumulator blocks that the epilogue adds.
 //
-// Data path per k-block of 32 (STAGES deep):
+// Data path per k-block of 32:
 //   warp 0     TMA: one unswizzled [32 k][128 n] box of W (512-byte row pieces; four 32-wide boxes streamed a fifth
-//              slower) and one 128B-swizzled [MT][32 k] box of A -> smem
+//              slower) into a ring of SW blocks
+//   warp 10    TMA: one 128B-swizzled [MT][32 k] box of A into a ring of SA blocks
 //   warps 2-9  converters (two groups of four warps on alternate k-blocks): thread (sub, lane) owns weight
 //              column sub*32+lane: it reads its 32 k values from shared memory (conflict-free), and writes the
 //              raw words and their lo parts straight into TMEM with tcgen05.st, so the weights never make a
-//              second trip through shared memory; the lo part of the small A tile goes into a twin tile at
+//              second trip through shared memory - and the W block is handed back to the TMA right then, long
+//              before the MMAs that use it complete; the lo part of the small A tile goes into a twin tile at
 //              the same swizzled offsets
 //   warp 1     one thread issues 4 k-steps x 2 tcgen05.mma with the weight operand read from TMEM and the
-//              activation operand from shared memory (K-major descriptor), then tcgen05.commit -> empty[s]
+//              activation operand from shared memory (K-major descriptor), then tcgen05.commit -> mma_done[s],
+//              which frees the A block, its lo twin and the TMEM weight block
 //   warps 2-9  epilogue: tcgen05.ld 32 lanes x 32 columns, store to C or to the split-K scratch
-// Measured with stages of the pipeline switched off: streaming alone (TMA + barriers, no conversion, no MMA)
-// runs the [64, 2048] x [2048, 128256] shape at 5.3 TB/s; the MMAs cost nothing on top (tensor pipe about 30 %
-// busy); the converters are what separates the full kernel from the streaming rate.
+// Measured on [64, 2048] x [2048, 128256] / [2048, 16384] (ring sizes and stages switched off one at a time):
+// the depth of the activation / TMEM ring sets the pace (2 blocks 449 / 59 us, 4 blocks 266 / 37 us, 6 blocks -
+// all that TMEM holds next to the accumulators - 228 / 34 us), the weight ring needs 4 blocks and gains nothing
+// beyond, one converter group is within 5 % of two or three, and with conversion and MMAs switched off entirely
+// the loads and barriers alone take 210 / 31 us: the k-block round trip (load, hand-offs through four mbarriers,
+// reload), not the arithmetic, bounds the kernel at about 0.5 us per 16 KB of weights per SM.
 //
 // Every mbarrier wait is bounded: on expiry the thread raises a CTA-wide abort flag, records
 // RMLK_ERR_TIMEOUT in the caller's status word, and every role falls through to the common exit where TMEM
@@ -66,21 +72,21 @@ static bool make_map_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint6
               swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MT, int STAGES>
+template <int MT, int SW, int SA, int G>
 static int launch(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tmA, const TcParams& p, dim3 grid) {
-    using L = SmemLayout<MT, STAGES>;
+    using L = SmemLayout<MT, SW, SA>;
     static bool configured[64] = {false};
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !configured[dev]) {
-        RMLK_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<MT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
+        RMLK_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<MT, SW, SA, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
         configured[dev] = true;
     }
     // launched so that it may be scheduled while the previous kernel of the stream drains (the kernel waits, see
     // dep_wait); with split-K inside a cluster the ksplit CTAs of one tile (grid y) form the cluster
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
-    cfg.blockDim = dim3(THREADS);
+    cfg.blockDim = dim3(threads_for(G));
     cfg.dynamicSmemBytes = L::TOTAL;
     cfg.stream = st;
     cudaLaunchAttribute at[2];
@@ -99,7 +105,7 @@ static int launch(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tm
     }
     cfg.attrs = at;
     cfg.numAttrs = na;
-    RMLK_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<MT, STAGES>, tmW, tmA, p));
+    RMLK_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<MT, SW, SA, G>, tmW, tmA, p));
     RMLK_CHECK_LAUNCH("tc_gemm_kernel");
     return RMLK_OK;
 }
@@ -185,8 +191,8 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
     p.w_static = (flags & RMLK_MATMUL_B_STATIC) ? 1 : 0;
     dim3 grid(static_cast<unsigned>(n / tc::BN), static_cast<unsigned>(ksplit), static_cast<unsigned>(ceil_div64(m, mt)));
     *ksplit_out = cluster ? 1 : ksplit;  // slabs left in `workspace` for the caller to add
-    if (mt == 64) return tc::launch<64, 6>(st, tmW, tmA, p, grid);
-    return tc::launch<128, 4>(st, tmW, tmA, p, grid);
+    if (mt == 64) return tc::launch<64, 4, 6, 2>(st, tmW, tmA, p, grid);
+    return tc::launch<128, 4, 4, 2>(st, tmW, tmA, p, grid);
 }
 
 }  // namespace rmlk

@@ -10,7 +10,8 @@ namespace tc {
 
 constexpr int BK = 32;    // fp32 elements per k-block: one 128-byte row
 constexpr int BN = 128;   // weight columns per CTA = MMA M = TMEM lanes
-constexpr int THREADS = 320;  // TMA warp, MMA warp, 2 x 4 converter / epilogue warps
+// weight-TMA warp, MMA warp, G x 4 converter / epilogue warps, activation-TMA warp
+constexpr int threads_for(int groups) { return 64 + 128 * groups + 32; }
 constexpr uint32_t SPIN_LIMIT = 1u << 20;
 constexpr uint32_t TF32_MASK = 0xffffe000u;  // sign, exponent and the 10 mantissa bits a tf32 MMA operand keeps
 
@@ -141,17 +142,23 @@ struct TcParams {
     int w_static;           // the weights are not written by work still in flight: their loads need not wait for the previous kernel
 };
 
-template <int MT, int STAGES>
+// Shared memory: a ring of SW raw weight blocks (freed as soon as the converters have moved a block into TMEM) and a
+// ring of SA activation blocks (raw tile + its lo twin, read by the MMA from shared memory, freed when the MMAs of
+// that k-block complete).  TMEM: two accumulator blocks + one (hi, lo) weight block per activation stage.
+template <int MT, int SW, int SA>
 struct SmemLayout {
     static constexpr uint32_t W_BYTES = BK * BN * 4;   // 16 KB raw weights: [32 k][128 n] row-major, unswizzled
     static constexpr uint32_t A_BYTES = MT * BK * 4;   // activations [MT rows][32 k], 128-byte swizzled
-    static constexpr uint32_t STAGE_BYTES = W_BYTES + 2 * A_BYTES;
-    static constexpr uint32_t TILE_BYTES = STAGES * STAGE_BYTES;
+    static constexpr uint32_t A_STAGE_BYTES = 2 * A_BYTES;
+    static constexpr uint32_t A_OFFSET = SW * W_BYTES;
+    static constexpr uint32_t TILE_BYTES = SW * W_BYTES + SA * A_STAGE_BYTES;
     static constexpr uint32_t BAR_OFFSET = TILE_BYTES;
-    static constexpr uint32_t TOTAL = TILE_BYTES + 256 + 1024;  // barriers + slack for 1024-byte alignment
-    static constexpr uint32_t TMEM_COLS_USED = 2 * MT + 64 * STAGES;  // two accumulator blocks + (hi, lo) weight blocks per stage
+    static constexpr uint32_t N_BARS = 2 * SW + 3 * SA + 1;
+    static constexpr uint32_t TOTAL = TILE_BYTES + 8 * N_BARS + 32 + 1024;  // barriers, TMEM slot + abort flag, slack for 1024-byte alignment
+    static constexpr uint32_t TMEM_COLS_USED = 2 * MT + 64 * SA;
     static constexpr uint32_t TMEM_COLS = TMEM_COLS_USED <= 64 ? 64 : TMEM_COLS_USED <= 128 ? 128 : TMEM_COLS_USED <= 256 ? 256 : 512;
     static_assert(TMEM_COLS_USED <= 512, "TMEM budget exceeded");
+    static_assert(TOTAL <= 227 * 1024, "shared memory budget exceeded");
 };
 
 }  // namespace tc

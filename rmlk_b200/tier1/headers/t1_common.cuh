@@ -135,14 +135,28 @@ __device__ __forceinline__ void expand_body(size_t n, size_t in_rank_, size_t ou
     const int in_rank = static_cast<int>(in_rank_), out_rank = static_cast<int>(out_rank_);
     const size_t *ishape = info, *istr = info + in_rank, *oshape = info + 2 * in_rank, *ostr = info + 2 * in_rank + out_rank;
     const int lead = out_rank - in_rank;
+    const bool small = n <= 0xffffffffull;
     for (size_t i = global_tid(); i < n; i += grid_threads()) {
-        size_t t = i, src = 0, dst = 0;
-        for (int d = out_rank - 1; d >= 0; d--) {
-            const size_t q = t / oshape[d], c = t - q * oshape[d];
-            t = q;
-            dst += c * ostr[d];
-            const int id = d - lead;
-            if (id >= 0 && ishape[id] != 1) src += c * istr[id];
+        size_t src = 0, dst = 0;
+        if (small) {  // 32-bit divides; stop once the remaining index is zero
+            uint32_t t = static_cast<uint32_t>(i);
+            for (int d = out_rank - 1; d >= 0 && t != 0; d--) {
+                const uint32_t m = static_cast<uint32_t>(oshape[d]);
+                const uint32_t q = t / m, c = t - q * m;
+                t = q;
+                dst += static_cast<size_t>(c) * ostr[d];
+                const int id = d - lead;
+                if (id >= 0 && ishape[id] != 1) src += static_cast<size_t>(c) * istr[id];
+            }
+        } else {
+            size_t t = i;
+            for (int d = out_rank - 1; d >= 0; d--) {
+                const size_t q = t / oshape[d], c = t - q * oshape[d];
+                t = q;
+                dst += c * ostr[d];
+                const int id = d - lead;
+                if (id >= 0 && ishape[id] != 1) src += c * istr[id];
+            }
         }
         out[dst] = in[src];
     }
@@ -153,13 +167,26 @@ template <typename T>
 __device__ __forceinline__ void transpose_body(size_t n, size_t rank_, const size_t* info, const size_t* perm, const T* src, T* dst) {
     const int rank = static_cast<int>(rank_);
     const size_t *dims = info, *sstr = info + rank, *dstr = info + 2 * rank;
+    const bool small = n <= 0xffffffffull;
     for (size_t i = global_tid(); i < n; i += grid_threads()) {
-        size_t t = i, so = 0, dof = 0;
-        for (int d = rank - 1; d >= 0; d--) {
-            const size_t q = t / dims[d], c = t - q * dims[d];
-            t = q;
-            so += c * sstr[perm[d]];
-            dof += c * dstr[d];
+        size_t so = 0, dof = 0;
+        if (small) {  // 32-bit divides; stop once the remaining index is zero
+            uint32_t t = static_cast<uint32_t>(i);
+            for (int d = rank - 1; d >= 0 && t != 0; d--) {
+                const uint32_t m = static_cast<uint32_t>(dims[d]);
+                const uint32_t q = t / m, c = t - q * m;
+                t = q;
+                so += static_cast<size_t>(c) * sstr[perm[d]];
+                dof += static_cast<size_t>(c) * dstr[d];
+            }
+        } else {
+            size_t t = i;
+            for (int d = rank - 1; d >= 0; d--) {
+                const size_t q = t / dims[d], c = t - q * dims[d];
+                t = q;
+                so += c * sstr[perm[d]];
+                dof += c * dstr[d];
+            }
         }
         dst[dof] = src[so];
     }
