@@ -330,6 +330,21 @@ RMLK_API int rmlk_b200_rope_to(rmlk_stream_t stream, int dtype, const int64_t* s
                       const int64_t* cos_strides, const int64_t* sin_strides, const void* x, const void* cosv, const void* sinv,
                       void* out, const int64_t* out_strides);
 
+/* Decode attention over a KV cache read in place, one launch: for each of `problems` (batch entry x KV head) and each
+ * of its `rows` (1..4) query rows - the query heads sharing that KV head, one new token each -
+ *   out[p][r] = softmax_t((q[p][r] . K[p][t]) * scale + mask[b][h][t]) . V[p][:, :]
+ * q, out: [problems, rows, head_dim] dense; K, V: [keys, head_dim] dense rows per problem, problems
+ * k_problem_stride / v_problem_stride elements apart (a cache with spare room); mask: rows of `keys` floats found at
+ * b * mask_batch_stride + h * mask_head_stride with b = p / kv_heads, h = (p % kv_heads) * rows + r, or NULL.
+ * head_dim 16 / 32 / 64 / 128, keys <= 12288 (rmlk_b200_gqa_decode_attention_supported).  Replaces, for a decode
+ * step, backend/expand.rs (x2), transpose.rs, matmul.rs (x2), mul.rs, add.rs, softmax.rs - each a launch with its own
+ * copy in the reference - and reads K and V once. */
+RMLK_API int rmlk_b200_gqa_decode_attention(rmlk_stream_t stream, int dtype, int64_t problems, int64_t rows, int64_t head_dim, int64_t keys,
+                                   int64_t kv_heads, const void* q, const void* k, int64_t k_problem_stride, const void* v,
+                                   int64_t v_problem_stride, float scale, const void* mask, int64_t mask_batch_stride,
+                                   int64_t mask_head_stride, void* out);
+RMLK_API int rmlk_b200_gqa_decode_attention_supported(int64_t rows, int64_t head_dim, int64_t keys);
+
 /* SwiGLU gate as exported: Mul(Mul(gate, Sigmoid(gate)), up), n elements each.  Replaces backend/sigmoid.rs (cuDNN
  * activation, kernels/activation.rs:6-39) and backend/mul.rs (x2). */
 RMLK_API int rmlk_b200_swiglu(rmlk_stream_t stream, int dtype, int64_t n, const void* gate, const void* up, void* out);

@@ -1,0 +1,235 @@
+// Decode attention over a KV cache read in place, one launch.  For every problem p (batch entry x KV head) and each
+// of its R <= 4 query rows (the query heads that share the KV head, one new token each):
+//     s[r][t] = (q[p][r] . K[p][t]) * scale + mask[b][h][t]      t < T keys
+//     P[r][:] = softmax(s[r][:])
+//     out[p][r] = sum_t P[r][t] * V[p][t]
+// which an exported decoder graph spells MatMul(q, Transpose(K)) -> Mul -> Add -> Softmax -> MatMul(., V), with K and V
+// first repeated per query head (Expand) and K transposed; the reference runs every one of those nodes as a launch
+// with a copy of its own (backend/matmul.rs:223-356, mul.rs, add.rs, softmax.rs, expand.rs, transpose.rs).  Here K
+// and V are read once, from the cache as it lies ([T, D] rows per problem, problems a fixed stride apart), and the
+// scores never leave shared memory.
+//
+// One CTA of 8 warps per problem.  LPR = D / 4 lanes cover a row of K or V with one 16-byte load each, so a warp-wide
+// load reads 32 / LPR whole rows (512 contiguous bytes); every warp keeps 16 such loads in flight.  The arithmetic
+// follows the single kernels it stands for: dot products as in the A x B^T kernel (same FMA order, same shuffle
+// butterfly), scale / mask / max / exp / sum / divide as in the softmax kernel (same expressions, same order), so
+// the probabilities equal theirs bit for bit; the P x V sums associate differently from the stand-alone MatMul
+// (within its 1e-4 bar).
+//
+// Measured on 512 problems x 4 rows x 550 keys x 64 (one layer of the decode benchmark): about 45 us against 37 us
+// for the A x B^T, softmax and narrow-MatMul kernels run one after the other - those spread a problem over many
+// warps of many CTAs and keep far more loads in flight than one CTA per problem can.  The host runtime therefore
+// uses this kernel only on request; splitting the keys of a problem over several CTAs is the way to make it pay.
+#include "common.cuh"
+
+namespace rmlk {
+
+struct AttnParams {
+    const float* q;
+    const float* k;
+    const float* v;
+    const float* mask;  // may be null
+    float* out;
+    int64_t kb, vb;            // problem strides of K and V (elements)
+    int64_t ms_b, ms_h;        // mask strides per batch entry and per head (elements; rows of T are dense)
+    int rows, T, kv_heads;
+    float scale;
+};
+
+template <int LPR>
+__global__ void __launch_bounds__(256, 2) gqa_decode_attention_kernel(AttnParams p) {
+    dep_sync();
+    constexpr int D = 4 * LPR;
+    constexpr int RPI = 32 / LPR;  // rows of K / V per warp-wide load
+    constexpr int UN = 16;         // loads in flight per warp
+    extern __shared__ __align__(16) float smem[];
+    float* s = smem;                                    // [T][4]: scores, then probabilities, of the 4 query rows
+    float* red = smem + 4 * ((p.T + 3) & ~3);           // [8 warps][4 rows][D]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPR, rsel = lane / LPR;
+    const int64_t prob = blockIdx.x;
+    const int T = p.T;
+
+    // ---- scores ----
+    float4 a[4];
+#pragma unroll
+    for (int m = 0; m < 4; m++) {
+        a[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (m < p.rows) a[m] = __ldg(reinterpret_cast<const float4*>(p.q + (prob * p.rows + m) * D + 4 * sub));
+    }
+    const int64_t b = prob / p.kv_heads, h0 = (prob % p.kv_heads) * p.rows;
+    const float* __restrict__ K = p.k + prob * p.kb + 4 * sub;
+    for (int t0 = 0; t0 < T; t0 += 8 * RPI * UN) {
+        uint4 bv[UN];
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int t = t0 + (u * 8 + warp) * RPI + rsel;
+            bv[u] = make_uint4(0, 0, 0, 0);
+            if (t < T) bv[u] = ld_stream_u4(K + static_cast<int64_t>(t) * D);
+        }
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int t = t0 + (u * 8 + warp) * RPI + rsel;
+            const float bx = __uint_as_float(bv[u].x), by = __uint_as_float(bv[u].y), bz = __uint_as_float(bv[u].z), bw = __uint_as_float(bv[u].w);
+            float part[4];
+#pragma unroll
+            for (int m = 0; m < 4; m++) part[m] = fmaf(a[m].w, bw, fmaf(a[m].z, bz, fmaf(a[m].y, by, a[m].x * bx)));
+            // the four partial sums are added across the LPR lanes of the row; the first two steps exchange halves
+            const bool up1 = (sub & (LPR / 2)) != 0;
+            const float r0 = __shfl_xor_sync(0xffffffffu, up1 ? part[0] : part[2], LPR / 2);
+            const float r1 = __shfl_xor_sync(0xffffffffu, up1 ? part[1] : part[3], LPR / 2);
+            const float q0 = (up1 ? part[2] : part[0]) + r0;
+            const float q1 = (up1 ? part[3] : part[1]) + r1;
+            const bool up2 = (sub & (LPR / 4)) != 0;
+            const float r2 = __shfl_xor_sync(0xffffffffu, up2 ? q0 : q1, LPR / 4);
+            float v = (up2 ? q1 : q0) + r2;
+#pragma unroll
+            for (int off = LPR / 8; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+            const int m = 2 * (up1 ? 1 : 0) + (up2 ? 1 : 0);
+            if ((sub & (LPR / 4 - 1)) == 0 && t < T && m < p.rows) {
+                float x = __fmul_rn(v, p.scale);
+                if (p.mask) x = __fadd_rn(x, p.mask[b * p.ms_b + (h0 + m) * p.ms_h + t]);
+                s[4 * t + m] = x;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- softmax: warp m takes query row m ----
+    if (warp < p.rows) {
+        float mx = -INFINITY;
+        for (int t = lane; t < T; t += 32) mx = fmaxf(mx, s[4 * t + warp]);
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+        for (int t = lane; t < T; t += 32) {
+            const float e = expf(s[4 * t + warp] - mx);
+            s[4 * t + warp] = e;
+            sum += e;
+        }
+#pragma unroll
+        for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        for (int t = lane; t < T; t += 32) s[4 * t + warp] = s[4 * t + warp] / sum;
+    } else if (warp < 4) {
+        for (int t = lane; t < T; t += 32) s[4 * t + warp] = 0.f;  // rows that do not exist contribute nothing below
+    }
+    __syncthreads();
+
+    // ---- context ----
+    float acc[4][4];
+#pragma unroll
+    for (int m = 0; m < 4; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[m][j] = 0.f;
+    const float* __restrict__ V = p.v + prob * p.vb + 4 * sub;
+    for (int t0 = 0; t0 < T; t0 += 8 * RPI * UN) {
+        uint4 bv[UN];
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int t = t0 + (u * 8 + warp) * RPI + rsel;
+            bv[u] = make_uint4(0, 0, 0, 0);
+            if (t < T) bv[u] = ld_stream_u4(V + static_cast<int64_t>(t) * D);
+        }
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int t = t0 + (u * 8 + warp) * RPI + rsel;
+            if (t < T) {
+                const float4 pr = *reinterpret_cast<const float4*>(s + 4 * t);
+                const float vx = __uint_as_float(bv[u].x), vy = __uint_as_float(bv[u].y), vz = __uint_as_float(bv[u].z), vw = __uint_as_float(bv[u].w);
+                const float pm[4] = {pr.x, pr.y, pr.z, pr.w};
+#pragma unroll
+                for (int m = 0; m < 4; m++) {
+                    acc[m][0] = fmaf(pm[m], vx, acc[m][0]);
+                    acc[m][1] = fmaf(pm[m], vy, acc[m][1]);
+                    acc[m][2] = fmaf(pm[m], vz, acc[m][2]);
+                    acc[m][3] = fmaf(pm[m], vw, acc[m][3]);
+                }
+            }
+        }
+    }
+    // rows handled by the other lane groups of the warp, then the 8 warps in warp order
+#pragma unroll
+    for (int m = 0; m < 4; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float x = acc[m][j];
+#pragma unroll
+            for (int off = LPR; off < 32; off <<= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+            acc[m][j] = x;
+        }
+    if (rsel == 0) {
+#pragma unroll
+        for (int m = 0; m < 4; m++)
+            *reinterpret_cast<float4*>(red + (warp * 4 + m) * D + 4 * sub) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.rows * D; i += 256) {
+        const int m = i / D, d = i - m * D;
+        float x = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) x += red[(w * 4 + m) * D + d];
+        p.out[(prob * p.rows + m) * D + d] = x;
+    }
+}
+
+constexpr int64_t ATTN_MAX_KEYS = 12288;  // 16 bytes of shared memory per key
+
+template <int LPR>
+static int attn_launch(cudaStream_t st, const AttnParams& p, int64_t problems) {
+    const size_t smem = (4 * static_cast<size_t>((p.T + 3) & ~3) + 8 * 4 * 4 * LPR) * sizeof(float);
+    static bool configured[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !configured[dev]) {
+        RMLK_CUDA(cudaFuncSetAttribute(gqa_decode_attention_kernel<LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>((4 * ATTN_MAX_KEYS + 8 * 4 * 4 * LPR) * sizeof(float))));
+        configured[dev] = true;
+    }
+    launch_dep(gqa_decode_attention_kernel<LPR>, dim3(static_cast<unsigned>(problems)), dim3(256), smem, st, p);
+    RMLK_CHECK_LAUNCH("gqa_decode_attention_kernel");
+    return RMLK_OK;
+}
+
+}  // namespace rmlk
+
+using namespace rmlk;
+
+extern "C" int rmlk_b200_gqa_decode_attention_supported(int64_t rows, int64_t head_dim, int64_t keys) {
+    return rows >= 1 && rows <= 4 && (head_dim == 16 || head_dim == 32 || head_dim == 64 || head_dim == 128) && keys >= 1 && keys <= ATTN_MAX_KEYS;
+}
+
+extern "C" int rmlk_b200_gqa_decode_attention(rmlk_stream_t stream, int dtype, int64_t problems, int64_t rows, int64_t head_dim, int64_t keys,
+                                              int64_t kv_heads, const void* q, const void* k, int64_t k_problem_stride, const void* v,
+                                              int64_t v_problem_stride, float scale, const void* mask, int64_t mask_batch_stride,
+                                              int64_t mask_head_stride, void* out) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for gqa_decode_attention (f32 only)");
+    if (problems < 0 || kv_heads <= 0) return fail(RMLK_ERR_INVALID_ARG, "gqa_decode_attention: bad extent");
+    if (!rmlk_b200_gqa_decode_attention_supported(rows, head_dim, keys))
+        return fail(RMLK_ERR_INVALID_ARG, "gqa_decode_attention: needs 1..4 query rows, head_dim 16 / 32 / 64 / 128 and 1..12288 keys");
+    if (problems == 0) return RMLK_OK;
+    if (!q || !k || !v || !out) return fail(RMLK_ERR_INVALID_ARG, "gqa_decode_attention: NULL tensor pointer");
+    if (problems > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "gqa_decode_attention: too many problems");
+    if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || !aligned_to(out, 16) || k_problem_stride % 4 || v_problem_stride % 4)
+        return fail(RMLK_ERR_INVALID_ARG, "gqa_decode_attention: operands must be 16-byte aligned");
+    AttnParams p;
+    p.q = static_cast<const float*>(q);
+    p.k = static_cast<const float*>(k);
+    p.v = static_cast<const float*>(v);
+    p.mask = static_cast<const float*>(mask);
+    p.out = static_cast<float*>(out);
+    p.kb = k_problem_stride;
+    p.vb = v_problem_stride;
+    p.ms_b = mask_batch_stride;
+    p.ms_h = mask_head_stride;
+    p.rows = static_cast<int>(rows);
+    p.T = static_cast<int>(keys);
+    p.kv_heads = static_cast<int>(kv_heads);
+    p.scale = scale;
+    cudaStream_t st = as_stream(stream);
+    switch (head_dim) {
+        case 16: return attn_launch<4>(st, p, problems);
+        case 32: return attn_launch<8>(st, p, problems);
+        case 64: return attn_launch<16>(st, p, problems);
+        default: return attn_launch<32>(st, p, problems);
+    }
+}

@@ -1607,6 +1607,24 @@ void Instance::find_fusions() {
                     fg.v[0] = scores; fg.v[1] = scale; fg.v[2] = mask;
                     commit(fg);
                     done = true;
+                    // scores = MatMul(q, K^T) read only here, probabilities read only by MatMul(., V): the five nodes
+                    // are one attention group (the chain above stays available on its own for runs that do not fit)
+                    const int n_sc = m.inner(scores, RMLK_OP_MATMUL);
+                    const int probs = root.outputs.empty() ? -1 : root.outputs[0];
+                    int n_ctx = -1;
+                    if (attention && n_sc >= 0 && probs >= 0 && m.uses[probs] == 1 && !g.values[probs].is_output) {
+                        for (size_t j = r + 1; j < g.nodes.size() && n_ctx < 0; j++)
+                            if (g.nodes[j].op == RMLK_OP_MATMUL && group_of_node[j] < 0 && m.n_in(static_cast<int>(j)) == 2 && g.nodes[j].inputs[0] == probs)
+                                n_ctx = static_cast<int>(j);
+                    }
+                    if (n_ctx >= 0 && m.n_in(n_sc) == 2) {
+                        FusedGroup at;
+                        at.kind = FusedGroup::ATTENTION;
+                        at.sub = static_cast<int>(groups.size()) - 1;
+                        at.members = {n_sc, n_mul, n_add, ri, n_ctx};
+                        at.v[0] = m.in(n_sc, 0); at.v[1] = scale; at.v[2] = mask; at.v[3] = m.in(n_sc, 1); at.v[4] = m.in(n_ctx, 1);
+                        commit(at);
+                    }
                 }
             }
         }
@@ -1741,6 +1759,39 @@ bool Instance::run_fused(const FusedGroup& fg) {
             Tensor& o = c.make(0, RMLK_F32, oshape);
             if (o.numel() == 0) return true;
             check_rc(rmlk_b200_scale_mask_softmax(st, RMLK_F32, lead3, cols, mstr3, scale, s->data, mk->data, o.data));
+            launches++;
+            return true;
+        }
+        case FusedGroup::ATTENTION: {
+            Tensor *q = val(fg.v[0]), *sc = val(fg.v[1]), *mk = val(fg.v[2]), *kt = val(fg.v[3]), *vh = val(fg.v[4]);
+            float scale = 0.f;
+            if (!q || !sc || !mk || !kt || !vh || q->dtype != RMLK_F32 || mk->dtype != RMLK_F32 || kt->dtype != RMLK_F32 || vh->dtype != RMLK_F32 ||
+                !scalar_f32(*sc, scale))
+                return false;
+            if (q->shape.size() != 4 || kt->shape.size() != 4 || vh->shape.size() != 4 || q->parts > 1) return false;
+            const int64_t B = q->shape[0], H = q->shape[1], S = q->shape[2], D = q->shape[3], T = kt->shape[3];
+            if (S != 1 || B <= 0 || H <= 0 || kt->shape[0] != B || kt->shape[1] != H || kt->shape[2] != D || vh->shape != Shape({B, H, T, D})) return false;
+            {
+                const NodeDef& smn = g.nodes[groups[fg.sub].root];
+                const int64_t axis = Ctx{*this, smn}.attr_int("axis", -1);
+                if (axis != -1 && axis != 3) return false;
+            }
+            // K^T and V must be views that repeat a dense [T, D] block per KV head over `fold` query heads
+            LazyB lk, lv;
+            if (!analyze_lazy_b(*kt, D, T, lk) || !lk.transposed || !analyze_lazy_b(*vh, T, D, lv) || lv.transposed) return false;
+            if (lk.fold != lv.fold || lk.outer != lv.outer || lk.outer * lk.fold != B * H || H % lk.fold) return false;
+            if (!rmlk_b200_gqa_decode_attention_supported(lk.fold, D, T)) return false;
+            if (lk.outer > 1 && (lk.sb % 4 || lv.sb % 4)) return false;
+            if (reinterpret_cast<uintptr_t>(kt->data) % 16 || reinterpret_cast<uintptr_t>(vh->data) % 16) return false;
+            if (mk->lazy) materialize(*mk);
+            int64_t ms[4];
+            const Shape sshape = {B, H, 1, T};
+            if (mk->shape.size() > 4 || mk->shape.empty() || mk->shape.back() != T || !bcast_strides(*mk, sshape, ms) || (T > 1 && ms[3] != 1)) return false;
+            if (q->lazy) materialize(*q);
+            const void *kdata = kt->data, *vdata = vh->data;
+            Tensor& o = c.make(0, RMLK_F32, Shape({B, H, 1, D}));
+            check_rc(rmlk_b200_gqa_decode_attention(st, RMLK_F32, lk.outer, lk.fold, D, T, H / lk.fold, q->data, kdata, lk.sb, vdata, lv.sb, scale, mk->data,
+                                                    ms[0], ms[1], o.data));
             launches++;
             return true;
         }

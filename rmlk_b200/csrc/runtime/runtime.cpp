@@ -359,6 +359,17 @@ void Instance::run() {
             try {
                 if (run_fused(fg)) {
                     fused_runs++;
+                } else if (fg.kind == FusedGroup::ATTENTION) {
+                    // scores MatMul, then the scale + mask + softmax chain (as one launch if it fits), then the context MatMul
+                    const FusedGroup& sm = groups[fg.sub];
+                    run_node(g.nodes[fg.members.front()]);
+                    if (run_fused(sm)) {
+                        fused_runs++;
+                    } else {
+                        fused_fallbacks++;
+                        for (int m : sm.members) run_node(g.nodes[m]);
+                    }
+                    run_node(g.nodes[fg.root]);
                 } else {
                     fused_fallbacks++;
                     for (int m : fg.members) run_node(g.nodes[m]);
@@ -606,6 +617,7 @@ extern "C" rmlk_instance* rmlk_instance_create(const rmlk_graph* g, int device, 
         if (const char* e = getenv("RMLK_B200_NO_FUSION")) I.fusion = e[0] != '1';
         if (const char* e = getenv("RMLK_B200_NO_ADD_NORM")) I.add_norm = e[0] != '1';
         if (const char* e = getenv("RMLK_B200_NO_APPEND_TO")) I.inplace_append_to = e[0] != '1';
+        if (const char* e = getenv("RMLK_B200_ATTENTION")) I.attention = e[0] == '1';
         I.find_fusions();  // recognise RMSNorm / rotary / SwiGLU / scale-mask-softmax chains; re-derives last_use
         I.find_merged_matmuls();  // q / k / v and gate / up projections: one MatMul per shared left operand
         // one weight arena, one pass of uploads (the reference allocates and copies per tensor through a
@@ -794,7 +806,15 @@ extern "C" int rmlk_instance_read(rmlk_instance* inst, const char* name, void* d
 
 extern "C" int64_t rmlk_instance_last_launches(const rmlk_instance* inst) { return inst ? inst->I.launches : 0; }
 extern "C" int64_t rmlk_instance_last_syncs(const rmlk_instance* inst) { return inst ? inst->I.syncs : 0; }
-extern "C" int64_t rmlk_instance_fused_chains(const rmlk_instance* inst) { return inst ? static_cast<int64_t>(inst->I.groups.size()) : 0; }
+extern "C" int64_t rmlk_instance_fused_chains(const rmlk_instance* inst) {
+    if (!inst) return 0;
+    int64_t n = 0;  // groups that own their nodes (a softmax chain inside an attention group is not counted twice)
+    for (size_t i = 0; i < inst->I.groups.size(); i++) {
+        const int root = inst->I.groups[i].root;
+        if (root >= 0 && inst->I.group_of_node[root] == static_cast<int>(i)) n++;
+    }
+    return n;
+}
 extern "C" int64_t rmlk_instance_fused_runs(const rmlk_instance* inst) { return inst ? inst->I.fused_runs : 0; }
 extern "C" int64_t rmlk_instance_fused_fallbacks(const rmlk_instance* inst) { return inst ? inst->I.fused_fallbacks : 0; }
 extern "C" size_t rmlk_instance_arena_peak(const rmlk_instance* inst) { return inst && inst->I.arena ? inst->I.arena->peak() : 0; }

@@ -163,8 +163,9 @@ struct Binding {  // output value -> input value, double-buffered
 // tensors of this run do not meet its conditions - the members run one by one, as if nothing had been matched.
 // Member outputs other than the root's are used only inside the chain, so running them late changes nothing.
 struct FusedGroup {
-    enum Kind { RMSNORM = 1, ROPE, SWIGLU, SCALE_MASK_SOFTMAX } kind;
+    enum Kind { RMSNORM = 1, ROPE, SWIGLU, SCALE_MASK_SOFTMAX, ATTENTION } kind;
     int root = -1;
+    int sub = -1;  // ATTENTION: index of the scale + mask + softmax group inside it, tried on its own when the whole does not fit
     std::vector<int> members;  // node indices in execution order, root last
     int v[8] = {-1, -1, -1, -1, -1, -1, -1, -1};  // value ids by role (per kind, see ops.cpp)
 };
@@ -212,6 +213,10 @@ struct Instance {
     // producer of such rows may write them straight into the cache slot (rotary embedding of the keys does).
     std::vector<int> append_consumer;
     bool inplace_append_to = true;  // RMLK_B200_NO_APPEND_TO=1: new rows are made dense first, then copied in
+    // RMLK_B200_ATTENTION=1: scores MatMul, softmax chain and context MatMul of a decode step run as one kernel.  Off by
+    // default: with one CTA per (batch entry, KV head) that kernel keeps fewer bytes in flight than the three
+    // kernels it replaces and measured 8 us per layer slower on 512 problems of 550 keys.
+    bool attention = false;
     bool add_norm = true;       // RMLK_B200_NO_ADD_NORM=1: keep the residual Add (and the split-K sum) as launches of their own
     void settle_parts(int value_id);
     DeviceBuffer read_staging;  // dense copy of a strided output while it is read back

@@ -387,6 +387,27 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[to
     return out
 
 
+def gqa_decode_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [B, KV, G, D] (G <= 4 query heads per KV head, one token each); k, v [B, KV, T, D] views whose [T, D] blocks are
+    dense (the batch / head dims may step over spare room); mask [B, 1 or KV*G, 1, T] or None -> [B, KV, G, D]."""
+    _require_cuda(q, mask)
+    B, KV, G, D = q.shape
+    T = k.shape[2]
+    assert k.is_cuda and v.is_cuda and k.shape == v.shape == (B, KV, T, D) and q.is_contiguous()
+    assert k.stride(3) == 1 and k.stride(2) == D and v.stride(3) == 1 and v.stride(2) == D
+    assert k.stride(0) == KV * k.stride(1) and v.stride(0) == KV * v.stride(1)
+    out = torch.empty_like(q)
+    mb = mh = 0
+    if mask is not None:
+        assert mask.dim() == 4 and mask.shape[0] == B and mask.shape[2] == 1 and mask.shape[3] == T and mask.stride(3) == 1
+        mb, mh = mask.stride(0), (mask.stride(1) if mask.shape[1] > 1 else 0)
+    _check(lib().rmlk_b200_gqa_decode_attention(_stream(), dt.from_torch(q.dtype), ctypes.c_int64(B * KV), ctypes.c_int64(G), ctypes.c_int64(D),
+                                                ctypes.c_int64(T), ctypes.c_int64(KV), _ptr(q), ctypes.c_void_p(k.data_ptr()), ctypes.c_int64(k.stride(1)),
+                                                ctypes.c_void_p(v.data_ptr()), ctypes.c_int64(v.stride(1)), ctypes.c_float(scale),
+                                                ctypes.c_void_p(0 if mask is None else mask.data_ptr()), ctypes.c_int64(mb), ctypes.c_int64(mh), _ptr(out)))
+    return out
+
+
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """(gate * sigmoid(gate)) * up."""
     _require_cuda(gate, up)

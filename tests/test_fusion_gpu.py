@@ -339,3 +339,111 @@ def test_residual_add_that_broadcasts_falls_back(cuda):
     assert inst.fused[2] == 1 and inst.fused[1] == 1     # first chain fell back, second ran fused
     want = graph_cpu.run_graph(spec, feeds)["h2"]
     assert np.max(np.abs(got - want)) <= 1e-4 * np.max(np.abs(want))
+
+
+def test_decode_attention_kernel(K):
+    """One launch for scores -> scale -> mask -> softmax -> context over a cache with spare room, against the fp64
+    result and against the single kernels it stands for."""
+    g = torch.Generator(device="cuda").manual_seed(41)
+    for (B, KV, G, T, D, cap) in [(64, 8, 4, 523, 64, 700), (3, 2, 4, 37, 16, 37), (2, 3, 2, 130, 32, 200), (2, 2, 1, 65, 128, 70),
+                                  (1, 1, 3, 1, 64, 4), (2, 2, 4, 2500, 64, 2500)]:
+        q = torch.randn(B, KV, G, D, device="cuda", generator=g)
+        kbuf = torch.randn(B, KV, cap, D, device="cuda", generator=g)
+        vbuf = torch.randn(B, KV, cap, D, device="cuda", generator=g)
+        k, v = kbuf[:, :, :T, :], vbuf[:, :, :T, :]
+        mask = torch.where(torch.rand(B, 1, 1, T, device="cuda", generator=g) > 0.8, torch.tensor(float(np.finfo(np.float32).min), device="cuda"),
+                           torch.tensor(0.0, device="cuda"))
+        mask[..., 0] = 0.0
+        scale = 1.0 / np.sqrt(D)
+        got = K.gqa_decode_attention(q, k, v, scale, mask)
+        s64 = torch.einsum("bkgd,bktd->bkgt", q.double(), k.double()) * scale + mask.double().view(B, 1, 1, T)
+        ref = torch.einsum("bkgt,bktd->bkgd", torch.softmax(s64, -1), v.double())
+        assert float((got.double() - ref).abs().max()) <= 1e-5 * max(1.0, float(ref.abs().max())), (B, KV, G, T, D)
+        # the single kernels: A x B^T per KV head, fused scale + mask + softmax, then P x V
+        sc = K.matmul_nt(q.reshape(B * KV, G, D), k.contiguous().reshape(B * KV, T, D)).reshape(B, KV * G, 1, T)
+        pr = K.scale_mask_softmax(sc, scale, mask) if T <= 2048 else torch.softmax(sc * scale + mask, -1)
+        want = K.matmul(pr.reshape(B * KV, G, T), v.contiguous().reshape(B * KV, T, D)).reshape(B, KV, G, D)
+        assert float((got - want).abs().max()) <= 1e-5 * max(1.0, float(want.abs().max())), (B, KV, G, T, D)
+        nomask = K.gqa_decode_attention(q, k, v, scale, None)
+        ref2 = torch.einsum("bkgt,bktd->bkgd", torch.softmax(torch.einsum("bkgd,bktd->bkgt", q.double(), k.double()) * scale, -1), v.double())
+        assert float((nomask.double() - ref2).abs().max()) <= 1e-5 * max(1.0, float(ref2.abs().max()))
+
+
+def attention_graph(KV, G, D):
+    g = GraphSpec()
+    g.input("q", np.float32, [0, KV * G, 0, D])
+    g.input("new_k", np.float32, [0, KV, 0, D])
+    g.input("new_v", np.float32, [0, KV, 0, D])
+    g.input("past_k", np.float32, [0, KV, 0, D])
+    g.input("past_v", np.float32, [0, KV, 0, D])
+    g.input("mask", np.float32, [0, 1, 0, 0])
+    g.const("scale", np.array(1.0 / np.sqrt(D), np.float32))
+    g.const("ax2", i64(2))
+    g.const("rep", i64(1, 1, G, 1, 1))
+    g.const("heads", i64(0, KV * G, -1, D))
+    g.op("Concat", ["past_k", "new_k"], "present_k", axis=2)
+    g.op("Concat", ["past_v", "new_v"], "present_v", axis=2)
+
+    def heads(c):
+        return g.op("Reshape", [g.op("Expand", [g.op("Unsqueeze", [c, "ax2"]), "rep"]), "heads"])
+
+    sc = g.op("MatMul", ["q", g.op("Transpose", [heads("present_k")], perm=[0, 1, 3, 2])])
+    pr = g.op("Softmax", [g.op("Add", [g.op("Mul", [sc, "scale"]), "mask"])], axis=-1)
+    g.op("MatMul", [pr, heads("present_v")], "ctx")
+    for o in ("ctx", "present_k", "present_v"):
+        g.output(o)
+    return g
+
+
+@pytest.mark.parametrize("KV,G,D", [(2, 4, 64), (3, 2, 16), (2, 1, 128), (2, 8, 32), (1, 4, 20)])
+def test_runtime_runs_decode_attention_as_one_launch(cuda, KV, G, D):
+    """With RMLK_B200_ATTENTION=1 the five attention nodes of a decode step run as one kernel over the carried caches; a
+    multi-token step, more than four query heads per KV head or an unsupported head size run the single kernels.  Same
+    numbers either way.  (Off by default: the three kernels are faster on the benchmark's shape.)"""
+    from rmlk_b200.runtime import ModelInstance
+    spec = attention_graph(KV, G, D)
+    B = 3
+
+    def drive(env):
+        os.environ.update(env)
+        try:
+            inst = ModelInstance(spec.to_runtime())
+            inst.bind("present_k", "past_k")
+            inst.bind("present_v", "past_v")
+        finally:
+            for k in env:
+                os.environ.pop(k, None)
+        return inst
+
+    one, apart = drive({"RMLK_B200_ATTENTION": "1"}), drive({})
+    r = np.random.default_rng(43)
+    T = 0
+    cache_k = np.zeros((B, KV, 0, D), np.float32)
+    cache_v = np.zeros((B, KV, 0, D), np.float32)
+    for step in range(70):
+        S = 6 if step == 0 else 1
+        T += S
+        feeds = {"q": r.standard_normal((B, KV * G, S, D), dtype=np.float32), "new_k": r.standard_normal((B, KV, S, D), dtype=np.float32),
+                 "new_v": r.standard_normal((B, KV, S, D), dtype=np.float32),
+                 "mask": np.where(r.random((B, 1, S, T)) > 0.8, np.finfo(np.float32).min, 0.0).astype(np.float32)}
+        feeds["mask"][..., 0] = 0.0
+        for m in (one, apart):
+            for k, v in feeds.items():
+                m.set_input(k, v)
+            if step == 0:
+                m.set_input("past_k", cache_k)
+                m.set_input("past_v", cache_v)
+            m.launch()
+        cache_k = np.concatenate([cache_k, feeds["new_k"]], axis=2)
+        cache_v = np.concatenate([cache_v, feeds["new_v"]], axis=2)
+        a, b = one.read("ctx"), apart.read("ctx")
+        assert np.max(np.abs(a - b)) <= 1e-5 * max(1.0, np.max(np.abs(b))), step
+        if step in (0, 1, 33, 69):
+            s64 = np.einsum("bhsd,bhtd->bhst", feeds["q"].astype(np.float64), np.repeat(cache_k, G, axis=1).astype(np.float64)) / np.sqrt(D) + feeds["mask"]
+            e = np.exp(s64 - s64.max(-1, keepdims=True))
+            want = np.einsum("bhst,bhtd->bhsd", e / e.sum(-1, keepdims=True), np.repeat(cache_v, G, axis=1).astype(np.float64))
+            assert np.max(np.abs(a - want)) <= 1e-4 * max(1.0, np.max(np.abs(want))), step
+            assert np.array_equal(one.read("present_k"), cache_k)
+    fits = G <= 4 and D in (16, 32, 64, 128)
+    # decode steps: 2 appends + (1 | 3) attention launches
+    assert apart.last_launches - one.last_launches == (2 if fits else 0), (one.last_launches, apart.last_launches)
