@@ -250,7 +250,7 @@ def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):
     # decode context: B*8 problems [4 q-heads, T] x [T, 64]
     p = torch.randn(B * 8, 4, T, device=dev)
     cx = torch.empty(B * 8, 4, 64, device=dev)
-    add("context", "skinny_kernel<4>", lambda i: K.matmul(p, kc[i % len(kc)], out=cx), 4 * B * 8 * (4 * T + 64 * T + 4 * 64),
+    add("context", "nn_narrow_kernel<4,16>", lambda i: K.matmul(p, kc[i % len(kc)], out=cx), 4 * B * 8 * (4 * T + 64 * T + 4 * 64),
         [B * 8, 4, T, 64], flops=2 * B * 32 * 64 * T)
     del kc, q, sc, p, cx
     # KV append Concat: [B, 8, T-1, 64] + [B, 8, 1, 64] along axis 2

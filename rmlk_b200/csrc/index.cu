@@ -340,8 +340,8 @@ template <> struct RangeOp<__half> {
 template <typename T>
 __global__ void __launch_bounds__(256) range_kernel(uint64_t n, T start, T delta, T* __restrict__ out) {
     dep_sync();
-    const uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
-    if (i < n) out[i] = RangeOp<T>::at(start, delta, i);
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < n; i += static_cast<uint64_t>(gridDim.x) * 256)
+        out[i] = RangeOp<T>::at(start, delta, i);
 }
 
 template <typename U>
@@ -829,7 +829,7 @@ extern "C" int rmlk_b200_range(rmlk_stream_t stream, int dtype, int64_t n, const
     if (n == 0) return RMLK_OK;
     if (!start || !delta || !out) return fail(RMLK_ERR_INVALID_ARG, "range: NULL pointer");
     cudaStream_t st = as_stream(stream);
-    const unsigned grid = static_cast<unsigned>((static_cast<uint64_t>(n) + 255) / 256);
+    const unsigned grid = flat_grid(n, 256, 32);  // grid-stride: a few thousand CTAs whatever n
 #define RMLK_CASE(DT, T)                                                                                                   \
     case DT:                                                                                                               \
         launch_dep(range_kernel<T>, dim3(grid), dim3(256), 0, st, static_cast<uint64_t>(n), *static_cast<const T*>(start), *static_cast<const T*>(delta), static_cast<T*>(out)); \
