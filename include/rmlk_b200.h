@@ -241,7 +241,8 @@ RMLK_API int rmlk_b200_store_small(rmlk_stream_t stream, int n_words, const uint
  * replaces rmlk_cuda::kernels::gemm::compute (cuda/src/kernels/gemm.rs:112-232,
  * cublasGemmStridedBatchedEx).  A is [m,k], B is [k,n], C is [m,n], each dense; batch strides are in
  * elements and may be 0 to broadcast an operand over the batch (the reference materialises copies,
- * backend/matmul.rs:48-86).  dtype f32.  `workspace` is optional caller-owned device scratch of
+ * backend/matmul.rs:48-86).  dtype f32, or f16 (half in and out, fp32 accumulation - the reference asks cuBLAS
+ * for CUBLAS_COMPUTE_16F there, cuda/src/params.rs:24-31; SIMT kernel, no workspace).  `workspace` is optional caller-owned device scratch of
  * `workspace_bytes` (see rmlk_b200_matmul_workspace_bytes); NULL selects kernels that need none. */
 RMLK_API int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                      const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,

@@ -614,6 +614,9 @@ size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, const float* w, float* c, void* workspace,
               size_t workspace_bytes, int* status, int* ksplit_out, int flags);
 bool tc_enabled();
+// matmul_f16.cu
+int matmul_f16(cudaStream_t st, int64_t batch, int64_t m, int64_t n, int64_t k, const void* a, int64_t sa, const void* b, int64_t sb, void* c,
+               int64_t sc);
 }  // namespace rmlk
 
 extern "C" size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k) {
@@ -672,7 +675,13 @@ extern "C" int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batc
 extern "C" int rmlk_b200_matmul_flags(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                                       const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
                                       int64_t c_batch_stride, void* workspace, size_t workspace_bytes, int* status, int flags) {
-    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for matmul (f32 only)");
+    if (dtype == RMLK_F16) {
+        if (batch < 0 || m < 0 || n < 0 || k < 0) return fail(RMLK_ERR_INVALID_ARG, "matmul: negative extent");
+        if (batch == 0 || m == 0 || n == 0) return RMLK_OK;
+        if (!c || (k > 0 && (!a || !b))) return fail(RMLK_ERR_INVALID_ARG, "matmul: NULL operand");
+        return matmul_f16(as_stream(stream), batch, m, n, k, a, a_batch_stride, b, b_batch_stride, c, c_batch_stride);
+    }
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for matmul (f32 and f16)");
     if (batch < 0 || m < 0 || n < 0 || k < 0) return fail(RMLK_ERR_INVALID_ARG, "matmul: negative extent");
     if (batch == 0 || m == 0 || n == 0) return RMLK_OK;
     if (!c) return fail(RMLK_ERR_INVALID_ARG, "matmul: NULL output");

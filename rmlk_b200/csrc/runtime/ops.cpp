@@ -631,7 +631,7 @@ void op_matmul(const Ctx& c) {
     Tensor* braw = c.raw(1);
     if (!braw) raise(RMLK_ERR_INVALID_ARG, "missing input 1");
     Tensor& b = *braw;  // may be a deferred view; made dense below unless the kernels can read it as it is
-    if (!in_set(a.dtype, {RMLK_F32})) unsupported_dtype(a.dtype, "matmul");
+    if (!in_set(a.dtype, {RMLK_F32, RMLK_F16})) unsupported_dtype(a.dtype, "matmul");
     if (b.dtype != a.dtype) raise(RMLK_ERR_INVALID_ARG, "matmul: operand data types differ");
     const size_t ar = a.shape.size(), br = b.shape.size();
     if (ar == 0 || br == 0) raise(RMLK_ERR_INVALID_ARG, "ZeroRank");
@@ -657,7 +657,7 @@ void op_matmul(const Ctx& c) {
         // base buffer directly: the repeats become extra rows of A (they share one B), the transposition
         // selects the A x B^T kernel.  Otherwise it is copied out once and the dense path below runs.
         LazyB lb;
-        bool usable = ar >= 2 && br >= 2 && (ba == bb || bb == 1) && ka > 0 && analyze_lazy_b(b, kb, n, lb) && lb.outer * lb.fold == bb;
+        bool usable = a.dtype == RMLK_F32 && ar >= 2 && br >= 2 && (ba == bb || bb == 1) && ka > 0 && analyze_lazy_b(b, kb, n, lb) && lb.outer * lb.fold == bb;
         const int64_t em = usable ? (bb == 1 ? ba : lb.fold) * m : 0;  // one shared B: every batch entry of A is extra rows
         usable = usable && (!lb.transposed || (em <= 8 && ka <= 128 && ka % 4 == 0));
         if (usable) {
@@ -689,7 +689,7 @@ void op_matmul(const Ctx& c) {
     const int ovid = c.n.outputs[0];
     // initializers were uploaded before the first run: nothing in flight writes them
     const int flags = c.I.g.values[c.n.inputs[1]].is_const ? RMLK_MATMUL_B_STATIC : 0;
-    if (need && eb == 1 && c.I.parts_owner < 0 && ovid < static_cast<int>(c.I.parts_ok_value.size()) && c.I.parts_ok_value[ovid]) {
+    if (need && a.dtype == RMLK_F32 && eb == 1 && c.I.parts_owner < 0 && ovid < static_cast<int>(c.I.parts_ok_value.size()) && c.I.parts_ok_value[ovid]) {
         // The only reader is a residual Add + RMSNorm chain whose kernel adds split-K slabs itself: leave them unreduced.
         void* slabs = c.I.parts_ws.ensure(need);
         int parts = 1;

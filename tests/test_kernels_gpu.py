@@ -346,6 +346,28 @@ def test_matmul_small_integers_exact():
     assert np.all(to_np(K.matmul(dev(a4), dev(b4))) == 78.0)
 
 
+@pytest.mark.parametrize("case", [(1, 64, 2048, 512), (1, 3, 5, 7), (1, 70, 130, 50), (3, 17, 33, 65), (8, 128, 64, 128), (2, 1, 100, 1), (1, 5, 9, 0)])
+def test_matmul_f16(case):
+    """f16 MatMul (cuBLAS with CUBLAS_COMPUTE_16F in the reference, cuda/src/params.rs:24-31): fp32 accumulation and one
+    rounding to f16 here, so the result is the correctly rounded f16 of the exact product up to one f16 ulp."""
+    batch, m, n, k = case
+    a = rng(5).normal(0, 1.0, size=(batch, m, k)).astype(np.float16)
+    b = rng(6).normal(0, 1.0, size=(batch, k, n)).astype(np.float16)
+    want = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    got = to_np(K.matmul(dev(a), dev(b)))
+    assert got.dtype == np.float16 and got.shape == want.shape
+    err = np.abs(got.astype(np.float64) - want)
+    assert np.all(err <= np.maximum(np.abs(want), 2.0 ** -14) * 2.0 ** -10 + 1e-6 * np.sqrt(max(k, 1))), case
+    if batch > 1:   # right operand shared by the batch
+        got_b = to_np(K.matmul(dev(a), dev(b[0])))
+        want_b = np.matmul(a.astype(np.float64), b[0].astype(np.float64))
+        assert np.all(np.abs(got_b.astype(np.float64) - want_b) <= np.maximum(np.abs(want_b), 2.0 ** -14) * 2.0 ** -10 + 1e-6 * np.sqrt(k))
+    # integer-valued operands: exact
+    ai = rng(7).integers(-4, 5, size=(batch, m, max(k, 1))).astype(np.float16)
+    bi = rng(8).integers(-4, 5, size=(batch, max(k, 1), n)).astype(np.float16)
+    assert np.array_equal(to_np(K.matmul(dev(ai), dev(bi))).astype(np.float64), np.matmul(ai.astype(np.float64), bi.astype(np.float64)))
+
+
 @pytest.mark.parametrize("dtype", [np.float32, np.int64, np.float16, np.uint8])
 def test_gather(dtype):
     cases = [((3, 4), [0, 2], 0), ((3, 4), [-3, -1], 0), ((3, 4), [1, 3], 1), ((2, 3, 4), [[1, 2], [0, -1]], 1),

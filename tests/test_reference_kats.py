@@ -117,6 +117,11 @@ def test_matmul_vs_host_triple_loop(rt):
         .output([1, 24, 6, 128])
     r4 = o4.run(np.float32)
     assert o4.result_shape == [1, 24, 6, 128] and np.all(r4 == 78.0)
+    # f16 (backend/matmul.rs:227 dispatches Float16 to the same cuBLAS call): these values are exact in half precision
+    ah, bh = a.astype(np.float16), b.astype(np.float16)
+    wh = (ah.reshape(n_mid, k).astype(np.float64) @ bh.reshape(k, n).astype(np.float64)).astype(np.float16)
+    outh = rt.OpTest(rt.Op.MatMul).input([1, n_mid, k], ah).input([k, n], bh).output([1, n_mid, n]).run(np.float16)
+    assert outh.dtype == np.float16 and np.array_equal(outh, wh.reshape(-1))
 
 
 def test_unary_basic(rt):
