@@ -347,7 +347,7 @@ def run_ours(args):
         inst.set_input_ptr("attention_mask", dt.I64, [B, t], mask_view.data_ptr(), False)
         inst.set_input_ptr("position_ids", dt.I64, [B, 1], pos_host.data_ptr(), False)
         inst.launch()
-        inst.read_into("logits", logits_host.data_ptr(), logits_host.numel() * 4)   # D2H + wait, like get_outputs
+        inst.wait_outputs()   # the logits were registered with stream_output: they arrive block by block behind the lm_head MatMul
         dec.context = t
         step_no["n"] += 1
         return B * 8 + B * t * 8 + B * 8
@@ -394,6 +394,7 @@ def run_ours(args):
         keep.clear()
 
         # ---- end to end: host buffers in, logits out, every step --------------------------------
+        inst.stream_output("logits", logits_host.data_ptr(), logits_host.numel() * 4)
         for _ in range(W):
             host_step()
         barrier()

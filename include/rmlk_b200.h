@@ -260,6 +260,13 @@ RMLK_API int rmlk_b200_matmul_ex(rmlk_stream_t stream, int dtype, int64_t batch,
 RMLK_API int rmlk_b200_matmul_flags(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                            const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
                            int64_t c_batch_stride, void* workspace, size_t workspace_bytes, int* status, int flags);
+/* C[:, 0:n] = A x B[:, 0:n] on a block of n columns: b and c point at the block's first column inside matrices whose rows
+ * are ld elements apart.  A wide product (the logits of a language model, [64, 2048] x [2048, 128256]) can so be issued
+ * block by block and each block copied to the host while the next is computed.  Only for shapes the tensor-core kernel
+ * runs without a K split (rmlk_b200_matmul_window_supported); same kernel, same values as rmlk_b200_matmul_ex. */
+RMLK_API int rmlk_b200_matmul_window(rmlk_stream_t stream, int dtype, int64_t m, int64_t n, int64_t k, const void* a, const void* b,
+                            void* c, int64_t ld, int* status, int flags);
+RMLK_API int rmlk_b200_matmul_window_supported(int64_t m, int64_t n, int64_t k, int64_t ld);
 /* Unbatched MatMul for a caller that adds split-K partial sums in its own next kernel (rmlk_b200_add_rmsnorm does).
  * When the kernel plan for the shape splits K through the workspace, the [*parts][m*n] slabs are left in `workspace`
  * (to be added in slab order starting from 0.f - the order rmlk_b200_matmul uses) and c is NOT written; otherwise c

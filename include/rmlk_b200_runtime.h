@@ -98,6 +98,13 @@ RMLK_API int rmlk_instance_synchronize(rmlk_instance* inst);
  * the whole cache per run, as the reference's Concat does, backend/concat.rs:28-76). */
 RMLK_API int rmlk_instance_value_info(rmlk_instance* inst, const char* name, int* dtype, int* rank, int64_t* dims,
                                       void** device_ptr);
+/* Registers host memory (pinned, for the copies to be asynchronous) that every following run delivers graph output
+ * `name` to, without a read call: the copy is enqueued as soon as the value exists, and for a wide MatMul - the logits
+ * of a language model - block of columns by block of columns on a second stream, while the rest of the product is
+ * still being computed.  rmlk_instance_wait_outputs returns when the data of the last run has arrived.  host_dst =
+ * NULL unregisters.  (The reference copies every output after the run, get_outputs, runtime/src/core/instance.rs:58-82.) */
+RMLK_API int rmlk_instance_stream_output(rmlk_instance* inst, const char* name, void* host_dst, size_t nbytes);
+RMLK_API int rmlk_instance_wait_outputs(rmlk_instance* inst);
 /* Copies a value to host memory and waits for it (get_outputs, runtime/src/core/instance.rs:58-82). */
 RMLK_API int rmlk_instance_read(rmlk_instance* inst, const char* name, void* dst, size_t nbytes);
 /* Number of kernels / async copies enqueued by the last run, and number of times it had to wait for

@@ -612,7 +612,8 @@ namespace rmlk {
 bool tc_matmul_eligible(int64_t m, int64_t n, int64_t k, const void* a, const void* w, const void* c);
 size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, const float* w, float* c, void* workspace,
-              size_t workspace_bytes, int* status, int* ksplit_out, int flags);
+              size_t workspace_bytes, int* status, int* ksplit_out, int flags, int64_t ld);
+int tc_matmul_plan(int64_t m, int64_t n, int64_t k);
 bool tc_enabled();
 // matmul_f16.cu
 int matmul_f16(cudaStream_t st, int64_t batch, int64_t m, int64_t n, int64_t k, const void* a, int64_t sa, const void* b, int64_t sb, void* c,
@@ -647,6 +648,24 @@ extern "C" int rmlk_b200_sum_parts(rmlk_stream_t stream, int dtype, int parts, i
     return RMLK_OK;
 }
 
+// C[:, 0:n] = A x B[:, 0:n] where b and c point at the first column of a block of n columns inside matrices whose rows are
+// ld elements apart: lets a wide product (the logits of a language model) be issued block by block, so that what
+// follows a block - a copy to the host - overlaps the next.  Only shapes the tensor-core kernel runs without a K split.
+extern "C" int rmlk_b200_matmul_window_supported(int64_t m, int64_t n, int64_t k, int64_t ld) {
+    return tc_enabled() && m > 16 && n > 0 && n % 128 == 0 && k >= 32 && k % 32 == 0 && ld >= n && ld % 4 == 0 && tc_matmul_plan(m, n, k) == 1;
+}
+
+extern "C" int rmlk_b200_matmul_window(rmlk_stream_t stream, int dtype, int64_t m, int64_t n, int64_t k, const void* a, const void* b, void* c,
+                                       int64_t ld, int* status, int flags) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for matmul_window (f32 only)");
+    if (!a || !b || !c) return fail(RMLK_ERR_INVALID_ARG, "matmul_window: NULL operand");
+    if (!rmlk_b200_matmul_window_supported(m, n, k, ld) || !tc_matmul_eligible(m, n, k, a, b, c))
+        return fail(RMLK_ERR_INVALID_ARG, "matmul_window: needs M > 16, N % 128 == 0, K % 32 == 0, 16-byte aligned operands and a shape without a K split");
+    int ksplit = 1;
+    return tc_matmul(as_stream(stream), m, n, k, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c), nullptr, 0,
+                     status, &ksplit, flags, ld);
+}
+
 // C[m,n] = A x B for a caller that adds the split-K partial sums itself (in its next kernel): when the plan for this
 // shape splits K through the workspace, the slabs are left there ([*parts][m*n] floats, to be added in slab order
 // starting from 0.f) and C is not written; otherwise C is complete and *parts = 1.
@@ -657,7 +676,7 @@ extern "C" int rmlk_b200_matmul_parts(rmlk_stream_t stream, int dtype, int64_t m
     if (dtype == RMLK_F32 && m > 0 && n > 0 && k > 0 && a && b && c && tc_matmul_eligible(m, n, k, a, b, c)) {
         int ksplit = 1;
         if (int rc = tc_matmul(as_stream(stream), m, n, k, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c),
-                               workspace, workspace_bytes, status, &ksplit, flags))
+                               workspace, workspace_bytes, status, &ksplit, flags, 0))
             return rc;
         *parts = ksplit;
         return RMLK_OK;
@@ -697,7 +716,7 @@ extern "C" int rmlk_b200_matmul_flags(rmlk_stream_t stream, int dtype, int64_t b
     if (batch == 1 && tc_matmul_eligible(m, n, k, a, b, c)) {
         int ksplit = 1;
         if (int rc = tc_matmul(st, m, n, k, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c), workspace,
-                               workspace_bytes, status, &ksplit, flags))
+                               workspace_bytes, status, &ksplit, flags, 0))
             return rc;
         if (ksplit > 1) {
             const int64_t total = m * n;

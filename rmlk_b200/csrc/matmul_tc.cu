@@ -61,11 +61,11 @@ static EncodeTiledFn encode_fn() {
 }
 
 static bool make_map_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t outer, uint32_t box_inner, uint32_t box_outer,
-                        CUtensorMapSwizzle swizzle) {
+                        CUtensorMapSwizzle swizzle, uint64_t row_pitch = 0) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return false;
     const cuuint64_t dims[2] = {inner, outer};
-    const cuuint64_t strides[1] = {inner * 4};
+    const cuuint64_t strides[1] = {(row_pitch ? row_pitch : inner) * 4};
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -167,7 +167,7 @@ size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k) {
 // Launches the tensor-core GEMM.  `ksplit_out` tells the caller how many partial slabs were written to
 // `workspace` (1 = the result is already in c).
 int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, const float* w, float* c, void* workspace,
-              size_t workspace_bytes, int* status, int* ksplit_out, int flags) {
+              size_t workspace_bytes, int* status, int* ksplit_out, int flags, int64_t ld) {
     const int mt = m <= 64 ? 64 : 128;
     int ksplit = tc_matmul_plan(m, n, k);
     if (ksplit > TC_CLUSTER_MAX && (!workspace || workspace_bytes < static_cast<size_t>(ksplit) * m * n * sizeof(float)))
@@ -177,13 +177,17 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
     ksplit = static_cast<int>(ceil_div64(k_iters, per));  // every split gets at least one k-block
     const bool cluster = ksplit > 1 && ksplit <= TC_CLUSTER_MAX;
     CUtensorMap tmW, tmA;
-    if (!tc::make_map_2d(&tmW, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), tc::BN, tc::BK, CU_TENSOR_MAP_SWIZZLE_NONE) ||
+    // ld > 0: w and c are blocks of n columns of matrices whose rows are ld elements apart (no K split in that form)
+    if (ld > 0 && ksplit > 1) return fail(RMLK_ERR_INVALID_ARG, "matmul: a column window needs a shape that runs without a K split");
+    if (!tc::make_map_2d(&tmW, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), tc::BN, tc::BK, CU_TENSOR_MAP_SWIZZLE_NONE,
+                         ld > 0 ? static_cast<uint64_t>(ld) : 0) ||
         !tc::make_map_2d(&tmA, a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), 32, static_cast<uint32_t>(mt), CU_TENSOR_MAP_SWIZZLE_128B))
         return fail(RMLK_ERR_INTERNAL, "matmul: cuTensorMapEncodeTiled failed");
     tc::TcParams p;
     p.cluster_reduce = cluster ? 1 : 0;
     p.out = (ksplit > 1 && !cluster) ? static_cast<float*>(workspace) : c;
     p.M = m; p.N = n; p.K = k;
+    p.ldc = ld > 0 ? ld : n;
     p.k_iters_per_split = per;
     p.k_iters_total = k_iters;
     p.ksplit = ksplit;

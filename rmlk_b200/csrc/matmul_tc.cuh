@@ -135,6 +135,7 @@ struct TcParams {
     int cluster_reduce;     // ksplit CTAs form a cluster along grid y and add their partial sums on chip
     float* out;             // C, or the split-K scratch [ksplit][M][N]
     int64_t M, N, K;
+    int64_t ldc;            // elements between rows of `out` (N, unless C is a block of columns of a wider matrix)
     int k_iters_per_split;  // k-blocks per split
     int k_iters_total;
     int ksplit;

@@ -193,7 +193,7 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     const int64_t m = m0 + c0 + j;
-                    if (m < p.M) out[m * p.N + n] = __uint_as_float(r[j]) + __uint_as_float(q[j]);
+                    if (m < p.M) out[m * p.ldc + n] = __uint_as_float(r[j]) + __uint_as_float(q[j]);
                 }
             }
         }
@@ -236,7 +236,7 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
                 if (row < static_cast<uint32_t>(MT) && m < p.M) {
                     float s = buf[ml * BN + n];
                     for (uint32_t r2 = 1; r2 < ks; r2++) s += buf[(r2 * rows_per + ml) * BN + n];
-                    p.out[m * p.N + n0 + n] = s;
+                    p.out[m * p.ldc + n0 + n] = s;
                 }
             }
         }

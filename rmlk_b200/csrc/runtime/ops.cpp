@@ -705,6 +705,48 @@ void op_matmul(const Ctx& c) {
         }
         return;
     }
+    const int hout = c.I.host_output_of(ovid);
+    if (hout >= 0 && !need && a.dtype == RMLK_F32 && eb == 1 && n % 128 == 0 && c.I.host_outputs[hout].nbytes == o.nbytes()) {
+        // An output the host is waiting for (logits): the product is issued in blocks of columns - one wave of tiles,
+        // then two waves each - and every block goes to the host on the copy stream while the next is computed.
+        int sm_attr = 148;
+        cudaDeviceGetAttribute(&sm_attr, cudaDevAttrMultiProcessorCount, c.I.device);
+        const int64_t sms = sm_attr > 0 ? sm_attr : 148, tiles = n / 128;
+        std::vector<int64_t> blocks;
+        for (int64_t left = tiles, first = 1; left > 0; first = 0) {
+            int64_t take = std::min<int64_t>(left, first ? sms : 2 * sms);
+            if (left - take < sms) take = left;  // a short tail joins the last block
+            blocks.push_back(take);
+            left -= take;
+        }
+        bool ok = blocks.size() > 1;
+        for (int64_t bt : blocks) ok = ok && rmlk_b200_matmul_window_supported(em, bt * 128, ka, n);
+        if (ok) {
+            HostOutput& h = c.I.host_outputs[hout];
+            while (c.I.copy_events.size() < blocks.size()) {
+                cudaEvent_t e = nullptr;
+                check_cuda(cudaEventCreateWithFlags(&e, cudaEventDisableTiming), "cudaEventCreate");
+                c.I.copy_events.push_back(e);
+            }
+            int64_t n0 = 0;
+            for (size_t i = 0; i < blocks.size(); i++) {
+                const int64_t nc = blocks[i] * 128;
+                check_rc(rmlk_b200_matmul_window(c.stream(), a.dtype, em, nc, ka, a.data, static_cast<const float*>(b.data) + n0,
+                                                 static_cast<float*>(o.data) + n0, n, static_cast<int*>(c.I.status_word.ptr), flags));
+                check_cuda(cudaEventRecord(c.I.copy_events[i], c.I.stream), "cudaEventRecord");
+                check_cuda(cudaStreamWaitEvent(c.I.copy_stream, c.I.copy_events[i], 0), "cudaStreamWaitEvent");
+                check_cuda(cudaMemcpy2DAsync(static_cast<char*>(h.dst) + n0 * 4, static_cast<size_t>(n) * 4, static_cast<const float*>(o.data) + n0,
+                                             static_cast<size_t>(n) * 4, static_cast<size_t>(nc) * 4, static_cast<size_t>(em), cudaMemcpyDeviceToHost,
+                                             c.I.copy_stream), "host output D2H");
+                n0 += nc;
+            }
+            h.delivered_run = c.I.run_counter;
+            c.I.copies_pending = true;
+            c.I.status_dirty = true;
+            c.launched(static_cast<int>(blocks.size()));
+            return;
+        }
+    }
     void* ws = need ? c.I.matmul_ws.ensure(need) : nullptr;
     check_rc(rmlk_b200_matmul_flags(c.stream(), a.dtype, eb, em, n, ka, a.data, sa, b.data, sb, o.data, sc, ws, need,
                                     static_cast<int*>(c.I.status_word.ptr), flags));

@@ -249,7 +249,14 @@ Instance::~Instance() {
     weights.release();
     status_word.release();
     matmul_ws.release();
+    parts_ws.release();
     read_staging.release();
+    if (copy_stream) {
+        cudaStreamSynchronize(copy_stream);
+        cudaStreamDestroy(copy_stream);
+    }
+    for (cudaEvent_t e : copy_events) cudaEventDestroy(e);
+    if (copies_done) cudaEventDestroy(copies_done);
     for (DeviceBuffer& b : input_bufs) b.release();
     for (MergedMatMul& m : merged) m.w.release();
     for (Binding& b : bindings) {
@@ -312,6 +319,26 @@ void Instance::settle_parts(int value_id) {
     if (parts_owner == value_id) parts_owner = -1;
 }
 
+void Instance::deliver_host_outputs() {
+    for (HostOutput& h : host_outputs) {
+        if (h.delivered_run == run_counter) continue;
+        Tensor& t = values[h.value_id];
+        if (!t.present) continue;
+        if (t.nbytes() != h.nbytes) raise(RMLK_ERR_INVALID_ARG, "host output `" + g.values[h.value_id].name + "`: size mismatch");
+        if (t.parts > 1) settle_parts(h.value_id);
+        if (t.lazy) materialize(t);
+        if (h.nbytes) check_cuda(cudaMemcpyAsync(h.dst, t.data, h.nbytes, cudaMemcpyDeviceToHost, stream), "host output D2H");
+        h.delivered_run = run_counter;
+    }
+    if (copies_pending) check_cuda(cudaEventRecord(copies_done, copy_stream), "cudaEventRecord");
+}
+
+void Instance::wait_host_outputs() {
+    check_cuda(cudaStreamSynchronize(stream), "cudaStreamSynchronize");
+    if (copy_stream) check_cuda(cudaStreamSynchronize(copy_stream), "cudaStreamSynchronize");
+    check_status();
+}
+
 void Instance::check_status() {
     if (!status_dirty) return;
     int code = 0;
@@ -340,6 +367,11 @@ void Instance::run() {
         values[i].parts = 0;
     }
     parts_owner = -1;
+    if (copies_pending) {
+        // last run's block-wise copies read buffers that this run is about to hand out again
+        check_cuda(cudaStreamWaitEvent(stream, copies_done, 0), "cudaStreamWaitEvent");
+        copies_pending = false;
+    }
     arena->reset();
     for (Binding& b : bindings) {
         if (b.have && !input_fed[b.in_id]) {
@@ -404,6 +436,7 @@ void Instance::run() {
         for (int v : n.outputs)
             if (v >= 0 && last_use[v] < 0 && !g.values[v].is_output) release_value(v);
     }
+    deliver_host_outputs();
     for (Binding& b : bindings) {
         b.carried = values[b.out_id];
         b.carried.storage = nullptr;
@@ -800,6 +833,42 @@ extern "C" int rmlk_instance_read(rmlk_instance* inst, const char* name, void* d
     if (nbytes) check_cuda(cudaMemcpyAsync(dst, src, nbytes, cudaMemcpyDeviceToHost, I.stream), "output D2H");
     check_cuda(cudaStreamSynchronize(I.stream), "cudaStreamSynchronize");
     I.check_status();
+    return RMLK_OK;
+    RT_CATCH
+}
+
+extern "C" int rmlk_instance_stream_output(rmlk_instance* inst, const char* name, void* host_dst, size_t nbytes) {
+    RT_TRY
+    if (!inst || !name) raise(RMLK_ERR_INVALID_ARG, "NULL argument");
+    Instance& I = inst->I;
+    const int id = I.g.find(name);
+    if (id < 0 || !I.g.values[id].is_output) raise(RMLK_ERR_INVALID_ARG, std::string("`") + name + "` is not a graph output");
+    check_cuda(cudaSetDevice(I.device), "cudaSetDevice");
+    I.wait_host_outputs();
+    const int at = I.host_output_of(id);
+    if (!host_dst) {
+        if (at >= 0) I.host_outputs.erase(I.host_outputs.begin() + at);
+        return RMLK_OK;
+    }
+    HostOutput h;
+    h.value_id = id;
+    h.dst = host_dst;
+    h.nbytes = nbytes;
+    if (at >= 0) I.host_outputs[at] = h;
+    else I.host_outputs.push_back(h);
+    if (!I.copy_stream) {
+        check_cuda(cudaStreamCreateWithFlags(&I.copy_stream, cudaStreamNonBlocking), "cudaStreamCreate");
+        check_cuda(cudaEventCreateWithFlags(&I.copies_done, cudaEventDisableTiming), "cudaEventCreate");
+    }
+    return RMLK_OK;
+    RT_CATCH
+}
+
+extern "C" int rmlk_instance_wait_outputs(rmlk_instance* inst) {
+    RT_TRY
+    if (!inst) raise(RMLK_ERR_INVALID_ARG, "NULL argument");
+    check_cuda(cudaSetDevice(inst->I.device), "cudaSetDevice");
+    inst->I.wait_host_outputs();
     return RMLK_OK;
     RT_CATCH
 }

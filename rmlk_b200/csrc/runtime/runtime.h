@@ -184,8 +184,31 @@ struct MergedMatMul {
     int64_t done_in_run = -1;   // run counter of the run in which the first member produced every output
 };
 
+// A graph output that every run delivers to (pinned) host memory without being asked: the copy is enqueued as soon
+// as the value exists - for a wide MatMul (the logits) block of columns by block of columns on a second stream, so
+// that most of the transfer overlaps the rest of the product.  The reference copies outputs after the run
+// (get_outputs, runtime/src/core/instance.rs:58-82).
+struct HostOutput {
+    int value_id = -1;
+    void* dst = nullptr;
+    size_t nbytes = 0;
+    int64_t delivered_run = -1;  // run whose value is (being) copied
+};
+
 struct Instance {
     Graph g;
+    std::vector<HostOutput> host_outputs;
+    cudaStream_t copy_stream = nullptr;
+    std::vector<cudaEvent_t> copy_events;   // chunk i of a run: recorded on `stream`, awaited by `copy_stream`
+    cudaEvent_t copies_done = nullptr;      // recorded on `copy_stream` behind the last copy of a run
+    bool copies_pending = false;
+    int host_output_of(int value_id) const {
+        for (size_t i = 0; i < host_outputs.size(); i++)
+            if (host_outputs[i].value_id == value_id) return static_cast<int>(i);
+        return -1;
+    }
+    void deliver_host_outputs();  // end of run: whatever was not streamed out while it was produced
+    void wait_host_outputs();
     std::vector<MergedMatMul> merged;
     std::vector<int> merged_of_node;  // per node: index into `merged`, or -1
     int64_t run_counter = 0;

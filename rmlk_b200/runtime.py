@@ -290,6 +290,14 @@ class ModelInstance:
         _check(_rt().rmlk_instance_read(self._h, name.encode(), out.ctypes.data, out.nbytes))
         return out
 
+    def stream_output(self, name: str, ptr: int, nbytes: int):
+        """Every following run delivers graph output `name` to the (pinned) host memory at `ptr`; see wait_outputs."""
+        _check(_rt().rmlk_instance_stream_output(self._h, name.encode(), ctypes.c_void_p(ptr), ctypes.c_size_t(nbytes)))
+
+    def wait_outputs(self):
+        """Returns when the outputs registered with stream_output hold the values of the last run."""
+        _check(_rt().rmlk_instance_wait_outputs(self._h))
+
     def read_into(self, name: str, ptr: int, nbytes: int):
         _check(_rt().rmlk_instance_read(self._h, name.encode(), ctypes.c_void_p(ptr), nbytes))
 

@@ -284,3 +284,46 @@ def test_new_rows_go_straight_into_the_cache(cuda):
         saved.append(staged.last_launches - direct.last_launches)
     # per decode step: the keys' append copy is gone, and the values' dense copy + append copy became one launch
     assert saved[10] == 2, saved[:12]
+
+
+def test_outputs_streamed_to_host_memory(cuda):
+    """Outputs registered with stream_output arrive in pinned host memory without a read call; a wide MatMul result is
+    sent block of columns by block of columns while the rest is computed.  Same bytes as reading the output."""
+    import torch
+    from rmlk_b200.runtime import ModelInstance
+    hidden, vocab = 256, 128 * 700
+    g = GraphSpec()
+    g.input("x", np.float32, [0, 1, hidden])
+    rng = np.random.default_rng(51)
+    g.const("w", (rng.standard_normal((hidden, vocab)) * 0.05).astype(np.float32))
+    g.const("two", np.array(2.0, np.float32))
+    g.op("MatMul", ["x", "w"], "logits")
+    g.op("Mul", ["x", "two"], "twice")
+    g.output("logits")
+    g.output("twice")
+    inst = ModelInstance(g.to_runtime())
+    B = 64
+    logits_host = torch.empty(B, 1, vocab, dtype=torch.float32).pin_memory()
+    twice_host = torch.empty(B, 1, hidden, dtype=torch.float32).pin_memory()
+    inst.stream_output("logits", logits_host.data_ptr(), logits_host.numel() * 4)
+    inst.stream_output("twice", twice_host.data_ptr(), twice_host.numel() * 4)
+    plain = ModelInstance(g.to_runtime())
+    for step in range(4):
+        x = rng.standard_normal((B, 1, hidden), dtype=np.float32)
+        logits_host.fill_(-1.0)
+        inst.set_input("x", x)
+        inst.launch()
+        inst.wait_outputs()
+        plain.set_input("x", x)
+        plain.launch()
+        want = plain.read("logits")
+        assert np.array_equal(logits_host.numpy(), want), step
+        assert np.array_equal(inst.read("logits"), want)
+        assert np.array_equal(twice_host.numpy(), x * 2)
+        ref = x.reshape(B, hidden).astype(np.float64) @ g.constants["w"].astype(np.float64)
+        assert np.max(np.abs(want.reshape(B, vocab) - ref)) <= 1e-4 * np.max(np.abs(ref))
+    assert inst.last_launches > plain.last_launches      # the product went out in several blocks
+    # a differently sized batch no longer matches the registered buffer
+    inst.set_input("x", rng.standard_normal((3, 1, hidden), dtype=np.float32))
+    with pytest.raises(Exception):
+        inst.launch()
