@@ -352,6 +352,16 @@ RMLK_API int rmlk_b200_gqa_decode_attention(rmlk_stream_t stream, int dtype, int
                                    int64_t v_problem_stride, float scale, const void* mask, int64_t mask_batch_stride,
                                    int64_t mask_head_stride, void* out);
 RMLK_API int rmlk_b200_gqa_decode_attention_supported(int64_t rows, int64_t head_dim, int64_t keys);
+/* Same, with the keys of a problem split over several CTAs (128 keys each) when `workspace` holds at least
+ * rmlk_b200_gqa_decode_attention_workspace_bytes(...) bytes: partial softmax results are merged through the workspace
+ * by the CTA that finishes last for a problem.  The first 16 * problems bytes of the workspace (arrival counters)
+ * must be zero on entry and are zero again on exit; the rest needs no initialisation.  Without a workspace, or for
+ * 128 keys or fewer, the one-CTA-per-problem kernel above runs. */
+RMLK_API int rmlk_b200_gqa_decode_attention_ws(rmlk_stream_t stream, int dtype, int64_t problems, int64_t rows, int64_t head_dim, int64_t keys,
+                                      int64_t kv_heads, const void* q, const void* k, int64_t k_problem_stride, const void* v,
+                                      int64_t v_problem_stride, float scale, const void* mask, int64_t mask_batch_stride,
+                                      int64_t mask_head_stride, void* out, void* workspace, size_t workspace_bytes);
+RMLK_API size_t rmlk_b200_gqa_decode_attention_workspace_bytes(int64_t problems, int64_t rows, int64_t head_dim, int64_t keys);
 
 /* SwiGLU gate as exported: Mul(Mul(gate, Sigmoid(gate)), up), n elements each.  Replaces backend/sigmoid.rs (cuDNN
  * activation, kernels/activation.rs:6-39) and backend/mul.rs (x2). */

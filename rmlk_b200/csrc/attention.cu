@@ -16,10 +16,10 @@
 // the probabilities equal theirs bit for bit; the P x V sums associate differently from the stand-alone MatMul
 // (within its 1e-4 bar).
 //
-// Measured on 512 problems x 4 rows x 550 keys x 64 (one layer of the decode benchmark): about 45 us against 37 us
-// for the A x B^T, softmax and narrow-MatMul kernels run one after the other - those spread a problem over many
-// warps of many CTAs and keep far more loads in flight than one CTA per problem can.  The host runtime therefore
-// uses this kernel only on request; splitting the keys of a problem over several CTAs is the way to make it pay.
+// Measured on 512 problems x 4 rows x 550 keys x 64 (one layer of the decode benchmark), as the difference it makes
+// to the 16-layer step: the one-CTA-per-problem kernel is about 15 us per layer slower than the A x B^T, softmax and
+// narrow-MatMul kernels run one after the other (37 us), the split-keys kernel below about 6 us slower.  The host
+// runtime therefore uses them only on request (RMLK_B200_ATTENTION=1).
 #include "common.cuh"
 
 namespace rmlk {
@@ -172,6 +172,190 @@ __global__ void __launch_bounds__(256, 2) gqa_decode_attention_kernel(AttnParams
     }
 }
 
+// The same computation with the keys of a problem split over several CTAs (128 keys each, 32 per warp): many small
+// CTAs keep far more loads in flight than one CTA per problem.  Every warp makes the softmax of its own 32 keys
+// (local maximum m, e = exp(s - m), l = sum e, a = sum e * V), the four warps of a CTA and then the CTAs of a problem
+// are merged by the usual rescaling (M = max m; L = sum l exp(m - M); A = sum a exp(m - M); out = A / L).  Partial
+// results go through a scratch buffer; the CTA that arrives last for a problem (a counter per problem, left at zero
+// again) merges them, in split order, so the result does not depend on timing.
+constexpr int SPLIT_KEYS = 128;
+
+struct AttnSplitParams {
+    AttnParams base;
+    int nsplit;
+    int* counters;   // [problems], zero on entry and on exit
+    float* partial;  // [problems][nsplit][8 + 4 * D]: M[4], L[4], A[4][D]
+};
+
+template <int LPR>
+__global__ void __launch_bounds__(128) gqa_decode_attention_split_kernel(AttnSplitParams sp) {
+    dep_sync();
+    const AttnParams& p = sp.base;
+    constexpr int D = 4 * LPR;
+    constexpr int RPI = 32 / LPR;   // rows of K / V per warp-wide load
+    constexpr int UN = 32 / RPI;    // loads per warp: 32 keys
+    constexpr int REC = 8 + 4 * D;  // floats per partial record
+    __shared__ __align__(16) float s_e[4][32][4];     // per warp: exp(score - local max) of its 32 keys, 4 rows
+    __shared__ float s_m[4][4], s_l[4][4];            // per warp: local max, local sum per row
+    __shared__ __align__(16) float s_a[4][4][D];      // per warp: sum e * V per row
+    __shared__ int s_last;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPR, rsel = lane / LPR;
+    const int64_t prob = blockIdx.y;
+    const int split = blockIdx.x;
+    const int T = p.T;
+    const int tw = split * SPLIT_KEYS + warp * 32;  // first key of this warp
+
+    float4 a[4];
+#pragma unroll
+    for (int m = 0; m < 4; m++) {
+        a[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (m < p.rows) a[m] = __ldg(reinterpret_cast<const float4*>(p.q + (prob * p.rows + m) * D + 4 * sub));
+    }
+    const int64_t b = prob / p.kv_heads, h0 = (prob % p.kv_heads) * p.rows;
+    const float* __restrict__ K = p.k + prob * p.kb + 4 * sub;
+    const float* __restrict__ V = p.v + prob * p.vb + 4 * sub;
+    uint4 bv[UN];
+#pragma unroll
+    for (int u = 0; u < UN; u++) {
+        const int t = tw + u * RPI + rsel;
+        bv[u] = make_uint4(0, 0, 0, 0);
+        if (t < T) bv[u] = ld_stream_u4(K + static_cast<int64_t>(t) * D);
+    }
+#pragma unroll
+    for (int u = 0; u < UN; u++) {
+        const int t = tw + u * RPI + rsel;
+        const float bx = __uint_as_float(bv[u].x), by = __uint_as_float(bv[u].y), bz = __uint_as_float(bv[u].z), bw = __uint_as_float(bv[u].w);
+        float part[4];
+#pragma unroll
+        for (int m = 0; m < 4; m++) part[m] = fmaf(a[m].w, bw, fmaf(a[m].z, bz, fmaf(a[m].y, by, a[m].x * bx)));
+        const bool up1 = (sub & (LPR / 2)) != 0;
+        const float r0 = __shfl_xor_sync(0xffffffffu, up1 ? part[0] : part[2], LPR / 2);
+        const float r1 = __shfl_xor_sync(0xffffffffu, up1 ? part[1] : part[3], LPR / 2);
+        const float q0 = (up1 ? part[2] : part[0]) + r0;
+        const float q1 = (up1 ? part[3] : part[1]) + r1;
+        const bool up2 = (sub & (LPR / 4)) != 0;
+        const float r2 = __shfl_xor_sync(0xffffffffu, up2 ? q0 : q1, LPR / 4);
+        float v = (up2 ? q1 : q0) + r2;
+#pragma unroll
+        for (int off = LPR / 8; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+        const int m = 2 * (up1 ? 1 : 0) + (up2 ? 1 : 0);
+        if ((sub & (LPR / 4 - 1)) == 0) {
+            float x = -INFINITY;  // keys beyond the end and rows that do not exist
+            if (t < T && m < p.rows) {
+                x = __fmul_rn(v, p.scale);
+                if (p.mask) x = __fadd_rn(x, p.mask[b * p.ms_b + (h0 + m) * p.ms_h + t]);
+            }
+            s_e[warp][u * RPI + rsel][m] = x;
+        }
+    }
+    // the values for the second pass are requested now; the softmax of the 32 keys runs while they are on their way
+#pragma unroll
+    for (int u = 0; u < UN; u++) {
+        const int t = tw + u * RPI + rsel;
+        bv[u] = make_uint4(0, 0, 0, 0);
+        if (t < T) bv[u] = ld_stream_u4(V + static_cast<int64_t>(t) * D);
+    }
+    __syncwarp();
+    {
+        // lane = key; the four rows one after the other
+        const float4 sc = *reinterpret_cast<const float4*>(&s_e[warp][lane][0]);
+        const float sv[4] = {sc.x, sc.y, sc.z, sc.w};
+        float ev[4];
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+            float mx = sv[m];
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float e = mx == -INFINITY ? 0.f : expf(sv[m] - mx);
+            float sum = e;
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            ev[m] = e;
+            if (lane == 0) {
+                s_m[warp][m] = mx;
+                s_l[warp][m] = sum;
+            }
+        }
+        __syncwarp();
+        *reinterpret_cast<float4*>(&s_e[warp][lane][0]) = make_float4(ev[0], ev[1], ev[2], ev[3]);
+    }
+    __syncwarp();
+    float acc[4][4];
+#pragma unroll
+    for (int m = 0; m < 4; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[m][j] = 0.f;
+#pragma unroll
+    for (int u = 0; u < UN; u++) {
+        const float4 pr = *reinterpret_cast<const float4*>(&s_e[warp][u * RPI + rsel][0]);
+        const float vx = __uint_as_float(bv[u].x), vy = __uint_as_float(bv[u].y), vz = __uint_as_float(bv[u].z), vw = __uint_as_float(bv[u].w);
+        const float pm[4] = {pr.x, pr.y, pr.z, pr.w};
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+            acc[m][0] = fmaf(pm[m], vx, acc[m][0]);
+            acc[m][1] = fmaf(pm[m], vy, acc[m][1]);
+            acc[m][2] = fmaf(pm[m], vz, acc[m][2]);
+            acc[m][3] = fmaf(pm[m], vw, acc[m][3]);
+        }
+    }
+#pragma unroll
+    for (int m = 0; m < 4; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float x = acc[m][j];
+#pragma unroll
+            for (int off = LPR; off < 32; off <<= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+            acc[m][j] = x;
+        }
+    if (rsel == 0) {
+#pragma unroll
+        for (int m = 0; m < 4; m++) *reinterpret_cast<float4*>(&s_a[warp][m][4 * sub]) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+    }
+    __syncthreads();
+    // the four warps of the CTA -> one partial record
+    float* rec = sp.partial + (prob * sp.nsplit + split) * REC;
+    for (int i = threadIdx.x; i < 4 * D; i += 128) {
+        const int m = i / D, d = i - m * D;
+        float M = s_m[0][m];
+#pragma unroll
+        for (int w = 1; w < 4; w++) M = fmaxf(M, s_m[w][m]);
+        float A = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; w++) {
+            const float f = s_m[w][m] == -INFINITY ? 0.f : expf(s_m[w][m] - M);
+            A = fmaf(s_a[w][m][d], f, A);
+            L = fmaf(s_l[w][m], f, L);
+        }
+        rec[8 + i] = A;
+        if (d == 0) {
+            rec[m] = M;
+            rec[4 + m] = L;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = atomicAdd(sp.counters + prob, 1) == sp.nsplit - 1;
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* recs = sp.partial + prob * sp.nsplit * REC;
+    for (int i = threadIdx.x; i < p.rows * D; i += 128) {
+        const int m = i / D;
+        float M = -INFINITY;
+        for (int k = 0; k < sp.nsplit; k++) M = fmaxf(M, __ldcg(recs + k * REC + m));
+        float A = 0.f, L = 0.f;
+        for (int k = 0; k < sp.nsplit; k++) {
+            const float mk = __ldcg(recs + k * REC + m);
+            const float f = mk == -INFINITY ? 0.f : expf(mk - M);
+            A = fmaf(__ldcg(recs + k * REC + 8 + i), f, A);
+            L = fmaf(__ldcg(recs + k * REC + 4 + m), f, L);
+        }
+        p.out[prob * p.rows * D + i] = A / L;
+    }
+    if (threadIdx.x == 0) sp.counters[prob] = 0;
+}
+
 constexpr int64_t ATTN_MAX_KEYS = 12288;  // 16 bytes of shared memory per key
 
 template <int LPR>
@@ -231,5 +415,56 @@ extern "C" int rmlk_b200_gqa_decode_attention(rmlk_stream_t stream, int dtype, i
         case 32: return attn_launch<8>(st, p, problems);
         case 64: return attn_launch<16>(st, p, problems);
         default: return attn_launch<32>(st, p, problems);
+    }
+}
+
+extern "C" size_t rmlk_b200_gqa_decode_attention_workspace_bytes(int64_t problems, int64_t rows, int64_t head_dim, int64_t keys) {
+    if (!rmlk_b200_gqa_decode_attention_supported(rows, head_dim, keys) || problems <= 0 || keys <= SPLIT_KEYS) return 0;
+    const int64_t nsplit = ceil_div64(keys, SPLIT_KEYS);
+    return static_cast<size_t>(problems) * (sizeof(int) * 4 + static_cast<size_t>(nsplit) * (8 + 4 * head_dim) * sizeof(float));
+}
+
+template <int LPR>
+static int attn_split_launch(cudaStream_t st, const AttnSplitParams& sp, int64_t problems) {
+    launch_dep(gqa_decode_attention_split_kernel<LPR>, dim3(static_cast<unsigned>(sp.nsplit), static_cast<unsigned>(problems)), dim3(128), 0, st, sp);
+    RMLK_CHECK_LAUNCH("gqa_decode_attention_split_kernel");
+    return RMLK_OK;
+}
+
+extern "C" int rmlk_b200_gqa_decode_attention_ws(rmlk_stream_t stream, int dtype, int64_t problems, int64_t rows, int64_t head_dim, int64_t keys,
+                                                 int64_t kv_heads, const void* q, const void* k, int64_t k_problem_stride, const void* v,
+                                                 int64_t v_problem_stride, float scale, const void* mask, int64_t mask_batch_stride,
+                                                 int64_t mask_head_stride, void* out, void* workspace, size_t workspace_bytes) {
+    const size_t need = rmlk_b200_gqa_decode_attention_workspace_bytes(problems, rows, head_dim, keys);
+    if (dtype != RMLK_F32 || !need || !workspace || workspace_bytes < need || problems > 65535 || !aligned_to(workspace, 16))
+        return rmlk_b200_gqa_decode_attention(stream, dtype, problems, rows, head_dim, keys, kv_heads, q, k, k_problem_stride, v, v_problem_stride, scale,
+                                              mask, mask_batch_stride, mask_head_stride, out);
+    if (kv_heads <= 0) return fail(RMLK_ERR_INVALID_ARG, "gqa_decode_attention: bad extent");
+    if (!q || !k || !v || !out) return fail(RMLK_ERR_INVALID_ARG, "gqa_decode_attention: NULL tensor pointer");
+    if (!aligned_to(q, 16) || !aligned_to(k, 16) || !aligned_to(v, 16) || !aligned_to(out, 16) || k_problem_stride % 4 || v_problem_stride % 4)
+        return fail(RMLK_ERR_INVALID_ARG, "gqa_decode_attention: operands must be 16-byte aligned");
+    AttnSplitParams sp;
+    sp.base.q = static_cast<const float*>(q);
+    sp.base.k = static_cast<const float*>(k);
+    sp.base.v = static_cast<const float*>(v);
+    sp.base.mask = static_cast<const float*>(mask);
+    sp.base.out = static_cast<float*>(out);
+    sp.base.kb = k_problem_stride;
+    sp.base.vb = v_problem_stride;
+    sp.base.ms_b = mask_batch_stride;
+    sp.base.ms_h = mask_head_stride;
+    sp.base.rows = static_cast<int>(rows);
+    sp.base.T = static_cast<int>(keys);
+    sp.base.kv_heads = static_cast<int>(kv_heads);
+    sp.base.scale = scale;
+    sp.nsplit = static_cast<int>(ceil_div64(keys, SPLIT_KEYS));
+    sp.counters = static_cast<int*>(workspace);
+    sp.partial = reinterpret_cast<float*>(static_cast<char*>(workspace) + static_cast<size_t>(problems) * sizeof(int) * 4);
+    cudaStream_t st = as_stream(stream);
+    switch (head_dim) {
+        case 16: return attn_split_launch<4>(st, sp, problems);
+        case 32: return attn_split_launch<8>(st, sp, problems);
+        case 64: return attn_split_launch<16>(st, sp, problems);
+        default: return attn_split_launch<32>(st, sp, problems);
     }
 }

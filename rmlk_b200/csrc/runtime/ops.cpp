@@ -1832,8 +1832,17 @@ bool Instance::run_fused(const FusedGroup& fg) {
             if (q->lazy) materialize(*q);
             const void *kdata = kt->data, *vdata = vh->data;
             Tensor& o = c.make(0, RMLK_F32, Shape({B, H, 1, D}));
-            check_rc(rmlk_b200_gqa_decode_attention(st, RMLK_F32, lk.outer, lk.fold, D, T, H / lk.fold, q->data, kdata, lk.sb, vdata, lv.sb, scale, mk->data,
-                                                    ms[0], ms[1], o.data));
+            const size_t ws_need = rmlk_b200_gqa_decode_attention_workspace_bytes(lk.outer, lk.fold, D, T);
+            void* ws = nullptr;
+            if (ws_need) {
+                ws = attn_ws.ensure(ws_need);
+                if (attn_ws.cap != attn_ws_zeroed) {  // a new buffer: the arrival counters must start at zero
+                    check_cuda(cudaMemsetAsync(attn_ws.ptr, 0, attn_ws.cap, stream), "attention workspace clear");
+                    attn_ws_zeroed = attn_ws.cap;
+                }
+            }
+            check_rc(rmlk_b200_gqa_decode_attention_ws(st, RMLK_F32, lk.outer, lk.fold, D, T, H / lk.fold, q->data, kdata, lk.sb, vdata, lv.sb, scale,
+                                                       mk->data, ms[0], ms[1], o.data, ws, ws_need));
             launches++;
             return true;
         }

@@ -250,6 +250,7 @@ Instance::~Instance() {
     status_word.release();
     matmul_ws.release();
     parts_ws.release();
+    attn_ws.release();
     read_staging.release();
     if (copy_stream) {
         cudaStreamSynchronize(copy_stream);

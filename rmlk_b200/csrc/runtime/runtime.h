@@ -229,6 +229,8 @@ struct Instance {
     std::unique_ptr<Arena> arena;
     DeviceBuffer status_word;   // device int for gather / scatter_nd diagnostics
     DeviceBuffer matmul_ws;     // split-K scratch
+    DeviceBuffer attn_ws;       // partial results + arrival counters of the split-keys attention kernel (kept zeroed)
+    size_t attn_ws_zeroed = 0;  // capacity that has been zero-filled
     DeviceBuffer parts_ws;      // split-K slabs that outlive their MatMul (Tensor::parts)
     int parts_owner = -1;       // value id whose slabs are in parts_ws, -1: free
     std::vector<uint8_t> parts_ok_value;  // per value id: MatMul output read only by a residual Add + RMSNorm chain
@@ -236,9 +238,9 @@ struct Instance {
     // producer of such rows may write them straight into the cache slot (rotary embedding of the keys does).
     std::vector<int> append_consumer;
     bool inplace_append_to = true;  // RMLK_B200_NO_APPEND_TO=1: new rows are made dense first, then copied in
-    // RMLK_B200_ATTENTION=1: scores MatMul, softmax chain and context MatMul of a decode step run as one kernel.  Off by
-    // default: with one CTA per (batch entry, KV head) that kernel keeps fewer bytes in flight than the three
-    // kernels it replaces and measured 8 us per layer slower on 512 problems of 550 keys.
+    // RMLK_B200_ATTENTION=1: scores MatMul, softmax chain and context MatMul of a decode step run as one kernel (keys of
+    // a problem split over CTAs of 128 keys).  Off by default: it measured 6 us per layer slower than the three kernels
+    // it replaces on 512 problems of 550 keys.
     bool attention = false;
     bool add_norm = true;       // RMLK_B200_NO_ADD_NORM=1: keep the residual Add (and the split-K sum) as launches of their own
     void settle_parts(int value_id);

@@ -387,7 +387,8 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[to
     return out
 
 
-def gqa_decode_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gqa_decode_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, mask: Optional[torch.Tensor] = None,
+                         split: bool = False) -> torch.Tensor:
     """q [B, KV, G, D] (G <= 4 query heads per KV head, one token each); k, v [B, KV, T, D] views whose [T, D] blocks are
     dense (the batch / head dims may step over spare room); mask [B, 1 or KV*G, 1, T] or None -> [B, KV, G, D]."""
     _require_cuda(q, mask)
@@ -401,10 +402,19 @@ def gqa_decode_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scal
     if mask is not None:
         assert mask.dim() == 4 and mask.shape[0] == B and mask.shape[2] == 1 and mask.shape[3] == T and mask.stride(3) == 1
         mb, mh = mask.stride(0), (mask.stride(1) if mask.shape[1] > 1 else 0)
-    _check(lib().rmlk_b200_gqa_decode_attention(_stream(), dt.from_torch(q.dtype), ctypes.c_int64(B * KV), ctypes.c_int64(G), ctypes.c_int64(D),
-                                                ctypes.c_int64(T), ctypes.c_int64(KV), _ptr(q), ctypes.c_void_p(k.data_ptr()), ctypes.c_int64(k.stride(1)),
-                                                ctypes.c_void_p(v.data_ptr()), ctypes.c_int64(v.stride(1)), ctypes.c_float(scale),
-                                                ctypes.c_void_p(0 if mask is None else mask.data_ptr()), ctypes.c_int64(mb), ctypes.c_int64(mh), _ptr(out)))
+    args = (_stream(), dt.from_torch(q.dtype), ctypes.c_int64(B * KV), ctypes.c_int64(G), ctypes.c_int64(D),
+            ctypes.c_int64(T), ctypes.c_int64(KV), _ptr(q), ctypes.c_void_p(k.data_ptr()), ctypes.c_int64(k.stride(1)),
+            ctypes.c_void_p(v.data_ptr()), ctypes.c_int64(v.stride(1)), ctypes.c_float(scale),
+            ctypes.c_void_p(0 if mask is None else mask.data_ptr()), ctypes.c_int64(mb), ctypes.c_int64(mh), _ptr(out))
+    if split:   # keys of a problem over several CTAs, merged through a zero-initialised workspace
+        fn = lib().rmlk_b200_gqa_decode_attention_workspace_bytes
+        fn.restype = ctypes.c_size_t
+        need = fn(ctypes.c_int64(B * KV), ctypes.c_int64(G), ctypes.c_int64(D), ctypes.c_int64(T))
+        ws = torch.zeros(max(need // 4, 4), dtype=torch.float32, device=q.device)
+        _check(lib().rmlk_b200_gqa_decode_attention_ws(*args, _ptr(ws), ctypes.c_size_t(need)))
+        assert need == 0 or int(ws.view(torch.int32)[: B * KV * 4].abs().sum()) == 0   # arrival counters are left at zero
+    else:
+        _check(lib().rmlk_b200_gqa_decode_attention(*args))
     return out
 
 

@@ -364,6 +364,9 @@ def test_decode_attention_kernel(K):
         pr = K.scale_mask_softmax(sc, scale, mask) if T <= 2048 else torch.softmax(sc * scale + mask, -1)
         want = K.matmul(pr.reshape(B * KV, G, T), v.contiguous().reshape(B * KV, T, D)).reshape(B, KV, G, D)
         assert float((got - want).abs().max()) <= 1e-5 * max(1.0, float(want.abs().max())), (B, KV, G, T, D)
+        got_split = K.gqa_decode_attention(q, k, v, scale, mask, split=True)   # keys of a problem over several CTAs
+        assert float((got_split.double() - ref).abs().max()) <= 1e-5 * max(1.0, float(ref.abs().max())), (B, KV, G, T, D)
+        assert torch.equal(got_split, K.gqa_decode_attention(q, k, v, scale, mask, split=True))   # merged in a fixed order
         nomask = K.gqa_decode_attention(q, k, v, scale, None)
         ref2 = torch.einsum("bkgt,bktd->bkgd", torch.softmax(torch.einsum("bkgd,bktd->bkgt", q.double(), k.double()) * scale, -1), v.double())
         assert float((nomask.double() - ref2).abs().max()) <= 1e-5 * max(1.0, float(ref2.abs().max()))
