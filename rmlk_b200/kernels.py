@@ -388,7 +388,7 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[to
 
 
 def gqa_decode_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, mask: Optional[torch.Tensor] = None,
-                         split: bool = False) -> torch.Tensor:
+                         split: bool = False, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [B, KV, G, D] (G <= 4 query heads per KV head, one token each); k, v [B, KV, T, D] views whose [T, D] blocks are
     dense (the batch / head dims may step over spare room); mask [B, 1 or KV*G, 1, T] or None -> [B, KV, G, D]."""
     _require_cuda(q, mask)
@@ -406,7 +406,9 @@ def gqa_decode_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scal
             ctypes.c_int64(T), ctypes.c_int64(KV), _ptr(q), ctypes.c_void_p(k.data_ptr()), ctypes.c_int64(k.stride(1)),
             ctypes.c_void_p(v.data_ptr()), ctypes.c_int64(v.stride(1)), ctypes.c_float(scale),
             ctypes.c_void_p(0 if mask is None else mask.data_ptr()), ctypes.c_int64(mb), ctypes.c_int64(mh), _ptr(out))
-    if split:   # keys of a problem over several CTAs, merged through a zero-initialised workspace
+    if workspace is not None:   # caller-owned workspace (zero-filled once): nothing allocated, nothing waited for
+        _check(lib().rmlk_b200_gqa_decode_attention_ws(*args, _ptr(workspace), ctypes.c_size_t(workspace.numel() * workspace.element_size())))
+    elif split:   # keys of a problem over several CTAs, merged through a zero-initialised workspace
         fn = lib().rmlk_b200_gqa_decode_attention_workspace_bytes
         fn.restype = ctypes.c_size_t
         need = fn(ctypes.c_int64(B * KV), ctypes.c_int64(G), ctypes.c_int64(D), ctypes.c_int64(T))

@@ -107,6 +107,7 @@ def cases():
         return name, build
 
     idx_rows = 32768
+    attn_ws = torch.zeros(1 << 20, device=dev)   # 4 MB, zero-filled once: arrival counters + partial results
     cs = [
         binary("add f32 same-shape 64M", (1 << 26,), (1 << 26,)),
         binary("mul f32 [32768,8192]*[32768,8192] (SwiGLU)", (32768, 8192), (32768, 8192), "mul"),
@@ -168,6 +169,13 @@ def cases():
                 lambda q, k: K.matmul_nt(q, k), flops=2 * 512 * 4 * 64 * 523),
         generic("matmul 512x[4,523]x[523,64] (decode context, cache in place)", lambda: (rnd(512, 4, 523), rnd(512, 523, 64)),
                 lambda p, v: K.matmul(p, v), flops=2 * 512 * 4 * 64 * 523),
+        # the same attention as one launch (scores, scale, mask-free softmax, context): one CTA per problem, and keys split over CTAs
+        generic("gqa_decode_attention 512x[4,64] over [523,64] K and V, one CTA per problem",
+                lambda: (rnd(64, 8, 4, 64), rnd(64, 8, 523, 64), rnd(64, 8, 523, 64)),
+                lambda q, k, v: K.gqa_decode_attention(q, k, v, 0.125), flops=4 * 512 * 4 * 64 * 523),
+        generic("gqa_decode_attention 512x[4,64] over [523,64] K and V, keys split over CTAs",
+                lambda: (rnd(64, 8, 4, 64), rnd(64, 8, 523, 64), rnd(64, 8, 523, 64)),
+                lambda q, k, v: K.gqa_decode_attention(q, k, v, 0.125, workspace=attn_ws), flops=4 * 512 * 4 * 64 * 523),
     ]
     return cs
 
