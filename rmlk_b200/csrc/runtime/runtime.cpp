@@ -327,8 +327,15 @@ void Instance::deliver_host_outputs() {
         if (!t.present) continue;
         if (t.nbytes() != h.nbytes) raise(RMLK_ERR_INVALID_ARG, "host output `" + g.values[h.value_id].name + "`: size mismatch");
         if (t.parts > 1) settle_parts(h.value_id);
-        if (t.lazy) materialize(t);
-        if (h.nbytes) check_cuda(cudaMemcpyAsync(h.dst, t.data, h.nbytes, cudaMemcpyDeviceToHost, stream), "host output D2H");
+        const void* src = t.data;
+        if (t.lazy && h.nbytes) {
+            // a strided view (a carried cache with spare room) stays as it is: gathered into a staging buffer for the copy
+            void* tmp = read_staging.ensure(h.nbytes);
+            check_rc(rmlk_b200_strided_copy(reinterpret_cast<rmlk_stream_t>(stream), static_cast<int>(dtype_size_of(t.dtype)),
+                                            static_cast<int>(t.pshape.size()), t.pshape.data(), t.pstride.data(), t.data, tmp));
+            src = tmp;
+        }
+        if (h.nbytes) check_cuda(cudaMemcpyAsync(h.dst, src, h.nbytes, cudaMemcpyDeviceToHost, stream), "host output D2H");
         h.delivered_run = run_counter;
     }
     if (copies_pending) check_cuda(cudaEventRecord(copies_done, copy_stream), "cudaEventRecord");

@@ -327,3 +327,32 @@ def test_outputs_streamed_to_host_memory(cuda):
     inst.set_input("x", rng.standard_normal((3, 1, hidden), dtype=np.float32))
     with pytest.raises(Exception):
         inst.launch()
+
+
+def test_streamed_output_of_a_carried_cache(cuda):
+    """A growing cache registered for delivery to the host (re-registered with its new size every step) is gathered
+    from its buffer with spare room without disturbing the in-place append."""
+    import torch
+    from rmlk_b200.runtime import ModelInstance
+    B, KV, D = 2, 3, 8
+    g = GraphSpec()
+    g.input("new", np.float32, [B, KV, 0, D])
+    g.input("past", np.float32, [B, KV, 0, D])
+    g.op("Concat", ["past", "new"], "present", axis=2)
+    g.output("present")
+    inst = ModelInstance(g.to_runtime())
+    inst.bind("present", "past")
+    r = np.random.default_rng(61)
+    cache = np.zeros((B, KV, 0, D), np.float32)
+    host = torch.empty(B * KV * 40 * D, dtype=torch.float32).pin_memory()
+    for step in range(30):
+        new = r.standard_normal((B, KV, 1, D), dtype=np.float32)
+        cache = np.concatenate([cache, new], axis=2)
+        inst.stream_output("present", host.data_ptr(), cache.size * 4)
+        inst.set_input("new", new)
+        if step == 0:
+            inst.set_input("past", np.zeros((B, KV, 0, D), np.float32))
+        inst.launch()
+        inst.wait_outputs()
+        assert np.array_equal(host.numpy()[: cache.size].reshape(cache.shape), cache), step
+    assert inst.last_launches <= 3   # the append, the gather into the staging buffer (and nothing that copies the cache back)
