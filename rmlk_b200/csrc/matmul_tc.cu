@@ -151,9 +151,10 @@ int tc_matmul_plan(int64_t m, int64_t n, int64_t k) {
     const int64_t max_s = k_iters / 8 > 0 ? k_iters / 8 : 1;  // at least 8 k-blocks per split
     if (s > max_s) s = max_s;
     if (s < 1) s = 1;
-    // Up to TC_CLUSTER_MAX splits add up on chip (one thread-block cluster per tile); a little above that the
-    // cluster form with fewer splits still wins over a scratch round trip plus a second kernel.
-    if (s > TC_CLUSTER_MAX && s <= TC_CLUSTER_MAX + TC_CLUSTER_MAX / 2) s = TC_CLUSTER_MAX;
+    // Up to TC_CLUSTER_MAX splits add up on chip (one thread-block cluster per tile); wider ones go through the
+    // scratch buffer and a second kernel.  (Snapping a 5- or 6-way split down to a 4-CTA cluster used to win; since
+    // the second kernel is scheduled under the tail of the first it no longer does: [64,2048]x[2048,3072] takes
+    // 13.4 us as 6 x 24 CTAs + sum against 14.3 us as 24 clusters of 4.)
     // (Capping a wider split at the cluster size for short K was measured and did not pay: [64,2048]x[2048,2048]
     // took 13.9 us as 4-CTA clusters against 11.0 us + a 2-3 us reduction as an 8-way scratch split.)
     return static_cast<int>(s > 32 ? 32 : s);
