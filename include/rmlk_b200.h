@@ -16,7 +16,14 @@
  *    passed the way the reference passes it to kernels: rank 1, shape {1}
  *    (runtime/src/providers/cuda/utils.rs:5-18).
  *  - `stream` is a cudaStream_t (NULL = legacy default stream).  Work is enqueued on it and the
- *    call returns; entry points are re-entrant and keep no mutable global state.
+ *    call returns.  Entry points may be called from several threads (one per GPU, or several per GPU on
+ *    different streams).  The only process-wide state is a set of lazily filled, write-once caches: the SM
+ *    count per device, the driver's tensor-map encoder, per-device "kernel configured" flags
+ *    (cudaFuncSetAttribute for kernels that need more than 48 KB of shared memory), the address of the
+ *    built-in scratch of rmlk_b200_matmul_static, and the environment switches read at first use.  They are
+ *    published with atomics / std::call_once, so concurrent first calls are safe.  The first call of a kernel
+ *    family on a device therefore does a little more host work than later ones (and should come before any
+ *    stream capture).
  *  - Return value: RMLK_OK, an RMLK_ERR_* code, or RMLK_ERR_CUDA_BASE + cudaError_t.  Nothing
  *    aborts or traps.  Kernels that can meet bad data (Gather / ScatterND indices) report through
  *    a caller-provided device status word, as the reference's ScatterND does
@@ -244,6 +251,9 @@ RMLK_API int rmlk_b200_store_small(rmlk_stream_t stream, int n_words, const uint
  * backend/matmul.rs:48-86).  dtype f32, or f16 (half in and out, fp32 accumulation - the reference asks cuBLAS
  * for CUBLAS_COMPUTE_16F there, cuda/src/params.rs:24-31; SIMT kernel, no workspace).  `workspace` is optional caller-owned device scratch of
  * `workspace_bytes` (see rmlk_b200_matmul_workspace_bytes); NULL selects kernels that need none. */
+/* rmlk_b200_matmul passes no status word: should a bounded wait inside the tensor-core kernel ever expire (it
+ * never has on a healthy device), the affected tiles of C are left unwritten and the call still returns RMLK_OK -
+ * callers that must detect this use rmlk_b200_matmul_ex with a status word. */
 RMLK_API int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                      const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
                      int64_t c_batch_stride, void* workspace, size_t workspace_bytes);
@@ -294,8 +304,10 @@ RMLK_API int rmlk_b200_matmul_nt(rmlk_stream_t stream, int dtype, int64_t batch,
  * library, held until the process exits.  Same arguments and results as rmlk_b200_matmul_ex otherwise.
  *  - Shapes whose scratch need (rmlk_b200_matmul_workspace_bytes) exceeds the array are rejected with
  *    RMLK_ERR_INVALID_ARG; nothing is launched.
- *  - The first call on each device looks up the array's device address; make that first call outside any
- *    stream capture.  No call allocates or frees memory.
+ *  - The first call on each device looks up the array's device address and, like the first call of any
+ *    MatMul here, configures the kernels it launches (cudaFuncSetAttribute, cudaGetDriverEntryPoint); make that
+ *    first call outside any stream capture and before other threads call in.  No call allocates or frees
+ *    device memory.
  *  - All calls share the one array and it keeps the previous call's partial sums; every call overwrites what
  *    it reads, so nothing needs clearing, but two calls that overlap on the GPU (different streams) race on
  *    it.  Keep calls on one stream, or order them with events. */

@@ -91,6 +91,12 @@ RMLK_API int rmlk_instance_bind(rmlk_instance* inst, const char* output, const c
  * returns when everything is enqueued, unless an op needed a device value on the host. */
 RMLK_API int rmlk_instance_run(rmlk_instance* inst);
 RMLK_API int rmlk_instance_synchronize(rmlk_instance* inst);
+/* How the runtime reports a non-zero device status word when it next waits for the device (synchronize, read,
+ * wait_outputs): 0 -> RMLK_OK; RMLK_ERR_TIMEOUT (a bounded wait inside a MatMul kernel expired) -> RMLK_ERR_TIMEOUT;
+ * any other value (1 = index out of range, 2 = offset past the end, from Gather / ScatterND:
+ * ScatterNdError::KernelFailed { code }, runtime/src/providers/cuda/backend/scatter_nd.rs:198-203) ->
+ * RMLK_ERR_KERNEL_STATUS.  Pure host function. */
+RMLK_API int rmlk_runtime_status_to_error(int status_word);
 /* Shape / dtype / device address of a graph output (or any named value) after a run.  *device_ptr is NULL for an
  * output kept as a strided view: a bound output that is Concat(bound input, new rows) - a KV cache - lives in a
  * buffer with spare room along the concat axis and is appended in place (rmlk_instance_bind); rmlk_instance_read

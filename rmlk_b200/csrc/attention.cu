@@ -20,6 +20,7 @@
 // to the 16-layer step: the one-CTA-per-problem kernel is about 15 us per layer slower than the A x B^T, softmax and
 // narrow-MatMul kernels run one after the other (37 us), the split-keys kernel below about 6 us slower.  The host
 // runtime therefore uses them only on request (RMLK_B200_ATTENTION=1).
+#include <mutex>
 #include "common.cuh"
 
 namespace rmlk {
@@ -361,14 +362,16 @@ constexpr int64_t ATTN_MAX_KEYS = 12288;  // 16 bytes of shared memory per key
 template <int LPR>
 static int attn_launch(cudaStream_t st, const AttnParams& p, int64_t problems) {
     const size_t smem = (4 * static_cast<size_t>((p.T + 3) & ~3) + 8 * 4 * 4 * LPR) * sizeof(float);
-    static bool configured[64] = {false};
+    static std::once_flag configured[64];  // once per device; a concurrent first call waits for the attribute to be set
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        RMLK_CUDA(cudaFuncSetAttribute(gqa_decode_attention_kernel<LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       static_cast<int>((4 * ATTN_MAX_KEYS + 8 * 4 * 4 * LPR) * sizeof(float))));
-        configured[dev] = true;
-    }
+    cudaError_t cfg_err = cudaSuccess;
+    if (dev >= 0 && dev < 64)
+        std::call_once(configured[dev], [&] {
+            cfg_err = cudaFuncSetAttribute(gqa_decode_attention_kernel<LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           static_cast<int>((4 * ATTN_MAX_KEYS + 8 * 4 * 4 * LPR) * sizeof(float)));
+        });
+    RMLK_CUDA(cfg_err);
     launch_dep(gqa_decode_attention_kernel<LPR>, dim3(static_cast<unsigned>(problems)), dim3(256), smem, st, p);
     RMLK_CHECK_LAUNCH("gqa_decode_attention_kernel");
     return RMLK_OK;

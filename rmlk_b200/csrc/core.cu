@@ -1,4 +1,5 @@
 // Library-wide helpers: thread-local error text, device capability cache, version.
+#include <atomic>
 #include "common.cuh"
 
 #include <cstdlib>
@@ -22,24 +23,23 @@ int cuda_fail(cudaError_t e, const char* what) {
 
 int sm_count() {
     // Immutable per-device capability table, filled on first use.
-    static int counts[64] = {0};
+    static std::atomic<int> counts[64];
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-    if (counts[dev] == 0) {
-        int n = 0;
+    int n = counts[dev].load(std::memory_order_relaxed);
+    if (n == 0) {
         if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-        counts[dev] = n;
+        counts[dev].store(n, std::memory_order_relaxed);
     }
-    return counts[dev];
+    return n;
 }
 
 bool dep_launch_enabled() {
-    static int v = -1;
-    if (v < 0) {
+    static const bool v = [] {
         const char* e = getenv("RMLK_B200_NO_PDL");
-        v = (e && e[0] == '1') ? 0 : 1;
-    }
-    return v == 1;
+        return !(e && e[0] == '1');
+    }();
+    return v;
 }
 
 }  // namespace rmlk

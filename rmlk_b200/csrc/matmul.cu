@@ -15,6 +15,8 @@
 //
 // The reference calls cublasGemmStridedBatchedEx with CUBLAS_COMPUTE_32F
 // (cuda/src/kernels/gemm.rs:206-231); both kernels accumulate in fp32 with FMA.
+#include <atomic>
+
 #include "common.cuh"
 
 namespace rmlk {
@@ -875,7 +877,9 @@ static __device__ __align__(256) unsigned char g_matmul_static_scratch[RMLK_STAT
 // In host code `g_matmul_static_scratch` is only a handle for the runtime, not a device address, so the
 // address kernels can use is looked up once per device (with that device current) and cached.
 static void* static_scratch_ptr(int* rc_out) {
-    static void* ptrs[64] = {nullptr};
+    // One slot per device.  Threads that race on a device's first call all look the same address up and store the same
+    // value; the atomic makes the publication well defined.
+    static std::atomic<void*> ptrs[64];
     *rc_out = RMLK_OK;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -887,16 +891,16 @@ static void* static_scratch_ptr(int* rc_out) {
         *rc_out = rmlk::fail(RMLK_ERR_INTERNAL, "matmul_static: device index out of range");
         return nullptr;
     }
-    if (!ptrs[dev]) {
-        void* p = nullptr;
+    void* p = ptrs[dev].load(std::memory_order_acquire);
+    if (!p) {
         e = cudaGetSymbolAddress(&p, g_matmul_static_scratch);
         if (e != cudaSuccess || !p) {
             *rc_out = rmlk::cuda_fail(e, "cudaGetSymbolAddress(matmul static scratch)");
             return nullptr;
         }
-        ptrs[dev] = p;
+        ptrs[dev].store(p, std::memory_order_release);
     }
-    return ptrs[dev];
+    return p;
 }
 
 extern "C" size_t rmlk_b200_matmul_static_scratch_bytes(void) { return RMLK_STATIC_SCRATCH_BYTES; }

@@ -38,6 +38,8 @@
 // Every mbarrier wait is bounded: on expiry the thread raises a CTA-wide abort flag, records
 // RMLK_ERR_TIMEOUT in the caller's status word, and every role falls through to the common exit where TMEM
 // is released.  Every TMA load targets this CTA's own shared memory.
+#include <mutex>
+
 #include "matmul_tc_kernel.cuh"
 
 namespace rmlk {
@@ -48,15 +50,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static bool tried = false;
-    if (!tried) {
-        tried = true;
+    // looked up once per process (function-local static: initialised exactly once, also under concurrent first calls)
+    static const EncodeTiledFn fn = [] {
         void* p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(p);
-    }
+            return reinterpret_cast<EncodeTiledFn>(p);
+        return static_cast<EncodeTiledFn>(nullptr);
+    }();
     return fn;
 }
 
@@ -75,13 +76,17 @@ static bool make_map_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint6
 template <int MT, int SW, int SA, int G>
 static int launch(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tmA, const TcParams& p, dim3 grid) {
     using L = SmemLayout<MT, SW, SA>;
-    static bool configured[64] = {false};
+    // The kernel's dynamic shared memory limit is raised once per device; std::call_once makes a thread that arrives
+    // during another thread's first call wait for the attribute to be set before it launches.
+    static std::once_flag configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !configured[dev]) {
-        RMLK_CUDA(cudaFuncSetAttribute(tc_gemm_kernel<MT, SW, SA, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL));
-        configured[dev] = true;
-    }
+    cudaError_t cfg_err = cudaSuccess;
+    if (dev >= 0 && dev < 64)
+        std::call_once(configured[dev], [&] {
+            cfg_err = cudaFuncSetAttribute(tc_gemm_kernel<MT, SW, SA, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        });
+    RMLK_CUDA(cfg_err);
     // launched so that it may be scheduled while the previous kernel of the stream drains (the kernel waits, see
     // dep_wait); with split-K inside a cluster the ksplit CTAs of one tile (grid y) form the cluster
     cudaLaunchConfig_t cfg = {};
@@ -113,12 +118,11 @@ static int launch(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tm
 }  // namespace tc
 
 bool tc_enabled() {
-    static int v = -1;
-    if (v < 0) {
+    static const bool v = [] {
         const char* e = getenv("RMLK_B200_NO_TC");
-        v = (e && e[0] == '1') ? 0 : 1;
-    }
-    return v == 1;
+        return !(e && e[0] == '1');
+    }();
+    return v;
 }
 
 // Eligibility of the tensor-core path for C[M,N] = A[M,K] x W[K,N].
@@ -133,12 +137,11 @@ bool tc_matmul_eligible(int64_t m, int64_t n, int64_t k, const void* a, const vo
 // two waves, twice the time), while clusters of up to 4 did; wider splits go through the scratch buffer.
 // RMLK_B200_TC_CLUSTER_MAX=1..8 overrides the limit; 1 sends every split through the scratch buffer.
 static int tc_cluster_max() {
-    static int v = 0;
-    if (v == 0) {
+    static const int v = [] {
         const char* e = getenv("RMLK_B200_TC_CLUSTER_MAX");
-        int x = e ? atoi(e) : 4;
-        v = x < 1 ? 1 : x > 8 ? 8 : x;
-    }
+        const int x = e ? atoi(e) : 4;
+        return x < 1 ? 1 : x > 8 ? 8 : x;
+    }();
     return v;
 }
 #define TC_CLUSTER_MAX (tc_cluster_max())

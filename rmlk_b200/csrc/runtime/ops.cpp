@@ -1836,10 +1836,18 @@ bool Instance::run_fused(const FusedGroup& fg) {
             void* ws = nullptr;
             if (ws_need) {
                 ws = attn_ws.ensure(ws_need);
-                if (attn_ws.cap != attn_ws_zeroed) {  // a new buffer: the arrival counters must start at zero
+                // The arrival counters (16 bytes per problem at the start of the workspace) must be zero when the kernel
+                // starts; the kernel leaves them at zero.  A new buffer is cleared whole.  When the number of problems
+                // changes the layout moves - last run's partial sums may lie where this run's counters are - so the
+                // counter prefix is cleared again.
+                const size_t counter_bytes = static_cast<size_t>(lk.outer) * 16;
+                if (attn_ws.cap != attn_ws_zeroed) {
                     check_cuda(cudaMemsetAsync(attn_ws.ptr, 0, attn_ws.cap, stream), "attention workspace clear");
                     attn_ws_zeroed = attn_ws.cap;
+                } else if (lk.outer != attn_ws_problems) {
+                    check_cuda(cudaMemsetAsync(attn_ws.ptr, 0, counter_bytes < attn_ws.cap ? counter_bytes : attn_ws.cap, stream), "attention counters clear");
                 }
+                attn_ws_problems = lk.outer;
             }
             check_rc(rmlk_b200_gqa_decode_attention_ws(st, RMLK_F32, lk.outer, lk.fold, D, T, H / lk.fold, q->data, kdata, lk.sb, vdata, lv.sb, scale,
                                                        mk->data, ms[0], ms[1], o.data, ws, ws_need));

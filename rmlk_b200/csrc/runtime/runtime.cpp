@@ -355,9 +355,16 @@ void Instance::check_status() {
     status_dirty = false;
     if (code != 0) {
         check_cuda(cudaMemsetAsync(status_word.ptr, 0, sizeof(int), stream), "status reset");
-        // ScatterNdError::KernelFailed { code } in the reference (backend/scatter_nd.rs:198-203)
-        raise(RMLK_ERR_KERNEL_STATUS, "kernel failed: index out of range (code " + std::to_string(code) + ")");
+        raise(rmlk_runtime_status_to_error(code), status_word_message(code));
     }
+}
+
+// The one device status word is shared by Gather / ScatterND (1 = index out of range, 2 = offset past the end:
+// ScatterNdError::KernelFailed { code } in the reference, backend/scatter_nd.rs:198-203) and by the MatMul kernels,
+// which store RMLK_ERR_TIMEOUT there when one of their bounded waits expires.
+std::string status_word_message(int word) {
+    if (word == RMLK_ERR_TIMEOUT) return "kernel failed: a bounded wait inside a MatMul kernel expired (code " + std::to_string(word) + "); its output is incomplete";
+    return "kernel failed: index out of range (code " + std::to_string(word) + ")";
 }
 
 void Instance::run() {
@@ -475,6 +482,11 @@ struct rmlk_instance {
     }                                                                     \
     catch (const Error& e) { return rmlk::fail(e.code, e.what()); }       \
     catch (const std::exception& e) { return rmlk::fail(RMLK_ERR_INTERNAL, e.what()); }
+
+extern "C" int rmlk_runtime_status_to_error(int word) {
+    if (word == 0) return RMLK_OK;
+    return word == RMLK_ERR_TIMEOUT ? RMLK_ERR_TIMEOUT : RMLK_ERR_KERNEL_STATUS;
+}
 
 extern "C" rmlk_graph* rmlk_graph_create(void) { return new (std::nothrow) rmlk_graph(); }
 extern "C" void rmlk_graph_destroy(rmlk_graph* g) { delete g; }

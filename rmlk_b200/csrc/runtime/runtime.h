@@ -231,6 +231,7 @@ struct Instance {
     DeviceBuffer matmul_ws;     // split-K scratch
     DeviceBuffer attn_ws;       // partial results + arrival counters of the split-keys attention kernel (kept zeroed)
     size_t attn_ws_zeroed = 0;  // capacity that has been zero-filled
+    int64_t attn_ws_problems = -1;  // problem count of the last run that used attn_ws (its counter prefix is clean for that count)
     DeviceBuffer parts_ws;      // split-K slabs that outlive their MatMul (Tensor::parts)
     int parts_owner = -1;       // value id whose slabs are in parts_ws, -1: free
     std::vector<uint8_t> parts_ok_value;  // per value id: MatMul output read only by a residual Add + RMSNorm chain
@@ -273,6 +274,7 @@ struct Instance {
 
 size_t dtype_size_of(int dt);
 
+std::string status_word_message(int word);  // text for a non-zero device status word
 void check_cuda(cudaError_t e, const char* what);
 void check_rc(int rc);
 

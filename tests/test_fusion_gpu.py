@@ -450,3 +450,48 @@ def test_runtime_runs_decode_attention_as_one_launch(cuda, KV, G, D):
     fits = G <= 4 and D in (16, 32, 64, 128)
     # decode steps: 2 appends + (1 | 3) attention launches
     assert apart.last_launches - one.last_launches == (2 if fits else 0), (one.last_launches, apart.last_launches)
+
+
+def test_one_launch_attention_when_the_batch_changes_between_runs(cuda):
+    """The split-keys attention kernel keeps arrival counters at the head of its workspace and partial sums behind them;
+    where the partial sums start depends on the number of problems.  An instance that runs 64 requests, then 8, then 64
+    again re-uses the workspace with a different layout each time: results must still equal the single kernels' and the
+    float64 definition (stale partial sums where counters are expected would leave the output unwritten)."""
+    from rmlk_b200.runtime import ModelInstance
+    KV, G, D, T0 = 2, 4, 64, 300   # 301+ keys: three splits of 128 keys per problem
+    spec = attention_graph(KV, G, D)
+    os.environ["RMLK_B200_ATTENTION"] = "1"
+    try:
+        one = ModelInstance(spec.to_runtime())
+    finally:
+        os.environ.pop("RMLK_B200_ATTENTION", None)
+    apart = ModelInstance(spec.to_runtime())
+    for m in (one, apart):
+        m.bind("present_k", "past_k")
+        m.bind("present_v", "past_v")
+    r = np.random.default_rng(77)
+    for B in (64, 8, 64, 2, 64):
+        cache_k = r.standard_normal((B, KV, T0, D), dtype=np.float32)
+        cache_v = r.standard_normal((B, KV, T0, D), dtype=np.float32)
+        for step in range(2):
+            T = cache_k.shape[2] + 1
+            feeds = {"q": r.standard_normal((B, KV * G, 1, D), dtype=np.float32), "new_k": r.standard_normal((B, KV, 1, D), dtype=np.float32),
+                     "new_v": r.standard_normal((B, KV, 1, D), dtype=np.float32),
+                     "mask": np.where(r.random((B, 1, 1, T)) > 0.8, np.finfo(np.float32).min, 0.0).astype(np.float32)}
+            feeds["mask"][..., 0] = 0.0
+            for m in (one, apart):
+                for k, v in feeds.items():
+                    m.set_input(k, v)
+                if step == 0:
+                    m.set_input("past_k", cache_k)
+                    m.set_input("past_v", cache_v)
+                m.launch()
+            cache_k = np.concatenate([cache_k, feeds["new_k"]], axis=2)
+            cache_v = np.concatenate([cache_v, feeds["new_v"]], axis=2)
+            a, b = one.read("ctx"), apart.read("ctx")
+            assert np.max(np.abs(a - b)) <= 1e-5 * max(1.0, np.max(np.abs(b))), (B, step)
+            s64 = np.einsum("bhsd,bhtd->bhst", feeds["q"].astype(np.float64), np.repeat(cache_k, G, axis=1).astype(np.float64)) / np.sqrt(D) + feeds["mask"]
+            e = np.exp(s64 - s64.max(-1, keepdims=True))
+            want = np.einsum("bhst,bhtd->bhsd", e / e.sum(-1, keepdims=True), np.repeat(cache_v, G, axis=1).astype(np.float64))
+            assert np.max(np.abs(a - want)) <= 1e-4 * max(1.0, np.max(np.abs(want))), (B, step)
+        assert apart.last_launches - one.last_launches == 2, "the one-launch path ran"

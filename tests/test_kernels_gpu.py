@@ -542,7 +542,9 @@ def test_large_elementwise_and_copy_roundtrip():
 TC_CASES = [(64, 8192, 2048), (64, 2048, 2048), (64, 512, 2048), (64, 2048, 8192), (17, 128, 32), (33, 256, 64), (100, 384, 96), (128, 1024, 256),
             (200, 256, 512), (300, 128, 2048), (64, 128256, 2048), (4096, 8192, 2048), (65, 128, 4096),
             # K split 7, 5 and 3 ways inside a thread-block cluster (rows of the tile not divisible by the split)
-            (64, 2688, 2048), (64, 3712, 2048), (64, 6272, 2048), (17, 2688, 2048), (128, 2688, 1024)]
+            (64, 2688, 2048), (64, 3712, 2048), (64, 6272, 2048), (17, 2688, 2048), (128, 2688, 1024),
+            # merged q|k|v and gate|up projections of the 1B shape; the 8B shape (hidden 4096, FFN 14336) at decode and prefill M
+            (64, 3072, 2048), (64, 16384, 2048), (64, 14336, 4096), (64, 4096, 14336), (4096, 14336, 4096), (4096, 4096, 14336)]
 
 
 @pytest.mark.parametrize("case", TC_CASES)
@@ -593,6 +595,29 @@ def test_matmul_tensor_core_3xtf32(case):
 NT_CASES = [(512, 4, 523, 64), (7, 1, 100, 64), (5, 2, 33, 16), (3, 3, 70, 128), (9, 8, 45, 32), (4, 4, 31, 4), (2, 4, 1000, 20),
             # shapes outside the warp-per-32-rows kernel: K not a multiple of 4, K > 128, M > 8
             (3, 2, 50, 30), (2, 3, 40, 300), (2, 20, 35, 64)]
+
+
+@pytest.mark.parametrize("m", [1, 8, 16])
+@pytest.mark.parametrize("kn", [(4096, 14336), (14336, 4096), (2048, 8192), (2048, 128256)])
+def test_matmul_decode_rows_on_8b_and_1b_shapes(m, kn):
+    """The memory-bound small-M MatMul (M <= 16) on the sweep's shapes: [M, 4096] x [4096, 14336] and [M, 14336] x
+    [14336, 4096] (8B shape), [M, 2048] x [2048, 8192] and the 1B lm_head; operands N(0, 0.02) as in the sweep, against
+    float64 on the same device; with and without split-K scratch; deterministic."""
+    k, n = kn
+    g = torch.Generator(device="cuda")
+    g.manual_seed(100 + m)
+    a = torch.randn(m, k, device="cuda", generator=g) * 0.02
+    w = torch.randn(k, n, device="cuda", generator=g) * 0.02
+    want = a.double() @ w.double()
+    scale = float(want.abs().max())
+    got = K.matmul(a, w)
+    assert float((got.double() - want).abs().max()) <= 1e-4 * scale
+    wsb = K.matmul_workspace_bytes(1, m, n, k)
+    if wsb:
+        ws = torch.empty(wsb // 4, device="cuda")
+        g2 = K.matmul(a, w, workspace=ws)
+        assert float((g2.double() - want).abs().max()) <= 1e-4 * scale
+        assert torch.equal(g2, K.matmul(a, w, workspace=ws))
 
 
 @pytest.mark.parametrize("case", NT_CASES)

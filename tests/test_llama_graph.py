@@ -6,6 +6,8 @@ KV cache.  GPU: the same graphs through librmlk_b200.so must match the interpret
 rel 1e-4 (the path's stated bar), including the single-layer configuration of the benchmark plan (one Llama-3.2-1B-shaped layer, 128-token prefill
 then 32 decode steps).
 """
+import os
+
 import numpy as np
 import pytest
 
@@ -189,3 +191,75 @@ def test_one_1b_shaped_layer_prefill_128_decode_32(cuda):
             gk = inst.read("present.0.key")
             assert np.max(np.abs(gk - cpu["present.0.key"])) <= 1e-4 * np.max(np.abs(cpu["present.0.key"]))
     assert worst <= 1e-4, worst
+
+
+@pytest.mark.gpu
+def test_1b_shaped_layer_lm_head_batch_64_every_fast_path(cuda):
+    """The benchmark's own configuration, one layer deep: 64 requests decoded as one batch through a 1B-shaped layer
+    (hidden 2048, 32 q / 8 kv heads, FFN 8192), the final RMSNorm and the lm_head (vocab 128256), fed token ids.  At
+    this batch the MatMuls run on the tensor-core kernel (weights marked static, dependent launch), q|k|v and gate|up
+    run merged, the split-K sum and the residual Add run inside RMSNorm and the KV cache is appended in place -
+    everything the timed run uses.  A short prefill and two decode steps are compared with the float64 CPU
+    interpreter (logits and the carried cache: rel 1e-4 of the scale, identical arg-max, the bar of
+    runtime/tests/e2e_ort/llama.rs:112-156); then the same run with each runtime shortcut switched off must agree
+    with the all-on run to 1e-5."""
+    from rmlk_b200.runtime import ModelInstance
+    cfg = llama.LlamaConfig(n_layers=1)
+    B, S0 = 64, 3
+    w = llama.make_weights_host(cfg, seed=5)
+    spec = llama.build_graph(cfg, w)
+    rng = np.random.default_rng(11)
+    ids = rng.integers(0, cfg.vocab, size=(B, S0 + 2))
+    steps = [(0, S0), (S0, S0 + 1), (S0 + 1, S0 + 2)]
+
+    def feeds(s0, s1):
+        return {"input_ids": ids[:, s0:s1], "attention_mask": np.ones((B, s1), np.int64),
+                "position_ids": np.broadcast_to(np.arange(s0, s1, dtype=np.int64), (B, s1 - s0)).copy()}
+
+    # float64 CPU interpreter, step by step with its own cache
+    empty = np.zeros((B, cfg.n_kv_heads, 0, cfg.head_dim), np.float32)
+    past = (empty, empty)
+    want = []
+    for s0, s1 in steps:
+        f = feeds(s0, s1)
+        f["past_key_values.0.key"], f["past_key_values.0.value"] = past
+        out = graph_cpu.run_graph(spec, f)
+        past = (out["present.0.key"], out["present.0.value"])
+        want.append((out["logits"], past[0], past[1]))
+
+    def drive(env):
+        os.environ.update(env)
+        try:
+            inst = ModelInstance(spec.to_runtime())
+            inst.bind("present.0.key", "past_key_values.0.key")
+            inst.bind("present.0.value", "past_key_values.0.value")
+        finally:
+            for k in env:
+                os.environ.pop(k, None)
+        got = []
+        for i, (s0, s1) in enumerate(steps):
+            for k, v in feeds(s0, s1).items():
+                inst.set_input(k, v)
+            if i == 0:
+                inst.set_input("past_key_values.0.key", empty)
+                inst.set_input("past_key_values.0.value", empty)
+            inst.launch()
+            got.append((inst.read("logits"), inst.read("present.0.key"), inst.read("present.0.value")))
+            assert inst.last_syncs == 0
+        return got, inst.last_launches
+
+    fast, fast_launches = drive({})
+    for (gl, gk, gv), (wl, wk, wv) in zip(fast, want):
+        assert gl.shape == wl.shape
+        assert np.max(np.abs(gl - wl)) <= 1e-4 * np.max(np.abs(wl))
+        assert np.array_equal(gl[:, -1].argmax(-1), wl[:, -1].argmax(-1))
+        assert np.max(np.abs(gk - wk)) <= 1e-4 * np.max(np.abs(wk))
+        assert np.max(np.abs(gv - wv)) <= 1e-4 * np.max(np.abs(wv))
+    for switch in ("RMLK_B200_NO_FUSION", "RMLK_B200_NO_MATMUL_MERGE", "RMLK_B200_NO_ADD_NORM", "RMLK_B200_NO_INPLACE_APPEND",
+                   "RMLK_B200_NO_APPEND_TO"):
+        slow, slow_launches = drive({switch: "1"})
+        assert slow_launches >= fast_launches, switch
+        for (gl, gk, gv), (sl, sk, sv) in zip(fast, slow):
+            assert np.max(np.abs(gl - sl)) <= 1e-5 * np.max(np.abs(sl)), switch
+            assert np.max(np.abs(gk - sk)) <= 1e-5 * np.max(np.abs(sk)), switch
+            assert np.max(np.abs(gv - sv)) <= 1e-5 * np.max(np.abs(sv)), switch
