@@ -164,21 +164,25 @@ def cpu_decode_sample(cfg, batch, context, steps, seed=0):
     return batch * len(times) / total, threads, f"{batch} requests x {len(times)} decode steps at context {context}, synthetic KV cache, numpy oracle interpreter"
 
 
+CPU_SAMPLE_STEPS = 2
+
+
 def run_reference(args):
     """--impl reference: the reference has no CPU build of its own for this path (Rust + CUDA only), so
-    the CPU arm is the numpy restatement of its op semantics (oracle/), on all host cores."""
+    the CPU arm is the numpy restatement of its op semantics (oracle/), on all host cores.  It runs the arm's own
+    configuration - the same 64 requests as one batch at context 512 - for a bounded number of decode steps."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from rmlk_b200 import llama
     cfg = llama.LLAMA_1B
-    batch = 8
-    steps = max(1, min(args.steps, 4))
-    v, threads, sample = cpu_decode_sample(cfg, batch, PROMPT, steps)
+    batch = args.requests
+    steps = max(1, min(args.steps, CPU_SAMPLE_STEPS))
+    v, threads, sample = cpu_decode_sample(cfg, batch, args.prompt, steps)
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": 1,
         "ms_per_step": 1000.0 * batch / v, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": workload_config(cfg, REQUESTS_PER_GPU, PROMPT),
+        "data": "synthetic", "config": dict(workload_config(cfg, batch, args.prompt), requests_run=batch, steps_run=steps),
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -213,10 +217,11 @@ def time_graph(fn_of_i, n=16, replays=4):
     return e0.elapsed_time(e1) / (n * replays)
 
 
-# ncu dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernel named by DOMINANT, from the
-# capture summarised under profiles/ (None until a capture of that kernel exists).
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the kernel named by DOMINANT, from one ncu capture of that
+# kernel on this shape (a cross-check of the algorithmic bytes, not a live measurement: it goes stale when the kernel changes)
 DOMINANT = "matmul_gate_up"
-NCU_TRAFFIC_BYTES = {"matmul_gate_up": 134_809_600 + 3_740_416}   # profiles/tc_gemm_kernel_ffn_m64.md
+NCU_TRAFFIC_BYTES = {"matmul_gate_up": 134_809_600 + 3_740_416}
+NCU_TRAFFIC_SOURCE = "ncu --set full capture of tc_gemm_kernel on [64,2048]x[2048,16384] (read 134.81 MB + write 3.74 MB per launch)"
 
 
 def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):
@@ -235,7 +240,7 @@ def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):
         ms = time_graph(fn)
         ach = algo_bytes / (ms * 1e-3) / 1e9
         e = {"bound": "hbm", "achieved": ach, "peak": peak_gbs, "unit": "GB/s", "frac": ach / peak_gbs,
-             "traffic": NCU_TRAFFIC_BYTES.get(name), "kernel": kernel, "shape": shape,
+             "traffic": NCU_TRAFFIC_BYTES.get(name), "traffic_source": NCU_TRAFFIC_SOURCE if name in NCU_TRAFFIC_BYTES else None, "kernel": kernel, "shape": shape,
              "algorithmic_bytes_per_launch": algo_bytes, "us_per_launch": ms * 1e3, "peak_kind": f"of {peak_kind} copy bandwidth"}
         if flops:
             e["tflops"] = flops / (ms * 1e-3) / 1e12
@@ -253,12 +258,6 @@ def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):
     add("context", "nn_narrow_kernel<4,16>", lambda i: K.matmul(p, kc[i % len(kc)], out=cx), 4 * B * 8 * (4 * T + 64 * T + 4 * 64),
         [B * 8, 4, T, 64], flops=2 * B * 32 * 64 * T)
     del kc, q, sc, p, cx
-    # KV append Concat: [B, 8, T-1, 64] + [B, 8, 1, 64] along axis 2
-    past = ring(lambda: torch.randn(B, 8, T - 1, 64, device=dev), 4 * B * 8 * T * 64)
-    new = torch.randn(B, 8, 1, 64, device=dev)
-    dst = torch.empty(B, 8, T, 64, device=dev)
-    add("concat_kv", "concat_kernel", lambda i: K.concat([past[i % len(past)], new], 2, out=dst), 8 * B * 8 * T * 64, [B, 8, T, 64])
-    del past, dst
     # weight-streaming MatMul at the FFN gate/up shape and at the lm_head
     # gate | up projections as the runtime runs them (one MatMul on the concatenated weights), the down projection, the lm_head
     for name, (m, k, n) in (("matmul_gate_up", (B, 2048, 16384)), ("matmul_qkv", (B, 2048, 3072)), ("matmul_down", (B, 8192, 2048)),
@@ -290,7 +289,7 @@ def run_ours(args):
 
     cfg = llama.LLAMA_1B
     B, P = args.requests, args.prompt
-    K_, W = args.steps, args.warmup
+    K_, W, R = args.steps, args.warmup, max(1, args.rounds)
     stream = torch.cuda.Stream()
     with torch.cuda.stream(stream):
         weights = llama.make_weights_device(cfg, seed=0)
@@ -299,58 +298,6 @@ def run_ours(args):
     dec = llama.Decoder(cfg, spec, device=local, stream=stream.cuda_stream, arena_bytes=(2 << 30))
     inst = dec.inst
     rng = np.random.default_rng(1234 + rank)
-
-    # ---- prefill (untimed set-up): all requests, full prompts -------------------------------------
-    dec.reset(B)
-    prompt_ids = rng.integers(0, cfg.vocab, size=(B, P))
-    dec.feed(prompt_ids)
-    inst.launch()
-    inst.synchronize()
-    prefill_launches = inst.last_launches
-
-    total_steps = 2 * (W + K_)
-    ids_all = torch.from_numpy(rng.integers(0, cfg.vocab, size=(total_steps, B, 1))).pin_memory()
-    ids_dev = ids_all.to("cuda", non_blocking=True)
-    torch.cuda.synchronize()
-    mask_dev = torch.ones(B, P + total_steps + 1, dtype=torch.int64, device="cuda")
-    mask_host = torch.ones(B, P + total_steps + 1, dtype=torch.int64).pin_memory()
-    pos_host = torch.empty(B, 1, dtype=torch.int64).pin_memory()
-    logits_host = torch.empty(B, 1, cfg.vocab, dtype=torch.float32).pin_memory()
-
-    step_no = {"n": 0}
-
-    # inputs of the device-resident phase are built in HBM before the clock starts
-    dev_masks = [torch.ones(B, P + s + 1, dtype=torch.int64, device="cuda") for s in range(W + K_)]
-    dev_pos = [torch.full((B, 1), P + s, dtype=torch.int64, device="cuda") for s in range(W + K_)]
-    del mask_dev
-    torch.cuda.synchronize()
-
-    def device_step():
-        s = step_no["n"]
-        t = dec.context + 1
-        ids, mask, pos = ids_dev[s], dev_masks[s], dev_pos[s]
-        assert mask.shape[1] == t
-        inst.set_input_ptr("input_ids", dt.I64, [B, 1], ids.data_ptr(), True)
-        inst.set_input_ptr("attention_mask", dt.I64, [B, t], mask.data_ptr(), True)
-        inst.set_input_ptr("position_ids", dt.I64, [B, 1], pos.data_ptr(), True)
-        inst.launch()
-        dec.context = t
-        step_no["n"] += 1
-        return (ids, mask, pos)
-
-    def host_step():
-        s = step_no["n"]
-        t = dec.context + 1
-        pos_host.fill_(dec.context)
-        mask_view = mask_host.view(-1)[: B * t].view(B, t)   # contiguous [B, t] of ones in pinned memory
-        inst.set_input_ptr("input_ids", dt.I64, [B, 1], ids_all[s].data_ptr(), False)
-        inst.set_input_ptr("attention_mask", dt.I64, [B, t], mask_view.data_ptr(), False)
-        inst.set_input_ptr("position_ids", dt.I64, [B, 1], pos_host.data_ptr(), False)
-        inst.launch()
-        inst.wait_outputs()   # the logits were registered with stream_output: they arrive block by block behind the lm_head MatMul
-        dec.context = t
-        step_no["n"] += 1
-        return B * 8 + B * t * 8 + B * 8
 
     def barrier():
         if world > 1:
@@ -364,55 +311,173 @@ def run_ours(args):
             return float(t.item())
         return ms
 
-    # ---- device-resident timing -----------------------------------------------------------------
+    class Workload:
+        """`batch` requests with `P`-token prompts: prefill (untimed set-up), then decode steps fed from device-resident or
+        pinned host inputs.  restore() brings the context back to the end of the prompt, so that every timed round covers
+        the same context lengths."""
+
+        def __init__(self, batch, n_steps):
+            self.batch, self.n_steps = batch, n_steps
+            self.prompt_ids = rng.integers(0, cfg.vocab, size=(batch, P))
+            self.ids_host = torch.from_numpy(rng.integers(0, cfg.vocab, size=(n_steps, batch, 1))).pin_memory()
+            self.ids_dev = self.ids_host.to("cuda", non_blocking=True)
+            self.masks_dev = [torch.ones(batch, P + s + 1, dtype=torch.int64, device="cuda") for s in range(n_steps)]
+            self.pos_dev = [torch.full((batch, 1), P + s, dtype=torch.int64, device="cuda") for s in range(n_steps)]
+            self.mask_host = torch.ones(batch, P + n_steps + 1, dtype=torch.int64).pin_memory()
+            self.pos_host = torch.empty(batch, 1, dtype=torch.int64).pin_memory()
+            self.step_no = 0
+            self.prefill_launches = 0
+            self.saved = None
+            torch.cuda.synchronize()
+
+        def prefill(self):
+            """The prompt through the graph (untimed set-up); the caches it leaves are kept on the host so that restore()
+            can bring the context back without running the prefill again (a prefill is seconds of tensor-core work that
+            would leave the GPU power-capped for the timed steps behind it)."""
+            dec.reset(self.batch)
+            dec.feed(self.prompt_ids)
+            inst.launch()
+            inst.synchronize()
+            self.prefill_launches = inst.last_launches
+            self.saved = [(inst.read(f"present.{l}.key"), inst.read(f"present.{l}.value")) for l in range(cfg.n_layers)]
+            self.step_no = 0
+
+        def restore(self):
+            if self.saved is None:
+                return self.prefill()
+            for l, (k, v) in enumerate(self.saved):
+                inst.set_input(f"past_key_values.{l}.key", k)
+                inst.set_input(f"past_key_values.{l}.value", v)
+            dec.context = P
+            self.step_no = 0
+            inst.synchronize()
+
+        def device_step(self):
+            s, b = self.step_no, self.batch
+            t = dec.context + 1
+            inst.set_input_ptr("input_ids", dt.I64, [b, 1], self.ids_dev[s].data_ptr(), True)
+            inst.set_input_ptr("attention_mask", dt.I64, [b, t], self.masks_dev[s].data_ptr(), True)
+            inst.set_input_ptr("position_ids", dt.I64, [b, 1], self.pos_dev[s].data_ptr(), True)
+            inst.launch()
+            dec.context = t
+            self.step_no += 1
+
+        def host_step(self):
+            s, b = self.step_no, self.batch
+            t = dec.context + 1
+            self.pos_host.fill_(dec.context)
+            mask_view = self.mask_host.view(-1)[: b * t].view(b, t)   # contiguous [b, t] of ones in pinned memory
+            inst.set_input_ptr("input_ids", dt.I64, [b, 1], self.ids_host[s].data_ptr(), False)
+            inst.set_input_ptr("attention_mask", dt.I64, [b, t], mask_view.data_ptr(), False)
+            inst.set_input_ptr("position_ids", dt.I64, [b, 1], self.pos_host.data_ptr(), False)
+            inst.launch()
+            inst.wait_outputs()   # the logits were registered with stream_output: they arrive block by block behind the lm_head MatMul
+            dec.context = t
+            self.step_no += 1
+            return b * 8 + b * t * 8 + b * 8
+
+        def timed_rounds(self, step_fn, rounds, windows, after_restore=None, before_restore=None):
+            """`rounds` times: restore the context, W warm-up steps, then EXACTLY K steps between two events on the launching
+            stream, with a barrier + device synchronise on both sides; per round the maximum over ranks.  Returns the
+            per-round milliseconds, per-round host enqueue milliseconds and the kernel launches of one round."""
+            ms, host_ms, launches = [], [], 0
+            for _ in range(rounds):
+                if before_restore:
+                    before_restore()
+                self.restore()
+                if after_restore:
+                    after_restore()
+                for _ in range(W):
+                    step_fn()
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                launches = 0
+                win0 = time.time()
+                e0.record(stream)
+                h0 = time.perf_counter()
+                for _ in range(K_):
+                    step_fn()
+                    launches += inst.last_launches
+                h1 = time.perf_counter()
+                e1.record(stream)
+                barrier()
+                wall = (time.perf_counter() - h0) * 1000.0
+                windows.append((win0, time.time()))
+                # a step that waits for its outputs on the host (end to end) is bounded by the wall clock as well
+                dev = e0.elapsed_time(e1)
+                ms.append(max_over_ranks(max(dev, wall) if step_fn == self.host_step else dev))
+                host_ms.append((h1 - h0) * 1000.0)
+            return ms, host_ms, launches
+
+    wl = Workload(B, W + K_ + 6)
     with torch.cuda.stream(stream):
-        # the clock sampler starts before the warm-up (nvidia-smi takes a moment to come up); only samples that
-        # fall inside the two timed regions are kept
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
         windows = []
-        keep = []
-        for _ in range(W):
-            keep.append(device_step())
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        launches = 0
-        win0 = time.time()
-        e0.record(stream)
-        host0 = time.perf_counter()
-        for _ in range(K_):
-            keep.append(device_step())
-            launches += inst.last_launches
-        host_enqueue_ms = (time.perf_counter() - host0) * 1000.0   # host time to enqueue the K steps (no waiting on the GPU)
-        e1.record(stream)
-        barrier()
-        windows.append((win0, time.time()))
-        dev_ms = max_over_ranks(e0.elapsed_time(e1))
+
+        # ---- device-resident timing ---------------------------------------------------------------
+        dev_rounds, host_rounds, launches = wl.timed_rounds(wl.device_step, R, windows)
         decode_launches = inst.last_launches
+        prefill_launches = wl.prefill_launches
+        # host cost of enqueuing one step, measured from an empty stream (inside the rounds above the host runs ahead of the
+        # GPU until the launch queue is full and then waits for it, so the loop's wall time only shows the device time)
+        host_one = []
+        for _ in range(5):
+            inst.synchronize()
+            h0 = time.perf_counter()
+            wl.device_step()
+            host_one.append((time.perf_counter() - h0) * 1000.0)
         inst.synchronize()
-        keep.clear()
 
         # ---- end to end: host buffers in, logits out, every step --------------------------------
-        inst.stream_output("logits", logits_host.data_ptr(), logits_host.numel() * 4)
-        for _ in range(W):
-            host_step()
-        barrier()
-        h2d = 0
-        t0 = torch.cuda.Event(enable_timing=True)
-        t1 = torch.cuda.Event(enable_timing=True)
-        win0 = time.time()
-        t0.record(stream)
-        wall0 = time.perf_counter()
-        for _ in range(K_):
-            h2d = host_step()
-        t1.record(stream)
-        barrier()
-        wall_ms = (time.perf_counter() - wall0) * 1000.0
-        windows.append((win0, time.time()))
+        logits_host = torch.empty(B, 1, cfg.vocab, dtype=torch.float32).pin_memory()
+        h2d = B * 8 + B * (P + W + K_) * 8 + B * 8   # ids + attention mask at the longest context + positions
+        # the logits of a decode step stream to pinned host memory; the registration is lifted around the prefill of restore(),
+        # whose logits have another shape and are not read
+        e2e_rounds, _, _ = wl.timed_rounds(wl.host_step, max(1, (R + 1) // 2), windows,
+                                           after_restore=lambda: inst.stream_output("logits", logits_host.data_ptr(), logits_host.numel() * 4),
+                                           before_restore=lambda: inst.stream_output("logits", 0, 0))
+        inst.stream_output("logits", 0, 0)
         clocks = sampler.stop(windows) if rank == 0 else {}
-        e2e_ms = max_over_ranks(max(t0.elapsed_time(t1), wall_ms))
 
+        # ---- other operating points (same model, same code path), reported beside the headline -------------
+        extra = {}
+        if not args.no_extras:
+            def side_run(batch):
+                w2 = Workload(batch, W + K_)
+                ms, _, _ = w2.timed_rounds(w2.device_step, 1, [])
+                return ms[0]
+            if world > 1 and B % world == 0:
+                # the same 64 requests in total, split over the GPUs (per-GPU batch shrinks, the weight stream does not)
+                ms = side_run(B // world)
+                extra["strong_64_total"] = {"value": B * K_ / (ms * 1e-3), "unit": UNIT, "requests_per_gpu": B // world, "ms_per_step": ms / K_,
+                                            "scaling": "strong"}
+            if world == 1:
+                ms = side_run(1)
+                floor_ms = (cfg.params * 4 + cfg.kv_bytes_per_token() * (P + W + K_ // 2)) / (measured_peaks()[0] * 1e9) * 1e3
+                extra["decode_batch1"] = {"value": K_ / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms / K_, "hbm_floor_ms_per_step": floor_ms,
+                                          "frac_of_hbm_floor": floor_ms / (ms / K_)}
+
+    # ---- self-check (untimed; run after every timed region because the float64 decoder is seconds of heavy work): the logits
+    # of the first decode step after the prompt, computed by the very path that was timed above, against a dense float64
+    # restatement of the decoder in torch for the first requests of the batch
+    selfcheck = None
+    if rank == 0 and not args.no_selfcheck:
+        wl.restore()
+        wl.device_step()
+        got = torch.from_numpy(inst.read("logits")).to("cuda")[:, 0]      # [B, vocab]
+        nchk = min(2, B)
+        seq = torch.from_numpy(np.concatenate([wl.prompt_ids[:nchk], wl.ids_host[0, :nchk].numpy()], axis=1)).to("cuda")
+        want = llama.dense_decoder_f64(cfg, weights, seq)
+        err = float((got[:nchk].double() - want).abs().max() / want.abs().max())
+        same = bool(torch.equal(got[:nchk].argmax(-1), want.argmax(-1)))
+        selfcheck = {"rel_err": err, "argmax_equal": same, "requests_checked": nchk, "against": "dense float64 decoder (torch) over the 513 tokens"}
+        del got, want, seq
+        torch.cuda.empty_cache()
+
+    dev_ms = statistics.median(dev_rounds)
+    e2e_ms = statistics.median(e2e_rounds)
     value = world * B * K_ / (dev_ms * 1e-3)
     e2e_value = world * B * K_ / (e2e_ms * 1e-3)
     if rank != 0:
@@ -429,16 +494,17 @@ def run_ours(args):
         roof["other_kernels"] = {k: {"kernel": v["kernel"], "achieved": v["achieved"], "frac": v["frac"], "us_per_launch": v["us_per_launch"]}
                                  for k, v in per_kernel.items() if k != DOMINANT}
     roof["peak_source"] = peak_kind
-    # whole-step view: algorithmic bytes of one decode step (weights once + KV cache read and rewritten) / step time
+    # whole-step view: algorithmic bytes of one decode step = the weights once + the KV cache read once + the appended rows
+    # (the runtime appends to the cache in place; nothing of the old cache is rewritten)
     ctx_mid = P + W + K_ // 2
-    step_bytes = cfg.params * 4 + 2 * B * cfg.kv_bytes_per_token() * ctx_mid
+    step_bytes = cfg.params * 4 + B * cfg.kv_bytes_per_token() * (ctx_mid + 1)
     roof["step_algorithmic_bytes"] = step_bytes
     roof["step_achieved_gbs"] = step_bytes / (dev_ms / K_ * 1e-3) / 1e9
     roof["step_frac"] = roof["step_achieved_gbs"] / peak
 
     cpu = None
     if world == 1 and not args.no_cpu_baseline:
-        v, threads, sample = cpu_decode_sample(cfg, 8, P, 2)
+        v, threads, sample = cpu_decode_sample(cfg, B, P, CPU_SAMPLE_STEPS)
         cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample}
 
     line = {
@@ -447,9 +513,13 @@ def run_ours(args):
         "config": workload_config(cfg, B, P),
         "roofline": roof, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * cfg.vocab * 4,
-                "ms_per_step": e2e_ms / K_},
+                "ms_per_step": e2e_ms / K_, "rounds_ms_per_step": [m / K_ for m in e2e_rounds]},
         "gpu_launches": launches, "launches_per_decode_step": decode_launches, "prefill_launches": prefill_launches,
-        "host_enqueue_ms_per_step": host_enqueue_ms / K_, "clocks": clocks, "context_range": [P + W, P + W + K_], "arena_peak_bytes": inst.arena_peak,
+        "timed_rounds": {"rounds": R, "each": f"{W} warm-up + {K_} timed steps from the end of the prompt", "reported": "median round",
+                         "ms_per_step": [m / K_ for m in dev_rounds]},
+        "host_enqueue_ms_per_step": statistics.median(host_one), "host_loop_ms_per_step": statistics.median(host_rounds) / K_, "selfcheck": selfcheck,
+        "selfcheck_rel_err": selfcheck["rel_err"] if selfcheck else None, "extra": extra,
+        "clocks": clocks, "context_range": [P + W, P + W + K_], "arena_peak_bytes": inst.arena_peak,
     }
     print(json.dumps(line))
     if world > 1:
@@ -464,7 +534,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--requests", type=int, default=REQUESTS_PER_GPU)
     ap.add_argument("--prompt", type=int, default=PROMPT)
+    ap.add_argument("--rounds", type=int, default=5, help="timed rounds of --steps steps each (the median round is reported)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-selfcheck", action="store_true")
+    ap.add_argument("--no-extras", action="store_true")
     ap.add_argument("--skip-kernel-roofline", action="store_true", help="leave out the per-kernel timing (launch-list profiling runs)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -271,6 +271,53 @@ def build_graph(cfg: LlamaConfig, weights: dict, device_weights: bool = False, w
     return g
 
 
+def dense_decoder_f64(cfg: LlamaConfig, weights: dict, ids, last_only: bool = True):
+    """The decoder written densely in float64 with torch on the weights' device: ids [B,T] -> logits of the last position
+    [B,vocab] (or of all positions).  No cache, no op graph, none of this library's kernels: an independent statement of
+    what build_graph's op list computes, used by the benchmark to check the logits of the very configuration it times."""
+    import torch
+    B, T = ids.shape
+    f64 = torch.float64
+
+    def W(name):
+        return weights[name].to(f64)
+
+    x = W("embed")[ids]
+    half = cfg.head_dim // 2
+    dev = x.device
+    inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=dev, dtype=f64) / cfg.head_dim))
+    ang = torch.arange(T, device=dev, dtype=f64)[:, None] * inv[None, :]
+    cos = torch.cos(torch.cat([ang, ang], -1))[None, None]
+    sin = torch.sin(torch.cat([ang, ang], -1))[None, None]
+
+    def norm(v, g):
+        return v / torch.sqrt((v * v).mean(-1, keepdim=True) + cfg.rms_eps) * g
+
+    def rope(v):
+        return v * cos + torch.cat([-v[..., half:], v[..., :half]], -1) * sin
+
+    pos = torch.arange(T, device=dev)
+    mask = torch.where(pos[None, :] > pos[:, None], float("-inf"), 0.0).to(f64)
+    rep = cfg.n_heads // cfg.n_kv_heads
+    for l in range(cfg.n_layers):
+        h = norm(x, W(f"l{l}.ln1"))
+        q = (h @ W(f"l{l}.wq")).reshape(B, T, cfg.n_heads, cfg.head_dim).transpose(1, 2)
+        k = (h @ W(f"l{l}.wk")).reshape(B, T, cfg.n_kv_heads, cfg.head_dim).transpose(1, 2)
+        v = (h @ W(f"l{l}.wv")).reshape(B, T, cfg.n_kv_heads, cfg.head_dim).transpose(1, 2)
+        q, k = rope(q), rope(k)
+        k = k.repeat_interleave(rep, dim=1)
+        v = v.repeat_interleave(rep, dim=1)
+        p = torch.softmax(q @ k.transpose(2, 3) / (cfg.head_dim ** 0.5) + mask, -1)
+        o = (p @ v).transpose(1, 2).reshape(B, T, cfg.hidden)
+        x = x + o @ W(f"l{l}.wo")
+        h2 = norm(x, W(f"l{l}.ln2"))
+        g = h2 @ W(f"l{l}.wgate")
+        x = x + ((g * torch.sigmoid(g)) * (h2 @ W(f"l{l}.wup"))) @ W(f"l{l}.wdown")
+    if last_only:
+        x = x[:, -1]
+    return norm(x, W("ln_f")) @ W("lm_head")
+
+
 class Decoder:
     """Greedy-decode driver around a ModelInstance, shaped like the reference's harness loop
     (runtime/examples/llama.rs:65-161): feed ids / mask / positions, run, read logits; the KV cache is

@@ -576,14 +576,17 @@ def test_matmul_tensor_core_3xtf32(case):
     got = run(None)
     assert int(status.item()) == 0, "a bounded wait expired"
     err = float((got.double() - want).abs().max()) / scale
-    assert err <= 5e-5, (case, err)  # measured about 1e-5; the bar is 1e-4
+    # The bar is 1e-4.  The tensor core adds into its fp32 accumulator with truncation, so the error grows with the number
+    # of k-steps accumulated in one tile: about 1e-5 at K = 2048, 4e-5 at 8192, 7e-5 at 14336 (cuBLAS fp32: 5e-6 there).
+    tol = 5e-5 if k <= 8192 else 1e-4
+    assert err <= tol, (case, err)
     wsb = K.matmul_workspace_bytes(1, m, n, k)
     if wsb:
         ws = torch.empty(wsb // 4, device="cuda")
         g2 = run(ws)
         g3 = run(ws)
         assert int(status.item()) == 0
-        assert float((g2.double() - want).abs().max()) / scale <= 5e-5
+        assert float((g2.double() - want).abs().max()) / scale <= tol
         assert torch.equal(g2, g3)
     # exact on small integers: hi/lo split must not lose anything when the products are exactly representable
     ai = torch.randint(-8, 9, (m, k), device="cuda").float()
