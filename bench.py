@@ -453,6 +453,15 @@ def run_ours(args):
                 ms = side_run(B // world)
                 extra["strong_64_total"] = {"value": B * K_ / (ms * 1e-3), "unit": UNIT, "requests_per_gpu": B // world, "ms_per_step": ms / K_,
                                             "scaling": "strong"}
+            if world > 1:
+                # the one workload with a real exchange step: the 8B-shaped MatMuls split by columns over the GPUs, each rank's block of
+                # columns stored into every rank's output over NVLink by the MatMul kernel itself, beside NCCL all-gather and one GPU
+                try:
+                    from rmlk_b200 import tpbench
+                    torch.cuda.synchronize()
+                    extra["tp_matmul"] = tpbench.sweep(world, rank, iters=10)
+                except Exception as e:  # reported, not fatal: the headline does not depend on it
+                    extra["tp_matmul_error"] = repr(e)[:300]
             if world == 1:
                 ms = side_run(1)
                 floor_ms = (cfg.params * 4 + cfg.kv_bytes_per_token() * (P + W + K_ // 2)) / (measured_peaks()[0] * 1e9) * 1e3

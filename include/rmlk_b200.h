@@ -302,8 +302,8 @@ RMLK_API int rmlk_b200_matmul_nt(rmlk_stream_t stream, int dtype, int64_t batch,
  * scratch that rmlk_b200_matmul takes as `workspace` lives in a fixed array inside the library:
  * rmlk_b200_matmul_static_scratch_bytes() bytes (8 MiB) of device memory on every GPU that loads the
  * library, held until the process exits.  Same arguments and results as rmlk_b200_matmul_ex otherwise.
- *  - Shapes whose scratch need (rmlk_b200_matmul_workspace_bytes) exceeds the array are rejected with
- *    RMLK_ERR_INVALID_ARG; nothing is launched.
+ *  - Shapes whose least scratch need exceeds the array are rejected with RMLK_ERR_INVALID_ARG; nothing is launched
+ *    (rmlk_b200_matmul_static_supported answers beforehand).
  *  - The first call on each device looks up the array's device address and, like the first call of any
  *    MatMul here, configures the kernels it launches (cudaFuncSetAttribute, cudaGetDriverEntryPoint); make that
  *    first call outside any stream capture and before other threads call in.  No call allocates or frees
@@ -315,7 +315,55 @@ RMLK_API int rmlk_b200_matmul_static(rmlk_stream_t stream, int dtype, int64_t ba
                             const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
                             int64_t c_batch_stride, int* status);
 RMLK_API size_t rmlk_b200_matmul_static_scratch_bytes(void);
+/* 1 if rmlk_b200_matmul_static takes the shape (its least scratch need fits the built-in array), 0 if it would be rejected. */
+RMLK_API int rmlk_b200_matmul_static_supported(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k);
 RMLK_API size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k);
+/* How the persistent tensor-core MatMul kernel (M >= 5, N % 128 == 0, K % 32 == 0) divides a shape over the SMs; pure
+ * host arithmetic, for inspection and tests (no counterpart in the reference: cuBLAS plans internally).  The work is the
+ * sequence of the k-blocks (32 of K) of all [rows x 128] tiles of C; CTA c of `ctas` takes units
+ * [units * c / ctas, units * (c + 1) / ctas), a unit being `k-blocks per unit` consecutive k-blocks.
+ * out[0..7] = rows per tile, k-blocks per tile, row tiles per column block, k-blocks per unit (1: a CTA's range may
+ * start and end inside a tile, whose partial sums then meet in the scratch buffer; k-blocks per tile: whole tiles only),
+ * ctas, tiles, units, scratch bytes needed (0 when no tile is shared). */
+RMLK_API int rmlk_b200_matmul_schedule(int64_t m, int64_t n, int64_t k, int64_t* out);
+
+/* y[m, n] = alpha * y + beta * c, in place, c read through element strides (0 broadcasts a dimension; c = NULL: y = alpha * y).
+ * The epilogue of ONNX Gemm after the MatMul: replaces the reference's alpha inside the cuBLAS call
+ * (runtime/src/providers/cuda/backend/gemm.rs:181-191) and its add_alpha_beta_inplace kernel for the bias
+ * (backend/gemm.rs:42-91, cuda/src/kernels/binary.rs compute_alpha_beta_inplace).  dtype f32 or f16 (arithmetic in fp32). */
+RMLK_API int rmlk_b200_scale_add_bias(rmlk_stream_t stream, int dtype, int64_t m, int64_t n, void* y, float alpha, const void* c,
+                             int64_t c_row_stride, int64_t c_col_stride, float beta);
+
+/* ---- column-split MatMul across the GPUs of one NVLink domain ------------------------------------------------------
+ * Y[m, n_total] = X[m, k] x W[k, n_total] with W split by columns over `world` ranks (one process per GPU).  The
+ * reference has no multi-GPU path (runtime/src/core/plan.rs:4-28 is a placeholder); where it would gather shard results
+ * with a collective after cublasGemmStridedBatchedEx (cuda/src/kernels/gemm.rs:206-231), this entry point has the rank
+ * that computes a block of columns store it into EVERY rank's output buffer from the MatMul kernel's epilogue (ordinary
+ * stores through peer mappings, over NVLink) and then raise a flag on every rank.
+ *
+ * Set-up (the caller's, once): every rank allocates an output buffer [m_max, n_total] floats and a flag array of
+ * `world` 32-bit words (zero-filled), makes both reachable from the other ranks (CUDA IPC or a symmetric-memory
+ * allocator) and fills rmlk_tp_peers with the addresses as seen from ITS OWN process: out[r] / flags[r] = rank r's
+ * buffers, r = 0..world-1 (out[rank] / flags[rank] are the local ones).
+ * A call: rmlk_b200_matmul_tp computes this rank's columns [col0, col0 + n_shard) from its shard w_shard[k, n_shard]
+ * (dense) and a[m, k] (the same on every rank), stores them into all `world` outputs and sets word `rank` of every
+ * flag array to `epoch`.  rmlk_b200_tp_wait then makes the stream wait until all words of the LOCAL flag array have
+ * reached `epoch`: what follows on the stream sees the complete Y.  The wait is bounded (a second or two): if a rank
+ * never arrives, RMLK_ERR_TIMEOUT is stored in *status (device word, may be NULL) and the stream goes on.
+ * Epochs must grow by one per call (all ranks alike).  A rank may be a call ahead of another, so the caller alternates
+ * between two output buffers (even / odd epochs); with that, stream order on every rank makes reuse safe.
+ * dtype f32; n_shard, col0 and n_total multiples of 4.  `workspace`: rmlk_b200_matmul_tp_workspace_bytes() bytes. */
+#define RMLK_TP_MAX_WORLD 8
+typedef struct rmlk_tp_peers {
+    int world, rank;
+    void* out[RMLK_TP_MAX_WORLD];
+    void* flags[RMLK_TP_MAX_WORLD];
+} rmlk_tp_peers;
+RMLK_API size_t rmlk_b200_matmul_tp_workspace_bytes(int dtype, int64_t m, int64_t n_shard, int64_t k);
+RMLK_API int rmlk_b200_matmul_tp(rmlk_stream_t stream, int dtype, int64_t m, int64_t n_shard, int64_t k, const void* a, const void* w_shard,
+                        int64_t n_total, int64_t col0, const rmlk_tp_peers* peers, unsigned int epoch, void* workspace,
+                        size_t workspace_bytes, int* status);
+RMLK_API int rmlk_b200_tp_wait(rmlk_stream_t stream, const void* local_flags, int world, unsigned int epoch, int* status);
 
 /* ---- op chains as one launch ----------------------------------------------------------------------------------
  * The reference has no fused ops: an exported decoder graph reaches it as single ops, each dispatched to its own

@@ -238,6 +238,36 @@ def matmul(a: np.ndarray, b: np.ndarray) -> np.ndarray:
     return r.reshape(tuple(lead) + (am.shape[1], bm.shape[2]))
 
 
+def gemm(a: np.ndarray, b: np.ndarray, c=None, alpha: float = 1.0, beta: float = 1.0, trans_a: bool = False, trans_b: bool = False) -> np.ndarray:
+    """ONNX Gemm as the reference's backend computes it (runtime/src/providers/cuda/backend/gemm.rs:149-216): rank-2 A and B, a
+    logical transpose per flag (cuda/src/kernels/gemm.rs:21-72), alpha inside the GEMM, then y += beta * C with C broadcast
+    to [M, N] (a vector of N entries is a row, one of M entries a column, backend/gemm.rs:225-227).  Evaluated in double.
+    (The reference's 2-D bias strides, backend/gemm.rs:228-238, use the extents themselves as strides; the ONNX broadcast
+    is restated here.)"""
+    if a.ndim != 2 or b.ndim != 2:
+        raise ValueError("expected inputs with rank 2")
+    am = a.T if trans_a else a
+    bm = b.T if trans_b else b
+    if am.shape[1] != bm.shape[0]:
+        raise ValueError("IncompatibleDimForMul")
+    m, n = am.shape[0], bm.shape[1]
+    y = np.float64(alpha) * np.matmul(am.astype(np.float64), bm.astype(np.float64))
+    if c is not None:
+        cc = np.asarray(c, dtype=np.float64)
+        if cc.ndim == 1 and cc.shape[0] == n:
+            cc = cc.reshape(1, n)
+        elif cc.ndim == 1 and cc.shape[0] == m:
+            cc = cc.reshape(m, 1)
+        elif cc.ndim == 2 and cc.shape[0] in (m, 1) and cc.shape[1] in (n, 1):
+            pass
+        elif cc.size == 1:
+            cc = cc.reshape(1, 1)
+        else:
+            raise ValueError("invalid tensor shape")
+        y = y + np.float64(beta) * cc
+    return y.astype(a.dtype)
+
+
 # ---------------------------------------------------------------------------------------------
 # indexing / layout
 # ---------------------------------------------------------------------------------------------

@@ -81,6 +81,10 @@ def run(op: str, inputs, attrs=None) -> np.ndarray:
     if op == "Softmax":
         _need(x[0].dtype, (np.float32,), "softmax")
         return O.softmax(x[0], int(a.get("axis", -1)))
+    if op == "Gemm":
+        _need(x[0].dtype, (np.float16, np.float32), "gemm")
+        return O.gemm(x[0], x[1], x[2] if len(x) > 2 else None, float(a.get("alpha", 1.0)), float(a.get("beta", 1.0)),
+                      bool(a.get("transA", 0)), bool(a.get("transB", 0)))
     if op == "MatMul":
         _need(x[0].dtype, (np.float32,), "matmul")
         return O.matmul(x[0], x[1])

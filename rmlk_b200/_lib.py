@@ -29,6 +29,7 @@ def lib() -> ctypes.CDLL:
         _lib.rmlk_b200_version.restype = ctypes.c_char_p
         _lib.rmlk_b200_dtype_size.restype = ctypes.c_size_t
         _lib.rmlk_b200_matmul_workspace_bytes.restype = ctypes.c_size_t
+        _lib.rmlk_b200_matmul_tp_workspace_bytes.restype = ctypes.c_size_t
     return _lib
 
 

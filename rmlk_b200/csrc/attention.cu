@@ -20,6 +20,7 @@
 // to the 16-layer step: the one-CTA-per-problem kernel is about 15 us per layer slower than the A x B^T, softmax and
 // narrow-MatMul kernels run one after the other (37 us), the split-keys kernel below about 6 us slower.  The host
 // runtime therefore uses them only on request (RMLK_B200_ATTENTION=1).
+#include <cstdlib>
 #include <mutex>
 #include "common.cuh"
 
@@ -357,6 +358,163 @@ __global__ void __launch_bounds__(128) gqa_decode_attention_split_kernel(AttnSpl
     if (threadIdx.x == 0) sp.counters[prob] = 0;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// One pass over K and V ("flash" decode): one CTA of 8 warps per problem, every warp works through blocks of 32 keys on
+// its own (block w, w + 8, ...) with a running softmax - maximum m, sum l and weighted value sums a[4][D] per query row,
+// rescaled whenever a block raises the maximum - and the 8 warps are merged once at the end (M = max m,
+// L = sum l exp(m - M), out = sum a exp(m - M) / L).  K and V of a block are read back to back, so the stream from HBM
+// never stops for a softmax over the whole row; nothing but the 4 x 32 probabilities of a block passes through shared
+// memory; any number of keys.
+//  scores   lane = key: a lane reads its whole K row (D floats, 16 bytes per load, 8 loads in flight) and forms the 4
+//           dot products with q read from shared memory as broadcasts - no shuffles in the inner loop;
+//  softmax  block maximum and sum by warp shuffles (2 x 5 steps per row and block);
+//  values   lane = 4 columns of a V row (a warp-wide load reads 32 / LPR whole rows, coalesced), probabilities from
+//           shared memory.
+// ---------------------------------------------------------------------------------------------------------------------
+template <int LPR>
+__global__ void __launch_bounds__(256, 2) gqa_decode_flash_kernel(AttnParams p) {
+    dep_sync();
+    constexpr int D = 4 * LPR;
+    constexpr int RPI = 32 / LPR;            // rows of V per warp-wide load
+    constexpr int KC = LPR < 8 ? LPR : 8;    // 16-byte pieces of a K row in flight per lane
+    __shared__ __align__(16) float s_q[4][D];
+    __shared__ __align__(16) float s_p[8][32][4];    // per warp: probabilities of the current block, [key][row]
+    __shared__ float s_m[8][4], s_l[8][4];
+    __shared__ __align__(16) float s_a[8][4][D];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sub = lane % LPR, rsel = lane / LPR;
+    const int64_t prob = blockIdx.x;
+    const int T = p.T;
+    for (int i = threadIdx.x; i < 4 * D; i += 256) {
+        const int m = i / D;
+        s_q[m][i - m * D] = m < p.rows ? p.q[(prob * p.rows + m) * D + (i - m * D)] : 0.f;
+    }
+    __syncthreads();
+    const int64_t b = prob / p.kv_heads, h0 = (prob % p.kv_heads) * p.rows;
+    const float* __restrict__ K = p.k + prob * p.kb;
+    const float* __restrict__ V = p.v + prob * p.vb + 4 * sub;
+    float m_run[4], l_run[4], acc[4][4];
+#pragma unroll
+    for (int m = 0; m < 4; m++) {
+        m_run[m] = -INFINITY;
+        l_run[m] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[m][j] = 0.f;
+    }
+    const int n_blocks = (T + 31) >> 5;
+    for (int blk = warp; blk < n_blocks; blk += 8) {
+        const int t = blk * 32 + lane;
+        const bool valid = t < T;
+        // ---- scores of this lane's key ----
+        float sc[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint4* krow = reinterpret_cast<const uint4*>(K + static_cast<int64_t>(valid ? t : 0) * D);
+#pragma unroll
+        for (int c0 = 0; c0 < LPR; c0 += KC) {
+            uint4 kv[KC];
+#pragma unroll
+            for (int c = 0; c < KC; c++) kv[c] = valid ? __ldg(krow + c0 + c) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int c = 0; c < KC; c++) {
+                const float kx = __uint_as_float(kv[c].x), ky = __uint_as_float(kv[c].y), kz = __uint_as_float(kv[c].z), kw = __uint_as_float(kv[c].w);
+#pragma unroll
+                for (int m = 0; m < 4; m++) {
+                    const float4 qv = *reinterpret_cast<const float4*>(&s_q[m][4 * (c0 + c)]);
+                    sc[m] = fmaf(qv.w, kw, fmaf(qv.z, kz, fmaf(qv.y, ky, fmaf(qv.x, kx, sc[m]))));
+                }
+            }
+        }
+        // ---- running softmax ----
+        float pr[4];
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+            float x = -INFINITY;
+            if (valid && m < p.rows) {
+                x = __fmul_rn(sc[m], p.scale);
+                if (p.mask) x = __fadd_rn(x, p.mask[b * p.ms_b + (h0 + m) * p.ms_h + t]);
+            }
+            float mx = x;
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_new = fmaxf(m_run[m], mx);
+            const float e = m_new == -INFINITY ? 0.f : expf(x - m_new);          // x = -inf gives 0
+            const float corr = m_run[m] == -INFINITY ? 0.f : expf(m_run[m] - m_new);
+            float sum = e;
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            l_run[m] = fmaf(l_run[m], corr, sum);
+            m_run[m] = m_new;
+            pr[m] = e;
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[m][j] *= corr;
+        }
+        __syncwarp();  // the previous block's probabilities have been read
+        *reinterpret_cast<float4*>(&s_p[warp][lane][0]) = make_float4(pr[0], pr[1], pr[2], pr[3]);
+        __syncwarp();
+        // ---- values: 32 keys, RPI rows per load ----
+#pragma unroll
+        for (int u0 = 0; u0 < LPR; u0 += 8) {
+            uint4 vv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                const int tt = blk * 32 + (u0 + u) * RPI + rsel;
+                vv[u] = make_uint4(0, 0, 0, 0);
+                if (u0 + u < LPR && tt < T) vv[u] = ld_stream_u4(V + static_cast<int64_t>(tt) * D);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                if (u0 + u < LPR) {
+                    const float4 pw = *reinterpret_cast<const float4*>(&s_p[warp][(u0 + u) * RPI + rsel][0]);
+                    const float vx = __uint_as_float(vv[u].x), vy = __uint_as_float(vv[u].y), vz = __uint_as_float(vv[u].z), vw = __uint_as_float(vv[u].w);
+                    const float pm[4] = {pw.x, pw.y, pw.z, pw.w};
+#pragma unroll
+                    for (int m = 0; m < 4; m++) {
+                        acc[m][0] = fmaf(pm[m], vx, acc[m][0]);
+                        acc[m][1] = fmaf(pm[m], vy, acc[m][1]);
+                        acc[m][2] = fmaf(pm[m], vz, acc[m][2]);
+                        acc[m][3] = fmaf(pm[m], vw, acc[m][3]);
+                    }
+                }
+            }
+        }
+    }
+    // the row groups of a warp (lanes that read different rows of V) add up, then the 8 warps are merged
+#pragma unroll
+    for (int m = 0; m < 4; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float x = acc[m][j];
+#pragma unroll
+            for (int off = LPR; off < 32; off <<= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+            acc[m][j] = x;
+        }
+    if (rsel == 0) {
+#pragma unroll
+        for (int m = 0; m < 4; m++) *reinterpret_cast<float4*>(&s_a[warp][m][4 * sub]) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int m = 0; m < 4; m++) {
+            s_m[warp][m] = m_run[m];
+            s_l[warp][m] = l_run[m];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < p.rows * D; i += 256) {
+        const int m = i / D, d = i - m * D;
+        float M = s_m[0][m];
+#pragma unroll
+        for (int w = 1; w < 8; w++) M = fmaxf(M, s_m[w][m]);
+        float A = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) {
+            const float f = s_m[w][m] == -INFINITY ? 0.f : expf(s_m[w][m] - M);
+            A = fmaf(s_a[w][m][d], f, A);
+            L = fmaf(s_l[w][m], f, L);
+        }
+        p.out[prob * p.rows * D + i] = A / L;
+    }
+}
+
 constexpr int64_t ATTN_MAX_KEYS = 12288;  // 16 bytes of shared memory per key
 
 template <int LPR>
@@ -375,6 +533,23 @@ static int attn_launch(cudaStream_t st, const AttnParams& p, int64_t problems) {
     launch_dep(gqa_decode_attention_kernel<LPR>, dim3(static_cast<unsigned>(problems)), dim3(256), smem, st, p);
     RMLK_CHECK_LAUNCH("gqa_decode_attention_kernel");
     return RMLK_OK;
+}
+
+template <int LPR>
+static int attn_flash_launch(cudaStream_t st, const AttnParams& p, int64_t problems) {
+    launch_dep(gqa_decode_flash_kernel<LPR>, dim3(static_cast<unsigned>(problems)), dim3(256), 0, st, p);
+    RMLK_CHECK_LAUNCH("gqa_decode_flash_kernel");
+    return RMLK_OK;
+}
+
+// RMLK_B200_ATTENTION_FLASH=0: the one-launch attention falls back to the two-pass kernels (scores of all keys in shared
+// memory, then the values) for A/B runs.
+static bool attn_flash_enabled() {
+    static const bool v = [] {
+        const char* e = getenv("RMLK_B200_ATTENTION_FLASH");
+        return !(e && e[0] == '0');
+    }();
+    return v;
 }
 
 }  // namespace rmlk
@@ -413,6 +588,14 @@ extern "C" int rmlk_b200_gqa_decode_attention(rmlk_stream_t stream, int dtype, i
     p.kv_heads = static_cast<int>(kv_heads);
     p.scale = scale;
     cudaStream_t st = as_stream(stream);
+    if (attn_flash_enabled()) {
+        switch (head_dim) {
+            case 16: return attn_flash_launch<4>(st, p, problems);
+            case 32: return attn_flash_launch<8>(st, p, problems);
+            case 64: return attn_flash_launch<16>(st, p, problems);
+            default: return attn_flash_launch<32>(st, p, problems);
+        }
+    }
     switch (head_dim) {
         case 16: return attn_launch<4>(st, p, problems);
         case 32: return attn_launch<8>(st, p, problems);

@@ -163,6 +163,14 @@ inline unsigned flat_grid(int64_t items, int block, int per_sm_blocks) {
     return static_cast<unsigned>(need < cap ? need : cap);
 }
 
+// Column-split MatMul across GPUs: other ranks' output buffers (mapped into this GPU's address space) that receive every
+// element of C as well as the local one.
+struct TcPeers {
+    int n_peer;
+    float* out[7];
+    int64_t ldc;  // elements between rows of C in every destination
+};
+
 inline cudaStream_t as_stream(rmlk_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 }  // namespace rmlk

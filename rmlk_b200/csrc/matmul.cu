@@ -146,6 +146,123 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_kernel(SkinnyParams p) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// wide-strip small-M MatMul (M <= 16, rows of B 16-byte aligned): the decode GEMV
+// ---------------------------------------------------------------------------------------------
+// Memory-bound: B is read exactly once.  A CTA owns a strip of 128 columns (a warp-wide load is one 512-byte piece
+// of a row of B; 128-byte pieces stream a fifth slower) and a range of K; its 8 warps take rows k, k + 8, ... of the
+// range, each thread holding 8 independent 128-bit loads in flight.  A round covers 64 rows of B: the loads go
+// out first, then the 64 x MB block of A is staged in shared memory as [k][m] under them, then the FMAs.  K is split
+// over enough CTAs to keep several per SM in flight (the partial sums go through the caller's scratch and the
+// fixed-order split-K sum); a thread's 8 k-lanes are added by a three-step tree through shared memory.
+constexpr int GW_COLS = 128;
+constexpr int GW_U = 8;                 // loads in flight per thread
+constexpr int GW_KR = 8 * GW_U;         // rows of B per round
+constexpr int GW_THREADS = 256;
+
+template <int MB>
+__global__ void __launch_bounds__(GW_THREADS) gemv_wide_kernel(SkinnyParams p) {
+    dep_sync();
+    __shared__ __align__(16) float sA[GW_KR * MB];
+    __shared__ __align__(16) float sRed[4 * MB * GW_COLS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t batch = blockIdx.z;
+    const int split = blockIdx.y;
+    const int64_t n0 = static_cast<int64_t>(blockIdx.x) * GW_COLS + lane * 4;
+    const float* __restrict__ A = p.a + batch * p.sa;
+    const float* __restrict__ B = p.b + batch * p.sb;
+    const int64_t kbeg = static_cast<int64_t>(split) * p.k_per_split;
+    const int64_t kend = kbeg + p.k_per_split < p.K ? kbeg + p.k_per_split : p.K;
+    const bool in_cols = n0 < p.N;  // N % 4 == 0: a column quad is inside or outside as a whole
+
+    float acc[MB][4];
+#pragma unroll
+    for (int m = 0; m < MB; m++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[m][j] = 0.f;
+
+    for (int64_t kc = kbeg; kc < kend; kc += GW_KR) {
+        const int kn = static_cast<int>(kend - kc < GW_KR ? kend - kc : GW_KR);
+        uint4 bv[GW_U];
+#pragma unroll
+        for (int u = 0; u < GW_U; u++) {
+            const int k = warp + u * 8;
+            bv[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (k < kn && in_cols) bv[u] = ld_stream_u4(B + (kc + k) * p.N + n0);
+        }
+        __syncthreads();  // the previous round's FMAs have read sA
+        for (int i = threadIdx.x; i < GW_KR * MB; i += GW_THREADS) {
+            const int m = i / GW_KR, k = i - m * GW_KR;  // consecutive threads -> consecutive k (coalesced)
+            float v = 0.f;
+            if (m < p.M && k < kn) v = A[static_cast<int64_t>(m) * p.K + kc + k];
+            sA[k * MB + m] = v;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < GW_U; u++) {
+            const float* arow = sA + (warp + u * 8) * MB;  // the same address across a warp: a broadcast
+            float av[MB];
+            if constexpr (MB % 4 == 0) {
+#pragma unroll
+                for (int m = 0; m < MB; m += 4) {
+                    const float4 t = *reinterpret_cast<const float4*>(arow + m);
+                    av[m] = t.x; av[m + 1] = t.y; av[m + 2] = t.z; av[m + 3] = t.w;
+                }
+            } else {
+#pragma unroll
+                for (int m = 0; m < MB; m++) av[m] = arow[m];
+            }
+            const float bx = __uint_as_float(bv[u].x), by = __uint_as_float(bv[u].y), bz = __uint_as_float(bv[u].z), bw = __uint_as_float(bv[u].w);
+#pragma unroll
+            for (int m = 0; m < MB; m++) {
+                acc[m][0] = fmaf(av[m], bx, acc[m][0]);
+                acc[m][1] = fmaf(av[m], by, acc[m][1]);
+                acc[m][2] = fmaf(av[m], bz, acc[m][2]);
+                acc[m][3] = fmaf(av[m], bw, acc[m][3]);
+            }
+        }
+    }
+    // add the 8 warps (k lanes): 4..7 into 0..3, 2..3 into 0..1, 1 into 0
+#pragma unroll
+    for (int half = 4; half >= 1; half >>= 1) {
+        __syncthreads();
+        if (warp >= half && warp < 2 * half) {
+#pragma unroll
+            for (int m = 0; m < MB; m++)
+                *reinterpret_cast<float4*>(sRed + ((warp - half) * MB + m) * GW_COLS + lane * 4) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+        }
+        __syncthreads();
+        if (warp < half) {
+#pragma unroll
+            for (int m = 0; m < MB; m++) {
+                const float4 t = *reinterpret_cast<const float4*>(sRed + (warp * MB + m) * GW_COLS + lane * 4);
+                acc[m][0] += t.x; acc[m][1] += t.y; acc[m][2] += t.z; acc[m][3] += t.w;
+            }
+        }
+    }
+    if (warp == 0 && in_cols) {
+        float* __restrict__ C = p.c + (p.ksplit > 1 ? (static_cast<int64_t>(split) * gridDim.z + batch) * p.M * p.N : batch * p.sc);
+#pragma unroll
+        for (int m = 0; m < MB; m++)
+            if (m < p.M) *reinterpret_cast<float4*>(C + static_cast<int64_t>(m) * p.N + n0) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
+    }
+}
+
+// K split of the wide-strip kernel: about six CTAs per SM, ranges that are multiples of a round, and partial sums that
+// stay below a tenth of the bytes of B.
+static int gemv_wide_plan(int64_t batch, int64_t m, int64_t n, int64_t k, int64_t* k_per_split) {
+    const int64_t strips = ceil_div64(n, GW_COLS) * batch;
+    int64_t s = ceil_div64(6ll * sm_count(), strips);
+    const int64_t by_traffic = k / (20 * m) > 0 ? k / (20 * m) : 1;
+    if (s > by_traffic) s = by_traffic;
+    const int64_t rounds = ceil_div64(k, GW_KR);
+    if (s > rounds) s = rounds;
+    if (s < 1) s = 1;
+    if (s > 64) s = 64;
+    *k_per_split = ceil_div64(rounds, s) * GW_KR;
+    return static_cast<int>(ceil_div64(k, *k_per_split));
+}
+
 // Many small problems with a short K (decode attention scores: batch x heads problems of [1, 64] x [64, T]).
 // One thread owns four adjacent columns of one problem and walks all of K itself: no shared memory, no
 // reduction, B read once with 128-bit loads (a warp reads 512 contiguous bytes of a B row per k), A read with
@@ -593,6 +710,14 @@ static void skinny_launch(cudaStream_t st, const SkinnyParams& p, dim3 grid) {
     launch_dep(skinny_kernel<MB>, dim3(grid), dim3(SK_THREADS), 0, st, p);
 }
 
+static bool gemv_wide_enabled() {
+    static const bool v = [] {
+        const char* e = getenv("RMLK_B200_NO_GEMV_WIDE");
+        return !(e && e[0] == '1');
+    }();
+    return v;
+}
+
 static int skinny_plan(int64_t batch, int64_t n, int64_t k) {
     // number of K splits that brings the grid to about two CTAs per SM
     const int64_t strips = ceil_div64(n, SK_COLS) * batch;
@@ -613,9 +738,13 @@ namespace rmlk {
 // tensor-core path (matmul_tc.cu)
 bool tc_matmul_eligible(int64_t m, int64_t n, int64_t k, const void* a, const void* w, const void* c);
 size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k);
+size_t tc_matmul_min_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, const float* w, float* c, void* workspace,
-              size_t workspace_bytes, int* status, int* ksplit_out, int flags, int64_t ld);
+              size_t workspace_bytes, int* status, int* ksplit_out, int flags, int64_t ld, const TcPeers* peers = nullptr);
 int tc_matmul_plan(int64_t m, int64_t n, int64_t k);
+// fewest rows of A the tensor-core path takes: from 5 rows on, one pass of the weight-streaming tensor-core kernel (its 64-row
+// tile mostly padding) beats the SIMT small-M kernels; up to 4 rows the wide-strip SIMT kernel is at the HBM stream's speed
+constexpr int64_t TC_MIN_ROWS = 5;
 bool tc_enabled();
 // matmul_f16.cu
 int matmul_f16(cudaStream_t st, int64_t batch, int64_t m, int64_t n, int64_t k, const void* a, int64_t sa, const void* b, int64_t sb, void* c,
@@ -624,10 +753,17 @@ int matmul_f16(cudaStream_t st, int64_t batch, int64_t m, int64_t n, int64_t k, 
 
 extern "C" size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k) {
     if (dtype != RMLK_F32 || batch <= 0 || m <= 0 || n <= 0 || k <= 0) return 0;
-    if (batch == 1 && m > 16 && tc_enabled() && n % 128 == 0 && k % 32 == 0) return tc_matmul_workspace_bytes(m, n, k);
+    if (batch == 1 && m >= TC_MIN_ROWS && tc_enabled() && n % 128 == 0 && k % 32 == 0 && k >= 32) return tc_matmul_workspace_bytes(m, n, k);
     if (m > 16) return 0;
     const int s = skinny_plan(batch, n, k);
-    return s > 1 ? static_cast<size_t>(s) * batch * m * n * sizeof(float) : 0;
+    size_t need = s > 1 ? static_cast<size_t>(s) * batch * m * n * sizeof(float) : 0;
+    if (n % 4 == 0 && n >= GW_COLS && gemv_wide_enabled()) {  // the wide-strip kernel's split (taken when the operands are aligned)
+        int64_t kps = k;
+        const int sw = gemv_wide_plan(batch, m, n, k, &kps);
+        const size_t need_w = sw > 1 ? static_cast<size_t>(sw) * batch * m * n * sizeof(float) : 0;
+        if (need_w > need) need = need_w;
+    }
+    return need;
 }
 
 extern "C" int rmlk_b200_matmul(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
@@ -654,7 +790,7 @@ extern "C" int rmlk_b200_sum_parts(rmlk_stream_t stream, int dtype, int parts, i
 // ld elements apart: lets a wide product (the logits of a language model) be issued block by block, so that what
 // follows a block - a copy to the host - overlaps the next.  Only shapes the tensor-core kernel runs without a K split.
 extern "C" int rmlk_b200_matmul_window_supported(int64_t m, int64_t n, int64_t k, int64_t ld) {
-    return tc_enabled() && m > 16 && n > 0 && n % 128 == 0 && k >= 32 && k % 32 == 0 && ld >= n && ld % 4 == 0 && tc_matmul_plan(m, n, k) == 1;
+    return tc_enabled() && m >= TC_MIN_ROWS && n > 0 && n % 128 == 0 && k >= 32 && k % 32 == 0 && ld >= n && ld % 4 == 0 && tc_matmul_plan(m, n, k) == 1;
 }
 
 extern "C" int rmlk_b200_matmul_window(rmlk_stream_t stream, int dtype, int64_t m, int64_t n, int64_t k, const void* a, const void* b, void* c,
@@ -662,7 +798,7 @@ extern "C" int rmlk_b200_matmul_window(rmlk_stream_t stream, int dtype, int64_t 
     if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for matmul_window (f32 only)");
     if (!a || !b || !c) return fail(RMLK_ERR_INVALID_ARG, "matmul_window: NULL operand");
     if (!rmlk_b200_matmul_window_supported(m, n, k, ld) || !tc_matmul_eligible(m, n, k, a, b, c))
-        return fail(RMLK_ERR_INVALID_ARG, "matmul_window: needs M > 16, N % 128 == 0, K % 32 == 0, 16-byte aligned operands and a shape without a K split");
+        return fail(RMLK_ERR_INVALID_ARG, "matmul_window: needs M >= 5, N % 128 == 0, K % 32 == 0, 16-byte aligned operands and a shape without a K split");
     int ksplit = 1;
     return tc_matmul(as_stream(stream), m, n, k, static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(c), nullptr, 0,
                      status, &ksplit, flags, ld);
@@ -774,6 +910,32 @@ extern "C" int rmlk_b200_matmul_flags(rmlk_stream_t stream, int dtype, int64_t b
             RMLK_CHECK_LAUNCH("nn_narrow_kernel");
             return RMLK_OK;
         }
+        if (b_rows_aligned && aligned_to(c, 16) && c_batch_stride % 4 == 0 && n >= GW_COLS && gemv_wide_enabled()) {
+            int64_t kps = k;
+            int ksplit = gemv_wide_plan(batch, m, n, k, &kps);
+            const size_t need = static_cast<size_t>(ksplit) * batch * m * n * sizeof(float);
+            if (ksplit > 1 && (!workspace || workspace_bytes < need || !aligned_to(workspace, 16))) {
+                ksplit = 1;
+                kps = k;
+            }
+            p.ksplit = ksplit;
+            p.k_per_split = kps;
+            p.c = ksplit > 1 ? static_cast<float*>(workspace) : static_cast<float*>(c);
+            dim3 grid(static_cast<unsigned>(ceil_div64(n, GW_COLS)), ksplit, static_cast<unsigned>(batch));
+            if (m == 1) launch_dep(gemv_wide_kernel<1>, grid, dim3(GW_THREADS), 0, st, p);
+            else if (m == 2) launch_dep(gemv_wide_kernel<2>, grid, dim3(GW_THREADS), 0, st, p);
+            else if (m <= 4) launch_dep(gemv_wide_kernel<4>, grid, dim3(GW_THREADS), 0, st, p);
+            else if (m <= 8) launch_dep(gemv_wide_kernel<8>, grid, dim3(GW_THREADS), 0, st, p);
+            else launch_dep(gemv_wide_kernel<16>, grid, dim3(GW_THREADS), 0, st, p);
+            RMLK_CHECK_LAUNCH("gemv_wide_kernel");
+            if (ksplit > 1) {
+                const int64_t total = batch * m * n;
+                launch_dep(splitk_reduce_kernel, dim3(static_cast<unsigned>(ceil_div64(total, 256))), dim3(256), 0, st,
+                           static_cast<const float*>(workspace), static_cast<float*>(c), ksplit, batch, m * n, c_batch_stride);
+                RMLK_CHECK_LAUNCH("splitk_reduce_kernel");
+            }
+            return RMLK_OK;
+        }
         int ksplit = skinny_plan(batch, n, k);
         const size_t need = static_cast<size_t>(ksplit) * batch * m * n * sizeof(float);
         if (ksplit > 1 && (!workspace || workspace_bytes < need)) ksplit = 1;
@@ -868,6 +1030,44 @@ extern "C" int rmlk_b200_matmul_nt(rmlk_stream_t stream, int dtype, int64_t batc
 }
 
 // ---------------------------------------------------------------------------------------------
+// Gemm epilogue: y = alpha * y + beta * c, c broadcast to [m, n] by strides (0 = broadcast)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) scale_add_bias_kernel(T* __restrict__ y, const T* __restrict__ c, int64_t total, uint32_t n, FastDiv ndiv,
+                                                             int64_t cs_row, int64_t cs_col, float alpha, float beta) {
+    dep_sync();
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * 256) {
+        float v = static_cast<float>(y[i]);
+        if (alpha != 1.f) v = __fmul_rn(alpha, v);
+        if (c) {
+            uint32_t row, col;
+            ndiv.divmod(static_cast<uint32_t>(i), row, col);
+            v = fmaf(beta, static_cast<float>(c[row * cs_row + col * cs_col]), v);
+        }
+        y[i] = static_cast<T>(v);
+    }
+}
+
+extern "C" int rmlk_b200_scale_add_bias(rmlk_stream_t stream, int dtype, int64_t m, int64_t n, void* y, float alpha, const void* c,
+                                        int64_t c_row_stride, int64_t c_col_stride, float beta) {
+    if (dtype != RMLK_F32 && dtype != RMLK_F16) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for scale_add_bias (f32 and f16)");
+    if (m < 0 || n < 0) return fail(RMLK_ERR_INVALID_ARG, "scale_add_bias: negative extent");
+    if (m == 0 || n == 0 || (alpha == 1.f && !c)) return RMLK_OK;
+    if (!y) return fail(RMLK_ERR_INVALID_ARG, "scale_add_bias: NULL output");
+    if (m * n > 0x7fffffffll || n > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "scale_add_bias: more than 2^31 elements");
+    const int64_t total = m * n;
+    const unsigned grid = flat_grid(total, 256, 8);
+    if (dtype == RMLK_F32)
+        launch_dep(scale_add_bias_kernel<float>, dim3(grid), dim3(256), 0, as_stream(stream), static_cast<float*>(y), static_cast<const float*>(c), total,
+                   static_cast<uint32_t>(n), FastDiv(static_cast<uint32_t>(n)), c_row_stride, c_col_stride, alpha, beta);
+    else
+        launch_dep(scale_add_bias_kernel<__half>, dim3(grid), dim3(256), 0, as_stream(stream), static_cast<__half*>(y), static_cast<const __half*>(c), total,
+                   static_cast<uint32_t>(n), FastDiv(static_cast<uint32_t>(n)), c_row_stride, c_col_stride, alpha, beta);
+    RMLK_CHECK_LAUNCH("scale_add_bias_kernel");
+    return RMLK_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
 // MatMul without any allocation by anyone: the split-K scratch is a fixed array inside the library.
 // ---------------------------------------------------------------------------------------------
 // 8 MiB of device memory per GPU that loads this library, held until the process exits.
@@ -905,10 +1105,22 @@ static void* static_scratch_ptr(int* rc_out) {
 
 extern "C" size_t rmlk_b200_matmul_static_scratch_bytes(void) { return RMLK_STATIC_SCRATCH_BYTES; }
 
+// The least scratch a shape can run with.  (rmlk_b200_matmul_workspace_bytes reports what lets every kernel choice run; the
+// tensor-core MatMul has a second schedule that wants more than the built-in array holds for some shapes, and
+// rmlk_b200_matmul_ex picks the schedule that fits what it is lent.)
+static size_t matmul_least_scratch(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k) {
+    if (dtype == RMLK_F32 && batch == 1 && m >= TC_MIN_ROWS && tc_enabled() && n % 128 == 0 && k % 32 == 0 && k >= 32) return tc_matmul_min_workspace_bytes(m, n, k);
+    return rmlk_b200_matmul_workspace_bytes(dtype, batch, m, n, k);
+}
+
+extern "C" int rmlk_b200_matmul_static_supported(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k) {
+    return matmul_least_scratch(dtype, batch, m, n, k) <= RMLK_STATIC_SCRATCH_BYTES ? 1 : 0;
+}
+
 extern "C" int rmlk_b200_matmul_static(rmlk_stream_t stream, int dtype, int64_t batch, int64_t m, int64_t n, int64_t k,
                                        const void* a, int64_t a_batch_stride, const void* b, int64_t b_batch_stride, void* c,
                                        int64_t c_batch_stride, int* status) {
-    const size_t need = rmlk_b200_matmul_workspace_bytes(dtype, batch, m, n, k);
+    const size_t need = matmul_least_scratch(dtype, batch, m, n, k);
     if (need > RMLK_STATIC_SCRATCH_BYTES)
         return rmlk::fail(RMLK_ERR_INVALID_ARG, "matmul_static: this shape needs " + std::to_string(need) +
                                                     " bytes of split-K scratch, the built-in array holds " +

@@ -38,9 +38,12 @@
 // Every mbarrier wait is bounded: on expiry the thread raises a CTA-wide abort flag, records
 // RMLK_ERR_TIMEOUT in the caller's status word, and every role falls through to the common exit where TMEM
 // is released.  Every TMA load targets this CTA's own shared memory.
+#include <atomic>
+#include <chrono>
 #include <mutex>
 
 #include "matmul_tc_kernel.cuh"
+#include "matmul_tc_stream.cuh"
 
 namespace rmlk {
 namespace tc {
@@ -115,7 +118,120 @@ static int launch(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tm
     return RMLK_OK;
 }
 
+template <int MT, int SW, int SA>
+static int launch_stream(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tmA, const StreamParams& p, unsigned grid) {
+    using L = StreamSmem<MT, SW, SA>;
+    static std::once_flag configured[64];  // once per device; a concurrent first call waits for the attribute to be set
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaError_t cfg_err = cudaSuccess;
+    if (dev >= 0 && dev < 64)
+        std::call_once(configured[dev], [&] {
+            cfg_err = cudaFuncSetAttribute(tc_stream_kernel<MT, SW, SA>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+        });
+    RMLK_CUDA(cfg_err);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(STREAM_THREADS);
+    cfg.dynamicSmemBytes = L::TOTAL;
+    cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    unsigned na = 0;
+    if (dep_launch_enabled()) {
+        at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    cfg.attrs = at;
+    cfg.numAttrs = na;
+    RMLK_CUDA(cudaLaunchKernelEx(&cfg, tc_stream_kernel<MT, SW, SA>, tmW, tmA, p));
+    RMLK_CHECK_LAUNCH("tc_stream_kernel");
+    return RMLK_OK;
+}
+
+// A value no earlier launch of this process has used (and, being 64 pseudo-random bits, one that leftover bytes in a
+// caller's scratch buffer will not hold): what a partial tile's flags are set to.
+static unsigned long long next_token() {
+    static std::atomic<unsigned long long> counter{static_cast<unsigned long long>(std::chrono::steady_clock::now().time_since_epoch().count())};
+    unsigned long long z = counter.fetch_add(0x9e3779b97f4a7c15ull, std::memory_order_relaxed) + 0x9e3779b97f4a7c15ull;
+    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    z ^= z >> 31;
+    return z | 1ull;  // never 0, the value of a cleared flag
+}
+
 }  // namespace tc
+
+// ---- the persistent kernel's schedule ------------------------------------------------------------------------------
+struct StreamPlan {
+    int mt, k_iters, m_tiles, gran;
+    bool strided = false;
+    unsigned grid;
+    int64_t tiles, units;
+    bool partials;
+    size_t flag_bytes, ws_bytes;
+};
+
+static bool tc_stream_enabled() {
+    static const bool v = [] {
+        const char* e = getenv("RMLK_B200_NO_TC_STREAM");
+        return !(e && e[0] == '1');
+    }();
+    return v;
+}
+
+static StreamPlan stream_plan(int64_t m, int64_t n, int64_t k) {
+    StreamPlan pl;
+    pl.mt = m <= 64 ? 64 : 128;
+    pl.k_iters = static_cast<int>(k / tc::BK);
+    pl.m_tiles = static_cast<int>(ceil_div64(m, pl.mt));
+    pl.tiles = (n / tc::BN) * pl.m_tiles;
+    const int64_t sms = sm_count();
+    const int64_t total_kb = pl.tiles * pl.k_iters;
+    // Whole tiles per CTA when that already balances (a multiple of the SM count, or so many tiles that one more or
+    // less does not matter); otherwise ranges of k-blocks that may cut a tile, at least 4 k-blocks each and long enough
+    // that no tile is shared by more than STREAM_MAX_GROUP CTAs.
+    static const int mode = [] { const char* e = getenv("RMLK_B200_TC_STREAM_MODE"); return e ? atoi(e) : 0; }();
+    pl.strided = mode == 2;
+    if (pl.tiles % sms == 0 || pl.tiles >= 8 * sms || mode >= 1) {
+        pl.gran = pl.k_iters;
+        pl.units = pl.tiles;
+        pl.grid = static_cast<unsigned>(pl.tiles < sms ? pl.tiles : sms);
+        pl.partials = false;
+    } else {
+        pl.gran = 1;
+        pl.units = total_kb;
+        int64_t per_min = ceil_div64(pl.k_iters, tc::STREAM_MAX_GROUP - 2);
+        if (per_min < 4) per_min = 4;
+        int64_t g = total_kb / per_min;
+        if (g > sms) g = sms;
+        if (g < 1) g = 1;
+        pl.grid = static_cast<unsigned>(g);
+        pl.partials = g > 1;
+    }
+    pl.flag_bytes = (static_cast<size_t>(2) * pl.grid * tc::STREAM_MAX_GROUP * sizeof(unsigned long long) + 255) & ~static_cast<size_t>(255);
+    pl.ws_bytes = pl.partials ? pl.flag_bytes + static_cast<size_t>(2) * pl.grid * pl.mt * tc::BN * sizeof(float) : 0;
+    return pl;
+}
+
+}  // namespace rmlk
+
+extern "C" int rmlk_b200_debug_stream_times(long long* out) {
+    return cudaMemcpyFromSymbol(out, rmlk::tc::g_stream_dbg, sizeof(long long) * 32) == cudaSuccess ? 0 : 1;
+}
+
+// The persistent MatMul kernel's schedule for a shape, for inspection and tests (pure host arithmetic):
+// out = {rows per tile, k-blocks per tile, row tiles, k-blocks per work unit, CTAs, tiles, work units, scratch bytes}.
+extern "C" int rmlk_b200_matmul_schedule(int64_t m, int64_t n, int64_t k, int64_t* out) {
+    if (!out || m < 5 || n <= 0 || n % rmlk::tc::BN || k < rmlk::tc::BK || k % rmlk::tc::BK)
+        return rmlk::fail(RMLK_ERR_INVALID_ARG, "matmul_schedule: needs M >= 5, N % 128 == 0, K % 32 == 0");
+    const rmlk::StreamPlan pl = rmlk::stream_plan(m, n, k);
+    out[0] = pl.mt; out[1] = pl.k_iters; out[2] = pl.m_tiles; out[3] = pl.gran; out[4] = pl.grid; out[5] = pl.tiles; out[6] = pl.units;
+    out[7] = static_cast<int64_t>(pl.ws_bytes);
+    return RMLK_OK;
+}
+
+namespace rmlk {
 
 bool tc_enabled() {
     static const bool v = [] {
@@ -127,7 +243,7 @@ bool tc_enabled() {
 
 // Eligibility of the tensor-core path for C[M,N] = A[M,K] x W[K,N].
 bool tc_matmul_eligible(int64_t m, int64_t n, int64_t k, const void* a, const void* w, const void* c) {
-    return tc_enabled() && m > 16 && (n % tc::BN == 0) && (k % tc::BK == 0) && k >= tc::BK && aligned_to(a, 16) && aligned_to(w, 16) &&
+    return tc_enabled() && m >= 5 && (n % tc::BN == 0) && (k % tc::BK == 0) && k >= tc::BK && aligned_to(a, 16) && aligned_to(w, 16) &&
            aligned_to(c, 16) && n < (1ll << 31) && k < (1ll << 31) && m < (1ll << 31) && ceil_div64(m, 128) <= 65535 &&
            tc::encode_fn() != nullptr;
 }
@@ -163,19 +279,62 @@ int tc_matmul_plan(int64_t m, int64_t n, int64_t k) {
     return static_cast<int>(s > 32 ? 32 : s);
 }
 
-size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+// Scratch the split-K form of tc_gemm_kernel needs (the smaller need: what a caller with little scratch must have).
+size_t tc_matmul_min_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     const int s = tc_matmul_plan(m, n, k);
     return s > TC_CLUSTER_MAX ? static_cast<size_t>(s) * m * n * sizeof(float) : 0;
+}
+
+// Scratch that lets every kernel choice run: the persistent kernel's partial-tile slots and flags when its schedule
+// cuts tiles, and never less than the split-K slabs of the one-tile-per-CTA kernel.
+size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+    const size_t a = tc_matmul_min_workspace_bytes(m, n, k);
+    const size_t b = (tc_stream_enabled() && m <= 64) ? stream_plan(m, n, k).ws_bytes : 0;
+    return a > b ? a : b;
 }
 
 // Launches the tensor-core GEMM.  `ksplit_out` tells the caller how many partial slabs were written to
 // `workspace` (1 = the result is already in c).
 int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, const float* w, float* c, void* workspace,
-              size_t workspace_bytes, int* status, int* ksplit_out, int flags, int64_t ld) {
+              size_t workspace_bytes, int* status, int* ksplit_out, int flags, int64_t ld, const TcPeers* peers) {
+    if (peers && (ld > 0 || peers->n_peer < 0 || peers->n_peer > tc::MAX_PEERS || peers->ldc < n || peers->ldc % 4))
+        return fail(RMLK_ERR_INVALID_ARG, "matmul: bad peer destinations");
+    const int64_t ldc = peers ? peers->ldc : (ld > 0 ? ld : n);
+    if (tc_stream_enabled() && m <= 64) {
+        // M <= 64 (the weight-streaming regime): the persistent kernel, unless its schedule cuts tiles and the caller lent too little scratch for the partial tiles
+        const StreamPlan pl = stream_plan(m, n, k);
+        if (!pl.partials || (workspace && workspace_bytes >= pl.ws_bytes && aligned_to(workspace, 16))) {
+            CUtensorMap tmW, tmA;
+            if (!tc::make_map_2d(&tmW, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), tc::BN, tc::BK, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                 ld > 0 ? static_cast<uint64_t>(ld) : 0) ||
+                !tc::make_map_2d(&tmA, a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), 32, static_cast<uint32_t>(pl.mt), CU_TENSOR_MAP_SWIZZLE_128B))
+                return fail(RMLK_ERR_INTERNAL, "matmul: cuTensorMapEncodeTiled failed");
+            tc::StreamParams sp;
+            sp.out = c;
+            sp.M = m; sp.N = n; sp.K = k;
+            sp.ldc = ldc;
+            sp.n_peer = peers ? peers->n_peer : 0;
+            for (int d = 0; d < sp.n_peer; d++) sp.peer_out[d] = peers->out[d];
+            sp.k_iters = pl.k_iters;
+            sp.m_tiles = pl.m_tiles;
+            sp.units = pl.units;
+            sp.gran = pl.gran;
+            sp.strided = pl.strided ? 1 : 0;
+            sp.flags = pl.partials ? static_cast<unsigned long long*>(workspace) : nullptr;
+            sp.slots = pl.partials ? reinterpret_cast<float*>(static_cast<char*>(workspace) + pl.flag_bytes) : nullptr;
+            sp.token = tc::next_token();
+            sp.status = status;
+            sp.w_static = (flags & RMLK_MATMUL_B_STATIC) ? 1 : 0;
+            static const int mma_mode = [] { const char* e = getenv("RMLK_B200_MMA_MODE"); return e ? atoi(e) : 1; }();
+            sp.mma_mode = mma_mode;
+            *ksplit_out = 1;
+            return tc::launch_stream<64, 6, 6>(st, tmW, tmA, sp, pl.grid);
+        }
+    }
     const int mt = m <= 64 ? 64 : 128;
     int ksplit = tc_matmul_plan(m, n, k);
-    if (ksplit > TC_CLUSTER_MAX && (!workspace || workspace_bytes < static_cast<size_t>(ksplit) * m * n * sizeof(float)))
-        ksplit = TC_CLUSTER_MAX;  // no scratch from the caller: stay within one cluster per tile
+    if (ksplit > TC_CLUSTER_MAX && (peers || !workspace || workspace_bytes < static_cast<size_t>(ksplit) * m * n * sizeof(float)))
+        ksplit = TC_CLUSTER_MAX;  // no scratch from the caller (or results that must reach other GPUs from this kernel): one cluster per tile
     const int k_iters = static_cast<int>(k / tc::BK);
     const int per = static_cast<int>(ceil_div64(k_iters, ksplit));
     ksplit = static_cast<int>(ceil_div64(k_iters, per));  // every split gets at least one k-block
@@ -191,7 +350,9 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
     p.cluster_reduce = cluster ? 1 : 0;
     p.out = (ksplit > 1 && !cluster) ? static_cast<float*>(workspace) : c;
     p.M = m; p.N = n; p.K = k;
-    p.ldc = ld > 0 ? ld : n;
+    p.ldc = ldc;
+    p.n_peer = peers ? peers->n_peer : 0;
+    for (int d = 0; d < p.n_peer; d++) p.peer_out[d] = peers->out[d];
     p.k_iters_per_split = per;
     p.k_iters_total = k_iters;
     p.ksplit = ksplit;

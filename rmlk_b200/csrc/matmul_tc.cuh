@@ -48,6 +48,27 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
+// Bounded wait for a barrier that is far away (the epilogue warps wait for a whole segment of MMAs): the thread is parked
+// in hardware for up to `hint_ns` per try instead of polling, so that it takes no issue slots from the warps that work.
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    constexpr uint32_t hint_ns = 20000;
+    for (uint32_t i = 0; i < (1u << 16); i++) {  // about a second in all
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity), "r"(hint_ns)
+            : "memory");
+        if (ok) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = 1;
+    if (status) atomicExch(status, RMLK_ERR_TIMEOUT);
+    return false;
+}
+
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
@@ -131,6 +152,8 @@ __device__ __forceinline__ void st_shared_cluster_f32(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
+constexpr int MAX_PEERS = 7;  // other ranks of one NVLink domain (8 GPUs)
+
 struct TcParams {
     int cluster_reduce;     // ksplit CTAs form a cluster along grid y and add their partial sums on chip
     float* out;             // C, or the split-K scratch [ksplit][M][N]
@@ -141,6 +164,10 @@ struct TcParams {
     int ksplit;
     int* status;
     int w_static;           // the weights are not written by work still in flight: their loads need not wait for the previous kernel
+    // Column-split MatMul across GPUs: every finished element of C is also stored at the same offset from each of these
+    // bases - the other ranks' output buffers, mapped into this GPU's address space (ordinary stores that cross NVLink).
+    int n_peer;
+    float* peer_out[MAX_PEERS];
 };
 
 // Shared memory: a ring of SW raw weight blocks (freed as soon as the converters have moved a block into TMEM) and a

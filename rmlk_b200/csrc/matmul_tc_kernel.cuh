@@ -119,9 +119,11 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
                     // a k-step of 8 is 8 TMEM columns of the weights and 32 bytes inside the swizzled activation rows
                     const uint64_t da_hi = smem_desc_k128(a_hi + kk * 32);
                     // hi x [hi; lo]: the lo tile follows the hi tile in shared memory, so one descriptor with N = 2 MT
-                    // covers both and fills accumulator columns [0, MT) and [MT, 2 MT); then lo x hi into [0, MT)
+                    // covers both and fills accumulator columns [0, MT) and [MT, 2 MT); then lo x hi into [MT, 2 MT)
                     tc_mma_tf32_ts(tmem_base, w_hi + kk * 8, da_hi, idesc_wide, (it > 0 || kk > 0) ? 1u : 0u);
-                    tc_mma_tf32_ts(tmem_base, w_lo + kk * 8, da_hi, idesc, 1u);
+                    // (into the hi x lo block: the tensor core truncates when it adds into the accumulator, and keeping the
+                    // small products out of the large hi x hi sums halves that error)
+                    tc_mma_tf32_ts(tmem_base + MT, w_lo + kk * 8, da_hi, idesc, 1u);
                 }
                 tc_commit(mma_done(s));
             }
@@ -193,7 +195,11 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
 #pragma unroll
                 for (int j = 0; j < 32; j++) {
                     const int64_t m = m0 + c0 + j;
-                    if (m < p.M) out[m * p.ldc + n] = __uint_as_float(r[j]) + __uint_as_float(q[j]);
+                    if (m < p.M) {
+                        const float v = __uint_as_float(r[j]) + __uint_as_float(q[j]);
+                        out[m * p.ldc + n] = v;
+                        for (int d = 0; d < p.n_peer; d++) p.peer_out[d][m * p.ldc + n] = v;
+                    }
                 }
             }
         }
@@ -237,6 +243,7 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
                     float s = buf[ml * BN + n];
                     for (uint32_t r2 = 1; r2 < ks; r2++) s += buf[(r2 * rows_per + ml) * BN + n];
                     p.out[m * p.ldc + n0 + n] = s;
+                    for (int d = 0; d < p.n_peer; d++) p.peer_out[d][m * p.ldc + n0 + n] = s;
                 }
             }
         }

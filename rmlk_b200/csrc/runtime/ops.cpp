@@ -626,6 +626,71 @@ void op_softmax(const Ctx& c) {
 // ---------------------------------------------------------------------------------------------
 // MatMul — backend/matmul.rs:223-356
 // ---------------------------------------------------------------------------------------------
+// ONNX Gemm: Y = alpha * op(A) * op(B) + beta * C for rank-2 A and B (backend/gemm.rs:149-216).  C broadcasts to [M, N] by the ONNX
+// rule (a vector of N entries is a row, a vector of M entries a column - the reference's two 1-D cases, backend/gemm.rs:225-227).
+void op_gemm(const Ctx& c) {
+    Tensor& a = c.req(0);
+    Tensor& b = c.req(1);
+    Tensor* bias = c.n.inputs.size() > 2 ? c.in(2) : nullptr;
+    if (!in_set(a.dtype, {RMLK_F32, RMLK_F16})) unsupported_dtype(a.dtype, "gemm");
+    if (b.dtype != a.dtype || (bias && bias->dtype != a.dtype)) raise(RMLK_ERR_INVALID_ARG, "gemm: operand data types differ");
+    if (a.shape.size() != 2 || b.shape.size() != 2) raise(RMLK_ERR_INVALID_ARG, "expected inputs with rank 2");
+    const bool ta = c.attr_int("transA", 0) != 0, tb = c.attr_int("transB", 0) != 0;
+    const Attr* aa = c.attr("alpha");
+    const Attr* ab = c.attr("beta");
+    const float alpha = (aa && aa->kind == Attr::FLOAT) ? aa->f : 1.f, beta = (ab && ab->kind == Attr::FLOAT) ? ab->f : 1.f;
+    const int64_t m = ta ? a.shape[1] : a.shape[0], k = ta ? a.shape[0] : a.shape[1];
+    const int64_t kb = tb ? b.shape[1] : b.shape[0], n = tb ? b.shape[0] : b.shape[1];
+    if (k != kb) raise(RMLK_ERR_INVALID_ARG, "IncompatibleDimForMul");
+    int64_t cs_row = 0, cs_col = 0;
+    if (bias) {
+        const Shape& s = bias->shape;
+        if (s.empty() || (s.size() == 1 && s[0] == 1)) { cs_row = cs_col = 0; }
+        else if (s.size() == 1 && s[0] == n) { cs_row = 0; cs_col = 1; }
+        else if (s.size() == 1 && s[0] == m) { cs_row = 1; cs_col = 0; }
+        else if (s.size() == 2 && (s[0] == m || s[0] == 1) && (s[1] == n || s[1] == 1)) { cs_row = s[0] == 1 ? 0 : s[1]; cs_col = s[1] == 1 ? 0 : 1; }
+        else raise(RMLK_ERR_INVALID_ARG, "invalid tensor shape");
+    }
+    Tensor& y = c.make(0, a.dtype, Shape({m, n}));
+    if (y.numel() == 0) return;
+    const size_t es = dtype_size_of(a.dtype);
+    const void* ap = a.data;
+    Storage* at = nullptr;
+    if (ta) {  // [k, m] -> [m, k]
+        at = c.I.arena->alloc(static_cast<size_t>(m) * k * es);
+        const int64_t perm[2] = {1, 0};
+        check_rc(rmlk_b200_transpose(c.stream(), static_cast<int>(es), 2, a.shape.data(), perm, a.data, at->ptr));
+        c.launched();
+        ap = at->ptr;
+    }
+    Storage* bt = nullptr;
+    if (tb && a.dtype == RMLK_F32) {
+        check_rc(rmlk_b200_matmul_nt(c.stream(), a.dtype, 1, m, n, k, ap, 0, b.data, 0, y.data, 0));  // B stored [n, k]: read as it lies
+        c.launched();
+    } else {
+        const void* bp = b.data;
+        if (tb) {
+            bt = c.I.arena->alloc(static_cast<size_t>(n) * k * es);
+            const int64_t perm[2] = {1, 0};
+            check_rc(rmlk_b200_transpose(c.stream(), static_cast<int>(es), 2, b.shape.data(), perm, b.data, bt->ptr));
+            c.launched();
+            bp = bt->ptr;
+        }
+        const size_t need = rmlk_b200_matmul_workspace_bytes(a.dtype, 1, m, n, k);
+        void* ws = need ? c.I.matmul_ws.ensure(need) : nullptr;
+        const int flags = (!tb && c.I.g.values[c.n.inputs[1]].is_const) ? RMLK_MATMUL_B_STATIC : 0;
+        check_rc(rmlk_b200_matmul_flags(c.stream(), a.dtype, 1, m, n, k, ap, 0, bp, 0, y.data, 0, ws, need, static_cast<int*>(c.I.status_word.ptr), flags));
+        c.I.status_dirty = true;
+        c.launched();
+    }
+    if (at) c.I.arena->release(at);
+    if (bt) c.I.arena->release(bt);
+    if (alpha != 1.f || bias) {
+        check_rc(rmlk_b200_scale_add_bias(c.stream(), a.dtype, m, n, y.data, alpha, bias ? bias->data : nullptr, cs_row, cs_col, beta));
+        c.launched();
+    }
+}
+
 void op_matmul(const Ctx& c) {
     Tensor& a = c.req(0);
     Tensor* braw = c.raw(1);
@@ -1832,7 +1897,8 @@ bool Instance::run_fused(const FusedGroup& fg) {
             if (q->lazy) materialize(*q);
             const void *kdata = kt->data, *vdata = vh->data;
             Tensor& o = c.make(0, RMLK_F32, Shape({B, H, 1, D}));
-            const size_t ws_need = rmlk_b200_gqa_decode_attention_workspace_bytes(lk.outer, lk.fold, D, T);
+            // one CTA per problem in one pass over K and V by default; RMLK_B200_ATTENTION=split: keys split over CTAs, merged through a workspace
+            const size_t ws_need = attention_split ? rmlk_b200_gqa_decode_attention_workspace_bytes(lk.outer, lk.fold, D, T) : 0;
             void* ws = nullptr;
             if (ws_need) {
                 ws = attn_ws.ensure(ws_need);
@@ -2048,6 +2114,7 @@ void Instance::run_node(const NodeDef& n) {
         case RMLK_OP_REDUCE_MEAN: return op_reduce_mean(c);
         case RMLK_OP_SOFTMAX: return op_softmax(c);
         case RMLK_OP_MATMUL: return op_matmul(c);
+        case RMLK_OP_GEMM: return op_gemm(c);
         case RMLK_OP_GATHER: return op_gather(c);
         case RMLK_OP_SCATTER_ND: return op_scatter_nd(c);
         case RMLK_OP_SLICE: return op_slice(c);

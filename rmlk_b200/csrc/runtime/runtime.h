@@ -243,6 +243,7 @@ struct Instance {
     // a problem split over CTAs of 128 keys).  Off by default: it measured 6 us per layer slower than the three kernels
     // it replaces on 512 problems of 550 keys.
     bool attention = false;
+    bool attention_split = false;  // RMLK_B200_ATTENTION=split
     bool add_norm = true;       // RMLK_B200_NO_ADD_NORM=1: keep the residual Add (and the split-K sum) as launches of their own
     void settle_parts(int value_id);
     DeviceBuffer read_staging;  // dense copy of a strided output while it is read back

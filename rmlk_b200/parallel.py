@@ -6,9 +6,11 @@ runtime/src/core/instance.rs:199-205):
 * request sharding - independent requests, weights replicated, no data-path collective.  `shard_range` gives a
   rank its contiguous share; `max_over_ranks` turns per-rank device times into the job's time.
 * column-split MatMul - for weights too large or too slow for one GPU, W[K, N] is split by columns, every rank
-  multiplies the same activations with its shard and the [M, N / world] results are gathered
-  (`ColumnParallelMatMul`).  The gather is the path's one real exchange step; it runs as one NCCL all-gather
-  followed by one permuting copy, both on the launching stream.
+  multiplies the same activations with its shard and every rank ends up with the whole [M, N] product.  Two forms of
+  that one real exchange step: `PeerStoreColumnParallelMatMul` has the MatMul kernel's epilogue store each rank's block
+  of columns straight into every rank's output buffer over NVLink (rmlk_b200_matmul_tp: peer stores + flags, no
+  collective call); `ColumnParallelMatMul` runs the shard MatMul, one NCCL all-gather and one permuting copy - the
+  baseline the first is measured against.
 
 The compute and copy steps are injected as callables so that the sharding and gathering logic can be exercised
 with gloo on CPU ranks; on GPUs they are the library's MatMul and transpose kernels.
@@ -123,3 +125,130 @@ class ColumnParallelMatMul:
             return y
         cols = torch.cat([torch.arange(r * self.n_max, r * self.n_max + w, device=y.device) for r, w in enumerate(self.widths)])
         return y.index_select(1, cols)
+
+
+class PeerBuffers:
+    """Device buffers of every rank of `group`, reachable from this process: what rmlk_b200_matmul_tp stores into.
+
+    Allocation and the exchange of addresses go through torch's symmetric memory (one allocation of the same size on
+    every rank, mapped into every process of the group).  `ptrs[r]` is rank r's buffer as seen from this process.
+    No multicast object is bound: the data path uses plain peer stores only."""
+
+    def __init__(self, nbytes: int, device: torch.device, group=None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch.distributed._symmetric_memory as symm_mem
+        group = group if group is not None else dist.group.WORLD
+        self.nbytes = (nbytes + 255) // 256 * 256
+        self.local = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+        self.handle = symm_mem.rendezvous(self.local, group=group)
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        if len(self.ptrs) != self.world:
+            raise RuntimeError("symmetric memory returned a pointer table of the wrong size")
+        self.local.zero_()
+
+
+def tp_layout(m_max: int, n_total: int, world: int):
+    """Byte layout of one rank's peer-visible buffer for PeerStoreColumnParallelMatMul: two output buffers
+    [m_max, n_total] fp32 (even / odd calls) followed by the flag array (`world` 32-bit words, padded to 256 bytes).
+    Returns (bytes of one output buffer, offset of the flags, total bytes)."""
+    if m_max <= 0 or n_total <= 0 or n_total % 4 or not 1 <= world <= 8:
+        raise ValueError("tp_layout: m_max, n_total must be positive, n_total a multiple of 4, world in 1..8")
+    out_bytes = (m_max * n_total * 4 + 255) // 256 * 256
+    return out_bytes, 2 * out_bytes, 2 * out_bytes + 256
+
+
+class PeerStoreColumnParallelMatMul:
+    """y[M, N] = x[M, K] @ W[K, N], W split by columns over the ranks of `group`; the rank that computes a block of
+    columns writes it into every rank's output from the MatMul kernel itself (include/rmlk_b200.h: rmlk_b200_matmul_tp,
+    rmlk_b200_tp_wait).  x must hold the same values on every rank.  The returned tensor is a view of one of two
+    alternating output buffers: it stays valid until the call after next."""
+
+    def __init__(self, w_shard: torch.Tensor, shards: Sequence[Tuple[int, int]], m_max: int, group=None, buffers=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        if len(shards) != self.world:
+            raise ValueError("one column range per rank")
+        self.shards = list(shards)
+        self.n = self.shards[-1][1]
+        a, b = self.shards[self.rank]
+        if w_shard.shape[1] != b - a:
+            raise ValueError(f"rank {self.rank}: weight shard has {w_shard.shape[1]} columns, expected {b - a}")
+        if any(lo % 4 or hi % 4 for lo, hi in self.shards):
+            raise ValueError("shard boundaries must be multiples of 4 columns")
+        self.w = w_shard.contiguous()
+        self.k = w_shard.shape[0]
+        self.m_max = m_max
+        self.out_bytes, self.flag_off, total = tp_layout(m_max, self.n, self.world)
+        self.buffers = buffers if buffers is not None else PeerBuffers(total, w_shard.device, group)
+        if self.buffers.nbytes < total:
+            raise ValueError("peer buffers are smaller than tp_layout() asks for")
+        self.epoch = 0
+        self._ws = None
+        from . import dtypes as dt
+        self._f32 = dt.F32
+        self._lib = self._load_library()
+        self._status = torch.zeros(1, dtype=torch.int32, device=w_shard.device)
+        if dist.is_initialized() and self.world > 1:
+            dist.barrier(group)   # every rank's flags are zero before anybody signals
+
+    def _load_library(self):
+        from ._lib import lib
+        return lib()
+
+    def _peers(self, buf: int):
+        import ctypes
+
+        class Peers(ctypes.Structure):
+            _fields_ = [("world", ctypes.c_int), ("rank", ctypes.c_int), ("out", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8)]
+
+        p = Peers()
+        p.world, p.rank = self.world, self.rank
+        for r in range(self.world):
+            p.out[r] = self.buffers.ptrs[r] + buf * self.out_bytes
+            p.flags[r] = self.buffers.ptrs[r] + self.flag_off
+        return p
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        m = x.shape[0]
+        if m > self.m_max or x.shape[1] != self.k:
+            raise ValueError(f"activations {tuple(x.shape)} do not fit m_max {self.m_max} / K {self.k}")
+        self.epoch += 1
+        buf = self.epoch & 1
+        self._store_block(x.contiguous(), buf)   # this rank's columns into every rank's buffer `buf`, then the flags
+        self._wait_all()                         # until every rank's flag in the local array has reached the epoch
+        return self.buffers.local[buf * self.out_bytes: buf * self.out_bytes + m * self.n * 4].view(torch.float32).view(m, self.n)
+
+    # The two device steps, as calls into the library; a host stand-in overrides them to exercise the bookkeeping on CPU ranks.
+    def _store_block(self, x: torch.Tensor, buf: int):
+        import ctypes
+        m = x.shape[0]
+        a, b = self.shards[self.rank]
+        need = int(self._lib.rmlk_b200_matmul_tp_workspace_bytes(self._f32, ctypes.c_int64(m), ctypes.c_int64(b - a), ctypes.c_int64(self.k)))
+        if self._ws is None or self._ws.numel() < need:
+            self._ws = torch.empty(max(need, 256), dtype=torch.uint8, device=x.device)
+        peers = self._peers(buf)
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        rc = self._lib.rmlk_b200_matmul_tp(stream, self._f32, ctypes.c_int64(m), ctypes.c_int64(b - a), ctypes.c_int64(self.k),
+                                           ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(self.w.data_ptr()), ctypes.c_int64(self.n), ctypes.c_int64(a),
+                                           ctypes.byref(peers), ctypes.c_uint(self.epoch), ctypes.c_void_p(self._ws.data_ptr()),
+                                           ctypes.c_size_t(self._ws.numel()), ctypes.c_void_p(self._status.data_ptr()))
+        if rc != 0:
+            from ._lib import last_error
+            raise RuntimeError(f"rmlk_b200_matmul_tp failed ({rc}): {last_error()}")
+
+    def _wait_all(self):
+        import ctypes
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        rc = self._lib.rmlk_b200_tp_wait(stream, ctypes.c_void_p(self.buffers.ptrs[self.rank] + self.flag_off), self.world, ctypes.c_uint(self.epoch),
+                                         ctypes.c_void_p(self._status.data_ptr()))
+        if rc != 0:
+            from ._lib import last_error
+            raise RuntimeError(f"rmlk_b200_tp_wait failed ({rc}): {last_error()}")
+
+    def status(self) -> int:
+        """Device status word (synchronises): 0, or RMLK_ERR_TIMEOUT (5) if a rank never arrived within the wait's bound."""
+        return int(self._status.item())

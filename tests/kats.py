@@ -11,7 +11,7 @@ KATS_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "k
 
 # Ops of the reference that are outside the operator path (CNN ops) or whose test relies on attribute
 # forms of shape-only ops that this build does not take (Constant's value_floats / value_ints ...).
-OUT_OF_SCOPE_OPS = {"Conv", "Gemm", "GlobalAveragePool", "MaxPool", "Constant"}
+OUT_OF_SCOPE_OPS = {"Conv", "GlobalAveragePool", "MaxPool", "Constant"}
 
 
 def _val(v):

@@ -216,3 +216,46 @@ def test_errors_match_reference_behaviour(rt):
     assert "IncompatibleDimForMul" in str(err)
     err = rt.OpTest(rt.Op.Softmax).input([2, 3], np.zeros(6, np.float32)).attr("axis", 0).run_err()
     assert "unsupported input" in str(err).lower()
+
+
+def test_gemm_alpha_beta_bias_and_transposes(rt):
+    """ONNX Gemm beyond the reference's two op tests (backend/gemm.rs:262-290): Y = alpha * op(A) * op(B) + beta * C with the
+    bias shapes its backend accepts (backend/gemm.rs:219-240: a vector of N entries, a vector of M entries, [M, N] with
+    ones), both transposes and non-default alpha / beta, against the oracle's float64 restatement at the MatMul bar."""
+    from oracle import run_op
+    r = np.random.default_rng(21)
+    M, K, N = 5, 7, 12
+    for ta in (0, 1):
+        for tb in (0, 1):
+            a = r.standard_normal((K, M) if ta else (M, K), dtype=np.float32)
+            b = r.standard_normal((N, K) if tb else (K, N), dtype=np.float32)
+            for cshape in (None, (N,), (M,), (M, N), (1, N), (M, 1), (1,)):
+                for alpha, beta in ((1.0, 1.0), (0.5, 2.0)):
+                    t = rt.OpTest(rt.Op.Gemm).input(list(a.shape), a).input(list(b.shape), b)
+                    ins = [a, b]
+                    if cshape is not None:
+                        c = r.standard_normal(cshape, dtype=np.float32)
+                        t.input(list(cshape), c)
+                        ins.append(c)
+                    attrs = {"transA": ta, "transB": tb, "alpha": alpha, "beta": beta}
+                    for k, v in attrs.items():
+                        t.attr(k, v)
+                    got = t.output([M, N]).run(np.float32)
+                    want = run_op.run("Gemm", ins, attrs)
+                    assert t.result_shape == [M, N]
+                    assert np.max(np.abs(got.reshape(M, N) - want)) <= 1e-4 * np.max(np.abs(want)), (ta, tb, cshape, alpha, beta)
+    # a shape the tensor-core MatMul takes, with a row bias (the classifier head of a CNN in the reference's own use)
+    a = r.standard_normal((64, 512), dtype=np.float32)
+    b = r.standard_normal((512, 1024), dtype=np.float32) * np.float32(0.05)
+    c = r.standard_normal((1024,), dtype=np.float32)
+    got = rt.OpTest(rt.Op.Gemm).input([64, 512], a).input([512, 1024], b).input([1024], c).output([64, 1024]).run(np.float32).reshape(64, 1024)
+    want = run_op.run("Gemm", [a, b, c], {})
+    assert np.max(np.abs(got - want)) <= 1e-4 * np.max(np.abs(want))
+    # f16: fp32 arithmetic, one rounding per stage
+    ah, bh, ch = a[:8, :64].astype(np.float16), b[:64, :32].astype(np.float16), c[:32].astype(np.float16)
+    goth = rt.OpTest(rt.Op.Gemm).input([8, 64], ah).input([64, 32], bh).input([32], ch).output([8, 32]).run(np.float16).reshape(8, 32)
+    wanth = run_op.run("Gemm", [ah, bh, ch], {}).astype(np.float64)
+    assert np.max(np.abs(goth.astype(np.float64) - wanth)) <= 4e-3 * max(1.0, np.max(np.abs(wanth)))
+    # rank-3 operands are rejected, as in backend/gemm.rs:196-204
+    err = rt.OpTest(rt.Op.Gemm).input([1, 2, 2], np.ones(4, np.float32)).input([2, 2], np.ones(4, np.float32)).output([2, 2]).run_err()
+    assert "rank 2" in str(err)

@@ -29,8 +29,10 @@ def test_static_scratch_matmul_matches_regular_entry_point(cuda, shape):
     m, n, k = shape
     l = lib()
     l.rmlk_b200_matmul_static_scratch_bytes.restype = ctypes.c_size_t
+    from rmlk_b200 import dtypes as dt
     need = K.matmul_workspace_bytes(1, m, n, k)
-    assert 0 < need <= l.rmlk_b200_matmul_static_scratch_bytes(), "case must exercise the split-K scratch"
+    assert need > 0, "case must exercise the split-K scratch"
+    assert l.rmlk_b200_matmul_static_supported(dt.F32, ctypes.c_int64(1), ctypes.c_int64(m), ctypes.c_int64(n), ctypes.c_int64(k)) == 1
     stream = torch.cuda.current_stream().cuda_stream
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     ws = torch.empty(need // 4, device="cuda")
@@ -58,7 +60,9 @@ def test_static_scratch_matmul_rejects_oversized_shapes(cuda):
     l = lib()
     l.rmlk_b200_matmul_static_scratch_bytes.restype = ctypes.c_size_t
     m, n, k = 256, 512, 8192   # eighteen K-splits of 512 KiB each: more than the 8 MiB array
+    from rmlk_b200 import dtypes as dt
     assert K.matmul_workspace_bytes(1, m, n, k) > l.rmlk_b200_matmul_static_scratch_bytes()
+    assert l.rmlk_b200_matmul_static_supported(dt.F32, ctypes.c_int64(1), ctypes.c_int64(m), ctypes.c_int64(n), ctypes.c_int64(k)) == 0
     a = torch.randn(m, k, device="cuda")
     w = torch.randn(k, n, device="cuda")
     out = torch.zeros(m, n, device="cuda")
