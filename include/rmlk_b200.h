@@ -318,14 +318,6 @@ RMLK_API size_t rmlk_b200_matmul_static_scratch_bytes(void);
 /* 1 if rmlk_b200_matmul_static takes the shape (its least scratch need fits the built-in array), 0 if it would be rejected. */
 RMLK_API int rmlk_b200_matmul_static_supported(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k);
 RMLK_API size_t rmlk_b200_matmul_workspace_bytes(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k);
-/* How the persistent tensor-core MatMul kernel (M >= 5, N % 128 == 0, K % 32 == 0) divides a shape over the SMs; pure
- * host arithmetic, for inspection and tests (no counterpart in the reference: cuBLAS plans internally).  The work is the
- * sequence of the k-blocks (32 of K) of all [rows x 128] tiles of C; CTA c of `ctas` takes units
- * [units * c / ctas, units * (c + 1) / ctas), a unit being `k-blocks per unit` consecutive k-blocks.
- * out[0..7] = rows per tile, k-blocks per tile, row tiles per column block, k-blocks per unit (1: a CTA's range may
- * start and end inside a tile, whose partial sums then meet in the scratch buffer; k-blocks per tile: whole tiles only),
- * ctas, tiles, units, scratch bytes needed (0 when no tile is shared). */
-RMLK_API int rmlk_b200_matmul_schedule(int64_t m, int64_t n, int64_t k, int64_t* out);
 
 /* y[m, n] = alpha * y + beta * c, in place, c read through element strides (0 broadcasts a dimension; c = NULL: y = alpha * y).
  * The epilogue of ONNX Gemm after the MatMul: replaces the reference's alpha inside the cuBLAS call

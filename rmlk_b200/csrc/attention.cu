@@ -362,36 +362,33 @@ __global__ void __launch_bounds__(128) gqa_decode_attention_split_kernel(AttnSpl
 // One pass over K and V ("flash" decode): one CTA of 8 warps per problem, every warp works through blocks of 32 keys on
 // its own (block w, w + 8, ...) with a running softmax - maximum m, sum l and weighted value sums a[4][D] per query row,
 // rescaled whenever a block raises the maximum - and the 8 warps are merged once at the end (M = max m,
-// L = sum l exp(m - M), out = sum a exp(m - M) / L).  K and V of a block are read back to back, so the stream from HBM
-// never stops for a softmax over the whole row; nothing but the 4 x 32 probabilities of a block passes through shared
-// memory; any number of keys.
-//  scores   lane = key: a lane reads its whole K row (D floats, 16 bytes per load, 8 loads in flight) and forms the 4
-//           dot products with q read from shared memory as broadcasts - no shuffles in the inner loop;
-//  softmax  block maximum and sum by warp shuffles (2 x 5 steps per row and block);
-//  values   lane = 4 columns of a V row (a warp-wide load reads 32 / LPR whole rows, coalesced), probabilities from
-//           shared memory.
+// L = sum l exp(m - M), out = sum a exp(m - M) / L).  K and V of a block are requested back to back (the V loads go out
+// before the block's softmax is worked out), so the stream from HBM never stops for a softmax over the whole row; only
+// the 4 x 32 scores / probabilities of a block pass through shared memory; any number of keys.  Loads are as in the
+// kernels above: LPR lanes cover a row with one 16-byte load each, dot products by the same FMA order and shuffle
+// butterfly.  D = 16 / 32 / 64.
 // ---------------------------------------------------------------------------------------------------------------------
 template <int LPR>
 __global__ void __launch_bounds__(256, 2) gqa_decode_flash_kernel(AttnParams p) {
     dep_sync();
     constexpr int D = 4 * LPR;
-    constexpr int RPI = 32 / LPR;            // rows of V per warp-wide load
-    constexpr int KC = LPR < 8 ? LPR : 8;    // 16-byte pieces of a K row in flight per lane
-    __shared__ __align__(16) float s_q[4][D];
-    __shared__ __align__(16) float s_p[8][32][4];    // per warp: probabilities of the current block, [key][row]
+    constexpr int RPI = 32 / LPR;   // rows of K / V per warp-wide load
+    constexpr int UN = LPR;         // loads per lane and block: 32 keys
+    __shared__ __align__(16) float s_e[8][32][4];    // per warp: scores, then probabilities, of the current block: [key][row]
     __shared__ float s_m[8][4], s_l[8][4];
     __shared__ __align__(16) float s_a[8][4][D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPR, rsel = lane / LPR;
     const int64_t prob = blockIdx.x;
     const int T = p.T;
-    for (int i = threadIdx.x; i < 4 * D; i += 256) {
-        const int m = i / D;
-        s_q[m][i - m * D] = m < p.rows ? p.q[(prob * p.rows + m) * D + (i - m * D)] : 0.f;
+    float4 a[4];
+#pragma unroll
+    for (int m = 0; m < 4; m++) {
+        a[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (m < p.rows) a[m] = __ldg(reinterpret_cast<const float4*>(p.q + (prob * p.rows + m) * D + 4 * sub));
     }
-    __syncthreads();
     const int64_t b = prob / p.kv_heads, h0 = (prob % p.kv_heads) * p.rows;
-    const float* __restrict__ K = p.k + prob * p.kb;
+    const float* __restrict__ K = p.k + prob * p.kb + 4 * sub;
     const float* __restrict__ V = p.v + prob * p.vb + 4 * sub;
     float m_run[4], l_run[4], acc[4][4];
 #pragma unroll
@@ -403,77 +400,89 @@ __global__ void __launch_bounds__(256, 2) gqa_decode_flash_kernel(AttnParams p) 
     }
     const int n_blocks = (T + 31) >> 5;
     for (int blk = warp; blk < n_blocks; blk += 8) {
-        const int t = blk * 32 + lane;
-        const bool valid = t < T;
-        // ---- scores of this lane's key ----
-        float sc[4] = {0.f, 0.f, 0.f, 0.f};
-        const uint4* krow = reinterpret_cast<const uint4*>(K + static_cast<int64_t>(valid ? t : 0) * D);
+        const int tw = blk * 32;
+        uint4 bv[UN];
 #pragma unroll
-        for (int c0 = 0; c0 < LPR; c0 += KC) {
-            uint4 kv[KC];
-#pragma unroll
-            for (int c = 0; c < KC; c++) kv[c] = valid ? __ldg(krow + c0 + c) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-            for (int c = 0; c < KC; c++) {
-                const float kx = __uint_as_float(kv[c].x), ky = __uint_as_float(kv[c].y), kz = __uint_as_float(kv[c].z), kw = __uint_as_float(kv[c].w);
-#pragma unroll
-                for (int m = 0; m < 4; m++) {
-                    const float4 qv = *reinterpret_cast<const float4*>(&s_q[m][4 * (c0 + c)]);
-                    sc[m] = fmaf(qv.w, kw, fmaf(qv.z, kz, fmaf(qv.y, ky, fmaf(qv.x, kx, sc[m]))));
-                }
-            }
-        }
-        // ---- running softmax ----
-        float pr[4];
-#pragma unroll
-        for (int m = 0; m < 4; m++) {
-            float x = -INFINITY;
-            if (valid && m < p.rows) {
-                x = __fmul_rn(sc[m], p.scale);
-                if (p.mask) x = __fadd_rn(x, p.mask[b * p.ms_b + (h0 + m) * p.ms_h + t]);
-            }
-            float mx = x;
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            const float m_new = fmaxf(m_run[m], mx);
-            const float e = m_new == -INFINITY ? 0.f : expf(x - m_new);          // x = -inf gives 0
-            const float corr = m_run[m] == -INFINITY ? 0.f : expf(m_run[m] - m_new);
-            float sum = e;
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            l_run[m] = fmaf(l_run[m], corr, sum);
-            m_run[m] = m_new;
-            pr[m] = e;
-#pragma unroll
-            for (int j = 0; j < 4; j++) acc[m][j] *= corr;
+        for (int u = 0; u < UN; u++) {
+            const int t = tw + u * RPI + rsel;
+            bv[u] = make_uint4(0, 0, 0, 0);
+            if (t < T) bv[u] = ld_stream_u4(K + static_cast<int64_t>(t) * D);
         }
         __syncwarp();  // the previous block's probabilities have been read
-        *reinterpret_cast<float4*>(&s_p[warp][lane][0]) = make_float4(pr[0], pr[1], pr[2], pr[3]);
-        __syncwarp();
-        // ---- values: 32 keys, RPI rows per load ----
 #pragma unroll
-        for (int u0 = 0; u0 < LPR; u0 += 8) {
-            uint4 vv[8];
+        for (int u = 0; u < UN; u++) {
+            const int t = tw + u * RPI + rsel;
+            const float bx = __uint_as_float(bv[u].x), by = __uint_as_float(bv[u].y), bz = __uint_as_float(bv[u].z), bw = __uint_as_float(bv[u].w);
+            float part[4];
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                const int tt = blk * 32 + (u0 + u) * RPI + rsel;
-                vv[u] = make_uint4(0, 0, 0, 0);
-                if (u0 + u < LPR && tt < T) vv[u] = ld_stream_u4(V + static_cast<int64_t>(tt) * D);
-            }
+            for (int m = 0; m < 4; m++) part[m] = fmaf(a[m].w, bw, fmaf(a[m].z, bz, fmaf(a[m].y, by, a[m].x * bx)));
+            const bool up1 = (sub & (LPR / 2)) != 0;
+            const float r0 = __shfl_xor_sync(0xffffffffu, up1 ? part[0] : part[2], LPR / 2);
+            const float r1 = __shfl_xor_sync(0xffffffffu, up1 ? part[1] : part[3], LPR / 2);
+            const float q0 = (up1 ? part[2] : part[0]) + r0;
+            const float q1 = (up1 ? part[3] : part[1]) + r1;
+            const bool up2 = (sub & (LPR / 4)) != 0;
+            const float r2 = __shfl_xor_sync(0xffffffffu, up2 ? q0 : q1, LPR / 4);
+            float v = (up2 ? q1 : q0) + r2;
 #pragma unroll
-            for (int u = 0; u < 8; u++) {
-                if (u0 + u < LPR) {
-                    const float4 pw = *reinterpret_cast<const float4*>(&s_p[warp][(u0 + u) * RPI + rsel][0]);
-                    const float vx = __uint_as_float(vv[u].x), vy = __uint_as_float(vv[u].y), vz = __uint_as_float(vv[u].z), vw = __uint_as_float(vv[u].w);
-                    const float pm[4] = {pw.x, pw.y, pw.z, pw.w};
-#pragma unroll
-                    for (int m = 0; m < 4; m++) {
-                        acc[m][0] = fmaf(pm[m], vx, acc[m][0]);
-                        acc[m][1] = fmaf(pm[m], vy, acc[m][1]);
-                        acc[m][2] = fmaf(pm[m], vz, acc[m][2]);
-                        acc[m][3] = fmaf(pm[m], vw, acc[m][3]);
-                    }
+            for (int off = LPR / 8; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+            const int m = 2 * (up1 ? 1 : 0) + (up2 ? 1 : 0);
+            if ((sub & (LPR / 4 - 1)) == 0) {
+                float x = -INFINITY;  // keys beyond the end and rows that do not exist
+                if (t < T && m < p.rows) {
+                    x = __fmul_rn(v, p.scale);
+                    if (p.mask) x = __fadd_rn(x, p.mask[b * p.ms_b + (h0 + m) * p.ms_h + t]);
                 }
+                s_e[warp][u * RPI + rsel][m] = x;
+            }
+        }
+        // the values are requested now; the block's softmax is worked out while they are on their way
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const int t = tw + u * RPI + rsel;
+            bv[u] = make_uint4(0, 0, 0, 0);
+            if (t < T) bv[u] = ld_stream_u4(V + static_cast<int64_t>(t) * D);
+        }
+        __syncwarp();
+        float corr[4];
+        {
+            const float4 sc = *reinterpret_cast<const float4*>(&s_e[warp][lane][0]);  // lane = key
+            const float sv[4] = {sc.x, sc.y, sc.z, sc.w};
+            float ev[4];
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                float mx = sv[m];
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                const float m_new = fmaxf(m_run[m], mx);
+                const float e = m_new == -INFINITY ? 0.f : expf(sv[m] - m_new);   // a score of -inf gives 0
+                corr[m] = m_run[m] == -INFINITY ? 0.f : expf(m_run[m] - m_new);
+                float sum = e;
+#pragma unroll
+                for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                l_run[m] = fmaf(l_run[m], corr[m], sum);
+                m_run[m] = m_new;
+                ev[m] = e;
+            }
+            __syncwarp();
+            *reinterpret_cast<float4*>(&s_e[warp][lane][0]) = make_float4(ev[0], ev[1], ev[2], ev[3]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int m = 0; m < 4; m++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[m][j] *= corr[m];
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            const float4 pw = *reinterpret_cast<const float4*>(&s_e[warp][u * RPI + rsel][0]);
+            const float vx = __uint_as_float(bv[u].x), vy = __uint_as_float(bv[u].y), vz = __uint_as_float(bv[u].z), vw = __uint_as_float(bv[u].w);
+            const float pm[4] = {pw.x, pw.y, pw.z, pw.w};
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                acc[m][0] = fmaf(pm[m], vx, acc[m][0]);
+                acc[m][1] = fmaf(pm[m], vy, acc[m][1]);
+                acc[m][2] = fmaf(pm[m], vz, acc[m][2]);
+                acc[m][3] = fmaf(pm[m], vw, acc[m][3]);
             }
         }
     }
@@ -593,7 +602,7 @@ extern "C" int rmlk_b200_gqa_decode_attention(rmlk_stream_t stream, int dtype, i
             case 16: return attn_flash_launch<4>(st, p, problems);
             case 32: return attn_flash_launch<8>(st, p, problems);
             case 64: return attn_flash_launch<16>(st, p, problems);
-            default: return attn_flash_launch<32>(st, p, problems);
+            default: break;  // head_dim 128: 32 loads of 16 bytes per lane and block do not fit the registers; the two-pass kernel below
         }
     }
     switch (head_dim) {

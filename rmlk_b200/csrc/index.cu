@@ -402,6 +402,32 @@ __global__ void __launch_bounds__(256) scatter_nd_kernel(ScatterParams p, const 
     }
 }
 
+// Plain assignment of whole slices in 16-byte units (slice length, bases and every slice offset multiples of 16 bytes):
+// four times fewer, four times wider accesses than the element kernel.
+__global__ void __launch_bounds__(256) scatter_nd_units_kernel(ScatterParams p, uint32_t unit_elems, const int64_t* __restrict__ indices,
+                                                               const uint4* __restrict__ updates, uint4* __restrict__ out, int* __restrict__ status) {
+    dep_sync();
+    const uint64_t slice_units = p.slice_len / unit_elems;
+    const uint64_t total = p.total / unit_elems;
+    for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<uint64_t>(gridDim.x) * 256) {
+        const uint64_t t = i / slice_units;
+        const uint64_t e = i - t * slice_units;
+        int64_t off = 0;
+        bool ok = true;
+        for (int j = 0; j < p.k; j++) {
+            int64_t ix = indices[t * p.k + j];
+            if (ix < 0) ix += p.dim[j];
+            if (ix < 0 || ix >= p.dim[j]) {
+                if (status && e == 0) *status = 1;
+                ok = false;
+                break;
+            }
+            off += ix * p.stride[j];
+        }
+        if (ok) out[static_cast<uint64_t>(off) / unit_elems + e] = updates[i];
+    }
+}
+
 template <typename T>
 static int scatter_typed(cudaStream_t st, int reduction, const ScatterParams& p, const void* indices, const void* updates, void* out, int* status) {
     const unsigned grid = static_cast<unsigned>((p.total + 255) / 256);
@@ -896,6 +922,15 @@ extern "C" int rmlk_b200_scatter_nd(rmlk_stream_t stream, int reduction, int dty
     if (data != out && run > 0) RMLK_CUDA(cudaMemcpyAsync(out, data, static_cast<size_t>(run) * es, cudaMemcpyDeviceToDevice, st));
     if (p.total == 0 || run == 0) return RMLK_OK;
     if (!indices || !updates) return fail(RMLK_ERR_INVALID_ARG, "scatter_nd: NULL tensor pointer");
+    if (reduction == RMLK_SCATTER_NONE && (p.slice_len * es) % 16 == 0 && aligned_to(out, 16) && aligned_to(updates, 16)) {
+        // every slice then starts on a 16-byte boundary: the strides of the indexed dimensions are multiples of the slice length
+        const uint32_t unit_elems = static_cast<uint32_t>(16 / es);
+        const uint64_t units = p.total / unit_elems;
+        launch_dep(scatter_nd_units_kernel, dim3(flat_grid(static_cast<int64_t>(units), 256, 16)), dim3(256), 0, st, p, unit_elems,
+                   static_cast<const int64_t*>(indices), static_cast<const uint4*>(updates), static_cast<uint4*>(out), status);
+        RMLK_CHECK_LAUNCH("scatter_nd_units_kernel");
+        return RMLK_OK;
+    }
     switch (dtype) {
         case RMLK_F16: return scatter_typed<__half>(st, reduction, p, indices, updates, out, status);
         case RMLK_F32: return scatter_typed<float>(st, reduction, p, indices, updates, out, status);

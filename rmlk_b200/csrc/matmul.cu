@@ -738,7 +738,6 @@ namespace rmlk {
 // tensor-core path (matmul_tc.cu)
 bool tc_matmul_eligible(int64_t m, int64_t n, int64_t k, const void* a, const void* w, const void* c);
 size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k);
-size_t tc_matmul_min_workspace_bytes(int64_t m, int64_t n, int64_t k);
 int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, const float* w, float* c, void* workspace,
               size_t workspace_bytes, int* status, int* ksplit_out, int flags, int64_t ld, const TcPeers* peers = nullptr);
 int tc_matmul_plan(int64_t m, int64_t n, int64_t k);
@@ -1105,11 +1104,7 @@ static void* static_scratch_ptr(int* rc_out) {
 
 extern "C" size_t rmlk_b200_matmul_static_scratch_bytes(void) { return RMLK_STATIC_SCRATCH_BYTES; }
 
-// The least scratch a shape can run with.  (rmlk_b200_matmul_workspace_bytes reports what lets every kernel choice run; the
-// tensor-core MatMul has a second schedule that wants more than the built-in array holds for some shapes, and
-// rmlk_b200_matmul_ex picks the schedule that fits what it is lent.)
 static size_t matmul_least_scratch(int dtype, int64_t batch, int64_t m, int64_t n, int64_t k) {
-    if (dtype == RMLK_F32 && batch == 1 && m >= TC_MIN_ROWS && tc_enabled() && n % 128 == 0 && k % 32 == 0 && k >= 32) return tc_matmul_min_workspace_bytes(m, n, k);
     return rmlk_b200_matmul_workspace_bytes(dtype, batch, m, n, k);
 }
 

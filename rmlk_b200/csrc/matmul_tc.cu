@@ -10,9 +10,11 @@
 // is exact in fp32.  The MMA itself reads only the tf32 part of an operand word, so the raw fp32 word serves
 // as hi without any conversion and only lo has to be computed (one AND, one subtraction).  Per k-step three
 // MMAs' worth of products, hi*hi + hi*lo + lo*hi, accumulate in fp32 (the dropped lo*lo term is below 2^-20
-// relative); measured error against fp64 is about 1e-5 of the result's scale.  The first two products are
-// issued as one MMA: the lo tile of the activations follows the raw tile in shared memory and a single
-// descriptor with N = 2 MT covers both, filling two accumulator blocks that the epilogue adds.
+// relative).  Two of them are issued as one MMA: an activation stage holds the lo tile followed by the raw tile, and a
+// single descriptor with N = 2 MT covers both, so W_hi x [x_lo; x_hi] fills two accumulator blocks (an MMA costs about the
+// same whatever its N; the number of MMAs per k-block is what bounds this kernel at small M).  W_lo x x_hi goes into the
+// hi x lo block: the tensor core truncates when it adds into its accumulator, and keeping both small products out of
+// the large hi x hi sums halves the error (about 5e-6 of the result's scale at K = 2048).  The epilogue adds the blocks.
 //
 // Data path per k-block of 32:
 //   warp 0     TMA: one unswizzled [32 k][128 n] box of W (512-byte row pieces; four 32-wide boxes streamed a fifth
@@ -38,12 +40,9 @@
 // Every mbarrier wait is bounded: on expiry the thread raises a CTA-wide abort flag, records
 // RMLK_ERR_TIMEOUT in the caller's status word, and every role falls through to the common exit where TMEM
 // is released.  Every TMA load targets this CTA's own shared memory.
-#include <atomic>
-#include <chrono>
 #include <mutex>
 
 #include "matmul_tc_kernel.cuh"
-#include "matmul_tc_stream.cuh"
 
 namespace rmlk {
 namespace tc {
@@ -76,7 +75,7 @@ static bool make_map_2d(CUtensorMap* map, const void* ptr, uint64_t inner, uint6
               swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MT, int SW, int SA, int G>
+template <int MT, int SW, int SA, int G, bool PEERS>
 static int launch(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tmA, const TcParams& p, dim3 grid) {
     using L = SmemLayout<MT, SW, SA>;
     // The kernel's dynamic shared memory limit is raised once per device; std::call_once makes a thread that arrives
@@ -87,7 +86,7 @@ static int launch(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tm
     cudaError_t cfg_err = cudaSuccess;
     if (dev >= 0 && dev < 64)
         std::call_once(configured[dev], [&] {
-            cfg_err = cudaFuncSetAttribute(tc_gemm_kernel<MT, SW, SA, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
+            cfg_err = cudaFuncSetAttribute(tc_gemm_kernel<MT, SW, SA, G, PEERS>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
         });
     RMLK_CUDA(cfg_err);
     // launched so that it may be scheduled while the previous kernel of the stream drains (the kernel waits, see
@@ -113,125 +112,12 @@ static int launch(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tm
     }
     cfg.attrs = at;
     cfg.numAttrs = na;
-    RMLK_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<MT, SW, SA, G>, tmW, tmA, p));
+    RMLK_CUDA(cudaLaunchKernelEx(&cfg, tc_gemm_kernel<MT, SW, SA, G, PEERS>, tmW, tmA, p));
     RMLK_CHECK_LAUNCH("tc_gemm_kernel");
     return RMLK_OK;
 }
 
-template <int MT, int SW, int SA>
-static int launch_stream(cudaStream_t st, const CUtensorMap& tmW, const CUtensorMap& tmA, const StreamParams& p, unsigned grid) {
-    using L = StreamSmem<MT, SW, SA>;
-    static std::once_flag configured[64];  // once per device; a concurrent first call waits for the attribute to be set
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaError_t cfg_err = cudaSuccess;
-    if (dev >= 0 && dev < 64)
-        std::call_once(configured[dev], [&] {
-            cfg_err = cudaFuncSetAttribute(tc_stream_kernel<MT, SW, SA>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::TOTAL);
-        });
-    RMLK_CUDA(cfg_err);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(STREAM_THREADS);
-    cfg.dynamicSmemBytes = L::TOTAL;
-    cfg.stream = st;
-    cudaLaunchAttribute at[1];
-    unsigned na = 0;
-    if (dep_launch_enabled()) {
-        at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        at[na].val.programmaticStreamSerializationAllowed = 1;
-        na++;
-    }
-    cfg.attrs = at;
-    cfg.numAttrs = na;
-    RMLK_CUDA(cudaLaunchKernelEx(&cfg, tc_stream_kernel<MT, SW, SA>, tmW, tmA, p));
-    RMLK_CHECK_LAUNCH("tc_stream_kernel");
-    return RMLK_OK;
-}
-
-// A value no earlier launch of this process has used (and, being 64 pseudo-random bits, one that leftover bytes in a
-// caller's scratch buffer will not hold): what a partial tile's flags are set to.
-static unsigned long long next_token() {
-    static std::atomic<unsigned long long> counter{static_cast<unsigned long long>(std::chrono::steady_clock::now().time_since_epoch().count())};
-    unsigned long long z = counter.fetch_add(0x9e3779b97f4a7c15ull, std::memory_order_relaxed) + 0x9e3779b97f4a7c15ull;
-    z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
-    z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
-    z ^= z >> 31;
-    return z | 1ull;  // never 0, the value of a cleared flag
-}
-
 }  // namespace tc
-
-// ---- the persistent kernel's schedule ------------------------------------------------------------------------------
-struct StreamPlan {
-    int mt, k_iters, m_tiles, gran;
-    bool strided = false;
-    unsigned grid;
-    int64_t tiles, units;
-    bool partials;
-    size_t flag_bytes, ws_bytes;
-};
-
-static bool tc_stream_enabled() {
-    static const bool v = [] {
-        const char* e = getenv("RMLK_B200_NO_TC_STREAM");
-        return !(e && e[0] == '1');
-    }();
-    return v;
-}
-
-static StreamPlan stream_plan(int64_t m, int64_t n, int64_t k) {
-    StreamPlan pl;
-    pl.mt = m <= 64 ? 64 : 128;
-    pl.k_iters = static_cast<int>(k / tc::BK);
-    pl.m_tiles = static_cast<int>(ceil_div64(m, pl.mt));
-    pl.tiles = (n / tc::BN) * pl.m_tiles;
-    const int64_t sms = sm_count();
-    const int64_t total_kb = pl.tiles * pl.k_iters;
-    // Whole tiles per CTA when that already balances (a multiple of the SM count, or so many tiles that one more or
-    // less does not matter); otherwise ranges of k-blocks that may cut a tile, at least 4 k-blocks each and long enough
-    // that no tile is shared by more than STREAM_MAX_GROUP CTAs.
-    static const int mode = [] { const char* e = getenv("RMLK_B200_TC_STREAM_MODE"); return e ? atoi(e) : 0; }();
-    pl.strided = mode == 2;
-    if (pl.tiles % sms == 0 || pl.tiles >= 8 * sms || mode >= 1) {
-        pl.gran = pl.k_iters;
-        pl.units = pl.tiles;
-        pl.grid = static_cast<unsigned>(pl.tiles < sms ? pl.tiles : sms);
-        pl.partials = false;
-    } else {
-        pl.gran = 1;
-        pl.units = total_kb;
-        int64_t per_min = ceil_div64(pl.k_iters, tc::STREAM_MAX_GROUP - 2);
-        if (per_min < 4) per_min = 4;
-        int64_t g = total_kb / per_min;
-        if (g > sms) g = sms;
-        if (g < 1) g = 1;
-        pl.grid = static_cast<unsigned>(g);
-        pl.partials = g > 1;
-    }
-    pl.flag_bytes = (static_cast<size_t>(2) * pl.grid * tc::STREAM_MAX_GROUP * sizeof(unsigned long long) + 255) & ~static_cast<size_t>(255);
-    pl.ws_bytes = pl.partials ? pl.flag_bytes + static_cast<size_t>(2) * pl.grid * pl.mt * tc::BN * sizeof(float) : 0;
-    return pl;
-}
-
-}  // namespace rmlk
-
-extern "C" int rmlk_b200_debug_stream_times(long long* out) {
-    return cudaMemcpyFromSymbol(out, rmlk::tc::g_stream_dbg, sizeof(long long) * 32) == cudaSuccess ? 0 : 1;
-}
-
-// The persistent MatMul kernel's schedule for a shape, for inspection and tests (pure host arithmetic):
-// out = {rows per tile, k-blocks per tile, row tiles, k-blocks per work unit, CTAs, tiles, work units, scratch bytes}.
-extern "C" int rmlk_b200_matmul_schedule(int64_t m, int64_t n, int64_t k, int64_t* out) {
-    if (!out || m < 5 || n <= 0 || n % rmlk::tc::BN || k < rmlk::tc::BK || k % rmlk::tc::BK)
-        return rmlk::fail(RMLK_ERR_INVALID_ARG, "matmul_schedule: needs M >= 5, N % 128 == 0, K % 32 == 0");
-    const rmlk::StreamPlan pl = rmlk::stream_plan(m, n, k);
-    out[0] = pl.mt; out[1] = pl.k_iters; out[2] = pl.m_tiles; out[3] = pl.gran; out[4] = pl.grid; out[5] = pl.tiles; out[6] = pl.units;
-    out[7] = static_cast<int64_t>(pl.ws_bytes);
-    return RMLK_OK;
-}
-
-namespace rmlk {
 
 bool tc_enabled() {
     static const bool v = [] {
@@ -279,18 +165,10 @@ int tc_matmul_plan(int64_t m, int64_t n, int64_t k) {
     return static_cast<int>(s > 32 ? 32 : s);
 }
 
-// Scratch the split-K form of tc_gemm_kernel needs (the smaller need: what a caller with little scratch must have).
-size_t tc_matmul_min_workspace_bytes(int64_t m, int64_t n, int64_t k) {
+// Scratch for the split-K slabs when the plan splits K more ways than one thread-block cluster adds up.
+size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k) {
     const int s = tc_matmul_plan(m, n, k);
     return s > TC_CLUSTER_MAX ? static_cast<size_t>(s) * m * n * sizeof(float) : 0;
-}
-
-// Scratch that lets every kernel choice run: the persistent kernel's partial-tile slots and flags when its schedule
-// cuts tiles, and never less than the split-K slabs of the one-tile-per-CTA kernel.
-size_t tc_matmul_workspace_bytes(int64_t m, int64_t n, int64_t k) {
-    const size_t a = tc_matmul_min_workspace_bytes(m, n, k);
-    const size_t b = (tc_stream_enabled() && m <= 64) ? stream_plan(m, n, k).ws_bytes : 0;
-    return a > b ? a : b;
 }
 
 // Launches the tensor-core GEMM.  `ksplit_out` tells the caller how many partial slabs were written to
@@ -300,37 +178,6 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
     if (peers && (ld > 0 || peers->n_peer < 0 || peers->n_peer > tc::MAX_PEERS || peers->ldc < n || peers->ldc % 4))
         return fail(RMLK_ERR_INVALID_ARG, "matmul: bad peer destinations");
     const int64_t ldc = peers ? peers->ldc : (ld > 0 ? ld : n);
-    if (tc_stream_enabled() && m <= 64) {
-        // M <= 64 (the weight-streaming regime): the persistent kernel, unless its schedule cuts tiles and the caller lent too little scratch for the partial tiles
-        const StreamPlan pl = stream_plan(m, n, k);
-        if (!pl.partials || (workspace && workspace_bytes >= pl.ws_bytes && aligned_to(workspace, 16))) {
-            CUtensorMap tmW, tmA;
-            if (!tc::make_map_2d(&tmW, w, static_cast<uint64_t>(n), static_cast<uint64_t>(k), tc::BN, tc::BK, CU_TENSOR_MAP_SWIZZLE_NONE,
-                                 ld > 0 ? static_cast<uint64_t>(ld) : 0) ||
-                !tc::make_map_2d(&tmA, a, static_cast<uint64_t>(k), static_cast<uint64_t>(m), 32, static_cast<uint32_t>(pl.mt), CU_TENSOR_MAP_SWIZZLE_128B))
-                return fail(RMLK_ERR_INTERNAL, "matmul: cuTensorMapEncodeTiled failed");
-            tc::StreamParams sp;
-            sp.out = c;
-            sp.M = m; sp.N = n; sp.K = k;
-            sp.ldc = ldc;
-            sp.n_peer = peers ? peers->n_peer : 0;
-            for (int d = 0; d < sp.n_peer; d++) sp.peer_out[d] = peers->out[d];
-            sp.k_iters = pl.k_iters;
-            sp.m_tiles = pl.m_tiles;
-            sp.units = pl.units;
-            sp.gran = pl.gran;
-            sp.strided = pl.strided ? 1 : 0;
-            sp.flags = pl.partials ? static_cast<unsigned long long*>(workspace) : nullptr;
-            sp.slots = pl.partials ? reinterpret_cast<float*>(static_cast<char*>(workspace) + pl.flag_bytes) : nullptr;
-            sp.token = tc::next_token();
-            sp.status = status;
-            sp.w_static = (flags & RMLK_MATMUL_B_STATIC) ? 1 : 0;
-            static const int mma_mode = [] { const char* e = getenv("RMLK_B200_MMA_MODE"); return e ? atoi(e) : 1; }();
-            sp.mma_mode = mma_mode;
-            *ksplit_out = 1;
-            return tc::launch_stream<64, 6, 6>(st, tmW, tmA, sp, pl.grid);
-        }
-    }
     const int mt = m <= 64 ? 64 : 128;
     int ksplit = tc_matmul_plan(m, n, k);
     if (ksplit > TC_CLUSTER_MAX && (peers || !workspace || workspace_bytes < static_cast<size_t>(ksplit) * m * n * sizeof(float)))
@@ -360,8 +207,12 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
     p.w_static = (flags & RMLK_MATMUL_B_STATIC) ? 1 : 0;
     dim3 grid(static_cast<unsigned>(n / tc::BN), static_cast<unsigned>(ksplit), static_cast<unsigned>(ceil_div64(m, mt)));
     *ksplit_out = cluster ? 1 : ksplit;  // slabs left in `workspace` for the caller to add
-    if (mt == 64) return tc::launch<64, 4, 6, 2>(st, tmW, tmA, p, grid);
-    return tc::launch<128, 4, 4, 2>(st, tmW, tmA, p, grid);
+    if (p.n_peer > 0) {
+        if (mt == 64) return tc::launch<64, 4, 6, 2, true>(st, tmW, tmA, p, grid);
+        return tc::launch<128, 4, 4, 2, true>(st, tmW, tmA, p, grid);
+    }
+    if (mt == 64) return tc::launch<64, 4, 6, 2, false>(st, tmW, tmA, p, grid);
+    return tc::launch<128, 4, 4, 2, false>(st, tmW, tmA, p, grid);
 }
 
 }  // namespace rmlk

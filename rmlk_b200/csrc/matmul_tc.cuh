@@ -48,27 +48,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     return false;
 }
 
-// Bounded wait for a barrier that is far away (the epilogue warps wait for a whole segment of MMAs): the thread is parked
-// in hardware for up to `hint_ns` per try instead of polling, so that it takes no issue slots from the warps that work.
-__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status) {
-    constexpr uint32_t hint_ns = 20000;
-    for (uint32_t i = 0; i < (1u << 16); i++) {  // about a second in all
-        uint32_t ok;
-        asm volatile(
-            "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-            "selp.u32 %0, 1, 0, p;\n\t}"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity), "r"(hint_ns)
-            : "memory");
-        if (ok) return true;
-        if (*abort_flag) return false;
-    }
-    *abort_flag = 1;
-    if (status) atomicExch(status, RMLK_ERR_TIMEOUT);
-    return false;
-}
-
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)

@@ -6,7 +6,7 @@
 namespace rmlk {
 namespace tc {
 
-template <int MT, int SW, int SA, int G>
+template <int MT, int SW, int SA, int G, bool PEERS>
 __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid_constant__ CUtensorMap tmW,
                                                               const __grid_constant__ CUtensorMap tmA, TcParams p) {
     using L = SmemLayout<MT, SW, SA>;
@@ -31,6 +31,8 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base_ptr + L::BAR_OFFSET + 8 * L::N_BARS + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // an activation stage holds two tiles: the lo twin first, then the raw tile (its own hi part)
+    constexpr uint32_t raw_off = L::A_BYTES, lo_off = 0u;
     const int n0 = blockIdx.x * BN;
     const int split = blockIdx.y;
     const int m0 = blockIdx.z * MT;
@@ -64,7 +66,7 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
         if (p.w_static) dep_wait();
         for (int it = 0; it < n_iters && it < SA; it++) {
             mbar_expect_tx(a_full(it), L::A_BYTES);
-            tma_load_2d(base + L::A_OFFSET + it * L::A_STAGE_BYTES, &tmA, (it_begin + it) * BK, m0, a_full(it));
+            tma_load_2d(base + L::A_OFFSET + it * L::A_STAGE_BYTES + raw_off, &tmA, (it_begin + it) * BK, m0, a_full(it));
         }
     }
     if (warp == 1) {
@@ -76,7 +78,7 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    // TMEM columns: [0, 2 MT) accumulators (hi*hi + lo*hi | hi*lo); activation stage s: weights hi at 2 MT + 64 s, lo 32 further
+    // TMEM columns: [0, 2 MT) accumulators (hi*lo + lo*hi | hi*hi); activation stage s: weights hi at 2 MT + 64 s, lo 32 further
     auto whi_col = [&](int s) { return static_cast<uint32_t>(2 * MT + 64 * s); };
 
     if (warp == 0) {
@@ -99,7 +101,7 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
                 const int s = it % SA;
                 if (!mbar_wait(mma_done(s), ((it / SA) - 1) & 1, abort_flag, p.status)) break;
                 mbar_expect_tx(a_full(s), L::A_BYTES);
-                tma_load_2d(base + L::A_OFFSET + s * L::A_STAGE_BYTES, &tmA, (it_begin + it) * BK, m0, a_full(s));
+                tma_load_2d(base + L::A_OFFSET + s * L::A_STAGE_BYTES + raw_off, &tmA, (it_begin + it) * BK, m0, a_full(s));
             }
         }
     } else if (warp == 1) {
@@ -112,18 +114,17 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
                 const int s = it % SA;
                 if (!mbar_wait(conv_bar(s), (it / SA) & 1, abort_flag, p.status)) break;
                 tc_fence_after();
-                const uint32_t a_hi = base + L::A_OFFSET + s * L::A_STAGE_BYTES;
+                const uint32_t stage = base + L::A_OFFSET + s * L::A_STAGE_BYTES, a_hi = stage + raw_off;
                 const uint32_t w_hi = tmem_base + whi_col(s), w_lo = w_hi + 32;
 #pragma unroll
                 for (int kk = 0; kk < BK / 8; kk++) {
-                    // a k-step of 8 is 8 TMEM columns of the weights and 32 bytes inside the swizzled activation rows
-                    const uint64_t da_hi = smem_desc_k128(a_hi + kk * 32);
-                    // hi x [hi; lo]: the lo tile follows the hi tile in shared memory, so one descriptor with N = 2 MT
-                    // covers both and fills accumulator columns [0, MT) and [MT, 2 MT); then lo x hi into [MT, 2 MT)
-                    tc_mma_tf32_ts(tmem_base, w_hi + kk * 8, da_hi, idesc_wide, (it > 0 || kk > 0) ? 1u : 0u);
-                    // (into the hi x lo block: the tensor core truncates when it adds into the accumulator, and keeping the
-                    // small products out of the large hi x hi sums halves that error)
-                    tc_mma_tf32_ts(tmem_base + MT, w_lo + kk * 8, da_hi, idesc, 1u);
+                    // a k-step of 8 is 8 TMEM columns of the weights and 32 bytes inside the swizzled activation rows.
+                    // One descriptor with N = 2 MT covers both tiles of the stage: W_hi x [first; second] fills accumulator
+                    // columns [0, MT) and [MT, 2 MT); then W_lo x x_hi goes into [0, MT).  With the lo tile first that block is
+                    // hi x lo: both small products stay out of the large hi x hi sums (the tensor core truncates when it adds
+                    // into its fp32 accumulator), which halves the error.
+                    tc_mma_tf32_ts(tmem_base, w_hi + kk * 8, smem_desc_k128(stage + kk * 32), idesc_wide, (it > 0 || kk > 0) ? 1u : 0u);
+                    tc_mma_tf32_ts(tmem_base, w_lo + kk * 8, smem_desc_k128(a_hi + kk * 32), idesc, 1u);
                 }
                 tc_commit(mma_done(s));
             }
@@ -164,8 +165,8 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
             }
             mbar_arrive(w_empty(sw));  // this thread's 32 values are in registers / on their way to TMEM: the block may be refilled
             // activations: the tile as loaded is its own hi part; lo goes into the twin tile at the same swizzled offsets
-            uint8_t* ahi = base_ptr + L::A_OFFSET + sa * L::A_STAGE_BYTES;
-            uint8_t* alo = ahi + L::A_BYTES;
+            uint8_t* ahi = base_ptr + L::A_OFFSET + sa * L::A_STAGE_BYTES + raw_off;
+            uint8_t* alo = base_ptr + L::A_OFFSET + sa * L::A_STAGE_BYTES + lo_off;
 #pragma unroll 2
             for (int c = t; c < static_cast<int>(L::A_BYTES / 16); c += 128) {
                 const float4 v = *reinterpret_cast<const float4*>(ahi + 16 * c);
@@ -198,7 +199,8 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
                     if (m < p.M) {
                         const float v = __uint_as_float(r[j]) + __uint_as_float(q[j]);
                         out[m * p.ldc + n] = v;
-                        for (int d = 0; d < p.n_peer; d++) p.peer_out[d][m * p.ldc + n] = v;
+                        if constexpr (PEERS)
+                            for (int d = 0; d < p.n_peer; d++) p.peer_out[d][m * p.ldc + n] = v;
                     }
                 }
             }
@@ -243,7 +245,8 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
                     float s = buf[ml * BN + n];
                     for (uint32_t r2 = 1; r2 < ks; r2++) s += buf[(r2 * rows_per + ml) * BN + n];
                     p.out[m * p.ldc + n0 + n] = s;
-                    for (int d = 0; d < p.n_peer; d++) p.peer_out[d][m * p.ldc + n0 + n] = s;
+                    if constexpr (PEERS)
+                        for (int d = 0; d < p.n_peer; d++) p.peer_out[d][m * p.ldc + n0 + n] = s;
                 }
             }
         }

@@ -22,7 +22,7 @@ def _call(fn, stream, m, n, k, a, w, out, extra):
               ctypes.c_void_p(out.data_ptr()), ctypes.c_int64(m * n), *extra)
 
 
-@pytest.mark.parametrize("shape", [(1, 2048, 2048), (8, 512, 2048), (16, 8192, 2048), (64, 256, 8192), (128, 512, 4096)])
+@pytest.mark.parametrize("shape", [(1, 2048, 2048), (8, 512, 2048), (16, 2048, 8192), (64, 256, 8192), (128, 512, 4096)])
 def test_static_scratch_matmul_matches_regular_entry_point(cuda, shape):
     from rmlk_b200 import kernels as K
     from rmlk_b200._lib import last_error, lib
