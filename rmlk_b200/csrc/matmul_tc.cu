@@ -180,8 +180,8 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
     const int64_t ldc = peers ? peers->ldc : (ld > 0 ? ld : n);
     const int mt = m <= 64 ? 64 : 128;
     int ksplit = tc_matmul_plan(m, n, k);
-    if (ksplit > TC_CLUSTER_MAX && (peers || !workspace || workspace_bytes < static_cast<size_t>(ksplit) * m * n * sizeof(float)))
-        ksplit = TC_CLUSTER_MAX;  // no scratch from the caller (or results that must reach other GPUs from this kernel): one cluster per tile
+    if (ksplit > TC_CLUSTER_MAX && (!workspace || workspace_bytes < static_cast<size_t>(ksplit) * m * n * sizeof(float)))
+        ksplit = TC_CLUSTER_MAX;  // no scratch from the caller: one cluster per tile
     const int k_iters = static_cast<int>(k / tc::BK);
     const int per = static_cast<int>(ceil_div64(k_iters, ksplit));
     ksplit = static_cast<int>(ceil_div64(k_iters, per));  // every split gets at least one k-block
@@ -197,8 +197,10 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
     p.cluster_reduce = cluster ? 1 : 0;
     p.out = (ksplit > 1 && !cluster) ? static_cast<float*>(workspace) : c;
     p.M = m; p.N = n; p.K = k;
-    p.ldc = ldc;
-    p.n_peer = peers ? peers->n_peer : 0;
+    // a split through the scratch leaves dense [ksplit][m][n] slabs; whoever adds them up writes C (and the peers' copies)
+    const bool slabs = ksplit > 1 && !cluster;
+    p.ldc = slabs ? n : ldc;
+    p.n_peer = (peers && !slabs) ? peers->n_peer : 0;
     for (int d = 0; d < p.n_peer; d++) p.peer_out[d] = peers->out[d];
     p.k_iters_per_split = per;
     p.k_iters_total = k_iters;

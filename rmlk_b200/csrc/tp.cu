@@ -39,6 +39,21 @@ __global__ void __launch_bounds__(256) tp_spread_kernel(const float4* __restrict
     }
 }
 
+// sum of the split-K slabs [parts][m][n] (in slab order, starting from 0.f, as the MatMul's own reduction does) -> every destination
+__global__ void __launch_bounds__(256) tp_sum_spread_kernel(const float4* __restrict__ slabs, int parts, TpDests d, int64_t m, int64_t n4, int64_t ldc4) {
+    dep_sync();
+    const int64_t total = m * n4;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x; i < total; i += static_cast<int64_t>(gridDim.x) * 256) {
+        const int64_t r = i / n4, c = i - r * n4;
+        float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < parts; k++) {
+            const float4 v = slabs[static_cast<int64_t>(k) * total + i];
+            s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+        }
+        for (int q = 0; q < d.n; q++) reinterpret_cast<float4*>(d.out[q])[r * ldc4 + c] = s;
+    }
+}
+
 // Runs after the kernels that stored the block (stream order): everything they wrote, to this GPU and to the peers, is
 // ordered before the flag words by the system-scope fence and release stores.
 __global__ void tp_signal_kernel(TpFlags f, unsigned int epoch) {
@@ -105,6 +120,16 @@ extern "C" int rmlk_b200_matmul_tp(rmlk_stream_t stream, int dtype, int64_t m, i
         if (int rc = tc_matmul(st, m, n_shard, k, static_cast<const float*>(a), static_cast<const float*>(w_shard), local, workspace, workspace_bytes,
                                status, &ksplit, RMLK_MATMUL_B_STATIC, 0, &tp))
             return rc;
+        if (ksplit > 1) {
+            // few tiles and a long K: the plan split K through the scratch; the sum of the slabs goes to every destination
+            TpDests d;
+            d.n = world;
+            for (int r = 0; r < world; r++) d.out[r] = static_cast<float*>(peers->out[r]) + col0;
+            const int64_t total = m * (n_shard / 4);
+            launch_dep(tp_sum_spread_kernel, dim3(flat_grid(total, 256, 8)), dim3(256), 0, st, reinterpret_cast<const float4*>(workspace), ksplit, d, m,
+                       n_shard / 4, n_total / 4);
+            RMLK_CHECK_LAUNCH("tp_sum_spread_kernel");
+        }
     } else {
         const size_t block = (static_cast<size_t>(m) * n_shard * sizeof(float) + 255) & ~static_cast<size_t>(255);
         if (!workspace || workspace_bytes < block || !aligned_to(workspace, 16))
