@@ -359,28 +359,87 @@ __global__ void __launch_bounds__(128) gqa_decode_attention_split_kernel(AttnSpl
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// One pass over K and V ("flash" decode): one CTA of 8 warps per problem, every warp works through blocks of 32 keys on
-// its own (block w, w + 8, ...) with a running softmax - maximum m, sum l and weighted value sums a[4][D] per query row,
-// rescaled whenever a block raises the maximum - and the 8 warps are merged once at the end (M = max m,
-// L = sum l exp(m - M), out = sum a exp(m - M) / L).  K and V of a block are requested back to back (the V loads go out
-// before the block's softmax is worked out), so the stream from HBM never stops for a softmax over the whole row; only
-// the 4 x 32 scores / probabilities of a block pass through shared memory; any number of keys.  Loads are as in the
-// kernels above: LPR lanes cover a row with one 16-byte load each, dot products by the same FMA order and shuffle
-// butterfly.  D = 16 / 32 / 64.
+// One pass over K and V ("flash" decode), fed by bulk copies.  One CTA of 8 warps per problem.  The keys are taken in
+// blocks of 64: one thread requests the block's K rows and V rows (16 KB each, contiguous in the cache) with
+// cp.async.bulk into a ring of three shared-memory stages, so up to 96 KB per CTA (192 KB per SM, two CTAs) are on their
+// way from HBM while the warps work on an earlier block - loads cost no registers and never wait for arithmetic.
+// Per block:
+//   scores   warp w takes keys 8 w .. 8 w + 7 of the block: LPR lanes read one K row from shared memory (16 bytes each, two
+//            rows per warp-wide load), dot products by the FMA order and shuffle butterfly of the kernels above; scale and
+//            mask; into shared memory.
+//   softmax  warp r (r < 4) keeps the running maximum and sum of query row r: block maximum, rescale factor for what has been
+//            accumulated, probabilities of the block back into shared memory.
+//   values   every warp: its 8 V rows times their probabilities into acc[4][4] (lane = 4 columns of the head).
+// The 8 warps share the running maximum, so at the end their partial sums simply add up (in warp order).
+// Waits on the copies are bounded; if one ever expired the problem's output would be NaN (never observed).
 // ---------------------------------------------------------------------------------------------------------------------
+constexpr int FL_KEYS = 64;     // keys per block
+constexpr int FL_STAGES = 3;
+
+template <int LPR>
+struct FlashSmem {
+    static constexpr int D = 4 * LPR;
+    static constexpr uint32_t BLOCK_BYTES = FL_KEYS * D * 4;                 // K (or V) rows of one block
+    static constexpr uint32_t STAGE_BYTES = 2 * BLOCK_BYTES;
+    static constexpr uint32_t RING_BYTES = FL_STAGES * STAGE_BYTES;
+    static constexpr uint32_t SCORES_OFF = RING_BYTES;                       // [64 keys][4 rows] floats
+    static constexpr uint32_t ACC_OFF = SCORES_OFF + FL_KEYS * 4 * 4;        // [8 warps][4 rows][D] floats
+    static constexpr uint32_t STATS_OFF = ACC_OFF + 8 * 4 * D * 4;           // m_run[4], l_run[4], corr[4], pad[4]
+    static constexpr uint32_t BAR_OFF = STATS_OFF + 16 * 4;                  // FL_STAGES mbarriers, then a flag word
+    static constexpr uint32_t TOTAL = BAR_OFF + 8 * FL_STAGES + 16;
+};
+
+__device__ __forceinline__ uint32_t fl_smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
 template <int LPR>
 __global__ void __launch_bounds__(256, 2) gqa_decode_flash_kernel(AttnParams p) {
-    dep_sync();
+    using L = FlashSmem<LPR>;
     constexpr int D = 4 * LPR;
-    constexpr int RPI = 32 / LPR;   // rows of K / V per warp-wide load
-    constexpr int UN = LPR;         // loads per lane and block: 32 keys
-    __shared__ __align__(16) float s_e[8][32][4];    // per warp: scores, then probabilities, of the current block: [key][row]
-    __shared__ float s_m[8][4], s_l[8][4];
-    __shared__ __align__(16) float s_a[8][4][D];
+    constexpr int RPI = 32 / LPR;          // rows per warp-wide 16-byte-per-lane access
+    constexpr int UN = 8 / RPI;            // accesses per warp and block: 8 keys
+    static_assert(8 % RPI == 0, "a warp's 8 keys must be whole accesses");
+    dep_trigger();
+    extern __shared__ __align__(128) uint8_t fl_smem[];
+    float* s_s = reinterpret_cast<float*>(fl_smem + L::SCORES_OFF);
+    float* s_a = reinterpret_cast<float*>(fl_smem + L::ACC_OFF);
+    float* s_m = reinterpret_cast<float*>(fl_smem + L::STATS_OFF);
+    float* s_l = s_m + 4;
+    float* s_c = s_m + 8;
+    volatile int* s_bad = reinterpret_cast<volatile int*>(fl_smem + L::BAR_OFF + 8 * FL_STAGES);
+    const uint32_t bars = fl_smem_u32(fl_smem + L::BAR_OFF);
+    const uint32_t ring = fl_smem_u32(fl_smem);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPR, rsel = lane / LPR;
     const int64_t prob = blockIdx.x;
     const int T = p.T;
+    const int n_blocks = (T + FL_KEYS - 1) / FL_KEYS;
+    const float* __restrict__ Kp = p.k + prob * p.kb;
+    const float* __restrict__ Vp = p.v + prob * p.vb;
+
+    auto request = [&](int blk) {  // one thread: K and V rows of block `blk` into stage blk % FL_STAGES
+        const int st = blk % FL_STAGES;
+        const int keys = T - blk * FL_KEYS < FL_KEYS ? T - blk * FL_KEYS : FL_KEYS;
+        const uint32_t bytes = static_cast<uint32_t>(keys) * D * 4;
+        const uint32_t bar = bars + 8u * st, dst = ring + st * L::STAGE_BYTES;
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dst), "l"(Kp + static_cast<int64_t>(blk) * FL_KEYS * D), "r"(bytes), "r"(bar) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(dst + L::BLOCK_BYTES), "l"(Vp + static_cast<int64_t>(blk) * FL_KEYS * D), "r"(bytes), "r"(bar) : "memory");
+    };
+
+    if (threadIdx.x == 0) {
+        for (int st = 0; st < FL_STAGES; st++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars + 8u * st) : "memory");
+        *s_bad = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (threadIdx.x < 4) {
+        s_m[threadIdx.x] = -INFINITY;
+        s_l[threadIdx.x] = 0.f;
+    }
+    dep_wait();  // the caches and q may have been written by the previous kernel of the stream
+    if (threadIdx.x == 0)
+        for (int blk = 0; blk < n_blocks && blk < FL_STAGES; blk++) request(blk);
     float4 a[4];
 #pragma unroll
     for (int m = 0; m < 4; m++) {
@@ -388,34 +447,39 @@ __global__ void __launch_bounds__(256, 2) gqa_decode_flash_kernel(AttnParams p) 
         if (m < p.rows) a[m] = __ldg(reinterpret_cast<const float4*>(p.q + (prob * p.rows + m) * D + 4 * sub));
     }
     const int64_t b = prob / p.kv_heads, h0 = (prob % p.kv_heads) * p.rows;
-    const float* __restrict__ K = p.k + prob * p.kb + 4 * sub;
-    const float* __restrict__ V = p.v + prob * p.vb + 4 * sub;
-    float m_run[4], l_run[4], acc[4][4];
+    float acc[4][4];
 #pragma unroll
-    for (int m = 0; m < 4; m++) {
-        m_run[m] = -INFINITY;
-        l_run[m] = 0.f;
+    for (int m = 0; m < 4; m++)
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[m][j] = 0.f;
-    }
-    const int n_blocks = (T + 31) >> 5;
-    for (int blk = warp; blk < n_blocks; blk += 8) {
-        const int tw = blk * 32;
-        uint4 bv[UN];
-#pragma unroll
-        for (int u = 0; u < UN; u++) {
-            const int t = tw + u * RPI + rsel;
-            bv[u] = make_uint4(0, 0, 0, 0);
-            if (t < T) bv[u] = ld_stream_u4(K + static_cast<int64_t>(t) * D);
+    __syncthreads();
+
+    for (int blk = 0; blk < n_blocks; blk++) {
+        const int st = blk % FL_STAGES;
+        {   // wait for the block's rows (bounded)
+            const uint32_t bar = bars + 8u * st, parity = (blk / FL_STAGES) & 1;
+            bool ok = false;
+            for (uint32_t spin = 0; spin < (1u << 22); spin++) {
+                uint32_t done;
+                asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+                if (done) { ok = true; break; }
+                if (*s_bad) break;
+            }
+            if (!ok) *s_bad = 1;
         }
-        __syncwarp();  // the previous block's probabilities have been read
+        const float* Ks = reinterpret_cast<const float*>(fl_smem + st * L::STAGE_BYTES);
+        const float* Vs = Ks + FL_KEYS * D;
+        const int t0 = blk * FL_KEYS;
+        // ---- scores of this warp's 8 keys ----
 #pragma unroll
         for (int u = 0; u < UN; u++) {
-            const int t = tw + u * RPI + rsel;
-            const float bx = __uint_as_float(bv[u].x), by = __uint_as_float(bv[u].y), bz = __uint_as_float(bv[u].z), bw = __uint_as_float(bv[u].w);
+            const int key = 8 * warp + u * RPI + rsel, t = t0 + key;
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t < T) kv = *reinterpret_cast<const float4*>(Ks + key * D + 4 * sub);
             float part[4];
 #pragma unroll
-            for (int m = 0; m < 4; m++) part[m] = fmaf(a[m].w, bw, fmaf(a[m].z, bz, fmaf(a[m].y, by, a[m].x * bx)));
+            for (int m = 0; m < 4; m++) part[m] = fmaf(a[m].w, kv.w, fmaf(a[m].z, kv.z, fmaf(a[m].y, kv.y, a[m].x * kv.x)));
             const bool up1 = (sub & (LPR / 2)) != 0;
             const float r0 = __shfl_xor_sync(0xffffffffu, up1 ? part[0] : part[2], LPR / 2);
             const float r1 = __shfl_xor_sync(0xffffffffu, up1 ? part[1] : part[3], LPR / 2);
@@ -433,60 +497,60 @@ __global__ void __launch_bounds__(256, 2) gqa_decode_flash_kernel(AttnParams p) 
                     x = __fmul_rn(v, p.scale);
                     if (p.mask) x = __fadd_rn(x, p.mask[b * p.ms_b + (h0 + m) * p.ms_h + t]);
                 }
-                s_e[warp][u * RPI + rsel][m] = x;
+                s_s[key * 4 + m] = x;
             }
         }
-        // the values are requested now; the block's softmax is worked out while they are on their way
+        __syncthreads();
+        // ---- running softmax: warp r keeps row r ----
+        if (warp < 4) {
+            const float x0 = s_s[lane * 4 + warp], x1 = s_s[(lane + 32) * 4 + warp];
+            float mx = fmaxf(x0, x1);
 #pragma unroll
-        for (int u = 0; u < UN; u++) {
-            const int t = tw + u * RPI + rsel;
-            bv[u] = make_uint4(0, 0, 0, 0);
-            if (t < T) bv[u] = ld_stream_u4(V + static_cast<int64_t>(t) * D);
+            for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            const float m_old = s_m[warp], m_new = fmaxf(m_old, mx);
+            const float e0 = m_new == -INFINITY ? 0.f : expf(x0 - m_new), e1 = m_new == -INFINITY ? 0.f : expf(x1 - m_new);
+            const float corr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+            float sum = e0 + e1;
+#pragma unroll
+            for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            s_s[lane * 4 + warp] = e0;
+            s_s[(lane + 32) * 4 + warp] = e1;
+            if (lane == 0) {
+                s_l[warp] = fmaf(s_l[warp], corr, sum);
+                s_m[warp] = m_new;
+                s_c[warp] = corr;
+            }
         }
-        __syncwarp();
-        float corr[4];
+        __syncthreads();
+        // ---- values of this warp's 8 keys ----
         {
-            const float4 sc = *reinterpret_cast<const float4*>(&s_e[warp][lane][0]);  // lane = key
-            const float sv[4] = {sc.x, sc.y, sc.z, sc.w};
-            float ev[4];
+            const float4 c4 = *reinterpret_cast<const float4*>(s_c);
+            const float cr[4] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
-            for (int m = 0; m < 4; m++) {
-                float mx = sv[m];
+            for (int m = 0; m < 4; m++)
 #pragma unroll
-                for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-                const float m_new = fmaxf(m_run[m], mx);
-                const float e = m_new == -INFINITY ? 0.f : expf(sv[m] - m_new);   // a score of -inf gives 0
-                corr[m] = m_run[m] == -INFINITY ? 0.f : expf(m_run[m] - m_new);
-                float sum = e;
-#pragma unroll
-                for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-                l_run[m] = fmaf(l_run[m], corr[m], sum);
-                m_run[m] = m_new;
-                ev[m] = e;
-            }
-            __syncwarp();
-            *reinterpret_cast<float4*>(&s_e[warp][lane][0]) = make_float4(ev[0], ev[1], ev[2], ev[3]);
+                for (int j = 0; j < 4; j++) acc[m][j] *= cr[m];
         }
-        __syncwarp();
-#pragma unroll
-        for (int m = 0; m < 4; m++)
-#pragma unroll
-            for (int j = 0; j < 4; j++) acc[m][j] *= corr[m];
 #pragma unroll
         for (int u = 0; u < UN; u++) {
-            const float4 pw = *reinterpret_cast<const float4*>(&s_e[warp][u * RPI + rsel][0]);
-            const float vx = __uint_as_float(bv[u].x), vy = __uint_as_float(bv[u].y), vz = __uint_as_float(bv[u].z), vw = __uint_as_float(bv[u].w);
-            const float pm[4] = {pw.x, pw.y, pw.z, pw.w};
+            const int key = 8 * warp + u * RPI + rsel, t = t0 + key;
+            if (t < T) {
+                const float4 pw = *reinterpret_cast<const float4*>(s_s + key * 4);
+                const float4 vv = *reinterpret_cast<const float4*>(Vs + key * D + 4 * sub);
+                const float pm[4] = {pw.x, pw.y, pw.z, pw.w};
 #pragma unroll
-            for (int m = 0; m < 4; m++) {
-                acc[m][0] = fmaf(pm[m], vx, acc[m][0]);
-                acc[m][1] = fmaf(pm[m], vy, acc[m][1]);
-                acc[m][2] = fmaf(pm[m], vz, acc[m][2]);
-                acc[m][3] = fmaf(pm[m], vw, acc[m][3]);
+                for (int m = 0; m < 4; m++) {
+                    acc[m][0] = fmaf(pm[m], vv.x, acc[m][0]);
+                    acc[m][1] = fmaf(pm[m], vv.y, acc[m][1]);
+                    acc[m][2] = fmaf(pm[m], vv.z, acc[m][2]);
+                    acc[m][3] = fmaf(pm[m], vv.w, acc[m][3]);
+                }
             }
         }
+        __syncthreads();  // the stage and the probabilities have been read by every warp
+        if (threadIdx.x == 0 && blk + FL_STAGES < n_blocks && !*s_bad) request(blk + FL_STAGES);
     }
-    // the row groups of a warp (lanes that read different rows of V) add up, then the 8 warps are merged
+    // the row groups of a warp add up by shuffles, the 8 warps through shared memory in warp order
 #pragma unroll
     for (int m = 0; m < 4; m++)
 #pragma unroll
@@ -498,29 +562,16 @@ __global__ void __launch_bounds__(256, 2) gqa_decode_flash_kernel(AttnParams p) 
         }
     if (rsel == 0) {
 #pragma unroll
-        for (int m = 0; m < 4; m++) *reinterpret_cast<float4*>(&s_a[warp][m][4 * sub]) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
-    }
-    if (lane == 0) {
-#pragma unroll
-        for (int m = 0; m < 4; m++) {
-            s_m[warp][m] = m_run[m];
-            s_l[warp][m] = l_run[m];
-        }
+        for (int m = 0; m < 4; m++) *reinterpret_cast<float4*>(s_a + (warp * 4 + m) * D + 4 * sub) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
     }
     __syncthreads();
+    const bool bad = *s_bad != 0;
     for (int i = threadIdx.x; i < p.rows * D; i += 256) {
         const int m = i / D, d = i - m * D;
-        float M = s_m[0][m];
+        float A = 0.f;
 #pragma unroll
-        for (int w = 1; w < 8; w++) M = fmaxf(M, s_m[w][m]);
-        float A = 0.f, L = 0.f;
-#pragma unroll
-        for (int w = 0; w < 8; w++) {
-            const float f = s_m[w][m] == -INFINITY ? 0.f : expf(s_m[w][m] - M);
-            A = fmaf(s_a[w][m][d], f, A);
-            L = fmaf(s_l[w][m], f, L);
-        }
-        p.out[prob * p.rows * D + i] = A / L;
+        for (int w = 0; w < 8; w++) A += s_a[(w * 4 + m) * D + d];
+        p.out[prob * p.rows * D + i] = bad ? __int_as_float(0x7fc00000) : A / s_l[m];
     }
 }
 
@@ -546,7 +597,17 @@ static int attn_launch(cudaStream_t st, const AttnParams& p, int64_t problems) {
 
 template <int LPR>
 static int attn_flash_launch(cudaStream_t st, const AttnParams& p, int64_t problems) {
-    launch_dep(gqa_decode_flash_kernel<LPR>, dim3(static_cast<unsigned>(problems)), dim3(256), 0, st, p);
+    using L = FlashSmem<LPR>;
+    static std::once_flag configured[64];  // once per device; a concurrent first call waits for the attribute to be set
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaError_t cfg_err = cudaSuccess;
+    if (dev >= 0 && dev < 64)
+        std::call_once(configured[dev], [&] {
+            cfg_err = cudaFuncSetAttribute(gqa_decode_flash_kernel<LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::TOTAL));
+        });
+    RMLK_CUDA(cfg_err);
+    launch_dep(gqa_decode_flash_kernel<LPR>, dim3(static_cast<unsigned>(problems)), dim3(256), L::TOTAL, st, p);
     RMLK_CHECK_LAUNCH("gqa_decode_flash_kernel");
     return RMLK_OK;
 }
@@ -602,7 +663,7 @@ extern "C" int rmlk_b200_gqa_decode_attention(rmlk_stream_t stream, int dtype, i
             case 16: return attn_flash_launch<4>(st, p, problems);
             case 32: return attn_flash_launch<8>(st, p, problems);
             case 64: return attn_flash_launch<16>(st, p, problems);
-            default: break;  // head_dim 128: 32 loads of 16 bytes per lane and block do not fit the registers; the two-pass kernel below
+            default: return attn_flash_launch<32>(st, p, problems);
         }
     }
     switch (head_dim) {

@@ -213,6 +213,7 @@ int tc_matmul(cudaStream_t st, int64_t m, int64_t n, int64_t k, const float* a, 
         if (mt == 64) return tc::launch<64, 4, 6, 2, true>(st, tmW, tmA, p, grid);
         return tc::launch<128, 4, 4, 2, true>(st, tmW, tmA, p, grid);
     }
+    // (weight rings of 6 and 8 blocks next to the 6 activation blocks measured 1-3 % slower than 4)
     if (mt == 64) return tc::launch<64, 4, 6, 2, false>(st, tmW, tmA, p, grid);
     return tc::launch<128, 4, 4, 2, false>(st, tmW, tmA, p, grid);
 }
