@@ -72,6 +72,18 @@ __device__ __forceinline__ void tc_mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem,
         : "memory");
 }
 
+// The same MMA with the shared-memory descriptor handed over as two 32-bit halves and the accumulator always added to:
+// the issuing thread keeps the constant upper half in a register and only adds to the lower one.
+__device__ __forceinline__ void tc_mma_tf32_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_desc_lo, uint32_t b_desc_hi, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 d;\n\t"
+        "mov.b64 d, {%2, %3};\n\t"
+        "setp.eq.b32 p, 0, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], d, %4, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "r"(b_desc_lo), "r"(b_desc_hi), "r"(idesc)
+        : "memory");
+}
+
 // K-major shared-memory operand descriptor, 128-byte swizzle, descriptor version 1.
 __device__ __forceinline__ uint64_t smem_desc_k128(uint32_t addr) {
     uint64_t d = 0;

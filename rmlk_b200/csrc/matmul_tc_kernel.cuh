@@ -110,23 +110,37 @@ __global__ void __launch_bounds__(threads_for(G), 1) tc_gemm_kernel(const __grid
             // D fp32; A (weights, from TMEM) and B (activations, smem) tf32, both K-major; M = 128, N = MT
             constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((MT >> 3) << 17) | ((BN >> 4) << 24);
             constexpr uint32_t idesc_wide = (1u << 4) | (2u << 7) | (2u << 10) | (((2 * MT) >> 3) << 17) | ((BN >> 4) << 24);
+            // This one thread's instruction stream is close to the critical path (eight MMAs per k-block of 16 KB), so the loop
+            // keeps running counters instead of dividing, and builds each operand descriptor with one addition: the upper
+            // half of a descriptor is constant and the lower half is the address in 16-byte units.
+            const uint64_t desc0 = smem_desc_k128(base + L::A_OFFSET);
+            const uint32_t desc_hi = static_cast<uint32_t>(desc0 >> 32), desc_lo0 = static_cast<uint32_t>(desc0);
+            uint32_t s = 0, phase = 0;
             for (int it = 0; it < n_iters; it++) {
-                const int s = it % SA;
-                if (!mbar_wait(conv_bar(s), (it / SA) & 1, abort_flag, p.status)) break;
+                if (!mbar_wait(conv_bar(s), phase, abort_flag, p.status)) break;
                 tc_fence_after();
-                const uint32_t stage = base + L::A_OFFSET + s * L::A_STAGE_BYTES, a_hi = stage + raw_off;
+                const uint32_t stage_lo = desc_lo0 + s * (L::A_STAGE_BYTES >> 4), raw_lo = stage_lo + (raw_off >> 4);
                 const uint32_t w_hi = tmem_base + whi_col(s), w_lo = w_hi + 32;
+                // a k-step of 8 is 8 TMEM columns of the weights and 32 bytes inside the swizzled activation rows.
+                // One descriptor with N = 2 MT covers both tiles of the stage: W_hi x [first; second] fills accumulator
+                // columns [0, MT) and [MT, 2 MT); then W_lo x x_hi goes into [0, MT).  With the lo tile first that block is
+                // hi x lo: both small products stay out of the large hi x hi sums (the tensor core truncates when it adds
+                // into its fp32 accumulator), which halves the error.
+                if (it == 0)
+                    tc_mma_tf32_ts(tmem_base, w_hi, smem_desc_k128(base + L::A_OFFSET), idesc_wide, 0u);
+                else
+                    tc_mma_tf32_ts_acc(tmem_base, w_hi, stage_lo, desc_hi, idesc_wide);
+                tc_mma_tf32_ts_acc(tmem_base, w_lo, raw_lo, desc_hi, idesc);
 #pragma unroll
-                for (int kk = 0; kk < BK / 8; kk++) {
-                    // a k-step of 8 is 8 TMEM columns of the weights and 32 bytes inside the swizzled activation rows.
-                    // One descriptor with N = 2 MT covers both tiles of the stage: W_hi x [first; second] fills accumulator
-                    // columns [0, MT) and [MT, 2 MT); then W_lo x x_hi goes into [0, MT).  With the lo tile first that block is
-                    // hi x lo: both small products stay out of the large hi x hi sums (the tensor core truncates when it adds
-                    // into its fp32 accumulator), which halves the error.
-                    tc_mma_tf32_ts(tmem_base, w_hi + kk * 8, smem_desc_k128(stage + kk * 32), idesc_wide, (it > 0 || kk > 0) ? 1u : 0u);
-                    tc_mma_tf32_ts(tmem_base, w_lo + kk * 8, smem_desc_k128(a_hi + kk * 32), idesc, 1u);
+                for (int kk = 1; kk < BK / 8; kk++) {
+                    tc_mma_tf32_ts_acc(tmem_base, w_hi + kk * 8, stage_lo + kk * 2, desc_hi, idesc_wide);
+                    tc_mma_tf32_ts_acc(tmem_base, w_lo + kk * 8, raw_lo + kk * 2, desc_hi, idesc);
                 }
                 tc_commit(mma_done(s));
+                if (++s == SA) {
+                    s = 0;
+                    phase ^= 1;
+                }
             }
             tc_commit(accum_bar);
         }
