@@ -359,40 +359,57 @@ __global__ void __launch_bounds__(128) gqa_decode_attention_split_kernel(AttnSpl
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// One pass over K and V ("flash" decode), fed by bulk copies.  One CTA of 8 warps per problem.  The keys are taken in
-// blocks of 64: one thread requests the block's K rows and V rows (16 KB each, contiguous in the cache) with
-// cp.async.bulk into a ring of three shared-memory stages, so up to 96 KB per CTA (192 KB per SM, two CTAs) are on their
-// way from HBM while the warps work on an earlier block - loads cost no registers and never wait for arithmetic.
-// Per block:
-//   scores   warp w takes keys 8 w .. 8 w + 7 of the block: LPR lanes read one K row from shared memory (16 bytes each, two
-//            rows per warp-wide load), dot products by the FMA order and shuffle butterfly of the kernels above; scale and
-//            mask; into shared memory.
-//   softmax  warp r (r < 4) keeps the running maximum and sum of query row r: block maximum, rescale factor for what has been
-//            accumulated, probabilities of the block back into shared memory.
-//   values   every warp: its 8 V rows times their probabilities into acc[4][4] (lane = 4 columns of the head).
-// The 8 warps share the running maximum, so at the end their partial sums simply add up (in warp order).
-// Waits on the copies are bounded; if one ever expired the problem's output would be NaN (never observed).
+// One pass over K and V ("flash" decode), fed by bulk copies.  One CTA per problem: 8 working warps and one warp that
+// feeds a ring of three shared-memory stages.  The keys are taken in blocks of 64: the feeding warp requests the block's K
+// rows and V rows (contiguous in the cache) with cp.async.bulk, so up to 96 KB per CTA (two CTAs per SM at head_dim 64)
+// are on their way from HBM while the warps work on earlier blocks - loads cost no registers and never wait for
+// arithmetic.  Inside the loop nothing synchronises the CTA: every warp keeps a running softmax of its own.
+// Per block, warp w takes keys 8 w .. 8 w + 7:
+//   scores   LPR lanes read one K row from shared memory (16 bytes each), dot products by the FMA order and shuffle
+//            butterfly of the kernels above; scale and mask; the 8 x 4 scores go to the warp's own 128 bytes of shared memory.
+//   softmax  lane i holds score (key i / 4, row i % 4): row maximum over the 8 keys by shuffles, one expf for the probability,
+//            one for the factor that rescales what the warp has accumulated so far; probabilities back to shared memory.
+//   values   the warp's 8 V rows times their probabilities into acc[4][4] (lane = 4 columns of the head).
+//   then lane 0 hands the stage back to the feeding warp (an mbarrier that counts the 8 warps).
+// At the end the 8 warps' maxima, sums and accumulators meet in shared memory and are combined in warp order.
+// Waits are bounded; if one ever expired the problem's output would be NaN (never observed).
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int FL_KEYS = 64;     // keys per block
 constexpr int FL_STAGES = 3;
+constexpr int FL_WARPS = 8;     // working warps; one more feeds the ring
+constexpr int FL_THREADS = 32 * (FL_WARPS + 1);
 
 template <int LPR>
 struct FlashSmem {
     static constexpr int D = 4 * LPR;
     static constexpr uint32_t BLOCK_BYTES = FL_KEYS * D * 4;                 // K (or V) rows of one block
     static constexpr uint32_t STAGE_BYTES = 2 * BLOCK_BYTES;
-    static constexpr uint32_t RING_BYTES = FL_STAGES * STAGE_BYTES;
-    static constexpr uint32_t SCORES_OFF = RING_BYTES;                       // [64 keys][4 rows] floats
-    static constexpr uint32_t ACC_OFF = SCORES_OFF + FL_KEYS * 4 * 4;        // [8 warps][4 rows][D] floats
-    static constexpr uint32_t STATS_OFF = ACC_OFF + 8 * 4 * D * 4;           // m_run[4], l_run[4], corr[4], pad[4]
-    static constexpr uint32_t BAR_OFF = STATS_OFF + 16 * 4;                  // FL_STAGES mbarriers, then a flag word
-    static constexpr uint32_t TOTAL = BAR_OFF + 8 * FL_STAGES + 16;
+    static constexpr uint32_t RING_BYTES = FL_STAGES * STAGE_BYTES;          // reused at the end: [8 warps][4 rows][D] partial outputs
+    static constexpr uint32_t SCORES_OFF = RING_BYTES;                       // [8 warps][8 keys][4 rows] floats
+    static constexpr uint32_t CORR_OFF = SCORES_OFF + FL_WARPS * 32 * 4;     // [8 warps][4 rows] rescale factors
+    static constexpr uint32_t STATS_OFF = CORR_OFF + FL_WARPS * 4 * 4;       // m[8 warps][4], then l[8 warps][4]
+    static constexpr uint32_t BAR_OFF = STATS_OFF + 2 * FL_WARPS * 4 * 4;    // full[FL_STAGES], empty[FL_STAGES] mbarriers, then a flag word
+    static constexpr uint32_t TOTAL = BAR_OFF + 16 * FL_STAGES + 16;
+    static_assert(RING_BYTES >= FL_WARPS * 4 * D * 4, "the ring must hold the warps' partial outputs");
 };
 
 __device__ __forceinline__ uint32_t fl_smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
 
+// Bounded wait on an mbarrier phase; false if it expired or another thread has given up.
+__device__ __forceinline__ bool fl_wait(uint32_t bar, uint32_t parity, volatile int* bad) {
+    for (uint32_t spin = 0; spin < (1u << 22); spin++) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+                     : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+        if (*bad) return false;
+    }
+    *bad = 1;
+    return false;
+}
+
 template <int LPR>
-__global__ void __launch_bounds__(256, 2) gqa_decode_flash_kernel(AttnParams p) {
+__global__ void __launch_bounds__(FL_THREADS, LPR <= 16 ? 2 : 1) gqa_decode_flash_kernel(AttnParams p) {
     using L = FlashSmem<LPR>;
     constexpr int D = 4 * LPR;
     constexpr int RPI = 32 / LPR;          // rows per warp-wide 16-byte-per-lane access
@@ -400,14 +417,14 @@ __global__ void __launch_bounds__(256, 2) gqa_decode_flash_kernel(AttnParams p) 
     static_assert(8 % RPI == 0, "a warp's 8 keys must be whole accesses");
     dep_trigger();
     extern __shared__ __align__(128) uint8_t fl_smem[];
-    float* s_s = reinterpret_cast<float*>(fl_smem + L::SCORES_OFF);
-    float* s_a = reinterpret_cast<float*>(fl_smem + L::ACC_OFF);
+    float* s_a = reinterpret_cast<float*>(fl_smem);
     float* s_m = reinterpret_cast<float*>(fl_smem + L::STATS_OFF);
-    float* s_l = s_m + 4;
-    float* s_c = s_m + 8;
-    volatile int* s_bad = reinterpret_cast<volatile int*>(fl_smem + L::BAR_OFF + 8 * FL_STAGES);
+    float* s_l = s_m + FL_WARPS * 4;
+    volatile int* s_bad = reinterpret_cast<volatile int*>(fl_smem + L::BAR_OFF + 16 * FL_STAGES);
     const uint32_t bars = fl_smem_u32(fl_smem + L::BAR_OFF);
     const uint32_t ring = fl_smem_u32(fl_smem);
+    auto full = [&](int st) { return bars + 8u * st; };
+    auto empty = [&](int st) { return bars + 8u * (FL_STAGES + st); };
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int sub = lane % LPR, rsel = lane / LPR;
     const int64_t prob = blockIdx.x;
@@ -416,162 +433,177 @@ __global__ void __launch_bounds__(256, 2) gqa_decode_flash_kernel(AttnParams p) 
     const float* __restrict__ Kp = p.k + prob * p.kb;
     const float* __restrict__ Vp = p.v + prob * p.vb;
 
-    auto request = [&](int blk) {  // one thread: K and V rows of block `blk` into stage blk % FL_STAGES
-        const int st = blk % FL_STAGES;
-        const int keys = T - blk * FL_KEYS < FL_KEYS ? T - blk * FL_KEYS : FL_KEYS;
-        const uint32_t bytes = static_cast<uint32_t>(keys) * D * 4;
-        const uint32_t bar = bars + 8u * st, dst = ring + st * L::STAGE_BYTES;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(dst), "l"(Kp + static_cast<int64_t>(blk) * FL_KEYS * D), "r"(bytes), "r"(bar) : "memory");
-        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                     ::"r"(dst + L::BLOCK_BYTES), "l"(Vp + static_cast<int64_t>(blk) * FL_KEYS * D), "r"(bytes), "r"(bar) : "memory");
-    };
-
     if (threadIdx.x == 0) {
-        for (int st = 0; st < FL_STAGES; st++) asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bars + 8u * st) : "memory");
+        for (int st = 0; st < FL_STAGES; st++) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(full(st)) : "memory");
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(empty(st)), "r"(FL_WARPS) : "memory");
+        }
         *s_bad = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (threadIdx.x < 4) {
-        s_m[threadIdx.x] = -INFINITY;
-        s_l[threadIdx.x] = 0.f;
-    }
     dep_wait();  // the caches and q may have been written by the previous kernel of the stream
-    if (threadIdx.x == 0)
-        for (int blk = 0; blk < n_blocks && blk < FL_STAGES; blk++) request(blk);
-    float4 a[4];
-#pragma unroll
-    for (int m = 0; m < 4; m++) {
-        a[m] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (m < p.rows) a[m] = __ldg(reinterpret_cast<const float4*>(p.q + (prob * p.rows + m) * D + 4 * sub));
-    }
-    const int64_t b = prob / p.kv_heads, h0 = (prob % p.kv_heads) * p.rows;
+    __syncthreads();
+
     float acc[4][4];
 #pragma unroll
     for (int m = 0; m < 4; m++)
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[m][j] = 0.f;
-    __syncthreads();
 
-    for (int blk = 0; blk < n_blocks; blk++) {
-        const int st = blk % FL_STAGES;
-        {   // wait for the block's rows (bounded)
-            const uint32_t bar = bars + 8u * st, parity = (blk / FL_STAGES) & 1;
-            bool ok = false;
-            for (uint32_t spin = 0; spin < (1u << 22); spin++) {
-                uint32_t done;
-                asm volatile("{\n\t.reg .pred q;\n\tmbarrier.try_wait.parity.shared::cta.b64 q, [%1], %2;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-                             : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-                if (done) { ok = true; break; }
-                if (*s_bad) break;
-            }
-            if (!ok) *s_bad = 1;
-        }
-        const float* Ks = reinterpret_cast<const float*>(fl_smem + st * L::STAGE_BYTES);
-        const float* Vs = Ks + FL_KEYS * D;
-        const int t0 = blk * FL_KEYS;
-        // ---- scores of this warp's 8 keys ----
-#pragma unroll
-        for (int u = 0; u < UN; u++) {
-            const int key = 8 * warp + u * RPI + rsel, t = t0 + key;
-            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t < T) kv = *reinterpret_cast<const float4*>(Ks + key * D + 4 * sub);
-            float part[4];
-#pragma unroll
-            for (int m = 0; m < 4; m++) part[m] = fmaf(a[m].w, kv.w, fmaf(a[m].z, kv.z, fmaf(a[m].y, kv.y, a[m].x * kv.x)));
-            const bool up1 = (sub & (LPR / 2)) != 0;
-            const float r0 = __shfl_xor_sync(0xffffffffu, up1 ? part[0] : part[2], LPR / 2);
-            const float r1 = __shfl_xor_sync(0xffffffffu, up1 ? part[1] : part[3], LPR / 2);
-            const float q0 = (up1 ? part[2] : part[0]) + r0;
-            const float q1 = (up1 ? part[3] : part[1]) + r1;
-            const bool up2 = (sub & (LPR / 4)) != 0;
-            const float r2 = __shfl_xor_sync(0xffffffffu, up2 ? q0 : q1, LPR / 4);
-            float v = (up2 ? q1 : q0) + r2;
-#pragma unroll
-            for (int off = LPR / 8; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-            const int m = 2 * (up1 ? 1 : 0) + (up2 ? 1 : 0);
-            if ((sub & (LPR / 4 - 1)) == 0) {
-                float x = -INFINITY;  // keys beyond the end and rows that do not exist
-                if (t < T && m < p.rows) {
-                    x = __fmul_rn(v, p.scale);
-                    if (p.mask) x = __fadd_rn(x, p.mask[b * p.ms_b + (h0 + m) * p.ms_h + t]);
-                }
-                s_s[key * 4 + m] = x;
+    if (warp == FL_WARPS) {
+        // ---------------- feeds the ring ----------------
+        if (lane == 0) {
+            for (int blk = 0; blk < n_blocks; blk++) {
+                const int st = blk % FL_STAGES;
+                if (blk >= FL_STAGES && !fl_wait(empty(st), ((blk / FL_STAGES) - 1) & 1, s_bad)) break;
+                const int keys = T - blk * FL_KEYS < FL_KEYS ? T - blk * FL_KEYS : FL_KEYS;
+                const uint32_t bytes = static_cast<uint32_t>(keys) * D * 4;
+                const uint32_t bar = full(st), dst = ring + st * L::STAGE_BYTES;
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2 * bytes) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(dst), "l"(Kp + static_cast<int64_t>(blk) * FL_KEYS * D), "r"(bytes), "r"(bar) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(dst + L::BLOCK_BYTES), "l"(Vp + static_cast<int64_t>(blk) * FL_KEYS * D), "r"(bytes), "r"(bar) : "memory");
             }
         }
-        __syncthreads();
-        // ---- running softmax: warp r keeps row r ----
-        if (warp < 4) {
-            const float x0 = s_s[lane * 4 + warp], x1 = s_s[(lane + 32) * 4 + warp];
-            float mx = fmaxf(x0, x1);
+    } else {
+        // ---------------- working warps ----------------
+        float* s_w = reinterpret_cast<float*>(fl_smem + L::SCORES_OFF) + warp * 32;
+        float* s_cw = reinterpret_cast<float*>(fl_smem + L::CORR_OFF) + warp * 4;
+        float4 a[4];
 #pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            const float m_old = s_m[warp], m_new = fmaxf(m_old, mx);
-            const float e0 = m_new == -INFINITY ? 0.f : expf(x0 - m_new), e1 = m_new == -INFINITY ? 0.f : expf(x1 - m_new);
-            const float corr = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
-            float sum = e0 + e1;
-#pragma unroll
-            for (int o = 16; o >= 1; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            s_s[lane * 4 + warp] = e0;
-            s_s[(lane + 32) * 4 + warp] = e1;
-            if (lane == 0) {
-                s_l[warp] = fmaf(s_l[warp], corr, sum);
-                s_m[warp] = m_new;
-                s_c[warp] = corr;
+        for (int m = 0; m < 4; m++) {
+            a[m] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (m < p.rows) a[m] = __ldg(reinterpret_cast<const float4*>(p.q + (prob * p.rows + m) * D + 4 * sub));
+        }
+        const int64_t b = prob / p.kv_heads, h0 = (prob % p.kv_heads) * p.rows;
+        float m_run = -INFINITY, l_part = 0.f;   // of row lane % 4: running maximum (the same in all its lanes) and this lane's share of the sum
+
+        for (int blk = 0; blk < n_blocks; blk++) {
+            const int st = blk % FL_STAGES;
+            const int t0 = blk * FL_KEYS;
+            // the mask value of this lane's (key, row) of the softmax step is asked for now, before the wait for the block
+            // and the dot products, and added there (the same two roundings, v * scale + mask, as in the kernels above)
+            float mk = 0.f;
+            {
+                const int tm = t0 + 8 * warp + (lane >> 2), rm = lane & 3;
+                if (p.mask && tm < T && rm < p.rows) mk = __ldg(p.mask + b * p.ms_b + (h0 + rm) * p.ms_h + tm);
             }
-        }
-        __syncthreads();
-        // ---- values of this warp's 8 keys ----
-        {
-            const float4 c4 = *reinterpret_cast<const float4*>(s_c);
-            const float cr[4] = {c4.x, c4.y, c4.z, c4.w};
+            if (!fl_wait(full(st), (blk / FL_STAGES) & 1, s_bad)) break;
+            const float* Ks = reinterpret_cast<const float*>(fl_smem + st * L::STAGE_BYTES);
+            const float* Vs = Ks + FL_KEYS * D;
+            // ---- scores of this warp's 8 keys ----
 #pragma unroll
-            for (int m = 0; m < 4; m++)
+            for (int u = 0; u < UN; u++) {
+                const int kl = u * RPI + rsel, key = 8 * warp + kl, t = t0 + key;
+                float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (t < T) kv = *reinterpret_cast<const float4*>(Ks + key * D + 4 * sub);
+                float part[4];
 #pragma unroll
-                for (int j = 0; j < 4; j++) acc[m][j] *= cr[m];
-        }
+                for (int m = 0; m < 4; m++) part[m] = fmaf(a[m].w, kv.w, fmaf(a[m].z, kv.z, fmaf(a[m].y, kv.y, a[m].x * kv.x)));
+                const bool up1 = (sub & (LPR / 2)) != 0;
+                const float r0 = __shfl_xor_sync(0xffffffffu, up1 ? part[0] : part[2], LPR / 2);
+                const float r1 = __shfl_xor_sync(0xffffffffu, up1 ? part[1] : part[3], LPR / 2);
+                const float q0 = (up1 ? part[2] : part[0]) + r0;
+                const float q1 = (up1 ? part[3] : part[1]) + r1;
+                const bool up2 = (sub & (LPR / 4)) != 0;
+                const float r2 = __shfl_xor_sync(0xffffffffu, up2 ? q0 : q1, LPR / 4);
+                float v = (up2 ? q1 : q0) + r2;
 #pragma unroll
-        for (int u = 0; u < UN; u++) {
-            const int key = 8 * warp + u * RPI + rsel, t = t0 + key;
-            if (t < T) {
-                const float4 pw = *reinterpret_cast<const float4*>(s_s + key * 4);
-                const float4 vv = *reinterpret_cast<const float4*>(Vs + key * D + 4 * sub);
-                const float pm[4] = {pw.x, pw.y, pw.z, pw.w};
-#pragma unroll
-                for (int m = 0; m < 4; m++) {
-                    acc[m][0] = fmaf(pm[m], vv.x, acc[m][0]);
-                    acc[m][1] = fmaf(pm[m], vv.y, acc[m][1]);
-                    acc[m][2] = fmaf(pm[m], vv.z, acc[m][2]);
-                    acc[m][3] = fmaf(pm[m], vv.w, acc[m][3]);
+                for (int off = LPR / 8; off >= 1; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                const int m = 2 * (up1 ? 1 : 0) + (up2 ? 1 : 0);
+                if ((sub & (LPR / 4 - 1)) == 0) {
+                    float x = -INFINITY;  // keys beyond the end and rows that do not exist
+                    if (t < T && m < p.rows) x = __fmul_rn(v, p.scale);
+                    s_w[kl * 4 + m] = x;
                 }
             }
+            __syncwarp();
+            // ---- running softmax: lane i has key i / 4, row i % 4 ----
+            {
+                float x = s_w[lane];
+                if (p.mask) x = __fadd_rn(x, mk);
+                float mx = x;
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+                const float m_new = fmaxf(m_run, mx);
+                const float e = m_new == -INFINITY ? 0.f : expf(x - m_new);
+                const float corr = m_run == -INFINITY ? 0.f : expf(m_run - m_new);
+                l_part = fmaf(l_part, corr, e);
+                m_run = m_new;
+                s_w[lane] = e;
+                if (lane < 4) s_cw[lane] = corr;
+            }
+            __syncwarp();
+            // ---- values of this warp's 8 keys ----
+            {
+                const float4 c4 = *reinterpret_cast<const float4*>(s_cw);
+                const float cr[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                for (int m = 0; m < 4; m++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) acc[m][j] *= cr[m];
+            }
+#pragma unroll
+            for (int u = 0; u < UN; u++) {
+                const int kl = u * RPI + rsel, key = 8 * warp + kl, t = t0 + key;
+                if (t < T) {
+                    const float4 pw = *reinterpret_cast<const float4*>(s_w + kl * 4);
+                    const float4 vv = *reinterpret_cast<const float4*>(Vs + key * D + 4 * sub);
+                    const float pm[4] = {pw.x, pw.y, pw.z, pw.w};
+#pragma unroll
+                    for (int m = 0; m < 4; m++) {
+                        acc[m][0] = fmaf(pm[m], vv.x, acc[m][0]);
+                        acc[m][1] = fmaf(pm[m], vv.y, acc[m][1]);
+                        acc[m][2] = fmaf(pm[m], vv.z, acc[m][2]);
+                        acc[m][3] = fmaf(pm[m], vv.w, acc[m][3]);
+                    }
+                }
+            }
+            __syncwarp();  // every lane has read the stage and the probabilities
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty(st)) : "memory");
         }
-        __syncthreads();  // the stage and the probabilities have been read by every warp
-        if (threadIdx.x == 0 && blk + FL_STAGES < n_blocks && !*s_bad) request(blk + FL_STAGES);
+        // the warp's totals: the sum of a row over its 8 lanes, the accumulators over the lane groups that took different keys
+        float l_row = l_part;
+        l_row += __shfl_xor_sync(0xffffffffu, l_row, 4);
+        l_row += __shfl_xor_sync(0xffffffffu, l_row, 8);
+        l_row += __shfl_xor_sync(0xffffffffu, l_row, 16);
+        if (lane < 4) {
+            s_m[warp * 4 + lane] = m_run;
+            s_l[warp * 4 + lane] = l_row;
+        }
+#pragma unroll
+        for (int m = 0; m < 4; m++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float x = acc[m][j];
+#pragma unroll
+                for (int off = LPR; off < 32; off <<= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
+                acc[m][j] = x;
+            }
     }
-    // the row groups of a warp add up by shuffles, the 8 warps through shared memory in warp order
-#pragma unroll
-    for (int m = 0; m < 4; m++)
-#pragma unroll
-        for (int j = 0; j < 4; j++) {
-            float x = acc[m][j];
-#pragma unroll
-            for (int off = LPR; off < 32; off <<= 1) x += __shfl_xor_sync(0xffffffffu, x, off);
-            acc[m][j] = x;
-        }
-    if (rsel == 0) {
+    __syncthreads();  // every requested block has arrived and been read: the ring is free for the warps' partial outputs
+    if (warp < FL_WARPS && rsel == 0) {
 #pragma unroll
         for (int m = 0; m < 4; m++) *reinterpret_cast<float4*>(s_a + (warp * 4 + m) * D + 4 * sub) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
     }
     __syncthreads();
     const bool bad = *s_bad != 0;
-    for (int i = threadIdx.x; i < p.rows * D; i += 256) {
+    for (int i = threadIdx.x; i < p.rows * D; i += FL_THREADS) {
         const int m = i / D, d = i - m * D;
-        float A = 0.f;
+        float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 8; w++) A += s_a[(w * 4 + m) * D + d];
-        p.out[prob * p.rows * D + i] = bad ? __int_as_float(0x7fc00000) : A / s_l[m];
+        for (int w = 0; w < FL_WARPS; w++) M = fmaxf(M, s_m[w * 4 + m]);
+        float A = 0.f, Lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < FL_WARPS; w++) {
+            const float mw = s_m[w * 4 + m];
+            const float f = mw == -INFINITY ? 0.f : expf(mw - M);
+            Lsum = fmaf(s_l[w * 4 + m], f, Lsum);
+            A = fmaf(s_a[(w * 4 + m) * D + d], f, A);
+        }
+        p.out[prob * p.rows * D + i] = bad ? __int_as_float(0x7fc00000) : A / Lsum;
     }
 }
 
@@ -607,7 +639,7 @@ static int attn_flash_launch(cudaStream_t st, const AttnParams& p, int64_t probl
             cfg_err = cudaFuncSetAttribute(gqa_decode_flash_kernel<LPR>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(L::TOTAL));
         });
     RMLK_CUDA(cfg_err);
-    launch_dep(gqa_decode_flash_kernel<LPR>, dim3(static_cast<unsigned>(problems)), dim3(256), L::TOTAL, st, p);
+    launch_dep(gqa_decode_flash_kernel<LPR>, dim3(static_cast<unsigned>(problems)), dim3(FL_THREADS), L::TOTAL, st, p);
     RMLK_CHECK_LAUNCH("gqa_decode_flash_kernel");
     return RMLK_OK;
 }

@@ -671,7 +671,7 @@ extern "C" rmlk_instance* rmlk_instance_create(const rmlk_graph* g, int device, 
         if (const char* e = getenv("RMLK_B200_NO_ADD_NORM")) I.add_norm = e[0] != '1';
         if (const char* e = getenv("RMLK_B200_NO_APPEND_TO")) I.inplace_append_to = e[0] != '1';
         if (const char* e = getenv("RMLK_B200_ATTENTION")) {
-            I.attention = e[0] == '1' || e[0] == 's';
+            I.attention = e[0] != '0';
             I.attention_split = e[0] == 's';
         }
         I.find_fusions();  // recognise RMSNorm / rotary / SwiGLU / scale-mask-softmax chains; re-derives last_use

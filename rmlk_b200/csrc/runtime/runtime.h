@@ -239,11 +239,12 @@ struct Instance {
     // producer of such rows may write them straight into the cache slot (rotary embedding of the keys does).
     std::vector<int> append_consumer;
     bool inplace_append_to = true;  // RMLK_B200_NO_APPEND_TO=1: new rows are made dense first, then copied in
-    // RMLK_B200_ATTENTION=1: scores MatMul, softmax chain and context MatMul of a decode step run as one kernel (keys of
-    // a problem split over CTAs of 128 keys).  Off by default: it measured 6 us per layer slower than the three kernels
-    // it replaces on 512 problems of 550 keys.
-    bool attention = false;
-    bool attention_split = false;  // RMLK_B200_ATTENTION=split
+    // Scores MatMul, softmax chain and context MatMul of a decode step run as one kernel, one CTA per problem (measured on
+    // 512 problems of 4 query rows over 550 keys, head size 64: 31 us against 39 us for the three kernels it replaces).
+    // RMLK_B200_ATTENTION=0 keeps the three kernels; =split uses the kernel that splits a problem's keys over CTAs of
+    // 128 keys and combines them through a workspace (slower on that shape).
+    bool attention = true;
+    bool attention_split = false;
     bool add_norm = true;       // RMLK_B200_NO_ADD_NORM=1: keep the residual Add (and the split-K sum) as launches of their own
     void settle_parts(int value_id);
     DeviceBuffer read_staging;  // dense copy of a strided output while it is read back

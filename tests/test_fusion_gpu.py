@@ -401,9 +401,9 @@ def attention_graph(KV, G, D):
 
 @pytest.mark.parametrize("KV,G,D", [(2, 4, 64), (3, 2, 16), (2, 1, 128), (2, 8, 32), (1, 4, 20)])
 def test_runtime_runs_decode_attention_as_one_launch(cuda, KV, G, D):
-    """With RMLK_B200_ATTENTION=1 the five attention nodes of a decode step run as one kernel over the carried caches; a
-    multi-token step, more than four query heads per KV head or an unsupported head size run the single kernels.  Same
-    numbers either way.  (Off by default: the three kernels are faster on the benchmark's shape.)"""
+    """The five attention nodes of a decode step run as one kernel over the carried caches (RMLK_B200_ATTENTION=0 keeps the
+    single kernels); a multi-token step, more than four query heads per KV head or an unsupported head size run the single
+    kernels anyway.  Same numbers either way."""
     from rmlk_b200.runtime import ModelInstance
     spec = attention_graph(KV, G, D)
     B = 3
@@ -419,7 +419,7 @@ def test_runtime_runs_decode_attention_as_one_launch(cuda, KV, G, D):
                 os.environ.pop(k, None)
         return inst
 
-    one, apart = drive({"RMLK_B200_ATTENTION": "1"}), drive({})
+    one, apart = drive({}), drive({"RMLK_B200_ATTENTION": "0"})
     r = np.random.default_rng(43)
     T = 0
     cache_k = np.zeros((B, KV, 0, D), np.float32)
@@ -468,7 +468,11 @@ def test_one_launch_attention_when_the_batch_changes_between_runs(cuda):
         one = ModelInstance(spec.to_runtime())
     finally:
         os.environ.pop("RMLK_B200_ATTENTION", None)
-    apart = ModelInstance(spec.to_runtime())
+    os.environ["RMLK_B200_ATTENTION"] = "0"
+    try:
+        apart = ModelInstance(spec.to_runtime())
+    finally:
+        os.environ.pop("RMLK_B200_ATTENTION", None)
     for m in (one, apart):
         m.bind("present_k", "past_k")
         m.bind("present_v", "past_v")
