@@ -359,24 +359,27 @@ __global__ void __launch_bounds__(128) gqa_decode_attention_split_kernel(AttnSpl
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// One pass over K and V ("flash" decode), fed by bulk copies.  One CTA per problem: 8 working warps and one warp that
-// feeds a ring of three shared-memory stages.  The keys are taken in blocks of 64: the feeding warp requests the block's K
-// rows and V rows (contiguous in the cache) with cp.async.bulk, so up to 96 KB per CTA (two CTAs per SM at head_dim 64)
-// are on their way from HBM while the warps work on earlier blocks - loads cost no registers and never wait for
-// arithmetic.  Inside the loop nothing synchronises the CTA: every warp keeps a running softmax of its own.
+// One pass over K and V ("flash" decode), fed by bulk copies.  One CTA per problem: 4 working warps and one warp that
+// feeds a ring of three shared-memory stages.  The keys are taken in blocks of 32: the feeding warp requests the block's K
+// rows and V rows (contiguous in the cache) with cp.async.bulk, so up to 48 KB per CTA at head_dim 64 are on their way
+// from HBM while the warps work on earlier blocks - loads cost no registers and never wait for arithmetic.  Four such
+// CTAs share an SM: 592 places on 148 SMs, so the 512 problems of 64 requests x 8 KV heads are all resident at once
+// (with 8 warps and 64-key blocks, two CTAs per SM, they ran as two uneven waves: 31 us against 27 us).  Inside the
+// loop nothing synchronises the CTA: every warp keeps a running softmax of its own.
 // Per block, warp w takes keys 8 w .. 8 w + 7:
 //   scores   LPR lanes read one K row from shared memory (16 bytes each), dot products by the FMA order and shuffle
-//            butterfly of the kernels above; scale and mask; the 8 x 4 scores go to the warp's own 128 bytes of shared memory.
-//   softmax  lane i holds score (key i / 4, row i % 4): row maximum over the 8 keys by shuffles, one expf for the probability,
-//            one for the factor that rescales what the warp has accumulated so far; probabilities back to shared memory.
+//            butterfly of the kernels above; scale; the 8 x 4 scores go to the warp's own 128 bytes of shared memory.
+//   softmax  lane i holds score (key i / 4, row i % 4) and adds its mask value: row maximum over the 8 keys by shuffles,
+//            one expf for the probability, one for the factor that rescales what the warp has accumulated so far;
+//            probabilities back to shared memory.
 //   values   the warp's 8 V rows times their probabilities into acc[4][4] (lane = 4 columns of the head).
-//   then lane 0 hands the stage back to the feeding warp (an mbarrier that counts the 8 warps).
-// At the end the 8 warps' maxima, sums and accumulators meet in shared memory and are combined in warp order.
+//   then lane 0 hands the stage back to the feeding warp (an mbarrier that counts the working warps).
+// At the end the warps' maxima, sums and accumulators meet in shared memory and are combined in warp order.
 // Waits are bounded; if one ever expired the problem's output would be NaN (never observed).
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int FL_KEYS = 64;     // keys per block
+constexpr int FL_KEYS = 32;     // keys per block
 constexpr int FL_STAGES = 3;
-constexpr int FL_WARPS = 8;     // working warps; one more feeds the ring
+constexpr int FL_WARPS = 4;     // working warps; one more feeds the ring
 constexpr int FL_THREADS = 32 * (FL_WARPS + 1);
 
 template <int LPR>
@@ -384,10 +387,10 @@ struct FlashSmem {
     static constexpr int D = 4 * LPR;
     static constexpr uint32_t BLOCK_BYTES = FL_KEYS * D * 4;                 // K (or V) rows of one block
     static constexpr uint32_t STAGE_BYTES = 2 * BLOCK_BYTES;
-    static constexpr uint32_t RING_BYTES = FL_STAGES * STAGE_BYTES;          // reused at the end: [8 warps][4 rows][D] partial outputs
-    static constexpr uint32_t SCORES_OFF = RING_BYTES;                       // [8 warps][8 keys][4 rows] floats
-    static constexpr uint32_t CORR_OFF = SCORES_OFF + FL_WARPS * 32 * 4;     // [8 warps][4 rows] rescale factors
-    static constexpr uint32_t STATS_OFF = CORR_OFF + FL_WARPS * 4 * 4;       // m[8 warps][4], then l[8 warps][4]
+    static constexpr uint32_t RING_BYTES = FL_STAGES * STAGE_BYTES;          // reused at the end: [warps][4 rows][D] partial outputs
+    static constexpr uint32_t SCORES_OFF = RING_BYTES;                       // [warps][8 keys][4 rows] floats
+    static constexpr uint32_t CORR_OFF = SCORES_OFF + FL_WARPS * 32 * 4;     // [warps][4 rows] rescale factors
+    static constexpr uint32_t STATS_OFF = CORR_OFF + FL_WARPS * 4 * 4;       // m[warps][4], then l[warps][4]
     static constexpr uint32_t BAR_OFF = STATS_OFF + 2 * FL_WARPS * 4 * 4;    // full[FL_STAGES], empty[FL_STAGES] mbarriers, then a flag word
     static constexpr uint32_t TOTAL = BAR_OFF + 16 * FL_STAGES + 16;
     static_assert(RING_BYTES >= FL_WARPS * 4 * D * 4, "the ring must hold the warps' partial outputs");
@@ -409,7 +412,7 @@ __device__ __forceinline__ bool fl_wait(uint32_t bar, uint32_t parity, volatile 
 }
 
 template <int LPR>
-__global__ void __launch_bounds__(FL_THREADS, LPR <= 16 ? 2 : 1) gqa_decode_flash_kernel(AttnParams p) {
+__global__ void __launch_bounds__(FL_THREADS, LPR <= 16 ? 4 : 2) gqa_decode_flash_kernel(AttnParams p) {
     using L = FlashSmem<LPR>;
     constexpr int D = 4 * LPR;
     constexpr int RPI = 32 / LPR;          // rows per warp-wide 16-byte-per-lane access

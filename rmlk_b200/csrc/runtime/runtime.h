@@ -240,7 +240,7 @@ struct Instance {
     std::vector<int> append_consumer;
     bool inplace_append_to = true;  // RMLK_B200_NO_APPEND_TO=1: new rows are made dense first, then copied in
     // Scores MatMul, softmax chain and context MatMul of a decode step run as one kernel, one CTA per problem (measured on
-    // 512 problems of 4 query rows over 550 keys, head size 64: 31 us against 39 us for the three kernels it replaces).
+    // 512 problems of 4 query rows over 523 keys, head size 64: 27 us against 39 us for the three kernels it replaces).
     // RMLK_B200_ATTENTION=0 keeps the three kernels; =split uses the kernel that splits a problem's keys over CTAs of
     // 128 keys and combines them through a workspace (slower on that shape).
     bool attention = true;
