@@ -246,18 +246,15 @@ def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):
             e["tflops"] = flops / (ms * 1e-3) / 1e12
         out[name] = e
 
-    # decode scores, read from the KV cache in place: B*8 problems [4 q-heads, 64] x [T, 64]^T (A x B^T kernel)
-    kc = ring(lambda: torch.randn(B * 8, T, 64, device=dev), 4 * B * 8 * T * 64)
-    q = torch.randn(B * 8, 4, 64, device=dev)
-    sc = torch.empty(B * 8, 4, T, device=dev)
-    add("scores", "nt_rows_kernel<4,16>", lambda i: K.matmul_nt(q, kc[i % len(kc)], out=sc), 4 * B * 8 * (4 * 64 + 64 * T + 4 * T),
-        [B * 8, 4, 64, T], flops=2 * B * 32 * 64 * T)
-    # decode context: B*8 problems [4 q-heads, T] x [T, 64]
-    p = torch.randn(B * 8, 4, T, device=dev)
-    cx = torch.empty(B * 8, 4, 64, device=dev)
-    add("context", "nn_narrow_kernel<4,16>", lambda i: K.matmul(p, kc[i % len(kc)], out=cx), 4 * B * 8 * (4 * T + 64 * T + 4 * 64),
-        [B * 8, 4, T, 64], flops=2 * B * 32 * 64 * T)
-    del kc, q, sc, p, cx
+    # decode attention as the step runs it: one launch per layer over the KV cache in place, B*8 problems of 4 query heads,
+    # scores + additive mask + softmax + context; K and V are read once
+    kc = ring(lambda: torch.randn(B, 8, T, 64, device=dev), 4 * B * 8 * T * 64)
+    q = torch.randn(B, 8, 4, 64, device=dev)
+    mask = torch.zeros(B, 1, 1, T, device=dev)
+    cx = torch.empty(B, 8, 4, 64, device=dev)
+    add("attention", "gqa_decode_flash_kernel<16>", lambda i: K.gqa_decode_attention(q, kc[i % len(kc)], kc[(i + 1) % len(kc)], 0.125, mask=mask, out=cx),
+        4 * B * 8 * (2 * 64 * T + 2 * 4 * 64) + 4 * B * T, [B * 8, 4, 64, T], flops=4 * B * 32 * 64 * T)
+    del kc, q, mask, cx
     # weight-streaming MatMul at the FFN gate/up shape and at the lm_head
     # gate | up projections as the runtime runs them (one MatMul on the concatenated weights), the down projection, the lm_head
     for name, (m, k, n) in (("matmul_gate_up", (B, 2048, 16384)), ("matmul_qkv", (B, 2048, 3072)), ("matmul_down", (B, 8192, 2048)),
@@ -274,6 +271,32 @@ def kernel_rooflines(batch, ctx, peak_gbs, peak_kind):
     return out
 
 
+def bind_to_gpu_numa_node(local):
+    """Runs this process (and so its pinned host buffers, which are placed where the allocating thread runs) on the CPUs
+    of the NUMA node the GPU hangs off: with several ranks per host, logits otherwise cross the socket link on their way
+    to memory.  Returns the node, or None when the topology cannot be read (then nothing is changed)."""
+    try:
+        import torch
+        bus = torch.cuda.get_device_properties(local).pci_bus_id
+        dom = torch.cuda.get_device_properties(local).pci_domain_id
+        dev = torch.cuda.get_device_properties(local).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
+        node = int(open(path).read().strip())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return node
+    except Exception:
+        return None
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -283,6 +306,7 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    numa_node = bind_to_gpu_numa_node(local) if world > 1 else None
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
@@ -519,7 +543,7 @@ def run_ours(args):
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": K_, "warmup": W, "ms_per_step": dev_ms / K_,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(cfg, B, P),
+        "config": dict(workload_config(cfg, B, P), **({"host_numa_node_of_rank0": numa_node} if numa_node is not None else {})),
         "roofline": roof, "cpu_baseline": cpu,
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * cfg.vocab * 4,
                 "ms_per_step": e2e_ms / K_, "rounds_ms_per_step": [m / K_ for m in e2e_rounds]},

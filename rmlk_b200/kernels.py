@@ -388,7 +388,7 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[to
 
 
 def gqa_decode_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, mask: Optional[torch.Tensor] = None,
-                         split: bool = False, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+                         split: bool = False, workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [B, KV, G, D] (G <= 4 query heads per KV head, one token each); k, v [B, KV, T, D] views whose [T, D] blocks are
     dense (the batch / head dims may step over spare room); mask [B, 1 or KV*G, 1, T] or None -> [B, KV, G, D]."""
     _require_cuda(q, mask)
@@ -397,7 +397,9 @@ def gqa_decode_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scal
     assert k.is_cuda and v.is_cuda and k.shape == v.shape == (B, KV, T, D) and q.is_contiguous()
     assert k.stride(3) == 1 and k.stride(2) == D and v.stride(3) == 1 and v.stride(2) == D
     assert k.stride(0) == KV * k.stride(1) and v.stride(0) == KV * v.stride(1)
-    out = torch.empty_like(q)
+    if out is None:
+        out = torch.empty_like(q)
+    assert out.shape == q.shape and out.is_contiguous() and out.dtype == q.dtype
     mb = mh = 0
     if mask is not None:
         assert mask.dim() == 4 and mask.shape[0] == B and mask.shape[2] == 1 and mask.shape[3] == T and mask.stride(3) == 1
