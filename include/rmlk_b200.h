@@ -390,6 +390,33 @@ RMLK_API int rmlk_b200_rope_to(rmlk_stream_t stream, int dtype, const int64_t* s
                       const int64_t* cos_strides, const int64_t* sin_strides, const void* x, const void* cosv, const void* sinv,
                       void* out, const int64_t* out_strides);
 
+/* Several small placements as ONE launch: rotary embeddings (as rmlk_b200_rope_to) and strided -> strided copies of 4-byte
+ * elements (as rmlk_b200_strided_copy_to, rank <= 5), e.g. the rotated queries, the rotated keys into their cache slot and
+ * the new values into theirs, which a decode step would otherwise issue as three launches of a few microseconds each.
+ * The jobs must be independent of one another (no job reads what another writes).  Every job may read its input as the
+ * sum of `in_parts` split-K slabs `in_part_stride` elements apart, added in slab order starting from 0.f as
+ * rmlk_b200_sum_parts does (in_parts <= 1: a plain tensor).  At most RMLK_BATCH_MAX_JOBS jobs. */
+#define RMLK_BATCH_MAX_JOBS 4
+#define RMLK_BATCH_ROPE 0
+#define RMLK_BATCH_COPY4 1
+typedef struct rmlk_batch_job {
+    int kind;                /* RMLK_BATCH_ROPE | RMLK_BATCH_COPY4 */
+    int rank;                /* ROPE: 4; COPY4: 1..5 */
+    int in_parts;            /* split-K slabs of the input (0 or 1: none) */
+    int reserved;
+    int64_t in_part_stride;  /* elements between slabs */
+    int64_t shape[5];
+    int64_t in_strides[5];   /* element strides */
+    int64_t out_strides[5];
+    int64_t cos_strides[4];  /* ROPE only */
+    int64_t sin_strides[4];
+    const void* in;
+    const void* cosv;
+    const void* sinv;
+    void* out;
+} rmlk_batch_job;
+RMLK_API int rmlk_b200_rope_copy_batch(rmlk_stream_t stream, int n_jobs, const rmlk_batch_job* jobs);
+
 /* Decode attention over a KV cache read in place, one launch: for each of `problems` (batch entry x KV head) and each
  * of its `rows` (1..4) query rows - the query heads sharing that KV head, one new token each -
  *   out[p][r] = softmax_t((q[p][r] . K[p][t]) * scale + mask[b][h][t]) . V[p][:, :]

@@ -184,6 +184,61 @@ __global__ void __launch_bounds__(256) rope_f32_kernel(RopeParams p, int64_t tot
     out[i0 * p.os[0] + i1 * p.os[1] + i2 * p.os[2] + j * p.os[3]] = __fadd_rn(__fmul_rn(xv, cosv[cb]), __fmul_rn(rot, sinv[sb]));
 }
 
+// ---- several rotary embeddings / 4-byte strided copies as one launch (blockIdx.y = job) -----------------------------------
+struct BatchJob {
+    int kind, rank, parts, pad;
+    int64_t part_stride, total;
+    int64_t d[5], is[5], os[5], cs[4], ss[4];
+    const float* in;
+    const float* cosv;
+    const float* sinv;
+    float* out;
+};
+struct BatchParams {
+    BatchJob job[RMLK_BATCH_MAX_JOBS];
+};
+
+// the value at element offset `off` of a tensor that may still be split-K slabs (added in slab order from 0.f)
+__device__ __forceinline__ float batch_load(const BatchJob& j, int64_t off) {
+    if (j.parts <= 1) return j.in[off];
+    float s = 0.f;
+    for (int k = 0; k < j.parts; k++) s += j.in[k * j.part_stride + off];
+    return s;
+}
+
+__global__ void __launch_bounds__(256) rope_copy_batch_kernel(const __grid_constant__ BatchParams bp) {
+    dep_sync();
+    const BatchJob& p = bp.job[blockIdx.y];
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= p.total) return;
+    if (p.kind == RMLK_BATCH_ROPE) {
+        // the expressions of rope_f32_kernel
+        const int64_t D = p.d[3], half = D / 2;
+        int64_t t = i;
+        const int64_t j = t % D;
+        t /= D;
+        const int64_t i2 = t % p.d[2];
+        t /= p.d[2];
+        const int64_t i1 = t % p.d[1];
+        const int64_t i0 = t / p.d[1];
+        const int64_t xb = i0 * p.is[0] + i1 * p.is[1] + i2 * p.is[2];
+        const int64_t cb = i0 * p.cs[0] + i1 * p.cs[1] + i2 * p.cs[2] + j * p.cs[3];
+        const int64_t sb = i0 * p.ss[0] + i1 * p.ss[1] + i2 * p.ss[2] + j * p.ss[3];
+        const float xv = batch_load(p, xb + j * p.is[3]);
+        const float rot = j < half ? __fmul_rn(batch_load(p, xb + (j + half) * p.is[3]), -1.0f) : batch_load(p, xb + (j - half) * p.is[3]);
+        p.out[i0 * p.os[0] + i1 * p.os[1] + i2 * p.os[2] + j * p.os[3]] = __fadd_rn(__fmul_rn(xv, p.cosv[cb]), __fmul_rn(rot, p.sinv[sb]));
+    } else {
+        int64_t t = i, io = 0, oo = 0;
+        for (int d = p.rank - 1; d >= 0; d--) {
+            const int64_t q = t / p.d[d], r = t - q * p.d[d];
+            io += r * p.is[d];
+            oo += r * p.os[d];
+            t = q;
+        }
+        p.out[oo] = batch_load(p, io);
+    }
+}
+
 __global__ void __launch_bounds__(256) swiglu_f32_kernel(int64_t n, const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ out) {
     dep_sync();
     const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
@@ -355,6 +410,58 @@ extern "C" int rmlk_b200_rope_to(rmlk_stream_t stream, int dtype, const int64_t*
     launch_dep(rope_f32_kernel, dim3(static_cast<unsigned>(ceil_div64(total, 256))), dim3(256), 0, as_stream(stream), 
         p, total, static_cast<const float*>(x), static_cast<const float*>(cosv), static_cast<const float*>(sinv), static_cast<float*>(out));
     RMLK_CHECK_LAUNCH("rope_f32_kernel");
+    return RMLK_OK;
+}
+
+extern "C" int rmlk_b200_rope_copy_batch(rmlk_stream_t stream, int n_jobs, const rmlk_batch_job* jobs) {
+    if (n_jobs < 0 || n_jobs > RMLK_BATCH_MAX_JOBS) return fail(RMLK_ERR_INVALID_ARG, "rope_copy_batch: between 0 and 4 jobs");
+    if (n_jobs == 0) return RMLK_OK;
+    if (!jobs) return fail(RMLK_ERR_INVALID_ARG, "rope_copy_batch: NULL jobs");
+    BatchParams bp;
+    int n = 0;
+    int64_t most = 0;
+    for (int q = 0; q < n_jobs; q++) {
+        const rmlk_batch_job& src = jobs[q];
+        if (src.kind != RMLK_BATCH_ROPE && src.kind != RMLK_BATCH_COPY4) return fail(RMLK_ERR_INVALID_ARG, "rope_copy_batch: unknown job kind");
+        const int rank = src.kind == RMLK_BATCH_ROPE ? 4 : src.rank;
+        if (rank < 1 || rank > 5) return fail(RMLK_ERR_INVALID_ARG, "rope_copy_batch: rank must be 1..5 (4 for a rotary job)");
+        BatchJob& j = bp.job[n];
+        j.kind = src.kind;
+        j.rank = rank;
+        j.parts = src.in_parts > 1 ? src.in_parts : 1;
+        j.pad = 0;
+        j.part_stride = src.in_part_stride;
+        j.total = 1;
+        for (int d = 0; d < 5; d++) {
+            j.d[d] = d < rank ? src.shape[d] : 1;
+            j.is[d] = d < rank ? src.in_strides[d] : 0;
+            j.os[d] = d < rank ? src.out_strides[d] : 0;
+            if (j.d[d] < 0) return fail(RMLK_ERR_INVALID_ARG, "rope_copy_batch: negative extent");
+            j.total *= j.d[d];
+        }
+        for (int d = 0; d < 4; d++) {
+            j.cs[d] = src.cos_strides[d];
+            j.ss[d] = src.sin_strides[d];
+        }
+        if (j.total == 0) continue;
+        if (src.kind == RMLK_BATCH_ROPE && (j.d[3] % 2)) return fail(RMLK_ERR_INVALID_ARG, "rope: head dim must be even");
+        if (!src.in || !src.out || (src.kind == RMLK_BATCH_ROPE && (!src.cosv || !src.sinv)))
+            return fail(RMLK_ERR_INVALID_ARG, "rope_copy_batch: NULL tensor pointer");
+        if (ceil_div64(j.total, 256) > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "rope_copy_batch: tensor too large");
+        j.in = static_cast<const float*>(src.in);
+        j.cosv = static_cast<const float*>(src.cosv);
+        j.sinv = static_cast<const float*>(src.sinv);
+        j.out = static_cast<float*>(src.out);
+        if (j.total > most) most = j.total;
+        n++;
+    }
+    if (n == 0) return RMLK_OK;
+    for (int q = n; q < RMLK_BATCH_MAX_JOBS; q++) {
+        bp.job[q] = bp.job[0];
+        bp.job[q].total = 0;
+    }
+    launch_dep(rope_copy_batch_kernel, dim3(static_cast<unsigned>(ceil_div64(most, 256)), static_cast<unsigned>(n)), dim3(256), 0, as_stream(stream), bp);
+    RMLK_CHECK_LAUNCH("rope_copy_batch_kernel");
     return RMLK_OK;
 }
 

@@ -1142,9 +1142,24 @@ bool concat_append(const Ctx& c) {
                         run *= ps[p2];
                     }
                 }
-                check_rc(rmlk_b200_strided_copy_to(c.stream(), static_cast<int>(ap.elem), static_cast<int>(ps.size()), ps.data(), pst.data(), ost.data(),
-                                                   add->data, slot));
-                c.launched();
+                if (ap.elem == 4 && ps.size() <= 5) {
+                    // collected with the rotary embeddings of the same layer: one launch for all of them
+                    rmlk_batch_job j = {};
+                    j.kind = RMLK_BATCH_COPY4;
+                    j.rank = static_cast<int>(ps.size());
+                    for (size_t d = 0; d < 5; d++) {
+                        j.shape[d] = d < ps.size() ? ps[d] : 1;
+                        j.in_strides[d] = d < ps.size() ? pst[d] : 0;
+                        j.out_strides[d] = d < ps.size() ? ost[d] : 0;
+                    }
+                    j.in = add->data;
+                    j.out = slot;
+                    c.I.defer_job(j);
+                } else {
+                    check_rc(rmlk_b200_strided_copy_to(c.stream(), static_cast<int>(ap.elem), static_cast<int>(ps.size()), ps.data(), pst.data(), ost.data(),
+                                                       add->data, slot));
+                    c.launched();
+                }
             } else {
                 c.I.materialize(*add);
             }
@@ -1747,6 +1762,29 @@ void Instance::find_fusions() {
 
 // Runs the fused kernel of `fg` if the tensors of this run meet its conditions.  False: nothing was launched and no
 // output was touched; the caller runs the member nodes instead.
+// a rotary embedding as a collected job (out_strides == nullptr: dense output)
+static rmlk_batch_job rope_job(const Shape& oshape, const int64_t* xstr, const int64_t* cstr, const int64_t* sstr, const void* x, const void* cosv,
+                               const void* sinv, void* out, const int64_t* out_strides) {
+    rmlk_batch_job j = {};
+    j.kind = RMLK_BATCH_ROPE;
+    j.rank = 4;
+    int64_t run = 1;
+    for (int d = 3; d >= 0; d--) {
+        j.shape[d] = oshape[d];
+        j.in_strides[d] = xstr[d];
+        j.cos_strides[d] = cstr[d];
+        j.sin_strides[d] = sstr[d];
+        j.out_strides[d] = out_strides ? out_strides[d] : run;
+        run *= oshape[d] > 0 ? oshape[d] : 1;
+    }
+    j.shape[4] = 1;
+    j.in = x;
+    j.cosv = cosv;
+    j.sinv = sinv;
+    j.out = out;
+    return j;
+}
+
 bool Instance::run_fused(const FusedGroup& fg) {
     const NodeDef& root = g.nodes[fg.root];
     Ctx c{*this, root};
@@ -1985,14 +2023,12 @@ bool Instance::run_fused(const FusedGroup& fg) {
                 o.parts = 0;
                 set_strided(o, slot, oshape, ost);
                 o.present = true;
-                check_rc(rmlk_b200_rope_to(st, RMLK_F32, oshape.data(), xstr, cstr, sstr, xdata, cs->data, sn->data, slot, ost.data()));
-                launches++;
+                defer_job(rope_job(oshape, xstr, cstr, sstr, xdata, cs->data, sn->data, slot, ost.data()));
                 return true;
             }
             Tensor& o = c.make(0, RMLK_F32, oshape);
             if (o.numel() == 0) return true;
-            check_rc(rmlk_b200_rope(st, RMLK_F32, oshape.data(), xstr, cstr, sstr, xdata, cs->data, sn->data, o.data));
-            launches++;
+            defer_job(rope_job(oshape, xstr, cstr, sstr, xdata, cs->data, sn->data, o.data, nullptr));
             return true;
         }
     }

@@ -27,12 +27,63 @@ void unsupported_dtype(int dt, const char* what) {
     raise(RMLK_ERR_UNSUPPORTED_DTYPE, std::string("unsupported data type: ") + dtype_name(dt) + " (" + what + ")");
 }
 
-void check_cuda(cudaError_t e, const char* what) {
+void check_cuda_fn(cudaError_t e, const char* what) {
     if (e != cudaSuccess) raise(RMLK_ERR_CUDA_BASE + static_cast<int>(e), std::string(what) + ": " + cudaGetErrorString(e));
 }
 
-void check_rc(int rc) {
+void check_rc_fn(int rc) {
     if (rc != RMLK_OK) raise(rc, rmlk_b200_last_error());
+}
+
+// the instance whose run() is executing on this thread (jobs are only ever collected inside run())
+static thread_local Instance* tl_running = nullptr;
+
+void flush_deferred() {
+    if (tl_running && !tl_running->pending_jobs.empty()) tl_running->flush_jobs();
+}
+
+void Instance::flush_jobs() {
+    if (pending_jobs.empty()) return;
+    std::vector<rmlk_batch_job> jobs;
+    jobs.swap(pending_jobs);  // empty before anything is enqueued: the launch below goes through no check_rc macro
+    check_rc_fn(rmlk_b200_rope_copy_batch(reinterpret_cast<rmlk_stream_t>(stream), static_cast<int>(jobs.size()), jobs.data()));
+    launches++;
+}
+
+// the byte range [lo, hi) a job's tensor covers (elements of 4 bytes; strides may be 0 or negative)
+static void job_span(const void* base, int rank, const int64_t* shape, const int64_t* strides, int parts, int64_t part_stride, const char*& lo,
+                     const char*& hi) {
+    int64_t mn = 0, mx = 0;
+    for (int d = 0; d < rank; d++) {
+        const int64_t ext = (shape[d] > 0 ? shape[d] - 1 : 0) * strides[d];
+        if (ext < 0) mn += ext; else mx += ext;
+    }
+    if (parts > 1) mx += static_cast<int64_t>(parts - 1) * part_stride;
+    lo = static_cast<const char*>(base) + mn * 4;
+    hi = static_cast<const char*>(base) + (mx + 1) * 4;
+}
+
+void Instance::defer_job(const rmlk_batch_job& job) {
+    if (!batch_jobs || tl_running != this) {
+        check_rc_fn((flush_deferred(), rmlk_b200_rope_copy_batch(reinterpret_cast<rmlk_stream_t>(stream), 1, &job)));
+        launches++;
+        return;
+    }
+    // a job may not read or overwrite what a collected job writes, nor overwrite what one reads: launch those first
+    const int rank = job.kind == RMLK_BATCH_ROPE ? 4 : job.rank;
+    const char *ilo, *ihi, *olo, *ohi;
+    job_span(job.in, rank, job.shape, job.in_strides, job.in_parts, job.in_part_stride, ilo, ihi);
+    job_span(job.out, rank, job.shape, job.out_strides, 0, 0, olo, ohi);
+    bool clash = pending_jobs.size() >= RMLK_BATCH_MAX_JOBS;
+    for (const rmlk_batch_job& p : pending_jobs) {
+        const int pr = p.kind == RMLK_BATCH_ROPE ? 4 : p.rank;
+        const char *plo, *phi, *qlo, *qhi;
+        job_span(p.in, pr, p.shape, p.in_strides, p.in_parts, p.in_part_stride, plo, phi);
+        job_span(p.out, pr, p.shape, p.out_strides, 0, 0, qlo, qhi);
+        if ((ilo < qhi && qlo < ihi) || (olo < qhi && qlo < ohi) || (olo < phi && plo < ohi)) clash = true;
+    }
+    if (clash) flush_jobs();
+    pending_jobs.push_back(job);
 }
 
 size_t Tensor::nbytes() const { return static_cast<size_t>(numel()) * dtype_size_of(dtype); }
@@ -368,6 +419,18 @@ std::string status_word_message(int word) {
 }
 
 void Instance::run() {
+    // jobs are collected only while this function runs; whatever is left goes out before the outputs are delivered,
+    // and nothing stays collected if the run ends with an error
+    struct Running {
+        Instance* self;
+        Instance* before;
+        explicit Running(Instance* s) : self(s), before(tl_running) { tl_running = s; }
+        ~Running() {
+            self->pending_jobs.clear();
+            tl_running = before;
+        }
+    } running(this);
+    pending_jobs.clear();
     check_cuda(cudaSetDevice(device), "cudaSetDevice");
     launches = 0;
     syncs = 0;
@@ -451,6 +514,7 @@ void Instance::run() {
         for (int v : n.outputs)
             if (v >= 0 && last_use[v] < 0 && !g.values[v].is_output) release_value(v);
     }
+    flush_jobs();
     deliver_host_outputs();
     for (Binding& b : bindings) {
         b.carried = values[b.out_id];
@@ -670,6 +734,7 @@ extern "C" rmlk_instance* rmlk_instance_create(const rmlk_graph* g, int device, 
         if (const char* e = getenv("RMLK_B200_NO_FUSION")) I.fusion = e[0] != '1';
         if (const char* e = getenv("RMLK_B200_NO_ADD_NORM")) I.add_norm = e[0] != '1';
         if (const char* e = getenv("RMLK_B200_NO_APPEND_TO")) I.inplace_append_to = e[0] != '1';
+        if (const char* e = getenv("RMLK_B200_NO_BATCH")) I.batch_jobs = e[0] != '1';
         if (const char* e = getenv("RMLK_B200_ATTENTION")) {
             I.attention = e[0] != '0';
             I.attention_split = e[0] == 's';

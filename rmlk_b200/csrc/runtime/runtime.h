@@ -267,6 +267,14 @@ struct Instance {
     // host view of a small tensor: mirror if valid, else a synchronous D2H copy
     std::vector<int64_t> host_i64(const Tensor& t);
     std::vector<double> host_f64(const Tensor& t);
+    // Small placements of a decode step (rotary embeddings with a placed output, 4-byte strided copies into a cache
+    // slot) are not launched where they come up but collected; whatever else is enqueued next - any kernel, copy or
+    // synchronisation goes through check_rc / check_cuda - launches the collected jobs first, as one kernel.  Stream
+    // order is therefore exactly what it would be without collecting.  RMLK_B200_NO_BATCH=1: every job launches at once.
+    bool batch_jobs = true;
+    std::vector<rmlk_batch_job> pending_jobs;
+    void defer_job(const rmlk_batch_job& job);
+    void flush_jobs();
     void run_node(const NodeDef& n);
     void release_value(int value_id);
     // replaces a deferred view by a dense copy in arena memory (no-op for a dense tensor)
@@ -277,8 +285,14 @@ struct Instance {
 size_t dtype_size_of(int dt);
 
 std::string status_word_message(int word);  // text for a non-zero device status word
-void check_cuda(cudaError_t e, const char* what);
-void check_rc(int rc);
+void check_cuda_fn(cudaError_t e, const char* what);
+void check_rc_fn(int rc);
+// launches the collected jobs of the instance that is running on this thread, if there are any
+void flush_deferred();
+// Every call into the kernel library and every CUDA call of the runtime is wrapped in one of these two: the collected
+// jobs go out before whatever the wrapped expression enqueues (the comma operator evaluates left to right).
+#define check_rc(expr) (::rmlk::rt::flush_deferred(), ::rmlk::rt::check_rc_fn(expr))
+#define check_cuda(expr, what) (::rmlk::rt::flush_deferred(), ::rmlk::rt::check_cuda_fn((expr), (what)))
 
 }  // namespace rt
 }  // namespace rmlk

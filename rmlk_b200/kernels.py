@@ -387,6 +387,48 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[to
     return out
 
 
+class _BatchJob(ctypes.Structure):
+    """rmlk_batch_job of include/rmlk_b200.h."""
+    _fields_ = [("kind", ctypes.c_int), ("rank", ctypes.c_int), ("in_parts", ctypes.c_int), ("reserved", ctypes.c_int),
+                ("in_part_stride", ctypes.c_int64), ("shape", ctypes.c_int64 * 5), ("in_strides", ctypes.c_int64 * 5),
+                ("out_strides", ctypes.c_int64 * 5), ("cos_strides", ctypes.c_int64 * 4), ("sin_strides", ctypes.c_int64 * 4),
+                ("inp", ctypes.c_void_p), ("cosv", ctypes.c_void_p), ("sinv", ctypes.c_void_p), ("out", ctypes.c_void_p)]
+
+
+def rope_copy_batch(jobs) -> None:
+    """Several placements as one launch.  jobs: up to 4 tuples, ("rope", x, cos, sin, out) or ("copy", src, dst), all fp32 CUDA
+    views (any strides; cos / sin broadcastable to x; out / dst may be slots of larger buffers).  A source given as
+    (slabs, parts) - a view [parts, *shape] whose first stride is the distance between slabs - is read as the sum of the
+    slabs in order."""
+    arr = (_BatchJob * len(jobs))()
+    keep = []
+    for j, job in zip(arr, jobs):
+        kind, src = job[0], job[1]
+        parts = 0
+        if isinstance(src, tuple):
+            src, parts = src
+            assert src.shape[0] == parts
+            j.in_part_stride = src.stride(0)
+            src = src[0]
+        dst = job[-1]
+        assert src.is_cuda and dst.is_cuda and src.dtype == torch.float32 and dst.dtype == torch.float32 and src.shape == dst.shape
+        j.kind = 0 if kind == "rope" else 1
+        j.rank = src.dim()
+        j.in_parts = parts
+        for d in range(src.dim()):
+            j.shape[d], j.in_strides[d], j.out_strides[d] = src.shape[d], src.stride(d), dst.stride(d)
+        if kind == "rope":
+            assert src.dim() == 4
+            for name, t in (("cos_strides", job[2]), ("sin_strides", job[3])):
+                st = (t if t.dim() == 4 else t.reshape([1] * (4 - t.dim()) + list(t.shape))).expand(src.shape).stride()
+                for d in range(4):
+                    getattr(j, name)[d] = st[d]
+            j.cosv, j.sinv = job[2].data_ptr(), job[3].data_ptr()
+        j.inp, j.out = src.data_ptr(), dst.data_ptr()
+        keep.append((src, dst))
+    _check(lib().rmlk_b200_rope_copy_batch(_stream(), len(jobs), arr))
+
+
 def gqa_decode_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, mask: Optional[torch.Tensor] = None,
                          split: bool = False, workspace: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [B, KV, G, D] (G <= 4 query heads per KV head, one token each); k, v [B, KV, T, D] views whose [T, D] blocks are

@@ -399,6 +399,54 @@ def attention_graph(KV, G, D):
     return g
 
 
+def test_rope_copy_batch_equals_the_single_launches(K):
+    """rmlk_b200_rope_copy_batch: rotated queries (dense), rotated keys and new values placed into cache slots, as one
+    launch - bit for bit what rmlk_b200_rope / rope_to / strided_copy_to give one by one; also with the source left as
+    split-K slabs (summed in slab order, as rmlk_b200_sum_parts would)."""
+    import torch
+    g = torch.Generator(device="cuda").manual_seed(5)
+    B, H, KV, D, T0, cap = 3, 8, 2, 64, 37, 64
+    qkv = torch.randn(B, (H + 2 * KV) * D, device="cuda", generator=g)
+    q = qkv[:, : H * D].view(B, 1, H, D).permute(0, 2, 1, 3)                   # [B, H, 1, D] views of the merged product
+    k = qkv[:, H * D: (H + KV) * D].view(B, 1, KV, D).permute(0, 2, 1, 3)
+    v = qkv[:, (H + KV) * D:].view(B, 1, KV, D).permute(0, 2, 1, 3)
+    cos = torch.randn(B, 1, 1, D, device="cuda", generator=g)
+    sin = torch.randn(B, 1, 1, D, device="cuda", generator=g)
+    kc1, vc1 = torch.zeros(B, KV, cap, D, device="cuda"), torch.zeros(B, KV, cap, D, device="cuda")
+    kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(vc1)
+    want_q = K.rope(q, cos, sin)
+    K.rope(k, cos, sin, out=kc1[:, :, T0: T0 + 1])
+    K.strided_copy_to(v, vc1[:, :, T0: T0 + 1])
+    got_q = torch.empty(B, H, 1, D, device="cuda")
+    K.rope_copy_batch([("rope", q, cos, sin, got_q), ("rope", k, cos, sin, kc2[:, :, T0: T0 + 1]), ("copy", v, vc2[:, :, T0: T0 + 1])])
+    assert torch.equal(got_q, want_q) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    # the same with the product still in 5 split-K slabs
+    parts = 5
+    slabs = torch.randn(parts, B, (H + 2 * KV) * D, device="cuda", generator=g)
+    total = torch.zeros(B, (H + 2 * KV) * D, device="cuda")
+    for p in range(parts):
+        total += slabs[p]
+    tq = total[:, : H * D].view(B, 1, H, D).permute(0, 2, 1, 3)
+    tv = total[:, (H + KV) * D:].view(B, 1, KV, D).permute(0, 2, 1, 3)
+    sq = slabs[:, :, : H * D].view(parts, B, 1, H, D).permute(0, 1, 3, 2, 4)
+    sv = slabs[:, :, (H + KV) * D:].view(parts, B, 1, KV, D).permute(0, 1, 3, 2, 4)
+    want_q = K.rope(tq, cos, sin)
+    vc3, vc4 = torch.zeros_like(vc1), torch.zeros_like(vc1)
+    K.strided_copy_to(tv, vc3[:, :, 5:6])
+    got_q = torch.empty(B, H, 1, D, device="cuda")
+    arr = [("rope", _slab_source(sq), cos, sin, got_q), ("copy", _slab_source(sv), vc4[:, :, 5:6])]
+    K.rope_copy_batch(arr)
+    assert torch.equal(got_q, want_q) and torch.equal(vc3, vc4)
+    with pytest.raises(Exception):
+        K.rope_copy_batch([("copy", v, vc2[:, :, 0:1])] * 5)   # more than RMLK_BATCH_MAX_JOBS
+
+
+class _slab_source(tuple):
+    """(view of slab 0, parts) with the slab stride taken from the slabs tensor: what rope_copy_batch reads as a sum."""
+    def __new__(cls, slabs):
+        return super().__new__(cls, (slabs, slabs.shape[0]))
+
+
 @pytest.mark.parametrize("KV,G,D", [(2, 4, 64), (3, 2, 16), (2, 1, 128), (2, 8, 32), (1, 4, 20)])
 def test_runtime_runs_decode_attention_as_one_launch(cuda, KV, G, D):
     """The five attention nodes of a decode step run as one kernel over the carried caches (RMLK_B200_ATTENTION=0 keeps the
