@@ -2096,10 +2096,25 @@ bool Instance::run_merged_matmul(int node_index) {
     Storage* y = arena->alloc(static_cast<size_t>(rows) * mm.n_total * sizeof(float));
     const size_t need = rmlk_b200_matmul_workspace_bytes(RMLK_F32, 1, rows, mm.n_total, mm.k);
     void* ws = need ? matmul_ws.ensure(need) : nullptr;
-    check_rc(rmlk_b200_matmul_flags(reinterpret_cast<rmlk_stream_t>(stream), RMLK_F32, 1, rows, mm.n_total, mm.k, a.data, 0, mm.w.ptr, 0, y->ptr,
-                                    rows * mm.n_total, ws, need, static_cast<int*>(status_word.ptr), flags));
+    if (batch_jobs && rows <= 64) {
+        // decode-sized product: the split-K slabs stay unsummed for the placements that read them (Instance::unsummed)
+        int parts = 1;
+        check_rc(rmlk_b200_matmul_parts(reinterpret_cast<rmlk_stream_t>(stream), RMLK_F32, rows, mm.n_total, mm.k, a.data, mm.w.ptr, y->ptr, ws, need,
+                                        static_cast<int*>(status_word.ptr), flags, &parts));
+        launches++;
+        if (parts > 1) {
+            unsummed.y = y;
+            unsummed.slabs = static_cast<const float*>(ws);
+            unsummed.parts = parts;
+            unsummed.part_stride = rows * mm.n_total;
+            y->refs++;
+        }
+    } else {
+        check_rc(rmlk_b200_matmul_flags(reinterpret_cast<rmlk_stream_t>(stream), RMLK_F32, 1, rows, mm.n_total, mm.k, a.data, 0, mm.w.ptr, 0, y->ptr,
+                                        rows * mm.n_total, ws, need, static_cast<int*>(status_word.ptr), flags));
+        launches += need ? 2 : 1;
+    }
     status_dirty = true;
-    launches += need ? 2 : 1;
     for (size_t j = 0; j < mm.nodes.size(); j++) {
         Tensor& o = values[g.nodes[mm.nodes[j]].outputs[0]];
         o.dtype = RMLK_F32;

@@ -39,15 +39,42 @@ void check_rc_fn(int rc) {
 static thread_local Instance* tl_running = nullptr;
 
 void flush_deferred() {
-    if (tl_running && !tl_running->pending_jobs.empty()) tl_running->flush_jobs();
+    if (!tl_running) return;
+    if (!tl_running->pending_jobs.empty()) tl_running->flush_jobs();
+    if (tl_running->unsummed.y) tl_running->resolve_unsummed();
 }
 
 void Instance::flush_jobs() {
     if (pending_jobs.empty()) return;
     std::vector<rmlk_batch_job> jobs;
     jobs.swap(pending_jobs);  // empty before anything is enqueued: the launch below goes through no check_rc macro
+    if (unsummed.y) {
+        // jobs that read the unsummed product read its slabs (same layout, `part_stride` elements apart)
+        const char* lo = static_cast<const char*>(unsummed.y->ptr);
+        const char* hi = lo + unsummed.y->size;
+        for (rmlk_batch_job& j : jobs) {
+            const char* in = static_cast<const char*>(j.in);
+            if (in >= lo && in < hi && j.in_parts <= 1) {
+                j.in = reinterpret_cast<const char*>(unsummed.slabs) + (in - lo);
+                j.in_parts = unsummed.parts;
+                j.in_part_stride = unsummed.part_stride;
+            }
+        }
+    }
     check_rc_fn(rmlk_b200_rope_copy_batch(reinterpret_cast<rmlk_stream_t>(stream), static_cast<int>(jobs.size()), jobs.data()));
     launches++;
+}
+
+void Instance::resolve_unsummed() {
+    if (!unsummed.y) return;
+    Unsummed u = unsummed;
+    unsummed = Unsummed();  // cleared first: nothing below goes through the check_rc macro, but keep the state simple
+    if (u.y->refs > 1) {
+        // a view of the product is still alive and may be read by what comes next: add the slabs up now
+        check_rc_fn(rmlk_b200_sum_parts(reinterpret_cast<rmlk_stream_t>(stream), RMLK_F32, u.parts, u.part_stride, u.slabs, u.y->ptr));
+        launches++;
+    }
+    arena->release(u.y);
 }
 
 // the byte range [lo, hi) a job's tensor covers (elements of 4 bytes; strides may be 0 or negative)
@@ -427,6 +454,7 @@ void Instance::run() {
         explicit Running(Instance* s) : self(s), before(tl_running) { tl_running = s; }
         ~Running() {
             self->pending_jobs.clear();
+            self->unsummed = Unsummed();  // (after an error; the arena is reset by the next run)
             tl_running = before;
         }
     } running(this);
@@ -515,6 +543,7 @@ void Instance::run() {
             if (v >= 0 && last_use[v] < 0 && !g.values[v].is_output) release_value(v);
     }
     flush_jobs();
+    resolve_unsummed();
     deliver_host_outputs();
     for (Binding& b : bindings) {
         b.carried = values[b.out_id];

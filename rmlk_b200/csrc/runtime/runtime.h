@@ -275,6 +275,17 @@ struct Instance {
     std::vector<rmlk_batch_job> pending_jobs;
     void defer_job(const rmlk_batch_job& job);
     void flush_jobs();
+    // A merged q|k|v product whose split-K slabs have not been added up: `y` is the dense buffer the outputs' views point
+    // into (not written yet; one reference is held here), the slabs lie in the MatMul workspace.  Collected jobs that read
+    // from `y` are pointed at the slabs instead and add them up themselves; when the next thing is enqueued and anything
+    // else still refers to `y`, the slabs are summed into it first - otherwise the sum never runs.
+    struct Unsummed {
+        Storage* y = nullptr;
+        const float* slabs = nullptr;
+        int parts = 0;
+        int64_t part_stride = 0;
+    } unsummed;
+    void resolve_unsummed();
     void run_node(const NodeDef& n);
     void release_value(int value_id);
     // replaces a deferred view by a dense copy in arena memory (no-op for a dense tensor)
