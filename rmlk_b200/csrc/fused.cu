@@ -85,12 +85,14 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_kernel(int64_t cols, float ex
     for (int64_t c = threadIdx.x; c < cols; c += 256) dst[c] = __fmul_rn(__fdiv_rn(row[c], sd), w[c]);
 }
 
-// Same, for rows of up to 256 * 4 * NP elements with 16-byte alignment: the row is read once and held in registers.
-template <int NP>
-__global__ void __launch_bounds__(256) rmsnorm_f32_regs_kernel(int cols, float exponent, float eps, const float* __restrict__ x,
-                                                              const float* __restrict__ w, float* __restrict__ out, RowAdd ra) {
+// Same, for rows of up to THREADS * 4 * NP elements with 16-byte alignment: the row is read once and held in registers.
+// A few rows (a decode step: 64) take 512 or 1024 threads with one pack each, so that the row, the residual and all
+// split-K slabs of a pack are requested at once - one trip to memory instead of several; many rows take 256 threads.
+template <int NP, int THREADS>
+__global__ void __launch_bounds__(THREADS) rmsnorm_f32_regs_kernel(int cols, float exponent, float eps, const float* __restrict__ x,
+                                                                  const float* __restrict__ w, float* __restrict__ out, RowAdd ra) {
     dep_sync();
-    __shared__ double part[8];
+    __shared__ double part[THREADS / 32];
     const int64_t r0 = static_cast<int64_t>(blockIdx.x) * cols;
     const float4* row = reinterpret_cast<const float4*>(x + r0);
     float4* dst = reinterpret_cast<float4*>(out + r0);
@@ -100,7 +102,7 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_regs_kernel(int cols, float e
     double acc = 0.0;
 #pragma unroll
     for (int i = 0; i < NP; i++) {
-        const int c = threadIdx.x + 256 * i;
+        const int c = threadIdx.x + THREADS * i;
         if (c < packs) {
             v[i] = row[c];
             if (ra.b) {
@@ -109,13 +111,14 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_regs_kernel(int cols, float e
                     y = *reinterpret_cast<const float4*>(ra.b + r0 + 4 * c);
                 } else {
                     y = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int k0 = 0; k0 < ra.parts; k0 += 8) {  // eight slab loads in flight, added in slab order
-                        float4 q[8];
+                    constexpr int CH = THREADS == 512 ? 16 : 8;  // slab loads in flight, added in slab order (registers allow 16 at 512 threads)
+                    for (int k0 = 0; k0 < ra.parts; k0 += CH) {
+                        float4 q[CH];
 #pragma unroll
-                        for (int j = 0; j < 8; j++)
+                        for (int j = 0; j < CH; j++)
                             if (k0 + j < ra.parts) q[j] = *reinterpret_cast<const float4*>(ra.b + (k0 + j) * ra.part_stride + r0 + 4 * c);
 #pragma unroll
-                        for (int j = 0; j < 8; j++)
+                        for (int j = 0; j < CH; j++)
                             if (k0 + j < ra.parts) {
                                 y.x += q[j].x; y.y += q[j].y; y.z += q[j].z; y.w += q[j].w;
                             }
@@ -138,12 +141,12 @@ __global__ void __launch_bounds__(256) rmsnorm_f32_regs_kernel(int cols, float e
     __syncthreads();
     double total = 0.0;
 #pragma unroll
-    for (int i = 0; i < 8; i++) total += part[i];
+    for (int i = 0; i < THREADS / 32; i++) total += part[i];
     const float mean = static_cast<float>(total / static_cast<double>(cols));
     const float sd = sqrtf(__fadd_rn(mean, eps));
 #pragma unroll
     for (int i = 0; i < NP; i++) {
-        const int c = threadIdx.x + 256 * i;
+        const int c = threadIdx.x + THREADS * i;
         if (c < packs) {
             const float4 g = wv[c];
             float4 r;
@@ -344,9 +347,12 @@ static int launch_rmsnorm(rmlk_stream_t stream, int64_t rows, int64_t cols, cons
     const bool add_ok = !ra.b || (aligned_to(ra.b, 16) && aligned_to(ra.sum, 16) && ra.part_stride % 4 == 0);
     if (cols % 4 == 0 && cols <= 4096 && aligned_to(x, 16) && aligned_to(weight, 16) && aligned_to(out, 16) && add_ok) {
         const int c = static_cast<int>(cols);
-        if (cols <= 1024) launch_dep(rmsnorm_f32_regs_kernel<1>, dim3(grid), dim3(256), 0, st, c, exponent, eps, xp, wp, op, ra);
-        else if (cols <= 2048) launch_dep(rmsnorm_f32_regs_kernel<2>, dim3(grid), dim3(256), 0, st, c, exponent, eps, xp, wp, op, ra);
-        else launch_dep(rmsnorm_f32_regs_kernel<4>, dim3(grid), dim3(256), 0, st, c, exponent, eps, xp, wp, op, ra);
+        const bool few = rows <= 512;  // too few rows to fill the GPU with 256-thread CTAs: widen the CTA instead
+        if (cols <= 1024) launch_dep(rmsnorm_f32_regs_kernel<1, 256>, dim3(grid), dim3(256), 0, st, c, exponent, eps, xp, wp, op, ra);
+        else if (cols <= 2048 && few) launch_dep(rmsnorm_f32_regs_kernel<1, 512>, dim3(grid), dim3(512), 0, st, c, exponent, eps, xp, wp, op, ra);
+        else if (cols <= 2048) launch_dep(rmsnorm_f32_regs_kernel<2, 256>, dim3(grid), dim3(256), 0, st, c, exponent, eps, xp, wp, op, ra);
+        else if (few) launch_dep(rmsnorm_f32_regs_kernel<1, 1024>, dim3(grid), dim3(1024), 0, st, c, exponent, eps, xp, wp, op, ra);
+        else launch_dep(rmsnorm_f32_regs_kernel<4, 256>, dim3(grid), dim3(256), 0, st, c, exponent, eps, xp, wp, op, ra);
     } else {
         launch_dep(rmsnorm_f32_kernel, dim3(grid), dim3(256), 0, st, cols, exponent, eps, xp, wp, op, ra);
     }
