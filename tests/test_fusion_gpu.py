@@ -27,7 +27,7 @@ def test_fused_kernels_equal_the_single_op_chain(K):
     g = torch.Generator(device="cuda").manual_seed(3)
     r = lambda *s: torch.randn(*s, device="cuda", generator=g)  # noqa: E731
     # RMSNorm
-    for rows, cols in [(64, 2048), (3, 7), (1, 4097), (130, 64)]:
+    for rows, cols in [(64, 2048), (3, 7), (1, 4097), (130, 64), (64, 4096), (600, 2048), (600, 4096), (9, 1028)]:
         x, w = r(rows, cols) * 3, r(cols)
         two, eps = torch.tensor(2.0, device="cuda"), torch.tensor(1e-5, device="cuda")
         var = K.reduce_mean(K.pow_(x, two), [-1], True)
@@ -38,7 +38,9 @@ def test_fused_kernels_equal_the_single_op_chain(K):
         assert float((got.double() - ref).abs().max()) <= 1e-5 * float(ref.abs().max())
     # residual Add in front of RMSNorm, with the second operand whole or as split-K slabs: the same bits as
     # (split-K sum ->) Add -> the RMSNorm kernel
-    for rows, cols, parts in [(64, 2048, 1), (64, 2048, 9), (3, 7, 1), (3, 7, 4), (2, 4097, 11), (130, 64, 2), (5, 4096, 8)]:
+    # (few rows take wide CTAs with one pack per thread and up to 16 / 8 slab loads at once; many rows the 256-thread form)
+    for rows, cols, parts in [(64, 2048, 1), (64, 2048, 9), (3, 7, 1), (3, 7, 4), (2, 4097, 11), (130, 64, 2), (5, 4096, 8), (5, 4096, 11),
+                              (64, 2048, 17), (600, 2048, 9), (600, 4096, 3), (64, 1536, 6), (7, 3072, 2)]:
         a, w = r(rows, cols) * 3, r(cols)
         slabs = r(parts, rows, cols)
         b = K.sum_parts(slabs) if parts > 1 else slabs[0]
