@@ -189,8 +189,9 @@ __global__ void __launch_bounds__(256) rope_f32_kernel(RopeParams p, int64_t tot
 
 // ---- several rotary embeddings / 4-byte strided copies as one launch (blockIdx.y = job) -----------------------------------
 struct BatchJob {
-    int kind, rank, parts, pad;
+    int kind, rank, parts, vec;   // vec: every row is contiguous, 16-byte aligned and a multiple of 4 (rotary: of 8) long
     int64_t part_stride, total;
+    int64_t threads;              // vec: 4 elements (rotary: two quads, j and j + D/2) per thread; else one element
     int64_t d[5], is[5], os[5], cs[4], ss[4];
     const float* in;
     const float* cosv;
@@ -209,12 +210,66 @@ __device__ __forceinline__ float batch_load(const BatchJob& j, int64_t off) {
     return s;
 }
 
+// four consecutive elements at element offset `off` (16-byte aligned), slabs added in order from 0.f per component
+__device__ __forceinline__ float4 batch_load4(const BatchJob& j, int64_t off) {
+    if (j.parts <= 1) return *reinterpret_cast<const float4*>(j.in + off);
+    float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < j.parts; k++) {
+        const float4 v = *reinterpret_cast<const float4*>(j.in + k * j.part_stride + off);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+    }
+    return s;
+}
+
 __global__ void __launch_bounds__(256) rope_copy_batch_kernel(const __grid_constant__ BatchParams bp) {
     dep_sync();
     const BatchJob& p = bp.job[blockIdx.y];
     const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
-    if (i >= p.total) return;
-    if (p.kind == RMLK_BATCH_ROPE) {
+    if (i >= p.threads) return;
+    if (p.vec && p.kind == RMLK_BATCH_ROPE) {
+        // One thread makes outputs j .. j + 3 and j + D/2 .. j + D/2 + 3 of a head (j < D/2): both quads need x[j ..] and
+        // x[j + D/2 ..], each possibly a sum of slabs, which are loaded once as 16-byte words.  Per element the expressions
+        // are those of rope_f32_kernel: out[j] = x[j] cos[j] + (x[j + D/2] * -1) sin[j]; out[j + D/2] = x[j + D/2] cos[..] + x[j] sin[..].
+        const int64_t half = p.d[3] / 2, quads = half / 4;
+        int64_t t = i;
+        const int64_t j = (t % quads) * 4;
+        t /= quads;
+        const int64_t i2 = t % p.d[2];
+        t /= p.d[2];
+        const int64_t i1 = t % p.d[1];
+        const int64_t i0 = t / p.d[1];
+        const int64_t xb = i0 * p.is[0] + i1 * p.is[1] + i2 * p.is[2];
+        const int64_t cb = i0 * p.cs[0] + i1 * p.cs[1] + i2 * p.cs[2];
+        const int64_t sb = i0 * p.ss[0] + i1 * p.ss[1] + i2 * p.ss[2];
+        const int64_t ob = i0 * p.os[0] + i1 * p.os[1] + i2 * p.os[2];
+        const float4 lo = batch_load4(p, xb + j), hi = batch_load4(p, xb + j + half);
+        const float4 c0 = *reinterpret_cast<const float4*>(p.cosv + cb + j), c1 = *reinterpret_cast<const float4*>(p.cosv + cb + j + half);
+        const float4 s0 = *reinterpret_cast<const float4*>(p.sinv + sb + j), s1 = *reinterpret_cast<const float4*>(p.sinv + sb + j + half);
+        float4 o0, o1;
+        o0.x = __fadd_rn(__fmul_rn(lo.x, c0.x), __fmul_rn(__fmul_rn(hi.x, -1.0f), s0.x));
+        o0.y = __fadd_rn(__fmul_rn(lo.y, c0.y), __fmul_rn(__fmul_rn(hi.y, -1.0f), s0.y));
+        o0.z = __fadd_rn(__fmul_rn(lo.z, c0.z), __fmul_rn(__fmul_rn(hi.z, -1.0f), s0.z));
+        o0.w = __fadd_rn(__fmul_rn(lo.w, c0.w), __fmul_rn(__fmul_rn(hi.w, -1.0f), s0.w));
+        o1.x = __fadd_rn(__fmul_rn(hi.x, c1.x), __fmul_rn(lo.x, s1.x));
+        o1.y = __fadd_rn(__fmul_rn(hi.y, c1.y), __fmul_rn(lo.y, s1.y));
+        o1.z = __fadd_rn(__fmul_rn(hi.z, c1.z), __fmul_rn(lo.z, s1.z));
+        o1.w = __fadd_rn(__fmul_rn(hi.w, c1.w), __fmul_rn(lo.w, s1.w));
+        *reinterpret_cast<float4*>(p.out + ob + j) = o0;
+        *reinterpret_cast<float4*>(p.out + ob + j + half) = o1;
+    } else if (p.vec) {
+        // copy: the innermost dim in 16-byte words
+        int64_t t = i, io = 0, oo = 0;
+        const int64_t quads = p.d[p.rank - 1] / 4;
+        const int64_t q4 = (t % quads) * 4;
+        t /= quads;
+        for (int d = p.rank - 2; d >= 0; d--) {
+            const int64_t q = t / p.d[d], r = t - q * p.d[d];
+            io += r * p.is[d];
+            oo += r * p.os[d];
+            t = q;
+        }
+        *reinterpret_cast<float4*>(p.out + oo + q4) = batch_load4(p, io + q4);
+    } else if (p.kind == RMLK_BATCH_ROPE) {
         // the expressions of rope_f32_kernel
         const int64_t D = p.d[3], half = D / 2;
         int64_t t = i;
@@ -435,7 +490,7 @@ extern "C" int rmlk_b200_rope_copy_batch(rmlk_stream_t stream, int n_jobs, const
         j.kind = src.kind;
         j.rank = rank;
         j.parts = src.in_parts > 1 ? src.in_parts : 1;
-        j.pad = 0;
+        j.vec = 0;
         j.part_stride = src.in_part_stride;
         j.total = 1;
         for (int d = 0; d < 5; d++) {
@@ -458,13 +513,28 @@ extern "C" int rmlk_b200_rope_copy_batch(rmlk_stream_t stream, int n_jobs, const
         j.cosv = static_cast<const float*>(src.cosv);
         j.sinv = static_cast<const float*>(src.sinv);
         j.out = static_cast<float*>(src.out);
-        if (j.total > most) most = j.total;
+        // 16-byte form: contiguous innermost dim on every tensor, all other strides and the bases multiples of 4 elements
+        static const bool vec_ok = [] {
+            const char* e = getenv("RMLK_B200_NO_BATCH_VEC");
+            return !(e && e[0] == '1');
+        }();
+        bool vec = vec_ok && j.d[rank - 1] % (src.kind == RMLK_BATCH_ROPE ? 8 : 4) == 0 && j.is[rank - 1] == 1 && j.os[rank - 1] == 1 &&
+                   aligned_to(src.in, 16) && aligned_to(src.out, 16) && j.part_stride % 4 == 0;
+        for (int d = 0; d < rank - 1 && vec; d++) vec = j.is[d] % 4 == 0 && j.os[d] % 4 == 0;
+        if (src.kind == RMLK_BATCH_ROPE && vec) {
+            vec = j.cs[3] == 1 && j.ss[3] == 1 && aligned_to(src.cosv, 16) && aligned_to(src.sinv, 16);
+            for (int d = 0; d < 3 && vec; d++) vec = j.cs[d] % 4 == 0 && j.ss[d] % 4 == 0;
+        }
+        j.vec = vec ? 1 : 0;
+        j.threads = !vec ? j.total : src.kind == RMLK_BATCH_ROPE ? j.total / 8 : j.total / 4;
+        if (j.threads > most) most = j.threads;
         n++;
     }
     if (n == 0) return RMLK_OK;
     for (int q = n; q < RMLK_BATCH_MAX_JOBS; q++) {
         bp.job[q] = bp.job[0];
         bp.job[q].total = 0;
+        bp.job[q].threads = 0;
     }
     launch_dep(rope_copy_batch_kernel, dim3(static_cast<unsigned>(ceil_div64(most, 256)), static_cast<unsigned>(n)), dim3(256), 0, as_stream(stream), bp);
     RMLK_CHECK_LAUNCH("rope_copy_batch_kernel");

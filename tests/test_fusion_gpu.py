@@ -401,13 +401,15 @@ def attention_graph(KV, G, D):
     return g
 
 
-def test_rope_copy_batch_equals_the_single_launches(K):
+@pytest.mark.parametrize("D", [64, 12, 128])
+def test_rope_copy_batch_equals_the_single_launches(K, D):
     """rmlk_b200_rope_copy_batch: rotated queries (dense), rotated keys and new values placed into cache slots, as one
     launch - bit for bit what rmlk_b200_rope / rope_to / strided_copy_to give one by one; also with the source left as
-    split-K slabs (summed in slab order, as rmlk_b200_sum_parts would)."""
+    split-K slabs (summed in slab order, as rmlk_b200_sum_parts would).  Head sizes that are multiples of 8 take the
+    16-byte form of the kernel, 12 the element-wise one."""
     import torch
     g = torch.Generator(device="cuda").manual_seed(5)
-    B, H, KV, D, T0, cap = 3, 8, 2, 64, 37, 64
+    B, H, KV, T0, cap = 3, 8, 2, 37, 64
     qkv = torch.randn(B, (H + 2 * KV) * D, device="cuda", generator=g)
     q = qkv[:, : H * D].view(B, 1, H, D).permute(0, 2, 1, 3)                   # [B, H, 1, D] views of the merged product
     k = qkv[:, H * D: (H + KV) * D].view(B, 1, KV, D).permute(0, 2, 1, 3)
