@@ -58,11 +58,50 @@ __global__ void __launch_bounds__(256) gather_kernel(uint64_t total_units, uint3
     out[u] = data[static_cast<uint64_t>(o) * in_outer_units + static_cast<uint64_t>(ix) * row_units + c];
 }
 
+// Rows of a multiple of four units: a thread takes four consecutive units of one row - one index load, then four data
+// loads in flight (with one unit per thread the two dependent loads of every thread left a gather of 8 KB rows at 0.80 of
+// the copy bandwidth).
+template <typename U, typename I>
+__global__ void __launch_bounds__(256) gather4_kernel(uint64_t total_quads, uint32_t row_quads, FastDiv row_div, uint32_t n_idx,
+                                                      FastDiv idx_div, int64_t axis_dim, uint64_t in_outer_units,
+                                                      const U* __restrict__ data, const I* __restrict__ indices,
+                                                      U* __restrict__ out, int* __restrict__ status) {
+    dep_sync();
+    const uint64_t q = static_cast<uint64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (q >= total_quads) return;
+    uint32_t row, c, o, j;
+    row_div.divmod(static_cast<uint32_t>(q), row, c);   // row = o * n_idx + j; c = quad inside the row
+    idx_div.divmod(row, o, j);
+    int64_t ix = static_cast<int64_t>(indices[j]);
+    if (ix < 0) ix += axis_dim;
+    if (ix < 0 || ix >= axis_dim) {
+        if (status && c == 0) *status = 1;
+        return;
+    }
+    const U* __restrict__ src = data + static_cast<uint64_t>(o) * in_outer_units + (static_cast<uint64_t>(ix) * row_quads + c) * 4;
+    const U v0 = src[0], v1 = src[1], v2 = src[2], v3 = src[3];
+    U* __restrict__ dst = out + q * 4;
+    dst[0] = v0; dst[1] = v1; dst[2] = v2; dst[3] = v3;
+}
+
 template <typename U>
 static int gather_units(cudaStream_t st, int idx_dtype, uint64_t total, uint32_t row_units, uint32_t n_idx, int64_t axis_dim,
                         const void* data, const void* indices, void* out, int* status) {
-    const unsigned grid = static_cast<unsigned>((total + 255) / 256);
     const uint64_t in_outer = static_cast<uint64_t>(axis_dim) * row_units;
+    if (row_units % 4 == 0 && row_units >= 16 && total / 4 < (1ull << 32)) {
+        const uint64_t quads = total / 4;
+        const uint32_t row_quads = row_units / 4;
+        const unsigned grid4 = static_cast<unsigned>((quads + 255) / 256);
+        if (idx_dtype == RMLK_I64)
+            launch_dep(gather4_kernel<U, int64_t>, dim3(grid4), dim3(256), 0, st, quads, row_quads, FastDiv(row_quads), n_idx, FastDiv(n_idx), axis_dim,
+                       in_outer, static_cast<const U*>(data), static_cast<const int64_t*>(indices), static_cast<U*>(out), status);
+        else
+            launch_dep(gather4_kernel<U, int32_t>, dim3(grid4), dim3(256), 0, st, quads, row_quads, FastDiv(row_quads), n_idx, FastDiv(n_idx), axis_dim,
+                       in_outer, static_cast<const U*>(data), static_cast<const int32_t*>(indices), static_cast<U*>(out), status);
+        RMLK_CHECK_LAUNCH("gather4_kernel");
+        return RMLK_OK;
+    }
+    const unsigned grid = static_cast<unsigned>((total + 255) / 256);
     if (idx_dtype == RMLK_I64)
         launch_dep(gather_kernel<U, int64_t>, dim3(grid), dim3(256), 0, st, total, row_units, FastDiv(row_units), n_idx, FastDiv(n_idx), axis_dim, in_outer,
                                                         static_cast<const U*>(data), static_cast<const int64_t*>(indices), static_cast<U*>(out), status);
