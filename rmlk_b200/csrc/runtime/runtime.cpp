@@ -445,6 +445,38 @@ std::string status_word_message(int word) {
     return "kernel failed: index out of range (code " + std::to_string(word) + ")";
 }
 
+void Instance::find_foldable() {
+    foldable.assign(g.nodes.size(), 0);
+    folded_ready.assign(g.nodes.size(), 0);
+    folded_out.assign(g.nodes.size(), {});
+    if (!fold_constants) return;
+    std::vector<uint8_t> constant(g.values.size(), 0);
+    for (size_t v = 0; v < g.values.size(); v++) constant[v] = g.values[v].is_const ? 1 : 0;
+    for (size_t i = 0; i < g.nodes.size(); i++) {
+        const NodeDef& n = g.nodes[i];
+        if (n.op == RMLK_OP_NOOP || n.op == RMLK_OP_CONST || n.op == RMLK_OP_CONSTANT) continue;
+        if (!group_of_node.empty() && group_of_node[i] >= 0) continue;     // members of a fused chain run at its last node
+        if (!merged_of_node.empty() && merged_of_node[i] >= 0) continue;
+        bool all = false;
+        for (int v : n.inputs) {
+            if (v < 0) continue;
+            all = true;
+            if (!constant[v]) {
+                all = false;
+                break;
+            }
+        }
+        if (!all) continue;
+        bool plain = true;
+        for (int v : n.outputs)
+            if (v >= 0 && (g.values[v].is_output || g.values[v].is_input)) plain = false;
+        if (!plain) continue;
+        foldable[i] = 1;
+        for (int v : n.outputs)
+            if (v >= 0) constant[v] = 1;
+    }
+}
+
 void Instance::run() {
     // jobs are collected only while this function runs; whatever is left goes out before the outputs are delivered,
     // and nothing stays collected if the run ends with an error
@@ -523,6 +555,12 @@ void Instance::run() {
             }
             continue;
         }
+        if (i < foldable.size() && foldable[i] && folded_ready[i]) {
+            // computed by an earlier run from initializers only: hand out the kept tensors
+            for (size_t k = 0; k < n.outputs.size(); k++)
+                if (n.outputs[k] >= 0) values[n.outputs[k]] = folded_out[i][k];
+            continue;
+        }
         try {
             if (host_profile) {
                 const auto t0 = std::chrono::steady_clock::now();
@@ -536,6 +574,34 @@ void Instance::run() {
         } catch (const Error& e) {
             throw Error(e.code, std::string(e.what()) + " [node " + std::to_string(i) + ", op " + std::to_string(n.op) + "]");
         }
+        if (i < foldable.size() && foldable[i]) {
+            // first run: keep the outputs in buffers of their own, with their host mirrors.  A node whose output is a view
+            // (Transpose / Expand of an initializer: no launch anyway) is left alone, so that its readers see the same
+            // kind of operand in every run.
+            bool view = false;
+            for (int v : n.outputs) view = view || (v >= 0 && (values[v].lazy || values[v].parts > 1));
+            if (view) {
+                foldable[i] = 0;
+                goto folded;
+            }
+            folded_out[i].assign(n.outputs.size(), Tensor());
+            for (size_t k = 0; k < n.outputs.size(); k++) {
+                if (n.outputs[k] < 0) continue;
+                Tensor& t = values[n.outputs[k]];
+                Tensor kept = t;
+                kept.storage = nullptr;
+                kept.parts = 0;
+                if (t.present && t.nbytes() > 0) {
+                    folded_store.emplace_back(new DeviceBuffer());
+                    void* dst = folded_store.back()->ensure(t.nbytes());
+                    check_cuda(cudaMemcpyAsync(dst, t.data, t.nbytes(), cudaMemcpyDeviceToDevice, stream), "keeping a constant result");
+                    kept.data = dst;
+                }
+                folded_out[i][k] = kept;
+            }
+            folded_ready[i] = 1;
+        }
+    folded:
         if (n.op == RMLK_OP_GATHER || n.op == RMLK_OP_SCATTER_ND) status_dirty = true;
         for (int v : n.inputs)
             if (v >= 0 && last_use[v] == static_cast<int>(i) && !g.values[v].is_output) release_value(v);
@@ -764,12 +830,14 @@ extern "C" rmlk_instance* rmlk_instance_create(const rmlk_graph* g, int device, 
         if (const char* e = getenv("RMLK_B200_NO_ADD_NORM")) I.add_norm = e[0] != '1';
         if (const char* e = getenv("RMLK_B200_NO_APPEND_TO")) I.inplace_append_to = e[0] != '1';
         if (const char* e = getenv("RMLK_B200_NO_BATCH")) I.batch_jobs = e[0] != '1';
+        if (const char* e = getenv("RMLK_B200_NO_FOLD")) I.fold_constants = e[0] != '1';
         if (const char* e = getenv("RMLK_B200_ATTENTION")) {
             I.attention = e[0] != '0';
             I.attention_split = e[0] == 's';
         }
         I.find_fusions();  // recognise RMSNorm / rotary / SwiGLU / scale-mask-softmax chains; re-derives last_use
         I.find_merged_matmuls();  // q / k / v and gate / up projections: one MatMul per shared left operand
+        I.find_foldable();        // nodes that depend on initializers only: computed in the first run, kept afterwards
         // one weight arena, one pass of uploads (the reference allocates and copies per tensor through a
         // 4 KiB bump allocator, runtime/src/providers/cuda/store.rs:95-262)
         size_t total = 0;

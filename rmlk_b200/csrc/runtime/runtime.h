@@ -271,6 +271,15 @@ struct Instance {
     // slot) are not launched where they come up but collected; whatever else is enqueued next - any kernel, copy or
     // synchronisation goes through check_rc / check_cuda - launches the collected jobs first, as one kernel.  Stream
     // order is therefore exactly what it would be without collecting.  RMLK_B200_NO_BATCH=1: every job launches at once.
+    // Nodes whose inputs are all initializers (or outputs of such nodes) give the same result in every run - the inverse
+    // frequencies of the rotary embedding are five of them in an exported Llama.  Their outputs are kept from the first run
+    // on (copied into buffers of their own) and the nodes are skipped afterwards.  RMLK_B200_NO_FOLD=1: recomputed every run.
+    bool fold_constants = true;
+    std::vector<uint8_t> foldable;                 // per node
+    std::vector<uint8_t> folded_ready;             // per node: outputs are in folded_out
+    std::vector<std::vector<Tensor>> folded_out;   // per node: its outputs as persistent tensors
+    std::vector<std::unique_ptr<DeviceBuffer>> folded_store;
+    void find_foldable();
     bool batch_jobs = true;
     std::vector<rmlk_batch_job> pending_jobs;
     void defer_job(const rmlk_batch_job& job);
