@@ -401,6 +401,63 @@ def attention_graph(KV, G, D):
     return g
 
 
+def test_unsummed_projection_is_summed_when_something_else_reads_it(cuda):
+    """A decode-sized merged q|k|v product leaves its split-K slabs unsummed for the collected rotary job, which adds them
+    up as it reads.  Here the key and value blocks of the same product are also read by ordinary ops (a Mul and a Neg)
+    while that job is still collected: the job goes out first, then the slabs are summed for the other readers.  Same bits
+    as with collecting switched off, on a second run too."""
+    from rmlk_b200.runtime import ModelInstance
+    B, H, KV, D, hidden = 64, 32, 8, 64, 2048
+    g = GraphSpec()
+    g.input("x", np.float32, [B, 0, hidden])
+    g.input("cos", np.float32, [B, 1, 0, D])
+    g.input("sin", np.float32, [B, 1, 0, D])
+    rng = np.random.default_rng(51)
+    g.const("wq", (rng.standard_normal((hidden, H * D)) * 0.03).astype(np.float32))
+    g.const("wk", (rng.standard_normal((hidden, KV * D)) * 0.03).astype(np.float32))
+    g.const("wv", (rng.standard_normal((hidden, KV * D)) * 0.03).astype(np.float32))
+    i64 = lambda *v: np.array(v, np.int64)  # noqa: E731
+    g.const("shape_q", i64(0, 0, H, D)); g.const("shape_kv", i64(0, 0, KV, D))
+    g.const("z", i64(0)); g.const("h", i64(D // 2)); g.const("d", i64(D)); g.const("ax", i64(3))
+    g.const("two", np.array(2.0, np.float32))
+    q4 = g.op("Transpose", [g.op("Reshape", [g.op("MatMul", ["x", "wq"]), "shape_q"])], perm=[0, 2, 1, 3])
+    k = g.op("MatMul", ["x", "wk"])
+    v = g.op("MatMul", ["x", "wv"])
+    lo = g.op("Slice", [q4, "z", "h", "ax"])
+    hi = g.op("Slice", [q4, "h", "d", "ax"])
+    rot = g.op("Concat", [g.op("Neg", [hi]), lo], axis=-1)
+    g.op("Add", [g.op("Mul", [q4, "cos"]), g.op("Mul", [rot, "sin"])], "qr")
+    g.op("Mul", [k, "two"], "k2")
+    g.op("Neg", [v], "vn")
+    for o in ("qr", "k2", "vn"):
+        g.output(o)
+
+    def drive(env):
+        os.environ.update(env)
+        try:
+            inst = ModelInstance(g.to_runtime())
+        finally:
+            for key in env:
+                os.environ.pop(key, None)
+        return inst
+
+    collected, plain = drive({}), drive({"RMLK_B200_NO_BATCH": "1"})
+    for step in range(2):
+        feeds = {"x": rng.standard_normal((B, 1, hidden), dtype=np.float32), "cos": rng.standard_normal((B, 1, 1, D), dtype=np.float32),
+                 "sin": rng.standard_normal((B, 1, 1, D), dtype=np.float32)}
+        outs = []
+        for m in (collected, plain):
+            for key, val in feeds.items():
+                m.set_input(key, val)
+            m.launch()
+            outs.append({o: m.read(o) for o in ("qr", "k2", "vn")})
+        for o in ("qr", "k2", "vn"):
+            assert np.array_equal(outs[0][o], outs[1][o]), (step, o)
+        want = graph_cpu.run_graph(g, feeds)
+        for o in ("qr", "k2", "vn"):
+            assert np.max(np.abs(outs[0][o] - want[o])) <= 1e-4 * np.max(np.abs(want[o])), (step, o)
+
+
 @pytest.mark.parametrize("D", [64, 12, 128])
 def test_rope_copy_batch_equals_the_single_launches(K, D):
     """rmlk_b200_rope_copy_batch: rotated queries (dense), rotated keys and new values placed into cache slots, as one
