@@ -401,6 +401,54 @@ def attention_graph(KV, G, D):
     return g
 
 
+def test_results_of_initializer_only_nodes_are_kept(cuda):
+    """Range -> Cast -> Div -> Pow -> Div over constants (the inverse frequencies of a rotary embedding) runs in the first
+    run only; later runs hand out the kept result and launch five kernels fewer.  A Transpose of an initializer stays a view
+    (never launched, never copied).  RMLK_B200_NO_FOLD=1 recomputes everything; same bits either way."""
+    from rmlk_b200.runtime import ModelInstance
+    D = 64
+    g = GraphSpec()
+    g.input("pos", np.float32, [0, 1])
+    g.input("x", np.float32, [0, D // 2])
+    g.const("i0", np.array(0, np.int64)); g.const("hd", np.array(D, np.int64)); g.const("i2", np.array(2, np.int64))
+    g.const("hd_f", np.array(float(D), np.float32)); g.const("theta", np.array(10000.0, np.float32)); g.const("one_f", np.array(1.0, np.float32))
+    g.const("w", np.arange(D // 2 * 8, dtype=np.float32).reshape(8, D // 2) / 7.0)
+    r = g.op("Range", ["i0", "hd", "i2"])
+    inv = g.op("Div", ["one_f", g.op("Pow", ["theta", g.op("Div", [g.op("Cast", [r], to=1), "hd_f"])])])
+    g.op("Mul", ["pos", inv], "freqs")
+    g.op("MatMul", ["x", g.op("Transpose", ["w"], perm=[1, 0])], "xw")
+    g.output("freqs")
+    g.output("xw")
+
+    def drive(env):
+        os.environ.update(env)
+        try:
+            inst = ModelInstance(g.to_runtime())
+        finally:
+            for key in env:
+                os.environ.pop(key, None)
+        return inst
+
+    kept, plain = drive({}), drive({"RMLK_B200_NO_FOLD": "1"})
+    rng = np.random.default_rng(9)
+    counts = {id(kept): [], id(plain): []}
+    for step in range(3):
+        feeds = {"pos": rng.standard_normal((5 + step, 1), dtype=np.float32), "x": rng.standard_normal((5 + step, D // 2), dtype=np.float32)}
+        outs = []
+        for m in (kept, plain):
+            for key, val in feeds.items():
+                m.set_input(key, val)
+            m.launch()
+            outs.append((m.read("freqs"), m.read("xw")))
+            counts[id(m)].append(m.last_launches)
+        assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1]), step
+        want = graph_cpu.run_graph(g, feeds)
+        assert np.max(np.abs(outs[0][0] - want["freqs"])) <= 1e-5 * np.max(np.abs(want["freqs"]))
+        assert np.max(np.abs(outs[0][1] - want["xw"])) <= 1e-4 * np.max(np.abs(want["xw"]))
+    a, b = counts[id(kept)], counts[id(plain)]
+    assert b[0] == b[1] == b[2] and a[0] >= b[0] and a[1] == a[2] == b[1] - 5, (a, b)
+
+
 def test_unsummed_projection_is_summed_when_something_else_reads_it(cuda):
     """A decode-sized merged q|k|v product leaves its split-K slabs unsummed for the collected rotary job, which adds them
     up as it reads.  Here the key and value blocks of the same product are also read by ordinary ops (a Mul and a Neg)
