@@ -390,6 +390,12 @@ RMLK_API int rmlk_b200_rope_to(rmlk_stream_t stream, int dtype, const int64_t* s
                       const int64_t* cos_strides, const int64_t* sin_strides, const void* x, const void* cosv, const void* sinv,
                       void* out, const int64_t* out_strides);
 
+/* The cos / sin tables of a rotary embedding as exported: f = Mul(a, b) with a [rows] (positions, one per row) and b [half]
+ * (inverse frequencies), emb = Concat(f, f) on the last axis, cos_out = Cos(emb), sin_out = Sin(emb), both [rows, 2 half].
+ * Replaces backend/mul.rs, concat.rs:28-198, cos.rs and sin.rs (four launches) with one; same functions, same bits. */
+RMLK_API int rmlk_b200_rope_tables(rmlk_stream_t stream, int dtype, int64_t rows, int64_t half, const void* a, const void* b, void* cos_out,
+                          void* sin_out);
+
 /* Several small placements as ONE launch: rotary embeddings (as rmlk_b200_rope_to) and strided -> strided copies of 4-byte
  * elements (as rmlk_b200_strided_copy_to, rank <= 5), e.g. the rotated queries, the rotated keys into their cache slot and
  * the new values into theirs, which a decode step would otherwise issue as three launches of a few microseconds each.

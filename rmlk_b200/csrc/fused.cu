@@ -297,6 +297,25 @@ __global__ void __launch_bounds__(256) rope_copy_batch_kernel(const __grid_const
     }
 }
 
+// cos / sin tables of a rotary embedding: emb = Concat(f, f) with f = a * b, a one value per row and b one per column of f;
+// cos_out, sin_out [rows, 2 half].  The same functions as the single ops (IEEE multiply, cosf, sinf), each computed once
+// and written to both halves of the row.
+__global__ void __launch_bounds__(256) rope_tables_kernel(int64_t total, int half, const float* __restrict__ a, const float* __restrict__ b,
+                                                         float* __restrict__ cos_out, float* __restrict__ sin_out) {
+    dep_sync();
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= total) return;
+    const int64_t row = i / half;
+    const int j = static_cast<int>(i - row * half);
+    const float f = __fmul_rn(a[row], b[j]);
+    const float c = cosf(f), sn = sinf(f);
+    const int64_t o = row * 2 * half + j;
+    cos_out[o] = c;
+    cos_out[o + half] = c;
+    sin_out[o] = sn;
+    sin_out[o + half] = sn;
+}
+
 __global__ void __launch_bounds__(256) swiglu_f32_kernel(int64_t n, const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ out) {
     dep_sync();
     const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
@@ -471,6 +490,20 @@ extern "C" int rmlk_b200_rope_to(rmlk_stream_t stream, int dtype, const int64_t*
     launch_dep(rope_f32_kernel, dim3(static_cast<unsigned>(ceil_div64(total, 256))), dim3(256), 0, as_stream(stream), 
         p, total, static_cast<const float*>(x), static_cast<const float*>(cosv), static_cast<const float*>(sinv), static_cast<float*>(out));
     RMLK_CHECK_LAUNCH("rope_f32_kernel");
+    return RMLK_OK;
+}
+
+extern "C" int rmlk_b200_rope_tables(rmlk_stream_t stream, int dtype, int64_t rows, int64_t half, const void* a, const void* b, void* cos_out,
+                                     void* sin_out) {
+    if (dtype != RMLK_F32) return fail(RMLK_ERR_UNSUPPORTED_DTYPE, "unsupported data type for rope_tables (f32 only)");
+    if (rows < 0 || half < 0 || half > 0x3fffffffll) return fail(RMLK_ERR_INVALID_ARG, "rope_tables: bad extent");
+    if (rows == 0 || half == 0) return RMLK_OK;
+    if (!a || !b || !cos_out || !sin_out) return fail(RMLK_ERR_INVALID_ARG, "rope_tables: NULL tensor pointer");
+    const int64_t total = rows * half;
+    if (ceil_div64(total, 256) > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "rope_tables: tensor too large");
+    launch_dep(rope_tables_kernel, dim3(static_cast<unsigned>(ceil_div64(total, 256))), dim3(256), 0, as_stream(stream), total, static_cast<int>(half),
+               static_cast<const float*>(a), static_cast<const float*>(b), static_cast<float*>(cos_out), static_cast<float*>(sin_out));
+    RMLK_CHECK_LAUNCH("rope_tables_kernel");
     return RMLK_OK;
 }
 

@@ -1713,6 +1713,39 @@ void Instance::find_fusions() {
                     done = true;
                 }
             }
+        } else if ((root.op == RMLK_OP_COS || root.op == RMLK_OP_SIN) && m.n_in(ri) == 1) {
+            // rotary tables: Cos(emb) and Sin(emb) with emb = Concat(f, f) on the last axis and f = Mul(a, b); the later of the
+            // two nodes is the root and both outputs are written there
+            const int emb = m.in(ri, 0);
+            const int n_cat = emb >= 0 ? m.producer[emb] : -1;
+            if (n_cat < 0 || g.nodes[n_cat].op != RMLK_OP_CONCAT || group_of_node[n_cat] >= 0 || m.n_in(n_cat) != 2 || m.uses[emb] != 2 ||
+                g.values[emb].is_output)
+                continue;
+            const int f = m.in(n_cat, 0);
+            if (f < 0 || m.in(n_cat, 1) != f || m.uses[f] != 2 || g.values[f].is_output) continue;
+            const int n_mul = m.producer[f];
+            if (n_mul < 0 || g.nodes[n_mul].op != RMLK_OP_MUL || group_of_node[n_mul] >= 0 || m.n_in(n_mul) != 2) continue;
+            const int64_t cat_axis = Ctx{*this, g.nodes[n_cat]}.attr_int("axis", 0);
+            if (cat_axis != -1) continue;
+            int partner = -1;
+            for (size_t j = 0; j < g.nodes.size() && partner < 0; j++)
+                if (static_cast<int>(j) != ri && (g.nodes[j].op == RMLK_OP_COS || g.nodes[j].op == RMLK_OP_SIN) && g.nodes[j].op != root.op &&
+                    m.n_in(static_cast<int>(j)) == 1 && m.in(static_cast<int>(j), 0) == emb && group_of_node[j] < 0)
+                    partner = static_cast<int>(j);
+            if (partner < 0 || partner > ri) continue;  // matched from the later node only
+            // nothing may read the earlier node's output before the root has run
+            const int early = g.nodes[partner].outputs.empty() ? -1 : g.nodes[partner].outputs[0];
+            bool later = early >= 0;
+            for (int j = 0; j <= ri && later; j++)
+                for (int v : g.nodes[j].inputs) later = later && v != early;
+            if (!later) continue;
+            FusedGroup fg;
+            fg.kind = FusedGroup::ROPE_TABLES;
+            fg.members = {n_mul, n_cat, partner, ri};
+            fg.v[0] = m.in(n_mul, 0); fg.v[1] = m.in(n_mul, 1);
+            fg.v[2] = root.op == RMLK_OP_COS ? ri : partner;   // node ids: Cos, Sin
+            fg.v[3] = root.op == RMLK_OP_SIN ? ri : partner;
+            commit(fg);
         } else if (root.op == RMLK_OP_SOFTMAX) {
             // Softmax(Add(Mul(scores, scale), mask))
             const int n_add = m.inner(m.in(ri, 0), RMLK_OP_ADD);
@@ -1955,6 +1988,37 @@ bool Instance::run_fused(const FusedGroup& fg) {
             }
             check_rc(rmlk_b200_gqa_decode_attention_ws(st, RMLK_F32, lk.outer, lk.fold, D, T, H / lk.fold, q->data, kdata, lk.sb, vdata, lv.sb, scale,
                                                        mk->data, ms[0], ms[1], o.data, ws, ws_need));
+            launches++;
+            return true;
+        }
+        case FusedGroup::ROPE_TABLES: {
+            Tensor *p0 = val(fg.v[0]), *p1 = val(fg.v[1]);
+            if (!p0 || !p1 || p0->dtype != RMLK_F32 || p1->dtype != RMLK_F32) return false;
+            // one operand holds one value per row ([..., 1]), the other one value per column ([half]); either order
+            Tensor *a = p0, *b = p1;
+            if (!(a->shape.size() >= 1 && a->shape.back() == 1)) std::swap(a, b);
+            if (a->shape.empty() || a->shape.back() != 1 || b->shape.size() != 1 || b->numel() < 1) return false;
+            if (a->lazy) {
+                // a regrouped view of a dense tensor (Unsqueeze) reads like the dense tensor; anything else is copied out
+                Shape ps, pst;
+                std::vector<std::pair<int, int>> gr;
+                bool dense = dims_of(*a, ps, pst, gr);
+                int64_t run = 1;
+                for (int d = static_cast<int>(ps.size()) - 1; d >= 0 && dense; d--) {
+                    if (ps[d] != 1 && pst[d] != run) dense = false;
+                    run *= ps[d];
+                }
+                if (!dense) materialize(*a);
+            }
+            if (b->lazy) materialize(*b);
+            const int64_t rows = a->numel(), half = b->numel();
+            Shape oshape = a->shape;
+            oshape.back() = 2 * half;
+            const void *ad = a->data, *bd = b->data;
+            Tensor& oc = Ctx{*this, g.nodes[fg.v[2]]}.make(0, RMLK_F32, oshape);
+            Tensor& os = Ctx{*this, g.nodes[fg.v[3]]}.make(0, RMLK_F32, oshape);
+            if (rows == 0) return true;
+            check_rc(rmlk_b200_rope_tables(st, RMLK_F32, rows, half, ad, bd, oc.data, os.data));
             launches++;
             return true;
         }

@@ -387,6 +387,18 @@ def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: Optional[to
     return out
 
 
+def rope_tables(a: torch.Tensor, b: torch.Tensor):
+    """cos, sin of Concat(f, f) with f = a[..., None] * b: a [rows] positions (f32), b [half] inverse frequencies -> two
+    [rows, 2 half] tables in one launch."""
+    _require_cuda(a, b)
+    rows, half = a.numel(), b.numel()
+    cos = torch.empty(rows, 2 * half, dtype=torch.float32, device=a.device)
+    sin = torch.empty_like(cos)
+    _check(lib().rmlk_b200_rope_tables(_stream(), dt.from_torch(a.dtype), ctypes.c_int64(rows), ctypes.c_int64(half), _ptr(a), _ptr(b), _ptr(cos),
+                                       _ptr(sin)))
+    return cos, sin
+
+
 class _BatchJob(ctypes.Structure):
     """rmlk_batch_job of include/rmlk_b200.h."""
     _fields_ = [("kind", ctypes.c_int), ("rank", ctypes.c_int), ("in_parts", ctypes.c_int), ("reserved", ctypes.c_int),

@@ -401,6 +401,55 @@ def attention_graph(KV, G, D):
     return g
 
 
+def test_rope_tables_equal_mul_concat_cos_sin(K, cuda):
+    """rmlk_b200_rope_tables: the same bits as Mul -> Concat -> Cos / Sin, as a kernel and inside the runtime (where the four
+    nodes of an exported rotary embedding become one launch; RMLK_B200_NO_FUSION=1 keeps them apart)."""
+    from rmlk_b200.runtime import ModelInstance
+    g0 = torch.Generator(device="cuda").manual_seed(2)
+    pos = torch.randint(0, 4096, (37,), device="cuda", generator=g0).float()
+    inv = (1.0 / (10000.0 ** (torch.arange(0, 64, 2, device="cuda").float() / 64.0))).contiguous()
+    f = K.binary("mul", pos[:, None].contiguous(), inv)
+    emb = torch.cat([f, f], dim=-1).contiguous()
+    cos, sin = K.rope_tables(pos, inv)
+    assert torch.equal(cos, K.unary("cos", emb)) and torch.equal(sin, K.unary("sin", emb))
+
+    g = GraphSpec()
+    g.input("pos", np.int64, [0, 0])
+    g.const("inv", inv.cpu().numpy())
+    g.const("ax2", np.array([2], np.int64)); g.const("ax1", np.array([1], np.int64))
+    pf = g.op("Unsqueeze", [g.op("Cast", ["pos"], to=1), "ax2"])
+    fr = g.op("Mul", [pf, "inv"])
+    emb_v = g.op("Concat", [fr, fr], axis=-1)
+    cos_v, sin_v = g.op("Cos", [emb_v]), g.op("Sin", [emb_v])   # (both tables are made before anything reads them, as exported)
+    g.op("Unsqueeze", [cos_v, "ax1"], "cos4")
+    g.op("Unsqueeze", [sin_v, "ax1"], "sin4")
+    g.output("cos4"); g.output("sin4")
+
+    def drive(env):
+        os.environ.update(env)
+        try:
+            inst = ModelInstance(g.to_runtime())
+        finally:
+            for key in env:
+                os.environ.pop(key, None)
+        return inst
+
+    fused, apart = drive({}), drive({"RMLK_B200_NO_FUSION": "1"})
+    rng = np.random.default_rng(4)
+    for shape in ((3, 1), (2, 17), (64, 1)):
+        p = rng.integers(0, 5000, size=shape)
+        outs = []
+        for m in (fused, apart):
+            m.set_input("pos", p)
+            m.launch()
+            outs.append((m.read("cos4"), m.read("sin4"), m.last_launches))
+        assert outs[0][0].shape == (shape[0], 1, shape[1], 64)
+        assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1]), shape
+        assert outs[1][2] - outs[0][2] >= 2, (outs[0][2], outs[1][2])   # Mul, Concat, Cos, Sin -> one launch
+        want = graph_cpu.run_graph(g, {"pos": p})
+        assert np.max(np.abs(outs[0][0] - want["cos4"])) <= 2e-6 and np.max(np.abs(outs[0][1] - want["sin4"])) <= 2e-6
+
+
 def test_results_of_initializer_only_nodes_are_kept(cuda):
     """Range -> Cast -> Div -> Pow -> Div over constants (the inverse frequencies of a rotary embedding) runs in the first
     run only; later runs hand out the kept result and launch five kernels fewer.  A Transpose of an initializer stays a view
