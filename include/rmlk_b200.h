@@ -390,6 +390,15 @@ RMLK_API int rmlk_b200_rope_to(rmlk_stream_t stream, int dtype, const int64_t* s
                       const int64_t* cos_strides, const int64_t* sin_strides, const void* x, const void* cosv, const void* sinv,
                       void* out, const int64_t* out_strides);
 
+/* The additive attention mask of an exported decoder as one launch, out [batch, 1, s_len, t_len] f32:
+ *   Where(Equal(Cast(attention_mask [batch, t_len] i64 -> f32), cmp_pad), v_pad,
+ *         Where(Equal(Trilu(ConstantOfShape([s_len, t_len], fill), k, upper = 1), cmp_tri), v_future, v_else))
+ * Replaces backend/constant_of_shape.rs, trilu.rs, equal.rs (x2), whereop.rs (x2), cast.rs: seven launches, same bits (only
+ * comparisons and selections of the given constants). */
+RMLK_API int rmlk_b200_causal_padding_mask(rmlk_stream_t stream, int64_t batch, int64_t s_len, int64_t t_len, int64_t k,
+                                  const void* attention_mask, float fill, float cmp_tri, float v_future, float v_else,
+                                  float cmp_pad, float v_pad, void* out);
+
 /* The cos / sin tables of a rotary embedding as exported: f = Mul(a, b) with a [rows] (positions, one per row) and b [half]
  * (inverse frequencies), emb = Concat(f, f) on the last axis, cos_out = Cos(emb), sin_out = Sin(emb), both [rows, 2 half].
  * Replaces backend/mul.rs, concat.rs:28-198, cos.rs and sin.rs (four launches) with one; same functions, same bits. */

@@ -316,6 +316,25 @@ __global__ void __launch_bounds__(256) rope_tables_kernel(int64_t total, int hal
     sin_out[o + half] = sn;
 }
 
+// Additive attention mask of an exported decoder, [B, 1, S, T]:
+//   tri = Trilu(ConstantOfShape([S, T], fill), k, upper): fill where t - s >= k, else 0
+//   causal = Where(Equal(tri, cmp_tri), v_future, v_else)
+//   out = Where(Equal(Cast(am -> f32), cmp_pad), v_pad, causal)          am [B, T] int64
+// Only comparisons and selections of the given constants: the same bits as the seven single ops.
+struct MaskChain {
+    int64_t B, S, T, k;
+    float fill, cmp_tri, v_future, v_else, cmp_pad, v_pad;
+};
+__global__ void __launch_bounds__(256) mask_chain_kernel(MaskChain p, const int64_t* __restrict__ am, float* __restrict__ out) {
+    dep_sync();
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
+    if (i >= p.B * p.S * p.T) return;
+    const int64_t t = i % p.T, s = (i / p.T) % p.S, b = i / (p.T * p.S);
+    const float tri = (t - s >= p.k) ? p.fill : 0.0f;
+    const float causal = (tri == p.cmp_tri) ? p.v_future : p.v_else;
+    out[i] = (static_cast<float>(am[b * p.T + t]) == p.cmp_pad) ? p.v_pad : causal;
+}
+
 __global__ void __launch_bounds__(256) swiglu_f32_kernel(int64_t n, const float* __restrict__ g, const float* __restrict__ u, float* __restrict__ out) {
     dep_sync();
     const int64_t i = static_cast<int64_t>(blockIdx.x) * 256 + threadIdx.x;
@@ -490,6 +509,20 @@ extern "C" int rmlk_b200_rope_to(rmlk_stream_t stream, int dtype, const int64_t*
     launch_dep(rope_f32_kernel, dim3(static_cast<unsigned>(ceil_div64(total, 256))), dim3(256), 0, as_stream(stream), 
         p, total, static_cast<const float*>(x), static_cast<const float*>(cosv), static_cast<const float*>(sinv), static_cast<float*>(out));
     RMLK_CHECK_LAUNCH("rope_f32_kernel");
+    return RMLK_OK;
+}
+
+extern "C" int rmlk_b200_causal_padding_mask(rmlk_stream_t stream, int64_t batch, int64_t s_len, int64_t t_len, int64_t k, const void* attention_mask,
+                                             float fill, float cmp_tri, float v_future, float v_else, float cmp_pad, float v_pad, void* out) {
+    if (batch < 0 || s_len < 0 || t_len < 0) return fail(RMLK_ERR_INVALID_ARG, "causal_padding_mask: negative extent");
+    const int64_t total = batch * s_len * t_len;
+    if (total == 0) return RMLK_OK;
+    if (!attention_mask || !out) return fail(RMLK_ERR_INVALID_ARG, "causal_padding_mask: NULL tensor pointer");
+    if (ceil_div64(total, 256) > 0x7fffffffll) return fail(RMLK_ERR_INVALID_ARG, "causal_padding_mask: tensor too large");
+    MaskChain p = {batch, s_len, t_len, k, fill, cmp_tri, v_future, v_else, cmp_pad, v_pad};
+    launch_dep(mask_chain_kernel, dim3(static_cast<unsigned>(ceil_div64(total, 256))), dim3(256), 0, as_stream(stream), p,
+               static_cast<const int64_t*>(attention_mask), static_cast<float*>(out));
+    RMLK_CHECK_LAUNCH("mask_chain_kernel");
     return RMLK_OK;
 }
 

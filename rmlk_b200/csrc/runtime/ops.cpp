@@ -1746,6 +1746,45 @@ void Instance::find_fusions() {
             fg.v[2] = root.op == RMLK_OP_COS ? ri : partner;   // node ids: Cos, Sin
             fg.v[3] = root.op == RMLK_OP_SIN ? ri : partner;
             commit(fg);
+        } else if (root.op == RMLK_OP_WHERE && m.n_in(ri) == 3) {
+            // attention mask of an exported decoder:
+            //   Where(Unsqueeze(Equal(Cast(attention_mask), c0)), X, Unsqueeze(Where(Equal(Trilu(ConstantOfShape(st), k), c1), Y, Z)))
+            const int n_u_pad = m.inner(m.in(ri, 0), RMLK_OP_UNSQUEEZE), n_u_c = m.inner(m.in(ri, 2), RMLK_OP_UNSQUEEZE);
+            const int xv = m.in(ri, 1);
+            if (n_u_pad < 0 || n_u_c < 0 || !m.is_const(xv)) continue;
+            const int n_eq_pad = m.inner(m.in(n_u_pad, 0), RMLK_OP_EQUAL), n_w2 = m.inner(m.in(n_u_c, 0), RMLK_OP_WHERE);
+            if (n_eq_pad < 0 || n_w2 < 0 || m.n_in(n_eq_pad) != 2 || m.n_in(n_w2) != 3) continue;
+            int n_cast = -1, c0 = -1;
+            for (int side = 0; side < 2 && n_cast < 0; side++) {
+                const int nc = m.inner(m.in(n_eq_pad, side), RMLK_OP_CAST);
+                if (nc >= 0 && m.is_const(m.in(n_eq_pad, 1 - side))) {
+                    n_cast = nc;
+                    c0 = m.in(n_eq_pad, 1 - side);
+                }
+            }
+            if (n_cast < 0) continue;
+            const int n_eq_tri = m.inner(m.in(n_w2, 0), RMLK_OP_EQUAL);
+            const int yv = m.in(n_w2, 1), zv = m.in(n_w2, 2);
+            if (n_eq_tri < 0 || m.n_in(n_eq_tri) != 2 || !m.is_const(yv) || !m.is_const(zv)) continue;
+            int n_tri = -1, c1 = -1;
+            for (int side = 0; side < 2 && n_tri < 0; side++) {
+                const int nt = m.inner(m.in(n_eq_tri, side), RMLK_OP_TRILU);
+                if (nt >= 0 && m.is_const(m.in(n_eq_tri, 1 - side))) {
+                    n_tri = nt;
+                    c1 = m.in(n_eq_tri, 1 - side);
+                }
+            }
+            if (n_tri < 0) continue;
+            const int n_ones = m.inner(m.in(n_tri, 0), RMLK_OP_CONSTANT_OF_SHAPE);
+            if (n_ones < 0) continue;
+            FusedGroup fg;
+            fg.kind = FusedGroup::MASK;
+            fg.members = {n_ones, n_tri, n_eq_tri, n_w2, n_u_c, n_cast, n_eq_pad, n_u_pad, ri};
+            fg.v[0] = m.in(n_cast, 0); fg.v[1] = m.in(n_ones, 0); fg.v[2] = m.in(n_tri, 1);
+            fg.v[3] = c1; fg.v[4] = yv; fg.v[5] = zv; fg.v[6] = c0; fg.v[7] = xv;
+            fg.v[8] = n_ones; fg.v[9] = n_tri; fg.v[10] = n_u_c; fg.v[11] = n_u_pad;   // node ids
+            commit(fg);
+            // (the Cast node id is members[5] before sorting; it is looked up again by op when the chain runs)
         } else if (root.op == RMLK_OP_SOFTMAX) {
             // Softmax(Add(Mul(scores, scale), mask))
             const int n_add = m.inner(m.in(ri, 0), RMLK_OP_ADD);
@@ -1988,6 +2027,51 @@ bool Instance::run_fused(const FusedGroup& fg) {
             }
             check_rc(rmlk_b200_gqa_decode_attention_ws(st, RMLK_F32, lk.outer, lk.fold, D, T, H / lk.fold, q->data, kdata, lk.sb, vdata, lv.sb, scale,
                                                        mk->data, ms[0], ms[1], o.data, ws, ws_need));
+            launches++;
+            return true;
+        }
+        case FusedGroup::MASK: {
+            Tensor *am = val(fg.v[0]), *shp = val(fg.v[1]);
+            Tensor* kt = fg.v[2] >= 0 ? val(fg.v[2]) : nullptr;
+            if (!am || !shp || am->dtype != RMLK_I64 || am->shape.size() != 2 || shp->dtype != RMLK_I64) return false;
+            if (fg.v[2] >= 0 && (!kt || !kt->is_scalar() || kt->dtype != RMLK_I64)) return false;
+            float c1, yv, zv, c0, xv;
+            Tensor *t3 = val(fg.v[3]), *t4 = val(fg.v[4]), *t5 = val(fg.v[5]), *t6 = val(fg.v[6]), *t7 = val(fg.v[7]);
+            if (!t3 || !t4 || !t5 || !t6 || !t7 || !scalar_f32(*t3, c1) || !scalar_f32(*t4, yv) || !scalar_f32(*t5, zv) || !scalar_f32(*t6, c0) ||
+                !scalar_f32(*t7, xv))
+                return false;
+            // the chain's own attributes: f32 fill value, upper triangle, Cast to f32, Unsqueeze axes [0, 1] and [1, 2]
+            float fill = 0.0f;
+            {
+                const Ctx cc{*this, g.nodes[fg.v[8]]};
+                if (const Attr* a = cc.attr("value")) {
+                    if (a->kind != Attr::TENSOR || a->t_dtype != RMLK_F32 || a->t_data.size() < 4) return false;
+                    std::memcpy(&fill, a->t_data.data(), 4);
+                }
+                if (Ctx{*this, g.nodes[fg.v[9]]}.attr_int("upper", 1) == 0) return false;
+            }
+            for (int mnode : fg.members)
+                if (g.nodes[mnode].op == RMLK_OP_CAST) {
+                    const Attr* to = Ctx{*this, g.nodes[mnode]}.attr("to");
+                    if (!to || to->kind != Attr::INT || onnx_to_dtype(to->i) != RMLK_F32) return false;
+                }
+            auto axes_are = [&](int node, int64_t a0, int64_t a1) {
+                const Ctx cu{*this, g.nodes[node]};
+                std::vector<int64_t> axes;
+                if (Tensor* at = cu.in(1)) axes = host_i64(*at);
+                else if (const Attr* a = cu.attr("axes")) axes = a->ints;
+                return axes.size() == 2 && axes[0] == a0 && axes[1] == a1;
+            };
+            if (!axes_are(fg.v[10], 0, 1) || !axes_are(fg.v[11], 1, 2)) return false;
+            const std::vector<int64_t> dims = host_i64(*shp);
+            if (dims.size() != 2 || dims[0] < 0 || dims[1] < 0 || dims[1] != am->shape[1]) return false;
+            const int64_t k = kt ? host_i64(*kt)[0] : 0;
+            if (am->lazy) materialize(*am);
+            const int64_t B = am->shape[0], S = dims[0], T = dims[1];
+            const void* amd = am->data;
+            Tensor& o = c.make(0, RMLK_F32, Shape{B, 1, S, T});
+            if (o.numel() == 0) return true;
+            check_rc(rmlk_b200_causal_padding_mask(st, B, S, T, k, amd, fill, c1, yv, zv, c0, xv, o.data));
             launches++;
             return true;
         }

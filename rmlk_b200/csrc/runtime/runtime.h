@@ -163,11 +163,11 @@ struct Binding {  // output value -> input value, double-buffered
 // tensors of this run do not meet its conditions - the members run one by one, as if nothing had been matched.
 // Member outputs other than the root's are used only inside the chain, so running them late changes nothing.
 struct FusedGroup {
-    enum Kind { RMSNORM = 1, ROPE, SWIGLU, SCALE_MASK_SOFTMAX, ATTENTION, ROPE_TABLES } kind;
+    enum Kind { RMSNORM = 1, ROPE, SWIGLU, SCALE_MASK_SOFTMAX, ATTENTION, ROPE_TABLES, MASK } kind;
     int root = -1;
     int sub = -1;  // ATTENTION: index of the scale + mask + softmax group inside it, tried on its own when the whole does not fit
     std::vector<int> members;  // node indices in execution order, root last
-    int v[8] = {-1, -1, -1, -1, -1, -1, -1, -1};  // value ids by role (per kind, see ops.cpp)
+    int v[12] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1};  // value ids by role (per kind, see ops.cpp)
 };
 
 // MatMul nodes that multiply the SAME left operand by constant [K, N_i] weights (q / k / v projections, gate / up

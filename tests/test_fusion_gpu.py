@@ -450,6 +450,61 @@ def test_rope_tables_equal_mul_concat_cos_sin(K, cuda):
         assert np.max(np.abs(outs[0][0] - want["cos4"])) <= 2e-6 and np.max(np.abs(outs[0][1] - want["sin4"])) <= 2e-6
 
 
+def test_mask_chain_is_one_launch(cuda):
+    """The causal + padding mask of an exported decoder (ConstantOfShape, Trilu, Equal, Where, Cast, Equal, Where with two
+    Unsqueeze views) runs as one launch; RMLK_B200_NO_FUSION=1 runs the seven ops.  Same bits, for decode and prefill shapes,
+    with padded positions."""
+    from rmlk_b200.runtime import ModelInstance
+    g = GraphSpec()
+    g.input("attention_mask", np.int64, [0, 0])
+    g.input("ids", np.int64, [0, 0])
+    g.input("past", np.float32, [0, 2, 0, 4])
+    i64 = lambda *v: np.array(v, np.int64)  # noqa: E731
+    g.const("i1", np.array(1, np.int64)); g.const("i2", np.array(2, np.int64))
+    g.const("ax0", i64(0)); g.const("ax01", i64(0, 1)); g.const("ax12", i64(1, 2))
+    g.const("one_f", np.array(1.0, np.float32)); g.const("zero_f", np.array(0.0, np.float32))
+    g.const("min_f", np.array(np.finfo(np.float32).min, np.float32))
+    s_len = g.op("Gather", [g.op("Shape", ["ids"]), "i1"], axis=0)
+    p_len = g.op("Gather", [g.op("Shape", ["past"]), "i2"], axis=0)
+    t_len = g.op("Add", [p_len, s_len])
+    st = g.op("Concat", [g.op("Unsqueeze", [s_len, "ax0"]), g.op("Unsqueeze", [t_len, "ax0"])], axis=0)
+    ones = g.op("ConstantOfShape", [st], value=np.array([1.0], np.float32))
+    tri = g.op("Trilu", [ones, g.op("Add", [p_len, "i1"])], upper=1)
+    causal = g.op("Where", [g.op("Equal", [tri, "one_f"]), "min_f", "zero_f"])
+    causal4 = g.op("Unsqueeze", [causal, "ax01"])
+    padded = g.op("Equal", [g.op("Cast", ["attention_mask"], to=1), "zero_f"])
+    padded4 = g.op("Unsqueeze", [padded, "ax12"])
+    g.op("Where", [padded4, "min_f", causal4], "mask")
+    g.output("mask")
+
+    def drive(env):
+        os.environ.update(env)
+        try:
+            inst = ModelInstance(g.to_runtime())
+        finally:
+            for key in env:
+                os.environ.pop(key, None)
+        return inst
+
+    fused, apart = drive({}), drive({"RMLK_B200_NO_FUSION": "1"})
+    rng = np.random.default_rng(8)
+    for B, P, S in ((3, 0, 5), (3, 5, 1), (64, 512, 1), (2, 7, 4)):
+        am = (rng.random((B, P + S)) > 0.2).astype(np.int64)
+        am[:, -1] = 1
+        feeds = {"attention_mask": am, "ids": np.zeros((B, S), np.int64), "past": np.zeros((B, 2, P, 4), np.float32)}
+        outs = []
+        for m in (fused, apart):
+            for key, val in feeds.items():
+                m.set_input(key, val)
+            m.launch()
+            outs.append((m.read("mask"), m.last_launches))
+        assert outs[0][0].shape == (B, 1, S, P + S)
+        assert np.array_equal(outs[0][0], outs[1][0]), (B, P, S)
+        assert outs[1][1] - outs[0][1] == 6, (outs[0][1], outs[1][1])
+        want = graph_cpu.run_graph(g, feeds)["mask"]
+        assert np.array_equal(outs[0][0], want)
+
+
 def test_results_of_initializer_only_nodes_are_kept(cuda):
     """Range -> Cast -> Div -> Pow -> Div over constants (the inverse frequencies of a rotary embedding) runs in the first
     run only; later runs hand out the kept result and launch five kernels fewer.  A Transpose of an initializer stays a view
